@@ -1,0 +1,170 @@
+/*
+ * awq_b200.h -- C ABI of libawq_b200.so: mlir-air's int4-AWQ LLM hot path as
+ * hand-written sm_100a CUDA kernels.
+ *
+ * Every entry point
+ *   - is extern "C", takes plain pointers and sizes, and returns an int status
+ *     (AWQ_OK == 0, negative on error; awq_b200_last_error() gives the text);
+ *   - works on DEVICE pointers the caller owns (16-byte aligned), on the CUDA
+ *     stream passed as `stream` (a cudaStream_t cast to void*; NULL = default
+ *     stream), and is asynchronous with respect to the host;
+ *   - never allocates device memory: kernels that need scratch take a caller-owned
+ *     `workspace` (size from awq_b200_workspace_bytes, zeroed once with
+ *     awq_b200_workspace_init).  One workspace must not be shared by calls that
+ *     can overlap on the GPU.
+ *
+ * Weight layout ("layout A", HF AutoAWQ gemm format, the layout handled by
+ * programming_examples/llms/llama32_1b_int4/awq_repacker.py:33-54):
+ *   qweight int32 [K, N/8]   nibble at bits [4i+3:4i] of word (k, j) is the
+ *                            uint4 of output column 8j + {0,2,4,6,1,3,5,7}[i]
+ *   qzeros  int32 [K/gs, N/8] same packing
+ *   scales  bf16  [K/gs, N]
+ *   W[k, n] = (q[k, n] - z[k / gs, n]) * s[k / gs, n]
+ * bf16 values cross the ABI as uint16_t bit patterns (the reference passes
+ * ml_dtypes.bfloat16 viewed as int16, python/air/backend/xrt.py:757-758).
+ */
+#ifndef AWQ_B200_H_
+#define AWQ_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AWQ_OK 0
+#define AWQ_ERR_INVALID_ARGUMENT (-1) /* bad shape / null / misaligned pointer       */
+#define AWQ_ERR_WORKSPACE (-2)        /* workspace missing or too small              */
+#define AWQ_ERR_CUDA (-3)             /* a CUDA runtime / driver call failed         */
+#define AWQ_ERR_DEVICE_TIMEOUT (-4)   /* a bounded device-side wait gave up          */
+#define AWQ_ERR_UNSUPPORTED (-5)      /* not an sm_100 device, or shape not covered  */
+
+typedef void *awq_stream_t;
+
+/* Library version (major * 10000 + minor * 100 + patch). */
+int awq_b200_version(void);
+
+/* Text of the calling thread's most recent error ("" if none).  Replaces the
+ * Python exceptions of the reference backend (python/air/backend/abc.py:52-61,
+ * python/air/backend/xrt.py:204-218). */
+const char *awq_b200_last_error(void);
+
+/* Choose the decode kernel: 0 = automatic (TMA + tensor-core stream-K kernel when the
+ * shape allows it, else the generic kernel), 1 = force generic, 2 = force stream-K
+ * (returns AWQ_ERR_UNSUPPORTED where it cannot run).  Process-wide; for tests. */
+int awq_b200_set_decode_kernel(int mode);
+
+/* ---- AWQ dequant --------------------------------------------------------------
+ * out bf16 [K, N] = bf16_rne((q - z) * s).  Bit-exact with dequant_to_bf16
+ * (programming_examples/llms/llama32_1b_int4/awq_repacker.py:57-82),
+ * awq_dequant_layer (.../awq_pack.py:84-104) and the device kernel
+ * dequant_int4_bf16 (programming_examples/dequant_awq/dequant.cc:42-85). */
+int awq_b200_dequant_bf16(const int32_t *qweight, const int32_t *qzeros, const uint16_t *scales,
+                          uint16_t *out, int K, int N, int group_size, awq_stream_t stream);
+
+/* 1-D form of programming_examples/dequant_awq/dequant_awq.py:382-396: n nibbles packed
+ * two per byte (low nibble = even index), one bf16 scale and one uint8 zero per group. */
+int awq_b200_dequant_1d_bf16(const uint8_t *packed_q, const uint16_t *scales, const uint8_t *zeros,
+                             uint16_t *out, int n, int group_size, awq_stream_t stream);
+
+/* ---- workspace ---------------------------------------------------------------- */
+/* Bytes of scratch the decode kernels need for a [B, K] x [K, N] product. */
+size_t awq_b200_workspace_bytes(int B, int K, int N);
+/* Zero the workspace (once after allocation, and again after any call that
+ * returned AWQ_ERR_DEVICE_TIMEOUT). */
+int awq_b200_workspace_init(void *workspace, size_t workspace_bytes, awq_stream_t stream);
+/* Synchronise `stream` and report whether any kernel using this workspace gave up on a
+ * bounded device-side wait (AWQ_ERR_DEVICE_TIMEOUT).  The counterpart of the reference's
+ * check that a run reached ERT_CMD_STATE_COMPLETED (python/air/backend/xrt.py:204-218). */
+int awq_b200_workspace_check(const void *workspace, awq_stream_t stream);
+
+/* ---- decode GEMV ----------------------------------------------------------------
+ * y bf16 [B, N] = bf16(x[B, K] @ W (+ residual[B, N])), f32 accumulate, one rounding.
+ * Replaces matvec_int4_bf16_packed / zero_vectorized_bf16 / partial_plus_r_bf16
+ * (programming_examples/matrix_vector_multiplication/int4_awq/mv_int4_bf16.cc:65-150,
+ * 391-436) and follows the goldens matvec_int4_packed.py:272-287 and
+ * matvec_int4_packed_add.py:302-319.  residual may be NULL.  1 <= B <= 64. */
+int awq_b200_gemv_bf16(const uint16_t *x, const int32_t *qweight, const int32_t *qzeros,
+                       const uint16_t *scales, const uint16_t *residual, uint16_t *y, int B, int K,
+                       int N, int group_size, void *workspace, size_t workspace_bytes,
+                       awq_stream_t stream);
+
+/* Same product, f32 output without rounding or residual: the per-rank partial of a
+ * K-split (row-parallel) down projection, summed across ranks by the caller. */
+int awq_b200_gemv_f32(const uint16_t *x, const int32_t *qweight, const int32_t *qzeros,
+                      const uint16_t *scales, float *y, int B, int K, int N, int group_size,
+                      void *workspace, size_t workspace_bytes, awq_stream_t stream);
+
+/* ---- RMSNorm ---------------------------------------------------------------------
+ * out bf16 [B, K] = bf16(x * rsqrt(mean(x^2) + eps) * gamma); the inline RMSNorm of
+ * programming_examples/decode_ffn_swiglu/matvec_int4_swiglu_rms.py:228-358, golden :496-500. */
+int awq_b200_rmsnorm_bf16(const uint16_t *x, const uint16_t *gamma, float eps, uint16_t *out, int B,
+                          int K, awq_stream_t stream);
+
+/* h_out bf16 [B, K] = bf16(h + partial_sum) and normed = rmsnorm(h_out, gamma): the residual
+ * add that follows the allreduce of a K-split down projection, fused with the next layer's norm.
+ * gamma/normed may be NULL (no norm). */
+int awq_b200_add_rmsnorm_bf16(const uint16_t *h, const float *partial_sum, const uint16_t *gamma,
+                              float eps, uint16_t *h_out, uint16_t *normed, int B, int K,
+                              awq_stream_t stream);
+
+/* ---- fused gate/up GEMV + SwiGLU ---------------------------------------------------
+ * One AWQ matrix [K, 2I] whose columns are gate/up interleaved (column 2i = gate_i,
+ * 2i+1 = up_i; the row interleave of llama32_1b_int4_weights.py:173-205 seen from
+ * layout A).  out bf16 [B, I] = bf16(silu(bf16(g)) * bf16(u)), silu(g) = g/2 (tanh(g/2)+1).
+ * Replaces the GEMV loop + SwiGLU of matvec_int4_swiglu_rms.py:374-459, golden :511-516. */
+int awq_b200_gateup_swiglu_bf16(const uint16_t *x, const int32_t *qweight, const int32_t *qzeros,
+                                const uint16_t *scales, uint16_t *out, int B, int K, int I,
+                                int group_size, void *workspace, size_t workspace_bytes,
+                                awq_stream_t stream);
+
+/* Interleave two [K, I] AWQ matrices (separate gate and up projections, as stored in an
+ * HF checkpoint) into the [K, 2I] form above.  Done once per weight. */
+int awq_b200_interleave_gate_up(const int32_t *qw_gate, const int32_t *qz_gate,
+                                const uint16_t *s_gate, const int32_t *qw_up, const int32_t *qz_up,
+                                const uint16_t *s_up, int32_t *qweight, int32_t *qzeros,
+                                uint16_t *scales, int K, int I, int group_size, awq_stream_t stream);
+
+/* ---- decode FFN ----------------------------------------------------------------------
+ * out bf16 [B, H] = bf16(down(swiglu(gateup . norm(x))) + residual) with
+ * norm = RMSNorm(gamma, eps) when gamma != NULL.  The LGU -> LD chain of
+ * llms/llama32_1b_int4/multi_launch_builder/o_gemv_ffn_int4_multi.py:9-12 and the four
+ * launches of ffn_swiglu/decode/ffn_decode.py:48-250.  `inter` (bf16 [B, I]) and `normed`
+ * (bf16 [B, H], only with gamma) are caller-provided intermediates, as they are function
+ * arguments in the reference (ffn_decode.py:300-303).  residual may be NULL. */
+int awq_b200_ffn_decode_bf16(const uint16_t *x, const uint16_t *gamma, float eps,
+                             const int32_t *qw_gateup, const int32_t *qz_gateup,
+                             const uint16_t *s_gateup, const int32_t *qw_down,
+                             const int32_t *qz_down, const uint16_t *s_down,
+                             const uint16_t *residual, uint16_t *normed, uint16_t *inter,
+                             uint16_t *out, int B, int H, int I, int group_size, void *workspace,
+                             size_t workspace_bytes, awq_stream_t stream);
+
+/* ---- prefill GEMM ----------------------------------------------------------------------
+ * C bf16 [M, N] = bf16(A[M, K] @ W), f32 accumulate.  Replaces
+ * matmul_int4_bf16_packed_f32 / zero_vectorized_f32_mn / f32_to_bf16_mn
+ * (mv_int4_bf16.cc:181-389), golden matrix_multiplication/int4_awq/matmul_int4_packed.py:89-105. */
+int awq_b200_gemm_bf16(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros,
+                       const uint16_t *scales, uint16_t *C, int M, int K, int N, int group_size,
+                       awq_stream_t stream);
+
+/* Choose the prefill kernel: 0 = automatic, 1 = generic CUDA-core kernel,
+ * 2 = tcgen05 tensor-core kernel (AWQ_ERR_UNSUPPORTED where it cannot run). */
+int awq_b200_set_gemm_kernel(int mode);
+
+/* ---- layout converters (once per weight) ------------------------------------------------
+ * Layout B is mlir-air's logical form (matvec_int4_packed.py:346-350):
+ *   A_q uint8 [M, K/2] (low nibble = even k), A_s bf16 [K/gs, M], A_z uint8 [K/gs, M], M = N.
+ * B -> A inverts repack_hf_awq_linear (awq_repacker.py:85-109); A -> B restates it. */
+int awq_b200_repack_B_to_A(const uint8_t *A_q, const uint16_t *A_s, const uint8_t *A_z,
+                           int32_t *qweight, int32_t *qzeros, uint16_t *scales, int M, int K,
+                           int group_size, awq_stream_t stream);
+int awq_b200_repack_A_to_B(const int32_t *qweight, const int32_t *qzeros, const uint16_t *scales,
+                           uint8_t *A_q, uint16_t *A_s, uint8_t *A_z, int M, int K, int group_size,
+                           awq_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AWQ_B200_H_ */

@@ -1,0 +1,185 @@
+// C ABI glue: argument checks, kernel selection, error strings, workspace helpers.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <atomic>
+
+#include "awq_common.cuh"
+
+namespace awq {
+
+static thread_local char g_error[512] = "";
+static std::atomic<int> g_decode_mode{0};
+static std::atomic<int> g_gemm_mode{0};
+
+int set_error(int code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int check_cuda(cudaError_t e, const char *what) {
+    if (e == cudaSuccess) return AWQ_OK;
+    return set_error(AWQ_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+struct DevInfo {
+    int sms = -1;
+    int major = -1;
+};
+static DevInfo query_device() {
+    static thread_local int cached_dev = -1;
+    static thread_local DevInfo cached;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) return DevInfo();
+    if (dev != cached_dev) {
+        DevInfo d;
+        if (cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) d.sms = -1;
+        if (cudaDeviceGetAttribute(&d.major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) d.major = -1;
+        cached = d;
+        cached_dev = dev;
+    }
+    return cached;
+}
+int device_sm_count() { return query_device().sms; }
+bool device_is_sm100() { return query_device().major == 10; }
+
+static int check_gemv_args(const char *who, const GemvArgs &a) {
+    AWQ_REQUIRE(a.B >= 0 && a.K >= 0 && a.N >= 0 && a.group_size > 0, "%s: negative size or group_size <= 0", who);
+    AWQ_REQUIRE(a.B <= 64, "%s: batch %d exceeds 64 (use the prefill GEMM)", who, a.B);
+    AWQ_REQUIRE(a.N % 8 == 0, "%s: N (%d) must be a multiple of 8", who, a.N);
+    AWQ_REQUIRE(a.K % a.group_size == 0, "%s: K (%d) must be a multiple of group_size (%d)", who, a.K, a.group_size);
+    if (a.B == 0 || a.N == 0) return AWQ_OK;
+    AWQ_REQUIRE(a.K > 0, "%s: K must be positive", who);
+    AWQ_REQUIRE(a.x && a.qweight && a.qzeros && a.scales && a.y, "%s: null pointer", who);
+    AWQ_REQUIRE(aligned16(a.scales), "%s: scales must be 16-byte aligned", who);
+    return AWQ_OK;
+}
+
+static int run_gemv(const char *who, const GemvArgs &a) {
+    int rc = check_gemv_args(who, a);
+    if (rc || a.B == 0 || a.N == 0) return rc;
+    const int mode = g_decode_mode.load();
+    const bool fast_ok = gemv_streamk_supported(a);
+    if (mode == 2 && !fast_ok)
+        return set_error(AWQ_ERR_UNSUPPORTED,
+                         "%s: stream-K kernel needs group 128, K %% 128 == 0, N %% 32 == 0, 16-byte aligned "
+                         "pointers and an sm_100 device (K=%d N=%d gs=%d)", who, a.K, a.N, a.group_size);
+    if (mode != 1 && fast_ok) return launch_gemv_streamk(a);
+    return launch_gemv_generic(a);
+}
+
+}  // namespace awq
+
+using namespace awq;
+
+extern "C" int awq_b200_version(void) { return 100; }
+extern "C" const char *awq_b200_last_error(void) { return g_error; }
+
+extern "C" int awq_b200_set_decode_kernel(int mode) {
+    AWQ_REQUIRE(mode >= 0 && mode <= 2, "set_decode_kernel: mode must be 0, 1 or 2");
+    g_decode_mode.store(mode);
+    return AWQ_OK;
+}
+extern "C" int awq_b200_set_gemm_kernel(int mode) {
+    AWQ_REQUIRE(mode >= 0 && mode <= 2, "set_gemm_kernel: mode must be 0, 1 or 2");
+    g_gemm_mode.store(mode);
+    return AWQ_OK;
+}
+
+extern "C" size_t awq_b200_workspace_bytes(int B, int K, int N) {
+    (void)B;
+    if (K <= 0 || N <= 0) return 256;
+    return gemv_streamk_workspace_bytes(K, N);
+}
+
+extern "C" int awq_b200_workspace_init(void *workspace, size_t workspace_bytes, awq_stream_t stream) {
+    AWQ_REQUIRE(workspace && workspace_bytes >= 256, "workspace_init: null or tiny workspace");
+    return check_cuda(cudaMemsetAsync(workspace, 0, workspace_bytes, as_stream(stream)), "workspace memset");
+}
+
+extern "C" int awq_b200_workspace_check(const void *workspace, awq_stream_t stream) {
+    AWQ_REQUIRE(workspace, "workspace_check: null workspace");
+    int flag = 0;
+    int rc = check_cuda(cudaMemcpyAsync(&flag, workspace, sizeof(int), cudaMemcpyDeviceToHost, as_stream(stream)),
+                        "workspace_check copy");
+    if (rc) return rc;
+    rc = check_cuda(cudaStreamSynchronize(as_stream(stream)), "workspace_check sync");
+    if (rc) return rc;
+    if (flag != 0)
+        return set_error(AWQ_ERR_DEVICE_TIMEOUT,
+                         "a device-side wait gave up (code %d: 1 = producer waiting for a free stage, "
+                         "2 = consumer waiting for data); re-initialise the workspace", flag);
+    return AWQ_OK;
+}
+
+extern "C" int awq_b200_gemv_bf16(const uint16_t *x, const int32_t *qweight, const int32_t *qzeros,
+                                  const uint16_t *scales, const uint16_t *residual, uint16_t *y, int B, int K,
+                                  int N, int group_size, void *workspace, size_t workspace_bytes,
+                                  awq_stream_t stream) {
+    GemvArgs a{x, qweight, qzeros, scales, residual, y, B, K, N, group_size, EPI_BF16,
+               workspace, workspace_bytes, as_stream(stream)};
+    return run_gemv("gemv_bf16", a);
+}
+
+extern "C" int awq_b200_gemv_f32(const uint16_t *x, const int32_t *qweight, const int32_t *qzeros,
+                                 const uint16_t *scales, float *y, int B, int K, int N, int group_size,
+                                 void *workspace, size_t workspace_bytes, awq_stream_t stream) {
+    GemvArgs a{x, qweight, qzeros, scales, nullptr, y, B, K, N, group_size, EPI_F32,
+               workspace, workspace_bytes, as_stream(stream)};
+    return run_gemv("gemv_f32", a);
+}
+
+extern "C" int awq_b200_gateup_swiglu_bf16(const uint16_t *x, const int32_t *qweight, const int32_t *qzeros,
+                                           const uint16_t *scales, uint16_t *out, int B, int K, int I,
+                                           int group_size, void *workspace, size_t workspace_bytes,
+                                           awq_stream_t stream) {
+    AWQ_REQUIRE(I >= 0 && I % 4 == 0, "gateup_swiglu: I (%d) must be a multiple of 4", I);
+    GemvArgs a{x, qweight, qzeros, scales, nullptr, out, B, K, 2 * I, group_size, EPI_SWIGLU,
+               workspace, workspace_bytes, as_stream(stream)};
+    return run_gemv("gateup_swiglu", a);
+}
+
+extern "C" int awq_b200_ffn_decode_bf16(const uint16_t *x, const uint16_t *gamma, float eps,
+                                        const int32_t *qw_gateup, const int32_t *qz_gateup,
+                                        const uint16_t *s_gateup, const int32_t *qw_down, const int32_t *qz_down,
+                                        const uint16_t *s_down, const uint16_t *residual, uint16_t *normed,
+                                        uint16_t *inter, uint16_t *out, int B, int H, int I, int group_size,
+                                        void *workspace, size_t workspace_bytes, awq_stream_t stream) {
+    AWQ_REQUIRE(inter, "ffn_decode: inter buffer is required");
+    AWQ_REQUIRE(!gamma || normed, "ffn_decode: normed buffer is required with gamma");
+    int rc;
+    const uint16_t *xin = x;
+    if (gamma) {
+        if ((rc = awq_b200_rmsnorm_bf16(x, gamma, eps, normed, B, H, stream))) return rc;
+        xin = normed;
+    }
+    if ((rc = awq_b200_gateup_swiglu_bf16(xin, qw_gateup, qz_gateup, s_gateup, inter, B, H, I, group_size, workspace,
+                                          workspace_bytes, stream)))
+        return rc;
+    return awq_b200_gemv_bf16(inter, qw_down, qz_down, s_down, residual, out, B, I, H, group_size, workspace,
+                              workspace_bytes, stream);
+}
+
+extern "C" int awq_b200_gemm_bf16(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros,
+                                  const uint16_t *scales, uint16_t *C, int M, int K, int N, int group_size,
+                                  awq_stream_t stream) {
+    AWQ_REQUIRE(M >= 0 && K >= 0 && N >= 0 && group_size > 0, "gemm: negative size or group_size <= 0");
+    AWQ_REQUIRE(N % 8 == 0, "gemm: N (%d) must be a multiple of 8", N);
+    AWQ_REQUIRE(K % group_size == 0, "gemm: K (%d) must be a multiple of group_size (%d)", K, group_size);
+    AWQ_REQUIRE(group_size % 32 == 0, "gemm: group_size must be a multiple of 32 (kernel inner vector width)");
+    if (M == 0 || N == 0) return AWQ_OK;
+    AWQ_REQUIRE(K > 0, "gemm: K must be positive");
+    AWQ_REQUIRE(A && qweight && qzeros && scales && C, "gemm: null pointer");
+    AWQ_REQUIRE(aligned16(A) && aligned16(scales), "gemm: A and scales must be 16-byte aligned");
+    const int mode = g_gemm_mode.load();
+    const bool tc_ok = gemm_tc_supported(M, K, N, group_size) && aligned16(qweight) && aligned16(qzeros) && aligned16(C);
+    if (mode == 2 && !tc_ok)
+        return set_error(AWQ_ERR_UNSUPPORTED, "gemm: tensor-core kernel does not cover M=%d K=%d N=%d gs=%d", M, K, N,
+                         group_size);
+    if (mode != 1 && tc_ok) return launch_gemm_tc(A, qweight, qzeros, scales, C, M, K, N, group_size, as_stream(stream));
+    return launch_gemm_generic(A, qweight, qzeros, scales, C, M, K, N, group_size, as_stream(stream));
+}

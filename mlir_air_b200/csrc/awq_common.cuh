@@ -1,0 +1,100 @@
+// Shared helpers for the int4-AWQ kernels: error plumbing, bf16 bit tricks, nibble unpack.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "awq_b200.h"
+
+namespace awq {
+
+// ---- host-side error plumbing -------------------------------------------------------
+int set_error(int code, const char *fmt, ...);
+int check_cuda(cudaError_t e, const char *what);
+inline cudaStream_t as_stream(awq_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+int device_sm_count();
+bool device_is_sm100();
+
+#define AWQ_REQUIRE(cond, ...)                                        \
+    do {                                                              \
+        if (!(cond)) return awq::set_error(AWQ_ERR_INVALID_ARGUMENT, __VA_ARGS__); \
+    } while (0)
+
+// ---- layout-A nibble order ------------------------------------------------------------
+// Bits [4i+3:4i] of a packed word hold column ORDER[i] = {0,2,4,6,1,3,5,7}[i]; column c
+// therefore sits at shift 4 * PERM[c], PERM = {0,4,1,5,2,6,3,7}.
+__host__ __device__ __forceinline__ constexpr int awq_shift_of_column(int c) {
+    return 4 * (((c & 1) << 2) | (c >> 1));
+}
+__host__ __device__ __forceinline__ uint32_t awq_nibble(uint32_t word, int c) {
+    return (word >> awq_shift_of_column(c)) & 0xFu;
+}
+
+// ---- bf16 helpers ------------------------------------------------------------------------
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t lo16) { return __uint_as_float(lo16 << 16); }
+__device__ __forceinline__ float bf16x2_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16x2_hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
+__device__ __forceinline__ uint16_t f32_to_bf16_bits(float f) {
+    return __bfloat16_as_ushort(__float2bfloat16_rn(f));
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    return (uint32_t)f32_to_bf16_bits(lo) | ((uint32_t)f32_to_bf16_bits(hi) << 16);
+}
+
+// (v & 0x000f000f) | 0x43004300: two nibbles (bits 0-3 and 16-19) become the bf16 pair
+// (128 + n_lo, 128 + n_hi): 0x4300 is 128.0 and its ulp is 1.
+__device__ __forceinline__ uint32_t nib2_to_bf16x2_biased(uint32_t v) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(v), "r"(0x000F000Fu), "r"(0x43004300u));
+    return r;
+}
+
+// silu(g) = g * 0.5 * (tanh(g / 2) + 1), the form of matvec_int4_swiglu_rms.py:515.
+__device__ __forceinline__ float silu_tanh(float g) { return g * 0.5f * (tanhf(g * 0.5f) + 1.0f); }
+
+// gate/up f32 sums -> bf16 -> silu * up -> bf16 bits (rounding points of
+// matvec_int4_swiglu_rms.py:512-516).
+__device__ __forceinline__ uint16_t swiglu_bits(float gate_sum, float up_sum) {
+    float g = __bfloat162float(__float2bfloat16_rn(gate_sum));
+    float u = __bfloat162float(__float2bfloat16_rn(up_sum));
+    return f32_to_bf16_bits(silu_tanh(g) * u);
+}
+
+enum Epilogue : int {
+    EPI_BF16 = 0,    // y bf16 [B, N] = bf16(sum (+ residual))
+    EPI_F32 = 1,     // y f32  [B, N] = sum
+    EPI_SWIGLU = 2,  // y bf16 [B, N/2] = swiglu(sum[2i], sum[2i+1])
+};
+
+struct GemvArgs {
+    const uint16_t *x;
+    const int32_t *qweight;
+    const int32_t *qzeros;
+    const uint16_t *scales;
+    const uint16_t *residual;  // EPI_BF16 only, may be null
+    void *y;
+    int B, K, N, group_size;
+    int epilogue;
+    void *workspace;
+    size_t workspace_bytes;
+    cudaStream_t stream;
+};
+
+// Generic CUDA-core kernel: any group size, any N % 8 == 0, B <= 64.
+int launch_gemv_generic(const GemvArgs &a);
+// TMA + mma.sync stream-K kernel: group 128, N % 32 == 0, K % 128 == 0, B <= 8.
+bool gemv_streamk_supported(const GemvArgs &a);
+int launch_gemv_streamk(const GemvArgs &a);
+size_t gemv_streamk_workspace_bytes(int K, int N);
+
+int launch_gemm_generic(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros,
+                        const uint16_t *scales, uint16_t *C, int M, int K, int N, int group_size,
+                        cudaStream_t stream);
+bool gemm_tc_supported(int M, int K, int N, int group_size);
+int launch_gemm_tc(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros,
+                   const uint16_t *scales, uint16_t *C, int M, int K, int N, int group_size,
+                   cudaStream_t stream);
+
+}  // namespace awq

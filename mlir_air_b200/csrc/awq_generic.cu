@@ -1,0 +1,412 @@
+// Generic CUDA-core kernels: the any-shape decode GEMV / prefill GEMM (used where the
+// specialised kernels' shape rules do not hold, and as an independent cross-check in the
+// tests), RMSNorm, residual-add + RMSNorm, and the once-per-weight layout converters.
+#include "awq_common.cuh"
+
+namespace awq {
+
+// =====================================================================================
+// Generic decode GEMV.  Block = 32 packed word columns (256 output columns) x 8 k-slices;
+// a warp reads 128 contiguous bytes of one k row.  f32 weights (q - z) * s, f32 accumulate,
+// k-slices reduced through shared memory in a fixed order.
+// =====================================================================================
+constexpr int GV_TB = 4;  // batch rows per pass
+
+template <int EPI>
+__global__ void __launch_bounds__(256)
+gemv_generic_kernel(const uint16_t *__restrict__ x, const uint32_t *__restrict__ qweight,
+                    const uint32_t *__restrict__ qzeros, const uint16_t *__restrict__ scales,
+                    const uint16_t *__restrict__ residual, void *__restrict__ y_, int B, int K,
+                    int N, int group_size) {
+    __shared__ float red[8][GV_TB][256];
+    const int nb = N >> 3;
+    const int cx = threadIdx.x & 31, ky = threadIdx.x >> 5;
+    const int j = blockIdx.x * 32 + cx;
+    const bool active = j < nb;
+    for (int b0 = 0; b0 < B; b0 += GV_TB) {
+        float acc[GV_TB][8];
+#pragma unroll
+        for (int b = 0; b < GV_TB; ++b)
+#pragma unroll
+            for (int c = 0; c < 8; ++c) acc[b][c] = 0.f;
+        if (active) {
+            int cur_group = -1;
+            float s[8];
+            int z[8];
+            for (int k = ky; k < K; k += 8) {
+                const int g = k / group_size;
+                if (g != cur_group) {
+                    cur_group = g;
+                    const uint32_t zw = qzeros[(size_t)g * nb + j];
+                    const uint4 sv = *reinterpret_cast<const uint4 *>(scales + (size_t)g * N + 8 * j);
+                    const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        z[c] = (int)awq_nibble(zw, c);
+                        s[c] = (c & 1) ? bf16x2_hi(sw[c >> 1]) : bf16x2_lo(sw[c >> 1]);
+                    }
+                }
+                const uint32_t qw = __ldg(qweight + (size_t)k * nb + j);
+                float w[8];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) w[c] = (float)((int)awq_nibble(qw, c) - z[c]) * s[c];
+#pragma unroll
+                for (int b = 0; b < GV_TB; ++b) {
+                    if (b0 + b < B) {
+                        const float xv = bf16_bits_to_f32(x[(size_t)(b0 + b) * K + k]);
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) acc[b][c] = fmaf(w[c], xv, acc[b][c]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < GV_TB; ++b)
+#pragma unroll
+            for (int c = 0; c < 8; ++c) red[ky][b][cx * 8 + c] = acc[b][c];
+        __syncthreads();
+        const int col = threadIdx.x;
+        const int n = blockIdx.x * 256 + col;
+#pragma unroll
+        for (int b = 0; b < GV_TB; ++b) {
+            float sum = 0.f;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) sum += red[q][b][col];
+            const int bb = b0 + b;
+            if (EPI == EPI_SWIGLU) {
+                const float other = __shfl_xor_sync(0xffffffffu, sum, 1);
+                if (bb < B && n < N && !(col & 1))
+                    reinterpret_cast<uint16_t *>(y_)[(size_t)bb * (N >> 1) + (n >> 1)] =
+                        swiglu_bits(sum, other);
+            } else if (bb < B && n < N) {
+                if (EPI == EPI_F32) {
+                    reinterpret_cast<float *>(y_)[(size_t)bb * N + n] = sum;
+                } else {
+                    if (residual) sum += bf16_bits_to_f32(residual[(size_t)bb * N + n]);
+                    reinterpret_cast<uint16_t *>(y_)[(size_t)bb * N + n] = f32_to_bf16_bits(sum);
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+int launch_gemv_generic(const GemvArgs &a) {
+    const int blocks = (a.N / 8 + 31) / 32;
+    const uint32_t *qw = reinterpret_cast<const uint32_t *>(a.qweight);
+    const uint32_t *qz = reinterpret_cast<const uint32_t *>(a.qzeros);
+    switch (a.epilogue) {
+        case EPI_BF16:
+            gemv_generic_kernel<EPI_BF16><<<blocks, 256, 0, a.stream>>>(
+                a.x, qw, qz, a.scales, a.residual, a.y, a.B, a.K, a.N, a.group_size);
+            break;
+        case EPI_F32:
+            gemv_generic_kernel<EPI_F32><<<blocks, 256, 0, a.stream>>>(
+                a.x, qw, qz, a.scales, nullptr, a.y, a.B, a.K, a.N, a.group_size);
+            break;
+        default:
+            gemv_generic_kernel<EPI_SWIGLU><<<blocks, 256, 0, a.stream>>>(
+                a.x, qw, qz, a.scales, nullptr, a.y, a.B, a.K, a.N, a.group_size);
+            break;
+    }
+    return check_cuda(cudaGetLastError(), "generic gemv launch");
+}
+
+// =====================================================================================
+// Generic prefill GEMM: 64 x 64 block tile, 4 x 4 per thread, k-step 32, operands staged
+// in shared memory as f32 (weights as the exact f32 product (q - z) * s).
+// =====================================================================================
+constexpr int GG_BM = 64, GG_BN = 64, GG_BK = 32;
+
+__global__ void __launch_bounds__(256)
+gemm_generic_kernel(const uint16_t *__restrict__ A, const uint32_t *__restrict__ qweight,
+                    const uint32_t *__restrict__ qzeros, const uint16_t *__restrict__ scales,
+                    uint16_t *__restrict__ C, int M, int K, int N, int group_size) {
+    __shared__ float As[GG_BK][GG_BM + 4];
+    __shared__ float Ws[GG_BK][GG_BN + 4];
+    const int nb = N >> 3;
+    const int m0 = blockIdx.y * GG_BM, n0 = blockIdx.x * GG_BN;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;  // 16 x 16 threads
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) acc[i][jj] = 0.f;
+
+    const int a_row = threadIdx.x >> 2, a_k8 = (threadIdx.x & 3) * 8;  // A: 64 rows x 4 chunks of 8 k
+    const int w_row = threadIdx.x >> 3, w_cb = threadIdx.x & 7;        // W: 32 rows x 8 words
+    for (int k0 = 0; k0 < K; k0 += GG_BK) {
+        {
+            uint32_t v[4] = {0u, 0u, 0u, 0u};
+            if (m0 + a_row < M) {
+                const uint4 t = *reinterpret_cast<const uint4 *>(A + (size_t)(m0 + a_row) * K + k0 + a_k8);
+                v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                As[a_k8 + 2 * e][a_row] = bf16x2_lo(v[e]);
+                As[a_k8 + 2 * e + 1][a_row] = bf16x2_hi(v[e]);
+            }
+        }
+        {
+            const int k = k0 + w_row, j = (n0 >> 3) + w_cb;
+            float w[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (j < nb) {
+                const int g = k / group_size;
+                const uint32_t qw = __ldg(qweight + (size_t)k * nb + j);
+                const uint32_t zw = __ldg(qzeros + (size_t)g * nb + j);
+                const uint4 sv = *reinterpret_cast<const uint4 *>(scales + (size_t)g * N + 8 * j);
+                const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const float s = (c & 1) ? bf16x2_hi(sw[c >> 1]) : bf16x2_lo(sw[c >> 1]);
+                    w[c] = (float)((int)awq_nibble(qw, c) - (int)awq_nibble(zw, c)) * s;
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < 8; ++c) Ws[w_row][w_cb * 8 + c] = w[c];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < GG_BK; ++kk) {
+            float av[4], wv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) av[i] = As[kk][ty * 4 + i];
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) wv[jj] = Ws[kk][tx * 4 + jj];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) acc[i][jj] = fmaf(av[i], wv[jj], acc[i][jj]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int m = m0 + ty * 4 + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+            const int n = n0 + tx * 4 + jj;
+            if (n < N) C[(size_t)m * N + n] = f32_to_bf16_bits(acc[i][jj]);
+        }
+    }
+}
+
+int launch_gemm_generic(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros,
+                        const uint16_t *scales, uint16_t *C, int M, int K, int N, int group_size,
+                        cudaStream_t stream) {
+    dim3 grid((N + GG_BN - 1) / GG_BN, (M + GG_BM - 1) / GG_BM);
+    gemm_generic_kernel<<<grid, 256, 0, stream>>>(A, reinterpret_cast<const uint32_t *>(qweight),
+                                                  reinterpret_cast<const uint32_t *>(qzeros), scales, C,
+                                                  M, K, N, group_size);
+    return check_cuda(cudaGetLastError(), "generic gemm launch");
+}
+
+// =====================================================================================
+// RMSNorm (one block per row) and residual-add + RMSNorm.
+// =====================================================================================
+__device__ __forceinline__ float block_sum_256(float v, float *smem) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += smem[w];
+    __syncthreads();
+    return t;
+}
+
+// normed = bf16((x * rstd) * gamma), rstd = 1 / sqrt(mean(x^2) + eps) with the mean formed
+// in f32 and the rsqrt in f64 as the numpy golden does (matvec_int4_swiglu_rms.py:496-500).
+__global__ void __launch_bounds__(256)
+rmsnorm_kernel(const uint16_t *__restrict__ h, const float *__restrict__ partial,
+               const uint16_t *__restrict__ gamma, float eps, uint16_t *__restrict__ h_out,
+               uint16_t *__restrict__ normed, int K) {
+    __shared__ float red[8];
+    const size_t row = (size_t)blockIdx.x * K;
+    float ss = 0.f;
+    for (int k = threadIdx.x; k < K; k += 256) {
+        float v = bf16_bits_to_f32(h[row + k]);
+        if (partial) {
+            const uint16_t r = f32_to_bf16_bits(v + partial[row + k]);
+            if (h_out) h_out[row + k] = r;
+            v = bf16_bits_to_f32(r);
+        }
+        ss = fmaf(v, v, ss);
+    }
+    if (!normed) return;
+    const float total = block_sum_256(ss, red);
+    const float rstd = (float)(1.0 / sqrt((double)(total / (float)K) + (double)eps));
+    for (int k = threadIdx.x; k < K; k += 256) {
+        float v;
+        if (partial)
+            v = bf16_bits_to_f32(f32_to_bf16_bits(bf16_bits_to_f32(h[row + k]) + partial[row + k]));
+        else
+            v = bf16_bits_to_f32(h[row + k]);
+        normed[row + k] = f32_to_bf16_bits((v * rstd) * bf16_bits_to_f32(gamma[k]));
+    }
+}
+
+// =====================================================================================
+// Layout converters (once per weight; clarity over speed).
+// =====================================================================================
+// [K, I] gate + [K, I] up -> [K, 2I] with column 2i = gate_i, 2i + 1 = up_i.
+__global__ void interleave_words_kernel(const uint32_t *__restrict__ g, const uint32_t *__restrict__ u,
+                                        uint32_t *__restrict__ out, int rows, int nb_out) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)rows * nb_out) return;
+    const int j = (int)(idx % nb_out);
+    const size_t r = idx / nb_out;
+    const int nb_in = nb_out >> 1;
+    const uint32_t gw = g[r * nb_in + (j >> 1)], uw = u[r * nb_in + (j >> 1)];
+    uint32_t o = 0;
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+        const int src = 4 * (j & 1) + m;
+        o |= awq_nibble(gw, src) << awq_shift_of_column(2 * m);
+        o |= awq_nibble(uw, src) << awq_shift_of_column(2 * m + 1);
+    }
+    out[idx] = o;
+}
+
+__global__ void interleave_scales_kernel(const uint16_t *__restrict__ g, const uint16_t *__restrict__ u,
+                                         uint16_t *__restrict__ out, int rows, int I) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)rows * I) return;
+    const size_t r = idx / I;
+    const int i = (int)(idx % I);
+    out[r * 2 * I + 2 * i] = g[idx];
+    out[r * 2 * I + 2 * i + 1] = u[idx];
+}
+
+// Layout B -> A words: word (k, j) gathers nibble k of rows 8j .. 8j+7 of A_q.
+__global__ void repack_B_to_A_q_kernel(const uint8_t *__restrict__ A_q, uint32_t *__restrict__ qweight,
+                                       int M, int K) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int nb = M >> 3;
+    if (idx >= (size_t)K * nb) return;
+    const int j = (int)(idx % nb);
+    const int k = (int)(idx / nb);
+    uint32_t o = 0;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        const uint32_t byte = A_q[(size_t)(8 * j + c) * (K >> 1) + (k >> 1)];
+        o |= ((byte >> (4 * (k & 1))) & 0xFu) << awq_shift_of_column(c);
+    }
+    qweight[idx] = o;
+}
+
+__global__ void repack_B_to_A_z_kernel(const uint8_t *__restrict__ A_z, uint32_t *__restrict__ qzeros,
+                                       int M, int G) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int nb = M >> 3;
+    if (idx >= (size_t)G * nb) return;
+    const int j = (int)(idx % nb);
+    const size_t g = idx / nb;
+    uint32_t o = 0;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) o |= ((uint32_t)A_z[g * M + 8 * j + c] & 0xFu) << awq_shift_of_column(c);
+    qzeros[idx] = o;
+}
+
+__global__ void repack_A_to_B_q_kernel(const uint32_t *__restrict__ qweight, uint8_t *__restrict__ A_q,
+                                       int M, int K) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int kh = K >> 1;
+    if (idx >= (size_t)M * kh) return;
+    const int k2 = (int)(idx % kh);
+    const int n = (int)(idx / kh);
+    const int nb = M >> 3;
+    const uint32_t w0 = qweight[(size_t)(2 * k2) * nb + (n >> 3)];
+    const uint32_t w1 = qweight[(size_t)(2 * k2 + 1) * nb + (n >> 3)];
+    A_q[idx] = (uint8_t)(awq_nibble(w0, n & 7) | (awq_nibble(w1, n & 7) << 4));
+}
+
+__global__ void repack_A_to_B_z_kernel(const uint32_t *__restrict__ qzeros, uint8_t *__restrict__ A_z,
+                                       int M, int G) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)G * M) return;
+    const int n = (int)(idx % M);
+    const size_t g = idx / M;
+    A_z[idx] = (uint8_t)awq_nibble(qzeros[g * (M >> 3) + (n >> 3)], n & 7);
+}
+
+static inline unsigned blocks_for(size_t n, int threads) { return (unsigned)((n + threads - 1) / threads); }
+
+}  // namespace awq
+
+using namespace awq;
+
+extern "C" int awq_b200_rmsnorm_bf16(const uint16_t *x, const uint16_t *gamma, float eps, uint16_t *out,
+                                     int B, int K, awq_stream_t stream) {
+    AWQ_REQUIRE(B >= 0 && K > 0, "rmsnorm: bad size");
+    if (B == 0) return AWQ_OK;
+    AWQ_REQUIRE(x && gamma && out, "rmsnorm: null pointer");
+    rmsnorm_kernel<<<B, 256, 0, as_stream(stream)>>>(x, nullptr, gamma, eps, nullptr, out, K);
+    return check_cuda(cudaGetLastError(), "rmsnorm launch");
+}
+
+extern "C" int awq_b200_add_rmsnorm_bf16(const uint16_t *h, const float *partial_sum, const uint16_t *gamma,
+                                         float eps, uint16_t *h_out, uint16_t *normed, int B, int K,
+                                         awq_stream_t stream) {
+    AWQ_REQUIRE(B >= 0 && K > 0, "add_rmsnorm: bad size");
+    if (B == 0) return AWQ_OK;
+    AWQ_REQUIRE(h && partial_sum && h_out, "add_rmsnorm: null pointer");
+    AWQ_REQUIRE((gamma == nullptr) == (normed == nullptr), "add_rmsnorm: gamma and normed go together");
+    AWQ_REQUIRE(h_out != h, "add_rmsnorm: h_out must not alias h");
+    rmsnorm_kernel<<<B, 256, 0, as_stream(stream)>>>(h, partial_sum, gamma, eps, h_out, normed, K);
+    return check_cuda(cudaGetLastError(), "add_rmsnorm launch");
+}
+
+extern "C" int awq_b200_interleave_gate_up(const int32_t *qw_gate, const int32_t *qz_gate,
+                                           const uint16_t *s_gate, const int32_t *qw_up,
+                                           const int32_t *qz_up, const uint16_t *s_up, int32_t *qweight,
+                                           int32_t *qzeros, uint16_t *scales, int K, int I, int group_size,
+                                           awq_stream_t stream) {
+    AWQ_REQUIRE(K > 0 && I > 0 && group_size > 0 && K % group_size == 0, "interleave: bad size");
+    AWQ_REQUIRE(I % 8 == 0, "interleave: I (%d) must be a multiple of 8", I);
+    AWQ_REQUIRE(qw_gate && qz_gate && s_gate && qw_up && qz_up && s_up && qweight && qzeros && scales,
+                "interleave: null pointer");
+    const int G = K / group_size, nb_out = 2 * I / 8;
+    cudaStream_t st = as_stream(stream);
+    interleave_words_kernel<<<blocks_for((size_t)K * nb_out, 256), 256, 0, st>>>(
+        (const uint32_t *)qw_gate, (const uint32_t *)qw_up, (uint32_t *)qweight, K, nb_out);
+    interleave_words_kernel<<<blocks_for((size_t)G * nb_out, 256), 256, 0, st>>>(
+        (const uint32_t *)qz_gate, (const uint32_t *)qz_up, (uint32_t *)qzeros, G, nb_out);
+    interleave_scales_kernel<<<blocks_for((size_t)G * I, 256), 256, 0, st>>>(s_gate, s_up, scales, G, I);
+    return check_cuda(cudaGetLastError(), "interleave launch");
+}
+
+extern "C" int awq_b200_repack_B_to_A(const uint8_t *A_q, const uint16_t *A_s, const uint8_t *A_z,
+                                      int32_t *qweight, int32_t *qzeros, uint16_t *scales, int M, int K,
+                                      int group_size, awq_stream_t stream) {
+    AWQ_REQUIRE(M > 0 && K > 0 && group_size > 0, "repack_B_to_A: bad size");
+    AWQ_REQUIRE(M % 8 == 0 && K % 2 == 0 && K % group_size == 0, "repack_B_to_A: M %% 8, K %% 2, K %% gs");
+    AWQ_REQUIRE(A_q && A_s && A_z && qweight && qzeros && scales, "repack_B_to_A: null pointer");
+    const int G = K / group_size;
+    cudaStream_t st = as_stream(stream);
+    repack_B_to_A_q_kernel<<<blocks_for((size_t)K * (M / 8), 256), 256, 0, st>>>(A_q, (uint32_t *)qweight, M, K);
+    repack_B_to_A_z_kernel<<<blocks_for((size_t)G * (M / 8), 256), 256, 0, st>>>(A_z, (uint32_t *)qzeros, M, G);
+    int rc = check_cuda(cudaMemcpyAsync(scales, A_s, (size_t)G * M * 2, cudaMemcpyDeviceToDevice, st),
+                        "repack scales copy");
+    if (rc) return rc;
+    return check_cuda(cudaGetLastError(), "repack_B_to_A launch");
+}
+
+extern "C" int awq_b200_repack_A_to_B(const int32_t *qweight, const int32_t *qzeros, const uint16_t *scales,
+                                      uint8_t *A_q, uint16_t *A_s, uint8_t *A_z, int M, int K, int group_size,
+                                      awq_stream_t stream) {
+    AWQ_REQUIRE(M > 0 && K > 0 && group_size > 0, "repack_A_to_B: bad size");
+    AWQ_REQUIRE(M % 8 == 0 && K % 2 == 0 && K % group_size == 0, "repack_A_to_B: M %% 8, K %% 2, K %% gs");
+    AWQ_REQUIRE(A_q && A_s && A_z && qweight && qzeros && scales, "repack_A_to_B: null pointer");
+    const int G = K / group_size;
+    cudaStream_t st = as_stream(stream);
+    repack_A_to_B_q_kernel<<<blocks_for((size_t)M * (K / 2), 256), 256, 0, st>>>((const uint32_t *)qweight, A_q, M, K);
+    repack_A_to_B_z_kernel<<<blocks_for((size_t)G * M, 256), 256, 0, st>>>((const uint32_t *)qzeros, A_z, M, G);
+    int rc = check_cuda(cudaMemcpyAsync(A_s, scales, (size_t)G * M * 2, cudaMemcpyDeviceToDevice, st),
+                        "repack scales copy");
+    if (rc) return rc;
+    return check_cuda(cudaGetLastError(), "repack_A_to_B launch");
+}

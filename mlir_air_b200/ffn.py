@@ -1,0 +1,213 @@
+"""Weight-resident decode FFN layers and stacks, single GPU or tensor-parallel.
+
+The reference keeps the weights of every layer resident in device buffers and only
+moves activations per token (`KernelCache.load_and_run` with `static_input_indices`,
+programming_examples/llms/shared/infra/cache.py:494-737); a layer is the LGU -> LD chain
+of llms/llama32_1b_int4/multi_launch_builder/o_gemv_ffn_int4_multi.py:9-12:
+
+    h <- bf16(h + down(swiglu(gateup . rmsnorm(h, gamma))))
+
+Tensor parallelism follows the reference's output-row split across cores
+(matvec_int4_packed.py:69-75) lifted to GPUs: gate/up is split over its output columns,
+down over its input rows (group-of-128 granularity, uneven when the group count does not
+divide), and the per-rank f32 partials of down are summed with one allreduce per layer.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from . import ops
+from ._lib import AwqBackendError
+from .ops import AwqWeight, Workspace
+
+
+def tp_shard_bounds(intermediate: int, tp: int, group_size: int = 128) -> List[Tuple[int, int]]:
+    """[i0, i1) of the intermediate dimension owned by each rank: whole quantisation groups,
+    as even as possible (the first `groups % tp` ranks get one more group)."""
+    if intermediate % group_size:
+        raise AwqBackendError(f"intermediate {intermediate} is not a multiple of the group size {group_size}")
+    groups = intermediate // group_size
+    if tp < 1 or tp > groups:
+        raise AwqBackendError(f"cannot split {groups} groups over {tp} ranks")
+    base, extra = divmod(groups, tp)
+    bounds, g0 = [], 0
+    for r in range(tp):
+        g1 = g0 + base + (1 if r < extra else 0)
+        bounds.append((g0 * group_size, g1 * group_size))
+        g0 = g1
+    return bounds
+
+
+def shard_gateup(w: AwqWeight, i0: int, i1: int) -> AwqWeight:
+    """Columns [2 i0, 2 i1) of a gate/up-interleaved [K, 2I] weight (a column-parallel shard)."""
+    if i0 % 4 or i1 % 4:
+        raise AwqBackendError("gate/up shard bounds must be multiples of 4")
+    return AwqWeight(w.qweight[:, 2 * i0 // 8:2 * i1 // 8].contiguous(), w.qzeros[:, 2 * i0 // 8:2 * i1 // 8].contiguous(),
+                     w.scales[:, 2 * i0:2 * i1].contiguous(), w.group_size)
+
+
+def shard_down(w: AwqWeight, i0: int, i1: int) -> AwqWeight:
+    """Rows [i0, i1) of a [I, H] weight (a row-parallel shard); bounds on group boundaries."""
+    gs = w.group_size
+    if i0 % gs or i1 % gs:
+        raise AwqBackendError("down shard bounds must be multiples of the group size")
+    return AwqWeight(w.qweight[i0:i1].contiguous(), w.qzeros[i0 // gs:i1 // gs].contiguous(),
+                     w.scales[i0 // gs:i1 // gs].contiguous(), gs)
+
+
+@dataclass
+class FFNLayer:
+    """One layer's resident weights (this rank's shard when tensor-parallel)."""
+    gateup: AwqWeight            # [H, 2 I_local], gate/up column-interleaved
+    down: AwqWeight              # [I_local, H]
+    gamma: Optional[torch.Tensor] = None  # RMSNorm weight bf16 [H]
+
+    @property
+    def nbytes(self):
+        return self.gateup.nbytes + self.down.nbytes
+
+
+def random_layer(hidden: int, intermediate: int, seed: int, device="cuda", group_size: int = 128,
+                 bounds: Optional[Tuple[int, int]] = None, with_gamma: bool = True) -> FFNLayer:
+    """Random-init AWQ layer with the BASELINE distributions (nibbles and zeros uniform 0..15,
+    scales ~U(0.001, 0.02), gamma ~ 1 + 0.1 N(0,1)), generated on the device.  With `bounds`
+    only the [i0, i1) shard of the intermediate dimension is generated."""
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    i0, i1 = bounds if bounds is not None else (0, intermediate)
+    il = i1 - i0
+
+    def rnd(K, N):
+        qw = torch.randint(-2 ** 31, 2 ** 31 - 1, (K, N // 8), dtype=torch.int32, device=device, generator=gen)
+        qz = torch.randint(-2 ** 31, 2 ** 31 - 1, (K // group_size, N // 8), dtype=torch.int32, device=device,
+                           generator=gen)
+        s = (torch.rand((K // group_size, N), device=device, generator=gen) * 0.019 + 0.001).to(torch.bfloat16)
+        return AwqWeight(qw, qz, s, group_size)
+
+    gamma = None
+    if with_gamma:
+        gamma = (torch.randn(hidden, device=device, generator=gen) * 0.1 + 1.0).to(torch.bfloat16)
+    return FFNLayer(rnd(hidden, 2 * il), rnd(il, hidden), gamma)
+
+
+class DecodeFFNStack:
+    """A stack of decode FFN layers with resident weights.
+
+    step(h)          device tensor in, device tensor out (eager launches)
+    forward_host(x)  host array in, host array out: pinned H2D, one CUDA-graph replay of the
+                     whole stack, D2H -- the call a serving loop makes per token batch.
+    With `group` (a torch.distributed process group) the layers are this rank's shards and
+    each layer ends in one allreduce of the f32 down-projection partials.
+    """
+
+    def __init__(self, layers: Sequence[FFNLayer], hidden: int, max_batch: int = 64, eps: float = 1e-5,
+                 group=None, device="cuda"):
+        self.layers = list(layers)
+        self.hidden = hidden
+        self.eps = eps
+        self.group = group
+        self.device = torch.device(device)
+        self.tp = 1 if group is None else torch.distributed.get_world_size(group)
+        self.max_batch = max_batch
+        maxK = max([hidden] + [l.down.K for l in self.layers])
+        maxN = max([hidden] + [l.gateup.N for l in self.layers])
+        self.ws = Workspace(maxK, maxN, device=device)
+        max_il = max(l.down.K for l in self.layers)
+        bf = dict(dtype=torch.bfloat16, device=device)
+        self._h = [torch.empty((max_batch, hidden), **bf) for _ in range(2)]
+        self._normed = torch.empty((max_batch, hidden), **bf)
+        self._inter = torch.empty((max_batch, max_il), **bf)
+        self._partial = torch.empty((max_batch, hidden), dtype=torch.float32, device=device)
+        self._graphs = {}
+        self._pin_in = torch.empty((max_batch, hidden), dtype=torch.bfloat16).pin_memory() if torch.cuda.is_available() else None
+        self._pin_out = torch.empty((max_batch, hidden), dtype=torch.bfloat16).pin_memory() if torch.cuda.is_available() else None
+
+    # kernels launched per step (this library's own), for accounting
+    def launches_per_step(self, batch: int) -> int:
+        passes = (batch + 7) // 8  # the decode kernels take 8 rows per launch
+        n = len(self.layers)
+        if self.tp == 1:
+            return n * (1 + 2 * passes)
+        return 1 + n * (2 * passes + 1)
+
+    @property
+    def weight_bytes(self):
+        return sum(l.nbytes for l in self.layers)
+
+    def _run(self, B: int):
+        """Enqueue the whole stack on the current stream; input in _h[0][:B], returns the buffer
+        holding the result."""
+        h, other = self._h[0][:B], self._h[1][:B]
+        normed, inter, partial = self._normed[:B], self._inter, self._partial[:B]
+        if self.tp == 1:
+            for l in self.layers:
+                il = l.down.K
+                ops.ffn_decode(h, l.gateup, l.down, self.ws, gamma=l.gamma, eps=self.eps, residual=h,
+                               normed=normed, inter=inter.view(-1)[:B * il].view(B, il), out=other)
+                h, other = other, h
+            return h
+        # tensor-parallel: norm of the first layer, then per layer gate/up -> down partial ->
+        # allreduce -> residual add fused with the next layer's norm
+        x = h
+        if self.layers[0].gamma is not None:
+            ops.rmsnorm(h, self.layers[0].gamma, self.eps, out=normed)
+            x = normed
+        for idx, l in enumerate(self.layers):
+            il = l.down.K
+            it = inter.view(-1)[:B * il].view(B, il)
+            ops.gateup_swiglu(x, l.gateup, self.ws, out=it)
+            ops.gemv(it, l.down, self.ws, out=partial, f32_out=True)
+            torch.distributed.all_reduce(partial, group=self.group)
+            nxt = self.layers[idx + 1].gamma if idx + 1 < len(self.layers) else None
+            ops.add_rmsnorm(h, partial, nxt, self.eps, h_out=other, normed=normed if nxt is not None else None)
+            h, other = other, h
+            x = normed if nxt is not None else h
+        return h
+
+    def step(self, h: torch.Tensor) -> torch.Tensor:
+        """Eager: run the stack on a device tensor [B, H]; returns a new device tensor."""
+        B = h.shape[0]
+        if B > self.max_batch or h.shape[1] != self.hidden:
+            raise AwqBackendError(f"input {tuple(h.shape)} does not fit [<= {self.max_batch}, {self.hidden}]")
+        self._h[0][:B].copy_(h)
+        return self._run(B).clone()
+
+    def capture(self, B: int):
+        """Capture the stack for batch B into a CUDA graph (after one eager warm-up run)."""
+        if B in self._graphs:
+            return self._graphs[B]
+        self._run(B)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            out = self._run(B)
+        self._graphs[B] = (g, out)
+        return self._graphs[B]
+
+    def replay(self, B: int):
+        """Replay the captured stack on whatever _h[0][:B] currently holds; returns the result buffer."""
+        g, out = self.capture(B)
+        g.replay()
+        return out
+
+    def load_input(self, h: torch.Tensor):
+        self._h[0][:h.shape[0]].copy_(h)
+
+    def forward_host(self, x: np.ndarray) -> np.ndarray:
+        """Host [B, H] bf16 (ml_dtypes) in, host [B, H] bf16 out."""
+        from ml_dtypes import bfloat16
+        B = x.shape[0]
+        src = torch.from_numpy(np.ascontiguousarray(x).view(np.int16)).view(torch.bfloat16)
+        self._pin_in[:B].copy_(src)
+        self._h[0][:B].copy_(self._pin_in[:B], non_blocking=True)
+        out = self.replay(B)
+        self._pin_out[:B].copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self._pin_out[:B].view(torch.int16).numpy().view(bfloat16).copy()
+
+    def check(self):
+        self.ws.check()

@@ -1,0 +1,256 @@
+"""Device-level operators: torch CUDA tensors in, torch CUDA tensors out, every one a
+single call into the C ABI on torch's current stream.  torch is used for device
+memory and streams only; no operator here has a PyTorch implementation."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _want(t: torch.Tensor, dtype, name: str):
+    if not t.is_cuda:
+        raise _lib.AwqBackendError(f"{name} must be a CUDA tensor")
+    if t.dtype != dtype:
+        raise _lib.AwqBackendError(f"{name} must be {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise _lib.AwqBackendError(f"{name} must be contiguous")
+    return t
+
+
+@dataclass
+class AwqWeight:
+    """One AWQ-quantised linear layer in HF AutoAWQ layout (layout A), resident on a GPU.
+
+    qweight int32 [K, N/8], qzeros int32 [K/gs, N/8], scales bf16 [K/gs, N].
+    """
+    qweight: torch.Tensor
+    qzeros: torch.Tensor
+    scales: torch.Tensor
+    group_size: int = 128
+
+    def __post_init__(self):
+        _want(self.qweight, torch.int32, "qweight")
+        _want(self.qzeros, torch.int32, "qzeros")
+        _want(self.scales, torch.bfloat16, "scales")
+        K, nb = self.qweight.shape
+        if self.qzeros.shape != (K // self.group_size, nb) or self.scales.shape != (K // self.group_size, nb * 8):
+            raise _lib.AwqBackendError(
+                f"qzeros {tuple(self.qzeros.shape)} / scales {tuple(self.scales.shape)} do not match "
+                f"qweight {tuple(self.qweight.shape)} with group size {self.group_size}")
+
+    @property
+    def K(self):
+        return self.qweight.shape[0]
+
+    @property
+    def N(self):
+        return self.qweight.shape[1] * 8
+
+    @property
+    def nbytes(self):
+        return sum(t.numel() * t.element_size() for t in (self.qweight, self.qzeros, self.scales))
+
+    @classmethod
+    def from_numpy(cls, qweight, qzeros, scales, group_size=128, device="cuda"):
+        """Host arrays (scales bf16 as ml_dtypes.bfloat16, or fp16/fp32 rounded to bf16 as
+        awq_repacker.py:74-78 does) -> device-resident weight."""
+        import numpy as np
+        from ml_dtypes import bfloat16
+        s = np.ascontiguousarray(np.asarray(scales).astype(bfloat16)).view(np.int16)
+        return cls(torch.from_numpy(np.ascontiguousarray(qweight, dtype=np.int32)).to(device),
+                   torch.from_numpy(np.ascontiguousarray(qzeros, dtype=np.int32)).to(device),
+                   torch.from_numpy(s).to(device).view(torch.bfloat16), group_size)
+
+
+class Workspace:
+    """Caller-owned scratch for the decode kernels (strip counters + split-K partials).
+    One per stream: calls that share a workspace must not overlap on the GPU."""
+
+    def __init__(self, K: int, N: int, device="cuda"):
+        self.nbytes = int(_lib.load().awq_b200_workspace_bytes(1, int(K), int(N)))
+        self.buf = torch.empty(self.nbytes, dtype=torch.uint8, device=device)
+        with torch.cuda.device(self.buf.device):
+            _lib.call("awq_b200_workspace_init", self.buf.data_ptr(), self.nbytes, _stream())
+
+    def fits(self, K, N):
+        return int(_lib.load().awq_b200_workspace_bytes(1, int(K), int(N))) <= self.nbytes
+
+    def check(self):
+        """Synchronise and raise if a device-side wait timed out."""
+        with torch.cuda.device(self.buf.device):
+            _lib.call("awq_b200_workspace_check", self.buf.data_ptr(), _stream())
+
+
+def set_decode_kernel(mode: str):
+    _lib.call("awq_b200_set_decode_kernel", {"auto": 0, "generic": 1, "streamk": 2}[mode])
+
+
+def set_gemm_kernel(mode: str):
+    _lib.call("awq_b200_set_gemm_kernel", {"auto": 0, "generic": 1, "tc": 2}[mode])
+
+
+def dequant(w: AwqWeight, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """bf16 [K, N] = (q - z) * s, bit-exact with awq_repacker.dequant_to_bf16."""
+    if out is None:
+        out = torch.empty((w.K, w.N), dtype=torch.bfloat16, device=w.qweight.device)
+    _want(out, torch.bfloat16, "out")
+    _lib.call("awq_b200_dequant_bf16", _ptr(w.qweight), _ptr(w.qzeros), _ptr(w.scales), _ptr(out), w.K, w.N,
+              w.group_size, _stream())
+    return out
+
+
+def dequant_1d(packed_q, scales, zeros, n, group_size, out=None):
+    if out is None:
+        out = torch.empty(n, dtype=torch.bfloat16, device=packed_q.device)
+    _lib.call("awq_b200_dequant_1d_bf16", _ptr(_want(packed_q, torch.uint8, "packed_q")),
+              _ptr(_want(scales, torch.bfloat16, "scales")), _ptr(_want(zeros, torch.uint8, "zeros")), _ptr(out),
+              int(n), int(group_size), _stream())
+    return out
+
+
+def _x2d(x, K):
+    _want(x, torch.bfloat16, "x")
+    if x.dim() == 1:
+        x = x.view(1, -1)
+    if x.dim() != 2 or x.shape[1] != K:
+        raise _lib.AwqBackendError(f"x must be [B, {K}], got {tuple(x.shape)}")
+    return x
+
+
+def gemv(x, w: AwqWeight, ws: Workspace, residual=None, out=None, f32_out=False):
+    """y [B, N] = x [B, K] @ W (+ residual); bf16 with one rounding, or the f32 partial."""
+    x = _x2d(x, w.K)
+    B = x.shape[0]
+    if out is None:
+        out = torch.empty((B, w.N), dtype=torch.float32 if f32_out else torch.bfloat16, device=x.device)
+    if f32_out:
+        if residual is not None:
+            raise _lib.AwqBackendError("f32 partial output takes no residual")
+        _lib.call("awq_b200_gemv_f32", _ptr(x), _ptr(w.qweight), _ptr(w.qzeros), _ptr(w.scales),
+                  _ptr(_want(out, torch.float32, "out")), B, w.K, w.N, w.group_size, _ptr(ws.buf), ws.nbytes, _stream())
+    else:
+        if residual is not None:
+            _want(residual, torch.bfloat16, "residual")
+        _lib.call("awq_b200_gemv_bf16", _ptr(x), _ptr(w.qweight), _ptr(w.qzeros), _ptr(w.scales), _ptr(residual),
+                  _ptr(_want(out, torch.bfloat16, "out")), B, w.K, w.N, w.group_size, _ptr(ws.buf), ws.nbytes,
+                  _stream())
+    return out
+
+
+def gateup_swiglu(x, w_gateup: AwqWeight, ws: Workspace, out=None):
+    """out [B, I] = silu(gate) * up for a gate/up-interleaved [K, 2I] weight."""
+    x = _x2d(x, w_gateup.K)
+    B, I = x.shape[0], w_gateup.N // 2
+    if out is None:
+        out = torch.empty((B, I), dtype=torch.bfloat16, device=x.device)
+    _lib.call("awq_b200_gateup_swiglu_bf16", _ptr(x), _ptr(w_gateup.qweight), _ptr(w_gateup.qzeros),
+              _ptr(w_gateup.scales), _ptr(_want(out, torch.bfloat16, "out")), B, w_gateup.K, I, w_gateup.group_size,
+              _ptr(ws.buf), ws.nbytes, _stream())
+    return out
+
+
+def interleave_gate_up(gate: AwqWeight, up: AwqWeight) -> AwqWeight:
+    """Two [K, I] weights -> one [K, 2I] weight with column 2i = gate_i, 2i+1 = up_i."""
+    if (gate.K, gate.N, gate.group_size) != (up.K, up.N, up.group_size):
+        raise _lib.AwqBackendError("gate and up must have the same shape and group size")
+    K, I, G = gate.K, gate.N, gate.K // gate.group_size
+    dev = gate.qweight.device
+    qw = torch.empty((K, 2 * I // 8), dtype=torch.int32, device=dev)
+    qz = torch.empty((G, 2 * I // 8), dtype=torch.int32, device=dev)
+    sc = torch.empty((G, 2 * I), dtype=torch.bfloat16, device=dev)
+    _lib.call("awq_b200_interleave_gate_up", _ptr(gate.qweight), _ptr(gate.qzeros), _ptr(gate.scales),
+              _ptr(up.qweight), _ptr(up.qzeros), _ptr(up.scales), _ptr(qw), _ptr(qz), _ptr(sc), K, I,
+              gate.group_size, _stream())
+    return AwqWeight(qw, qz, sc, gate.group_size)
+
+
+def rmsnorm(x, gamma, eps=1e-5, out=None):
+    _want(x, torch.bfloat16, "x")
+    x2 = x.view(1, -1) if x.dim() == 1 else x
+    if out is None:
+        out = torch.empty_like(x2)
+    _lib.call("awq_b200_rmsnorm_bf16", _ptr(x2), _ptr(_want(gamma, torch.bfloat16, "gamma")), float(eps), _ptr(out),
+              x2.shape[0], x2.shape[1], _stream())
+    return out
+
+
+def add_rmsnorm(h, partial_sum, gamma=None, eps=1e-5, h_out=None, normed=None):
+    """h_out = bf16(h + partial_sum); normed = rmsnorm(h_out, gamma) when gamma is given."""
+    _want(h, torch.bfloat16, "h")
+    _want(partial_sum, torch.float32, "partial_sum")
+    if h_out is None:
+        h_out = torch.empty_like(h)
+    if gamma is not None and normed is None:
+        normed = torch.empty_like(h)
+    _lib.call("awq_b200_add_rmsnorm_bf16", _ptr(h), _ptr(partial_sum), _ptr(gamma), float(eps), _ptr(h_out),
+              _ptr(normed), h.shape[0], h.shape[1], _stream())
+    return h_out, normed
+
+
+def ffn_decode(x, w_gateup: AwqWeight, w_down: AwqWeight, ws: Workspace, gamma=None, eps=1e-5, residual=None,
+               normed=None, inter=None, out=None):
+    """out [B, H] = down(swiglu(gateup . norm(x))) (+ residual): one C-ABI call, three kernels."""
+    x = _x2d(x, w_gateup.K)
+    B, H, I = x.shape[0], w_gateup.K, w_gateup.N // 2
+    if w_down.K != I or w_down.N != H:
+        raise _lib.AwqBackendError(f"down weight must be [{I}, {H}], got [{w_down.K}, {w_down.N}]")
+    dev = x.device
+    if gamma is not None and normed is None:
+        normed = torch.empty((B, H), dtype=torch.bfloat16, device=dev)
+    if inter is None:
+        inter = torch.empty((B, I), dtype=torch.bfloat16, device=dev)
+    if out is None:
+        out = torch.empty((B, H), dtype=torch.bfloat16, device=dev)
+    _lib.call("awq_b200_ffn_decode_bf16", _ptr(x), _ptr(gamma), float(eps), _ptr(w_gateup.qweight),
+              _ptr(w_gateup.qzeros), _ptr(w_gateup.scales), _ptr(w_down.qweight), _ptr(w_down.qzeros),
+              _ptr(w_down.scales), _ptr(residual), _ptr(normed), _ptr(inter), _ptr(out), B, H, I, w_gateup.group_size,
+              _ptr(ws.buf), ws.nbytes, _stream())
+    return out
+
+
+def gemm(A, w: AwqWeight, out=None):
+    """C [M, N] = A [M, K] @ W, f32 accumulate, bf16 out (prefill)."""
+    _want(A, torch.bfloat16, "A")
+    if A.dim() != 2 or A.shape[1] != w.K:
+        raise _lib.AwqBackendError(f"A must be [M, {w.K}], got {tuple(A.shape)}")
+    if out is None:
+        out = torch.empty((A.shape[0], w.N), dtype=torch.bfloat16, device=A.device)
+    _lib.call("awq_b200_gemm_bf16", _ptr(A), _ptr(w.qweight), _ptr(w.qzeros), _ptr(w.scales), _ptr(out), A.shape[0],
+              w.K, w.N, w.group_size, _stream())
+    return out
+
+
+def repack_B_to_A(A_q, A_s, A_z, group_size=128) -> AwqWeight:
+    """mlir-air logical layout (A_q u8 [M, K/2], A_s bf16 [G, M], A_z u8 [G, M]) -> layout A."""
+    M, K = A_q.shape[0], A_q.shape[1] * 2
+    G = K // group_size
+    dev = A_q.device
+    qw = torch.empty((K, M // 8), dtype=torch.int32, device=dev)
+    qz = torch.empty((G, M // 8), dtype=torch.int32, device=dev)
+    sc = torch.empty((G, M), dtype=torch.bfloat16, device=dev)
+    _lib.call("awq_b200_repack_B_to_A", _ptr(_want(A_q, torch.uint8, "A_q")), _ptr(_want(A_s, torch.bfloat16, "A_s")),
+              _ptr(_want(A_z, torch.uint8, "A_z")), _ptr(qw), _ptr(qz), _ptr(sc), M, K, group_size, _stream())
+    return AwqWeight(qw, qz, sc, group_size)
+
+
+def repack_A_to_B(w: AwqWeight):
+    M, K, G = w.N, w.K, w.K // w.group_size
+    dev = w.qweight.device
+    A_q = torch.empty((M, K // 2), dtype=torch.uint8, device=dev)
+    A_s = torch.empty((G, M), dtype=torch.bfloat16, device=dev)
+    A_z = torch.empty((G, M), dtype=torch.uint8, device=dev)
+    _lib.call("awq_b200_repack_A_to_B", _ptr(w.qweight), _ptr(w.qzeros), _ptr(w.scales), _ptr(A_q), _ptr(A_s),
+              _ptr(A_z), M, K, w.group_size, _stream())
+    return A_q, A_s, A_z
