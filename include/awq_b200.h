@@ -90,6 +90,20 @@ int awq_b200_gemv_bf16(const uint16_t *x, const int32_t *qweight, const int32_t 
                        int N, int group_size, void *workspace, size_t workspace_bytes,
                        awq_stream_t stream);
 
+/* The same product as awq_b200_gemv_bf16 for callers that cannot allocate device memory
+ * (a plugin interface that carries only inputs and outputs, a serving process that bans
+ * cudaMalloc after start-up, plain C hosts without an allocator).  It has no counterpart in
+ * the reference.  The kernel's scratch is a fixed array inside the library image, about
+ * 2.5 MB on every GPU that loads the library, held until the process exits; nothing is
+ * allocated or freed by this call.  Limits: N <= 32768, group size 128, K % 128 == 0,
+ * N % 32 == 0, 1 <= B <= 64; anything else returns an error rather than falling back.
+ * The first call on each device looks up the array's device address, so make that first
+ * call outside any stream capture.  All calls on a device share the one array: calls that
+ * may run at the same time on the GPU (different streams) race and give wrong results. */
+int awq_b200_gemv_bf16_static(const uint16_t *x, const int32_t *qweight, const int32_t *qzeros,
+                              const uint16_t *scales, const uint16_t *residual, uint16_t *y, int B,
+                              int K, int N, int group_size, awq_stream_t stream);
+
 /* Same product, f32 output without rounding or residual: the per-rank partial of a
  * K-split (row-parallel) down projection, summed across ranks by the caller. */
 int awq_b200_gemv_f32(const uint16_t *x, const int32_t *qweight, const int32_t *qzeros,

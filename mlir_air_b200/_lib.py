@@ -42,6 +42,7 @@ SIGNATURES = {
     "awq_b200_workspace_init": (c_int, [_P, c_size_t, _P]),
     "awq_b200_workspace_check": (c_int, [_P, _P]),
     "awq_b200_gemv_bf16": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P, c_size_t, _P]),
+    "awq_b200_gemv_bf16_static": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P]),
     "awq_b200_gemv_f32": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P, c_size_t, _P]),
     "awq_b200_rmsnorm_bf16": (c_int, [_P, _P, c_float, _P, c_int, c_int, _P]),
     "awq_b200_add_rmsnorm_bf16": (c_int, [_P, _P, _P, c_float, _P, _P, c_int, c_int, _P]),

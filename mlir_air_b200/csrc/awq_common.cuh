@@ -88,6 +88,7 @@ int launch_gemv_generic(const GemvArgs &a);
 bool gemv_streamk_supported(const GemvArgs &a);
 int launch_gemv_streamk(const GemvArgs &a);
 size_t gemv_streamk_workspace_bytes(int K, int N);
+size_t gemv_streamk_workspace_clear_bytes();
 
 int launch_gemm_generic(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros,
                         const uint16_t *scales, uint16_t *C, int M, int K, int N, int group_size,

@@ -76,6 +76,9 @@ size_t gemv_streamk_workspace_bytes(int K, int N) {
     return SK_WS_PARTIALS + (V + (size_t)sms) * SK_PARTIAL_FLOATS * 4;
 }
 
+// Leading bytes of a workspace (error flag + strip counters) that must be zero before a launch.
+size_t gemv_streamk_workspace_clear_bytes() { return SK_WS_PARTIALS; }
+
 // Conflict-free position of (batch row b, strip column col) inside a reduction slot, both for
 // the MMA accumulator layout (lanes vary in col / 32 and b) and for column-contiguous readers.
 __device__ __forceinline__ int sk_red_idx(int b, int col) {
