@@ -94,7 +94,7 @@ int awq_b200_gemv_bf16(const uint16_t *x, const int32_t *qweight, const int32_t 
  * (a plugin interface that carries only inputs and outputs, a serving process that bans
  * cudaMalloc after start-up, plain C hosts without an allocator).  It has no counterpart in
  * the reference.  The kernel's scratch is a fixed array inside the library image, about
- * 2.5 MB on every GPU that loads the library, held until the process exits; nothing is
+ * 7 MB on every GPU that loads the library, held until the process exits; nothing is
  * allocated or freed by this call.  Limits: N <= 32768, group size 128, K % 128 == 0,
  * N % 32 == 0, 1 <= B <= 64; anything else returns an error rather than falling back.
  * The first call on each device looks up the array's device address, so make that first

@@ -3,27 +3,28 @@
 //   y[B, N] = x[B, K] @ W,   W[k, n] = (q - z) * s,   B <= 8 per launch.
 //
 // HBM-bound (0.52 B per weight, each weight used once), so the design is about keeping
-// bytes in flight and spending about one issue slot per weight:
+// bytes in flight and spending well under two issue slots per weight:
 //
-//  * Work unit = one 256-column strip x one quantisation group of 128 k: a 16 KB box of
-//    packed words, 2 KB of activations, 512 B of scales and 128 B of zeros, fetched by one
-//    producer thread with four TMA tensor copies into a 10-deep shared-memory ring (about
-//    190 KB in flight per SM).  Units are numbered strip-major; CTA c of C takes the
-//    contiguous range [c U / C, (c + 1) U / C) (stream-K), so all SMs stream the same number
-//    of bytes whatever the shape.
-//  * Eight consumer warps take units round-robin.  A lane reads four 16-byte chunks
-//    (4 packed words x 4 k rows) with bank-conflict-free LDS.128 from the 128B-swizzled box,
-//    pairs rows k/k+1 with two PRMT, and turns nibbles into bf16 pairs (128 + q) with one
-//    LOP3 each: that is directly the A fragment of mma.sync.m16n8k16 (rows = 16 output
-//    columns, k = 16).  The activations are the B fragment (ldmatrix from swizzled smem).
+//  * Work unit = one 512-column strip x one quantisation group of 128 k: two 16 KB boxes of
+//    packed words, 2 KB of activations, 1 KB of scales and 256 B of zeros, fetched by one
+//    producer thread with seven TMA tensor copies into a 3-deep shared-memory ring.  Two CTAs
+//    run per SM.  Units are numbered strip-major; CTA c of C takes the contiguous range
+//    [c U / C, (c + 1) U / C) (stream-K), so all SMs stream the same number of bytes whatever
+//    the shape.
+//  * Each of the eight consumer warps owns 64 columns of the strip for the CTA's whole range,
+//    so no warp ever needs another warp's sums: there is no block-level barrier after set-up.
+//    A lane reads one packed word (8 columns) from four k rows with bank-conflict-free LDS.32
+//    from the 128B-swizzled box, pairs rows k/k+1 with two PRMT, and turns nibbles into bf16
+//    pairs (128 + q) with one LOP3 each: that is directly the A fragment of
+//    mma.sync.m16n8k16 (rows = 16 output columns, k = 16).  The activations are the B
+//    fragment (ldmatrix from swizzled smem).
 //  * The zero point and scale never touch the inner loop:
 //        sum_k (q - z) s x = s (sum_k (128 + q) x  -  (128 + z) sum_k x)
 //    per group; sum_k x comes from one extra MMA with an all-ones A fragment.
-//  * At the end of a strip segment the eight warps' f32 partials are summed in shared
-//    memory in a fixed order.  If the CTA covered the whole strip it applies the epilogue;
-//    otherwise it stores its partial to the workspace and bumps the strip's counter, and
-//    the CTA that arrives last sums all partials in CTA order (deterministic) and applies
-//    the epilogue.  Nothing waits on another CTA.
+//  * At the end of a strip segment a warp that covered the whole strip applies the epilogue
+//    from registers.  Otherwise it stores its f32 partial to the workspace and bumps the
+//    counter of its 64-column sub-strip; the warp that arrives last sums all partials in CTA
+//    order (deterministic) and applies the epilogue.  Nothing waits on another CTA.
 //
 // Epilogues: bf16 (+ residual), f32 (tensor-parallel partial), SwiGLU over interleaved
 // gate/up column pairs (matvec_int4_swiglu_rms.py:511-516 rounding points).
@@ -36,62 +37,98 @@
 
 namespace awq {
 
-constexpr int SK_STRIP = 256;
+constexpr int SK_STRIP = 512;                 // columns per unit
+constexpr int SK_BOX_COLS = 256;              // columns per 128-byte-wide TMA box
 constexpr int SK_GROUP = 128;
-constexpr int SK_CONSUMER_WARPS = 8;
-constexpr int SK_CONSUMER_THREADS = SK_CONSUMER_WARPS * 32;
-constexpr int SK_THREADS = SK_CONSUMER_THREADS + 32;
-constexpr int SK_STAGES = 10;
-constexpr int SK_W_BYTES = SK_GROUP * 128;  // 128 k rows x 32 packed words
-constexpr int SK_X_BYTES = 2 * 1024;        // two boxes of 8 batch rows x 64 k (bf16)
+constexpr int SK_CONSUMER_WARPS = SK_STRIP / 64;
+constexpr int SK_THREADS = SK_CONSUMER_WARPS * 32 + 32;
+constexpr int SK_CTAS_PER_SM = 2;
+constexpr int SK_STAGES = 3;
+constexpr int SK_WBOX_BYTES = SK_GROUP * 128;          // 128 k rows x 32 packed words
+constexpr int SK_W_BYTES = (SK_STRIP / SK_BOX_COLS) * SK_WBOX_BYTES;
+constexpr int SK_X_BYTES = 2 * 1024;                   // two boxes of 8 batch rows x 64 k (bf16)
 constexpr int SK_S_BYTES = SK_STRIP * 2;
 constexpr int SK_Z_BYTES = SK_STRIP / 8 * 4;
 constexpr int SK_TX_BYTES = SK_W_BYTES + SK_X_BYTES + SK_S_BYTES + SK_Z_BYTES;
 constexpr int SK_OFF_X = SK_W_BYTES;
 constexpr int SK_OFF_S = SK_OFF_X + SK_X_BYTES;
 constexpr int SK_OFF_Z = SK_OFF_S + SK_S_BYTES;
-constexpr int SK_STAGE_BYTES = 19 * 1024;
-constexpr int SK_RED_PITCH = 260;  // floats per batch row of a reduction slot
-constexpr int SK_RED_SLOT = 8 * SK_RED_PITCH;
-constexpr int SK_RED_BYTES = 4 * SK_RED_SLOT * 4;
+constexpr int SK_STAGE_BYTES = 36 * 1024;
 constexpr int SK_BAR_BYTES = 2 * SK_STAGES * 8 + 16;
-constexpr int SK_SMEM_BYTES = SK_STAGES * SK_STAGE_BYTES + SK_RED_BYTES + SK_BAR_BYTES + 1024;
-constexpr int SK_PARTIAL_FLOATS = 8 * SK_STRIP;
+constexpr int SK_SMEM_BYTES = SK_STAGES * SK_STAGE_BYTES + SK_BAR_BYTES + 1024;
+constexpr int SK_PARTIAL_FLOATS = 8 * SK_STRIP;        // one slot: [warp][batch 8][64 columns]
 static_assert(SK_TX_BYTES <= SK_STAGE_BYTES, "stage too small");
-static_assert(SK_SMEM_BYTES <= 227 * 1024, "shared memory budget");
+static_assert(SK_CTAS_PER_SM * (SK_SMEM_BYTES + 1024) <= 228 * 1024, "shared memory budget");
 
-// Workspace: [0, 256) header (int error flag), then a fixed region of strip counters, then
-// partial slots.  The layout does not depend on the shape, so one workspace can serve
-// products of different shapes back to back (the counters are all zero between launches).
+// Workspace: [0, 256) header (int error flag), then a fixed region of sub-strip counters (one per
+// 64 columns), then partial slots.  The layout does not depend on the shape, so one workspace
+// can serve products of different shapes back to back (the counters are all zero between
+// launches).
 constexpr size_t SK_WS_HEADER = 256;
-constexpr int SK_MAX_STRIPS = 4032;  // N up to 1,032,192 columns
-constexpr size_t SK_WS_PARTIALS = SK_WS_HEADER + (size_t)SK_MAX_STRIPS * 4;  // 16 KB
-constexpr int SK_MAX_CTAS = 1024;
+constexpr int SK_MAX_STRIPS = 504;  // N up to 258,048 columns
+constexpr size_t SK_WS_PARTIALS = SK_WS_HEADER + (size_t)SK_MAX_STRIPS * SK_CONSUMER_WARPS * 4;  // 16 KB
+constexpr int SK_MAX_CTAS = 2048;
 
 size_t gemv_streamk_workspace_bytes(int K, int N) {
     (void)K;
     const size_t V = (size_t)(N + SK_STRIP - 1) / SK_STRIP;
     int sms = device_sm_count();
     if (sms <= 0) sms = 148;
-    return SK_WS_PARTIALS + (V + (size_t)sms) * SK_PARTIAL_FLOATS * 4;
+    return SK_WS_PARTIALS + (V + (size_t)sms * SK_CTAS_PER_SM) * SK_PARTIAL_FLOATS * 4;
 }
 
-// Leading bytes of a workspace (error flag + strip counters) that must be zero before a launch.
+// Leading bytes of a workspace (error flag + counters) that must be zero before a launch.
 size_t gemv_streamk_workspace_clear_bytes() { return SK_WS_PARTIALS; }
-
-// Conflict-free position of (batch row b, strip column col) inside a reduction slot, both for
-// the MMA accumulator layout (lanes vary in col / 32 and b) and for column-contiguous readers.
-__device__ __forceinline__ int sk_red_idx(int b, int col) {
-    return b * SK_RED_PITCH + (col & ~31) + ((col + (col >> 5)) & 31);
-}
 
 // CTA that owns unit x when U units are split over C CTAs as [c U / C, (c + 1) U / C).
 __host__ __device__ __forceinline__ long long sk_owner(long long x, long long C, long long U) {
     return ((x + 1) * C + U - 1) / U - 1;
 }
 
+// One lane's share of a finished strip: 8 consecutive columns (n .. n+7) for batch rows 2t and
+// 2t+1.  v[e][0..3] = (col 2e, row 2t), (col 2e, row 2t+1), (col 2e+1, row 2t), (col 2e+1, row 2t+1).
 template <int EPI>
-__global__ void __launch_bounds__(SK_THREADS, 1)
+__device__ __forceinline__ void sk_epilogue(const float (&v)[4][4], const uint16_t *__restrict__ residual,
+                                            void *__restrict__ y_, int B, int N, int n, int row0) {
+    if (n >= N) return;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int b = row0 + h;
+        if (b >= B) continue;
+        if (EPI == EPI_SWIGLU) {
+            uint32_t o[2];
+#pragma unroll
+            for (int e = 0; e < 4; e += 2)
+                o[e >> 1] = (uint32_t)swiglu_bits(v[e][h], v[e][2 + h]) |
+                            ((uint32_t)swiglu_bits(v[e + 1][h], v[e + 1][2 + h]) << 16);
+            *reinterpret_cast<uint2 *>(reinterpret_cast<uint16_t *>(y_) + (size_t)b * (N >> 1) + (n >> 1)) =
+                make_uint2(o[0], o[1]);
+        } else if (EPI == EPI_F32) {
+            float4 *dst = reinterpret_cast<float4 *>(reinterpret_cast<float *>(y_) + (size_t)b * N + n);
+            dst[0] = make_float4(v[0][h], v[0][2 + h], v[1][h], v[1][2 + h]);
+            dst[1] = make_float4(v[2][h], v[2][2 + h], v[3][h], v[3][2 + h]);
+        } else {
+            float r[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (residual) {
+                const uint4 rv = *reinterpret_cast<const uint4 *>(residual + (size_t)b * N + n);
+                const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    r[2 * e] = bf16x2_lo(rw[e]);
+                    r[2 * e + 1] = bf16x2_hi(rw[e]);
+                }
+            }
+            uint32_t o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[e] = pack_bf16x2(v[e][h] + r[2 * e], v[e][2 + h] + r[2 * e + 1]);
+            *reinterpret_cast<uint4 *>(reinterpret_cast<uint16_t *>(y_) + (size_t)b * N + n) =
+                make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM)
 gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                     const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmZ,
                     const uint16_t *__restrict__ residual, void *__restrict__ y_, int B, int N, int G,
@@ -99,11 +136,7 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                     int *__restrict__ err_flag) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    float *red = reinterpret_cast<float *>(smem_gen + SK_STAGES * SK_STAGE_BYTES);
-    const uint32_t bar_base = smem_base + SK_STAGES * SK_STAGE_BYTES + SK_RED_BYTES;
-    int *s_flag = reinterpret_cast<int *>(smem_gen + SK_STAGES * SK_STAGE_BYTES + SK_RED_BYTES +
-                                          2 * SK_STAGES * 8);
+    const uint32_t bar_base = smem_base + SK_STAGES * SK_STAGE_BYTES;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (SK_STAGES + s); };
 
@@ -115,7 +148,7 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     if (threadIdx.x == 0) {
         for (int s = 0; s < SK_STAGES; ++s) {
             mbar_init(full_bar(s), 1);
-            mbar_init(empty_bar(s), 1);
+            mbar_init(empty_bar(s), SK_CONSUMER_WARPS);
         }
         mbar_fence_init();
     }
@@ -138,216 +171,159 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                 const long long u = u0 + i;
                 const int v = (int)(u / G), g = (int)(u % G);
                 const uint32_t st = smem_base + slot * SK_STAGE_BYTES;
-                mbar_expect_tx(full_bar(slot), SK_TX_BYTES);
-                tma_load_2d_hint(st, &tmW, v * (SK_STRIP / 8), g * SK_GROUP, full_bar(slot), stream_policy);
-                tma_load_2d(st + SK_OFF_X, &tmX, g * SK_GROUP, 0, full_bar(slot));
-                tma_load_2d(st + SK_OFF_X + 1024, &tmX, g * SK_GROUP + 64, 0, full_bar(slot));
-                tma_load_2d(st + SK_OFF_S, &tmS, v * SK_STRIP, g, full_bar(slot));
-                tma_load_2d(st + SK_OFF_Z, &tmZ, v * (SK_STRIP / 8), g, full_bar(slot));
+                const uint32_t bar = full_bar(slot);
+                mbar_expect_tx(bar, SK_TX_BYTES);
+#pragma unroll
+                for (int bx = 0; bx < SK_STRIP / SK_BOX_COLS; ++bx)
+                    tma_load_2d_hint(st + bx * SK_WBOX_BYTES, &tmW, (v * SK_STRIP + bx * SK_BOX_COLS) / 8, g * SK_GROUP,
+                                     bar, stream_policy);
+                tma_load_2d(st + SK_OFF_X, &tmX, g * SK_GROUP, 0, bar);
+                tma_load_2d(st + SK_OFF_X + 1024, &tmX, g * SK_GROUP + 64, 0, bar);
+#pragma unroll
+                for (int bx = 0; bx < SK_STRIP / SK_BOX_COLS; ++bx)
+                    tma_load_2d(st + SK_OFF_S + bx * SK_BOX_COLS * 2, &tmS, v * SK_STRIP + bx * SK_BOX_COLS, g, bar);
+                tma_load_2d(st + SK_OFF_Z, &tmZ, v * (SK_STRIP / 8), g, bar);
             }
         }
         return;
     }
 
     // ------------------------------ consumers ------------------------------
+    // Warp w owns strip columns [64 w, 64 w + 64); lane (g8, t4) owns packed word g8 of them.
     const int g8 = lane >> 2, t4 = lane & 3;
+    const uint32_t w_box = (warp >> 2) * SK_WBOX_BYTES;          // which 256-column box
+    const uint32_t chunk = 2 * (warp & 3) + (g8 >> 2);           // 16-byte chunk inside a box row
     // Rows 2t and 2t+1 of a 16-row k-step; rows +8 share the swizzle (row & 7 unchanged).
-    const uint32_t offA = (2 * t4) * 128 + ((g8 ^ (2 * t4)) << 4);
-    const uint32_t offB = (2 * t4 + 1) * 128 + ((g8 ^ (2 * t4 + 1)) << 4);
+    const uint32_t offA = w_box + (2 * t4) * 128 + ((chunk ^ (2 * t4)) << 4) + (g8 & 3) * 4;
+    const uint32_t offB = w_box + (2 * t4 + 1) * 128 + ((chunk ^ (2 * t4 + 1)) << 4) + (g8 & 3) * 4;
     const int xm = lane >> 3, xb = lane & 7;  // ldmatrix: matrix index, batch row
     const uint32_t ONES = 0x3F803F80u;
-    const int tid = threadIdx.x;  // 0..255: strip column owned in the epilogue
+    const int col0 = warp * 64 + g8 * 8;      // first of this lane's 8 strip columns
     bool failed = false;
 
-    int i_begin = 0;
-    while (i_begin < n_units) {
-        const long long ub = u0 + i_begin;
-        const int v = (int)(ub / G);
-        const int i_end = (int)min((long long)n_units, (long long)(v + 1) * G - u0);
+    float res[4][4];
+    int cur_v = -1;
 
-        float res[16][4];
-#pragma unroll
-        for (int m = 0; m < 16; ++m)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) res[m][e] = 0.f;
-
-        // first local unit index >= i_begin that is congruent to this warp modulo 8
-        int i = i_begin + ((warp - i_begin) & (SK_CONSUMER_WARPS - 1));
-        for (; i < i_end; i += SK_CONSUMER_WARPS) {
-            const int slot = i % SK_STAGES, round = i / SK_STAGES;
-            // A parity wait cannot tell phase r from phase r - 2.  The slot's previous round belongs
-            // to another warp, so first see that round released (then the full barrier is in phase
-            // r or later and its parity is unambiguous).
-            if (!failed && round > 0 && !mbar_wait_bounded(empty_bar(slot), (round - 1) & 1)) {
-                failed = true;
-                if (lane == 0) atomicExch(err_flag, 3);
-            }
-            if (!failed && !mbar_wait_bounded(full_bar(slot), round & 1)) {
-                failed = true;
-                if (lane == 0) atomicExch(err_flag, 2);
-            }
-            if (failed) continue;
-            const uint32_t st = smem_base + slot * SK_STAGE_BYTES;
-
-            float acc[16][4];
-            float sx[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int m = 0; m < 16; ++m)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) acc[m][e] = 0.f;
-
-#pragma unroll 1
-            for (int p = 0; p < 4; ++p) {
-                // activations for k-steps 2p and 2p+1: 16-byte chunk q = 4p + matrix index
-                const int q = 4 * p + xm;
-                uint32_t bx[4];
-                ldmatrix_x4(bx, st + SK_OFF_X + (q >> 3) * 1024 + xb * 128 + (((q & 7) ^ xb) << 4));
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint32_t rb = st + (2 * p + h) * 2048;
-                    const uint4 w0 = lds128(rb + offA);
-                    const uint4 w1 = lds128(rb + offB);
-                    const uint4 w2 = lds128(rb + 1024 + offA);
-                    const uint4 w3 = lds128(rb + 1024 + offB);
-                    const uint32_t b0 = bx[2 * h], b1 = bx[2 * h + 1];
-                    mma_bf16_16816(sx, ONES, ONES, ONES, ONES, b0, b1);
-                    const uint32_t q0[4] = {w0.x, w0.y, w0.z, w0.w};
-                    const uint32_t q1[4] = {w1.x, w1.y, w1.z, w1.w};
-                    const uint32_t q2[4] = {w2.x, w2.y, w2.z, w2.w};
-                    const uint32_t q3[4] = {w3.x, w3.y, w3.z, w3.w};
-#pragma unroll
-                    for (int cb = 0; cb < 4; ++cb) {
-                        // low halves hold nibbles 0-3 (columns 0,2,4,6), high halves nibbles 4-7
-                        // (columns 1,3,5,7); pair rows k and k+1 of the same column in one register
-                        const uint32_t lo01 = __byte_perm(q0[cb], q1[cb], 0x5410);
-                        const uint32_t hi01 = __byte_perm(q0[cb], q1[cb], 0x7632);
-                        const uint32_t lo23 = __byte_perm(q2[cb], q3[cb], 0x5410);
-                        const uint32_t hi23 = __byte_perm(q2[cb], q3[cb], 0x7632);
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            // MMA row g8 = column 8cb + 2e, row g8 + 8 = column 8cb + 2e + 1
-                            mma_bf16_16816(acc[cb * 4 + e], nib2_to_bf16x2_biased(lo01 >> (4 * e)),
-                                           nib2_to_bf16x2_biased(hi01 >> (4 * e)),
-                                           nib2_to_bf16x2_biased(lo23 >> (4 * e)),
-                                           nib2_to_bf16x2_biased(hi23 >> (4 * e)), b0, b1);
-                        }
-                    }
-                }
-            }
-
-            // group fix-up: res += s * (acc - (128 + z) * sum_x)
-            const uint4 zv = lds128(st + SK_OFF_Z + g8 * 16);
-            const uint32_t zw[4] = {zv.x, zv.y, zv.z, zv.w};
-#pragma unroll
-            for (int cb = 0; cb < 4; ++cb) {
-                const uint4 sv = lds128(st + SK_OFF_S + g8 * 64 + cb * 16);
-                const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const uint32_t zz = nib2_to_bf16x2_biased(zw[cb] >> (4 * e));
-                    const float z_even = bf16x2_lo(zz), z_odd = bf16x2_hi(zz);
-                    const float s_even = bf16x2_lo(sw[e]), s_odd = bf16x2_hi(sw[e]);
-                    float(&a)[4] = acc[cb * 4 + e];
-                    float(&r)[4] = res[cb * 4 + e];
-                    r[0] = fmaf(s_even, fmaf(-z_even, sx[0], a[0]), r[0]);
-                    r[1] = fmaf(s_even, fmaf(-z_even, sx[1], a[1]), r[1]);
-                    r[2] = fmaf(s_odd, fmaf(-z_odd, sx[0], a[2]), r[2]);
-                    r[3] = fmaf(s_odd, fmaf(-z_odd, sx[1], a[3]), r[3]);
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(empty_bar(slot));
-        }
-
-        // ---- sum the eight warps' partials (fixed order), one strip column per thread ----
-        if (warp < 4) {
-            float *slot = red + warp * SK_RED_SLOT;
-#pragma unroll
-            for (int m = 0; m < 16; ++m) {
-                const int col = 32 * g8 + 8 * (m >> 2) + 2 * (m & 3);
-                slot[sk_red_idx(2 * t4, col)] = res[m][0];
-                slot[sk_red_idx(2 * t4 + 1, col)] = res[m][1];
-                slot[sk_red_idx(2 * t4, col + 1)] = res[m][2];
-                slot[sk_red_idx(2 * t4 + 1, col + 1)] = res[m][3];
-            }
-        }
-        named_bar_sync(1, SK_CONSUMER_THREADS);
-        if (warp >= 4) {
-            float *slot = red + (warp - 4) * SK_RED_SLOT;
-#pragma unroll
-            for (int m = 0; m < 16; ++m) {
-                const int col = 32 * g8 + 8 * (m >> 2) + 2 * (m & 3);
-                slot[sk_red_idx(2 * t4, col)] += res[m][0];
-                slot[sk_red_idx(2 * t4 + 1, col)] += res[m][1];
-                slot[sk_red_idx(2 * t4, col + 1)] += res[m][2];
-                slot[sk_red_idx(2 * t4 + 1, col + 1)] += res[m][3];
-            }
-        }
-        named_bar_sync(1, SK_CONSUMER_THREADS);
-        float val[8];
-#pragma unroll
-        for (int b = 0; b < 8; ++b) {
-            const int idx = sk_red_idx(b, tid);
-            val[b] = ((red[idx] + red[SK_RED_SLOT + idx]) + red[2 * SK_RED_SLOT + idx]) + red[3 * SK_RED_SLOT + idx];
-        }
-        named_bar_sync(1, SK_CONSUMER_THREADS);
-
-        // ---- strips shared between CTAs: last arriver sums the partials in CTA order ----
+    // Finish the strip segment this warp has been accumulating (strip cur_v).
+    auto flush = [&]() {
+        const int v = cur_v;
+        const int n = v * SK_STRIP + col0;
         const long long c_lo = sk_owner((long long)v * G, C, U);
         const long long c_hi = sk_owner((long long)(v + 1) * G - 1, C, U);
-        bool do_epilogue = true;
-        if (c_hi > c_lo) {
-            float *mine = partials + (size_t)(c + v) * SK_PARTIAL_FLOATS;
+        if (c_hi == c_lo) {
+            if (!failed) sk_epilogue<EPI>(res, residual, y_, B, N, n, 2 * t4);
+            return;
+        }
+        // [slot][warp][batch row][64 columns]
+        float *mine = partials + (size_t)(c + v) * SK_PARTIAL_FLOATS + warp * 512 + g8 * 8;
 #pragma unroll
-            for (int b = 0; b < 8; ++b)
-                if (b < B) mine[b * SK_STRIP + tid] = val[b];
-            __threadfence();
-            named_bar_sync(1, SK_CONSUMER_THREADS);
-            if (tid == 0) {
-                const int old = atomicAdd(&counters[v], 1);
-                *s_flag = (old == (int)(c_hi - c_lo)) ? 1 : 0;
+        for (int h = 0; h < 2; ++h) {
+            float4 *dst = reinterpret_cast<float4 *>(mine + (2 * t4 + h) * 64);
+            dst[0] = make_float4(res[0][h], res[0][2 + h], res[1][h], res[1][2 + h]);
+            dst[1] = make_float4(res[2][h], res[2][2 + h], res[3][h], res[3][2 + h]);
+        }
+        __threadfence();
+        __syncwarp();
+        int old = 0;
+        if (lane == 0) old = atomicAdd(&counters[v * SK_CONSUMER_WARPS + warp], 1);
+        old = __shfl_sync(0xffffffffu, old, 0);
+        if (old != (int)(c_hi - c_lo)) return;
+        __threadfence();
+        float sum[4][4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) sum[e][q] = 0.f;
+        for (long long cc = c_lo; cc <= c_hi; ++cc) {
+            const float *src = partials + (size_t)(cc + v) * SK_PARTIAL_FLOATS + warp * 512 + g8 * 8;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const float4 a = __ldcg(reinterpret_cast<const float4 *>(src + (2 * t4 + h) * 64));
+                const float4 b = __ldcg(reinterpret_cast<const float4 *>(src + (2 * t4 + h) * 64) + 1);
+                sum[0][h] += a.x; sum[0][2 + h] += a.y; sum[1][h] += a.z; sum[1][2 + h] += a.w;
+                sum[2][h] += b.x; sum[2][2 + h] += b.y; sum[3][h] += b.z; sum[3][2 + h] += b.w;
             }
-            named_bar_sync(1, SK_CONSUMER_THREADS);
-            do_epilogue = (*s_flag != 0);
-            if (do_epilogue) {
-                __threadfence();
+        }
+        __syncwarp();
+        if (lane == 0) counters[v * SK_CONSUMER_WARPS + warp] = 0;  // ready for the next launch
+        if (!failed) sk_epilogue<EPI>(sum, residual, y_, B, N, n, 2 * t4);
+    };
+
+    for (int i = 0; i < n_units; ++i) {
+        const long long u = u0 + i;
+        const int v = (int)(u / G);
+        if (v != cur_v) {
+            if (cur_v >= 0) flush();
+            cur_v = v;
 #pragma unroll
-                for (int b = 0; b < 8; ++b) {
-                    float s = 0.f;
-                    if (b < B)
-                        for (long long cc = c_lo; cc <= c_hi; ++cc)
-                            s += __ldcg(partials + (size_t)(cc + v) * SK_PARTIAL_FLOATS + b * SK_STRIP + tid);
-                    val[b] = s;
+            for (int e = 0; e < 4; ++e)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) res[e][q] = 0.f;
+        }
+        const int slot = i % SK_STAGES, round = i / SK_STAGES;
+        if (!failed && !mbar_wait_bounded(full_bar(slot), round & 1)) {
+            failed = true;
+            if (lane == 0) atomicExch(err_flag, 2);
+        }
+        if (failed) continue;
+        const uint32_t st = smem_base + slot * SK_STAGE_BYTES;
+
+        float acc[4][4];
+        float sx[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) acc[e][q] = 0.f;
+
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            // activations for k-steps 2p and 2p+1: 16-byte chunk q = 4p + matrix index
+            const int q = 4 * p + xm;
+            uint32_t bx[4];
+            ldmatrix_x4(bx, st + SK_OFF_X + (q >> 3) * 1024 + xb * 128 + (((q & 7) ^ xb) << 4));
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t rb = st + (2 * p + h) * 2048;
+                const uint32_t w0 = lds32(rb + offA);
+                const uint32_t w1 = lds32(rb + offB);
+                const uint32_t w2 = lds32(rb + 1024 + offA);
+                const uint32_t w3 = lds32(rb + 1024 + offB);
+                const uint32_t b0 = bx[2 * h], b1 = bx[2 * h + 1];
+                mma_bf16_16816(sx, ONES, ONES, ONES, ONES, b0, b1);
+                // low halves hold nibbles 0-3 (columns 0,2,4,6), high halves nibbles 4-7
+                // (columns 1,3,5,7); pair rows k and k+1 of the same column in one register
+                const uint32_t lo01 = __byte_perm(w0, w1, 0x5410);
+                const uint32_t hi01 = __byte_perm(w0, w1, 0x7632);
+                const uint32_t lo23 = __byte_perm(w2, w3, 0x5410);
+                const uint32_t hi23 = __byte_perm(w2, w3, 0x7632);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    // MMA row g8 = column 2e of the lane's word, row g8 + 8 = column 2e + 1
+                    mma_bf16_16816(acc[e], nib2_to_bf16x2_biased(lo01 >> (4 * e)),
+                                   nib2_to_bf16x2_biased(hi01 >> (4 * e)), nib2_to_bf16x2_biased(lo23 >> (4 * e)),
+                                   nib2_to_bf16x2_biased(hi23 >> (4 * e)), b0, b1);
                 }
-                if (tid == 0) counters[v] = 0;  // leave the workspace ready for the next launch
             }
         }
 
-        if (do_epilogue && !failed) {
-            const int n = v * SK_STRIP + tid;
-            if (EPI == EPI_SWIGLU) {
-                uint16_t *out = reinterpret_cast<uint16_t *>(y_);
+        // group fix-up: res += s * (acc - (128 + z) * sum_x)
+        const uint32_t zw = lds32(st + SK_OFF_Z + (col0 >> 3) * 4);
+        const uint4 sv = lds128(st + SK_OFF_S + col0 * 2);
+        const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_bar(slot));  // all of this warp's reads of the slot are done
 #pragma unroll
-                for (int b = 0; b < 8; ++b) {
-                    const float other = __shfl_xor_sync(0xffffffffu, val[b], 1);
-                    if (b < B && n < N && !(tid & 1)) out[(size_t)b * (N >> 1) + (n >> 1)] = swiglu_bits(val[b], other);
-                }
-            } else if (n < N) {
-#pragma unroll
-                for (int b = 0; b < 8; ++b) {
-                    if (b >= B) continue;
-                    if (EPI == EPI_F32) {
-                        reinterpret_cast<float *>(y_)[(size_t)b * N + n] = val[b];
-                    } else {
-                        float s = val[b];
-                        if (residual) s += bf16_bits_to_f32(residual[(size_t)b * N + n]);
-                        reinterpret_cast<uint16_t *>(y_)[(size_t)b * N + n] = f32_to_bf16_bits(s);
-                    }
-                }
-            }
+        for (int e = 0; e < 4; ++e) {
+            const uint32_t zz = nib2_to_bf16x2_biased(zw >> (4 * e));
+            const float z_even = bf16x2_lo(zz), z_odd = bf16x2_hi(zz);
+            const float s_even = bf16x2_lo(sw[e]), s_odd = bf16x2_hi(sw[e]);
+            res[e][0] = fmaf(s_even, fmaf(-z_even, sx[0], acc[e][0]), res[e][0]);
+            res[e][1] = fmaf(s_even, fmaf(-z_even, sx[1], acc[e][1]), res[e][1]);
+            res[e][2] = fmaf(s_odd, fmaf(-z_odd, sx[0], acc[e][2]), res[e][2]);
+            res[e][3] = fmaf(s_odd, fmaf(-z_odd, sx[1], acc[e][3]), res[e][3]);
         }
-        i_begin = i_end;
     }
+    if (cur_v >= 0) flush();
 }
 
 // ---------------------------------------------------------------------------------------
@@ -410,14 +386,14 @@ static int launch_one(const GemvArgs &a, const uint16_t *x, const uint16_t *resi
                                    CU_TENSOR_MAP_SWIZZLE_128B)))
         return rc;
     if ((rc = encode_tensor_map_2d(&tmS, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a.scales, a.N, G, (uint64_t)a.N * 2,
-                                   SK_STRIP, 1, CU_TENSOR_MAP_SWIZZLE_NONE)))
+                                   SK_BOX_COLS, 1, CU_TENSOR_MAP_SWIZZLE_NONE)))
         return rc;
-    if ((rc = encode_tensor_map_2d(&tmZ, CU_TENSOR_MAP_DATA_TYPE_INT32, a.qzeros, nb, G, (uint64_t)nb * 4, 32, 1,
-                                   CU_TENSOR_MAP_SWIZZLE_NONE)))
+    if ((rc = encode_tensor_map_2d(&tmZ, CU_TENSOR_MAP_DATA_TYPE_INT32, a.qzeros, nb, G, (uint64_t)nb * 4,
+                                   SK_STRIP / 8, 1, CU_TENSOR_MAP_SWIZZLE_NONE)))
         return rc;
 
     const long long U = (long long)V * G;
-    int ctas = device_sm_count();
+    int ctas = device_sm_count() * SK_CTAS_PER_SM;
     if (ctas > SK_MAX_CTAS) ctas = SK_MAX_CTAS;
     if ((long long)ctas > U) ctas = (int)U;
     uint8_t *ws = reinterpret_cast<uint8_t *>(a.workspace);

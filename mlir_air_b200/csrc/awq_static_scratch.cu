@@ -5,7 +5,7 @@
 // cudaMalloc once serving has started, or C code that links the .so without any allocator of
 // its own.  For them the scratch of the stream-K decode kernel (strip counters and split-K
 // partials) lives in a fixed array inside the library image instead of a caller-owned
-// workspace.  Every GPU that loads the library holds that array (about 2.5 MB) until the
+// workspace.  Every GPU that loads the library holds that array (about 7 MB) until the
 // process exits.
 #include <mutex>
 
@@ -13,10 +13,10 @@
 
 namespace awq {
 
-// Room for 128 strips of 256 columns (N <= 32768) on a GPU with up to 192 SMs:
-// 16 KB of header + counters, then (128 + 192) partial slots of 8 KB.
+// Room for 64 strips of 512 columns (N <= 32768) on a GPU with up to 192 SMs (two CTAs each):
+// 16 KB of header + counters, then (64 + 2 * 192) partial slots of 16 KB.
 constexpr int STATIC_MAX_N = 32768;
-constexpr size_t STATIC_SCRATCH_BYTES = 16384 + (size_t)(128 + 192) * 8192;
+constexpr size_t STATIC_SCRATCH_BYTES = 16384 + (size_t)(64 + 2 * 192) * 16384;
 
 static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
 
