@@ -50,9 +50,17 @@ int awq_b200_version(void);
  * python/air/backend/xrt.py:204-218). */
 const char *awq_b200_last_error(void);
 
+/* 16-bit activation formats of the *_act entry points.  Public inputs and outputs are bf16; fp16
+ * is the format activations take between the kernels of one FFN (exact for bf16-rounded values
+ * inside the fp16 range), because the GEMV kernel multiplies fp16 activations fastest. */
+#define AWQ_ACT_BF16 0
+#define AWQ_ACT_F16 1
+
 /* Choose the decode kernel: 0 = automatic (TMA + tensor-core stream-K kernel when the
  * shape allows it, else the generic kernel), 1 = force generic, 2 = force stream-K
- * (returns AWQ_ERR_UNSUPPORTED where it cannot run).  Process-wide; for tests. */
+ * (returns AWQ_ERR_UNSUPPORTED where it cannot run), 3 = stream-K multiplying bf16
+ * activations as they are (no fp16 conversion; for activations beyond the fp16 range).
+ * Process-wide; for tests. */
 int awq_b200_set_decode_kernel(int mode);
 
 /* ---- AWQ dequant --------------------------------------------------------------
@@ -69,7 +77,8 @@ int awq_b200_dequant_1d_bf16(const uint8_t *packed_q, const uint16_t *scales, co
                              uint16_t *out, int n, int group_size, awq_stream_t stream);
 
 /* ---- workspace ---------------------------------------------------------------- */
-/* Bytes of scratch the decode kernels need for a [B, K] x [K, N] product. */
+/* Bytes of scratch the decode kernels need for a [B, K] x [K, N] product (counters, split-K
+ * partials, and room to convert B rows of bf16 activations to fp16). */
 size_t awq_b200_workspace_bytes(int B, int K, int N);
 /* Zero the workspace (once after allocation, and again after any call that
  * returned AWQ_ERR_DEVICE_TIMEOUT). */
@@ -104,6 +113,12 @@ int awq_b200_gemv_bf16_static(const uint16_t *x, const int32_t *qweight, const i
                               const uint16_t *scales, const uint16_t *residual, uint16_t *y, int B,
                               int K, int N, int group_size, awq_stream_t stream);
 
+/* General form: x in `x_format` (AWQ_ACT_*), y bf16 (y_is_f32 = 0, optional residual) or f32. */
+int awq_b200_gemv_act(const void *x, int x_format, const int32_t *qweight, const int32_t *qzeros,
+                      const uint16_t *scales, const uint16_t *residual, void *y, int y_is_f32, int B,
+                      int K, int N, int group_size, void *workspace, size_t workspace_bytes,
+                      awq_stream_t stream);
+
 /* Same product, f32 output without rounding or residual: the per-rank partial of a
  * K-split (row-parallel) down projection, summed across ranks by the caller. */
 int awq_b200_gemv_f32(const uint16_t *x, const int32_t *qweight, const int32_t *qzeros,
@@ -116,12 +131,19 @@ int awq_b200_gemv_f32(const uint16_t *x, const int32_t *qweight, const int32_t *
 int awq_b200_rmsnorm_bf16(const uint16_t *x, const uint16_t *gamma, float eps, uint16_t *out, int B,
                           int K, awq_stream_t stream);
 
+int awq_b200_rmsnorm_act(const uint16_t *x, const uint16_t *gamma, float eps, void *out, int out_format,
+                         int B, int K, awq_stream_t stream);
+
 /* h_out bf16 [B, K] = bf16(h + partial_sum) and normed = rmsnorm(h_out, gamma): the residual
  * add that follows the allreduce of a K-split down projection, fused with the next layer's norm.
  * gamma/normed may be NULL (no norm). */
 int awq_b200_add_rmsnorm_bf16(const uint16_t *h, const float *partial_sum, const uint16_t *gamma,
                               float eps, uint16_t *h_out, uint16_t *normed, int B, int K,
                               awq_stream_t stream);
+
+int awq_b200_add_rmsnorm_act(const uint16_t *h, const float *partial_sum, const uint16_t *gamma,
+                             float eps, uint16_t *h_out, void *normed, int normed_format, int B, int K,
+                             awq_stream_t stream);
 
 /* ---- fused gate/up GEMV + SwiGLU ---------------------------------------------------
  * One AWQ matrix [K, 2I] whose columns are gate/up interleaved (column 2i = gate_i,
@@ -132,6 +154,11 @@ int awq_b200_gateup_swiglu_bf16(const uint16_t *x, const int32_t *qweight, const
                                 const uint16_t *scales, uint16_t *out, int B, int K, int I,
                                 int group_size, void *workspace, size_t workspace_bytes,
                                 awq_stream_t stream);
+
+int awq_b200_gateup_swiglu_act(const void *x, int x_format, const int32_t *qweight,
+                               const int32_t *qzeros, const uint16_t *scales, void *out, int out_format,
+                               int B, int K, int I, int group_size, void *workspace,
+                               size_t workspace_bytes, awq_stream_t stream);
 
 /* Interleave two [K, I] AWQ matrices (separate gate and up projections, as stored in an
  * HF checkpoint) into the [K, 2I] form above.  Done once per weight. */
@@ -144,9 +171,10 @@ int awq_b200_interleave_gate_up(const int32_t *qw_gate, const int32_t *qz_gate,
  * out bf16 [B, H] = bf16(down(swiglu(gateup . norm(x))) + residual) with
  * norm = RMSNorm(gamma, eps) when gamma != NULL.  The LGU -> LD chain of
  * llms/llama32_1b_int4/multi_launch_builder/o_gemv_ffn_int4_multi.py:9-12 and the four
- * launches of ffn_swiglu/decode/ffn_decode.py:48-250.  `inter` (bf16 [B, I]) and `normed`
- * (bf16 [B, H], only with gamma) are caller-provided intermediates, as they are function
- * arguments in the reference (ffn_decode.py:300-303).  residual may be NULL. */
+ * launches of ffn_swiglu/decode/ffn_decode.py:48-250.  `inter` (16-bit [B, I]) and `normed`
+ * (16-bit [B, H], only with gamma) are caller-provided scratch for the intermediates, as they
+ * are function arguments in the reference (ffn_decode.py:300-303); their contents are in the
+ * library's internal activation format (fp16).  residual may be NULL. */
 int awq_b200_ffn_decode_bf16(const uint16_t *x, const uint16_t *gamma, float eps,
                              const int32_t *qw_gateup, const int32_t *qz_gateup,
                              const uint16_t *s_gateup, const int32_t *qw_down,
@@ -166,6 +194,15 @@ int awq_b200_gemm_bf16(const uint16_t *A, const int32_t *qweight, const int32_t 
 /* Choose the prefill kernel: 0 = automatic, 1 = generic CUDA-core kernel,
  * 2 = tcgen05 tensor-core kernel (AWQ_ERR_UNSUPPORTED where it cannot run). */
 int awq_b200_set_gemm_kernel(int mode);
+
+/* ---- bf16 sibling path (un-quantised weights) ----------------------------------------------
+ * y bf16 [M, N] = bf16(x[M, K] @ W[N, K]^T): the GEMV/GEMM of ffn_swiglu/decode/ffn_kernels.cc:52-117
+ * (matvec_vectorized_bf16_bf16) and ffn_swiglu/prefill/ffn_kernels.cc:55-83 (matmul_bf16).
+ * out = bf16(g * sigmoid(g) * u): swiglu_bf16 (ffn_kernels.cc:123-151), golden ffn_decode.py:309-311. */
+int awq_b200_linear_bf16(const uint16_t *x, const uint16_t *W, uint16_t *y, int M, int K, int N,
+                         awq_stream_t stream);
+int awq_b200_silu_mul_bf16(const uint16_t *gate, const uint16_t *up, uint16_t *out, size_t n,
+                           awq_stream_t stream);
 
 /* ---- layout converters (once per weight) ------------------------------------------------
  * Layout B is mlir-air's logical form (matvec_int4_packed.py:346-350):

@@ -42,6 +42,10 @@ SIGNATURES = {
     "awq_b200_workspace_init": (c_int, [_P, c_size_t, _P]),
     "awq_b200_workspace_check": (c_int, [_P, _P]),
     "awq_b200_gemv_bf16": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P, c_size_t, _P]),
+    "awq_b200_gemv_act": (c_int, [_P, c_int, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, c_size_t, _P]),
+    "awq_b200_gateup_swiglu_act": (c_int, [_P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, c_size_t, _P]),
+    "awq_b200_rmsnorm_act": (c_int, [_P, _P, c_float, _P, c_int, c_int, c_int, _P]),
+    "awq_b200_add_rmsnorm_act": (c_int, [_P, _P, _P, c_float, _P, _P, c_int, c_int, c_int, _P]),
     "awq_b200_gemv_bf16_static": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P]),
     "awq_b200_gemv_f32": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P, c_size_t, _P]),
     "awq_b200_rmsnorm_bf16": (c_int, [_P, _P, c_float, _P, c_int, c_int, _P]),
@@ -50,6 +54,8 @@ SIGNATURES = {
     "awq_b200_interleave_gate_up": (c_int, [_P] * 9 + [c_int, c_int, c_int, _P]),
     "awq_b200_ffn_decode_bf16": (c_int, [_P, _P, c_float] + [_P] * 10 + [c_int, c_int, c_int, c_int, _P, c_size_t, _P]),
     "awq_b200_gemm_bf16": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P]),
+    "awq_b200_linear_bf16": (c_int, [_P, _P, _P, c_int, c_int, c_int, _P]),
+    "awq_b200_silu_mul_bf16": (c_int, [_P, _P, _P, c_size_t, _P]),
     "awq_b200_repack_B_to_A": (c_int, [_P] * 6 + [c_int, c_int, c_int, _P]),
     "awq_b200_repack_A_to_B": (c_int, [_P] * 6 + [c_int, c_int, c_int, _P]),
 }

@@ -1,0 +1,303 @@
+"""Runner and backend with the reference's interface, executing on a B200.
+
+Mirrors `XRTRunner` (python/air/backend/xrt_runner.py:60-373) and `XRTBackend`
+(python/air/backend/xrt.py:221-929): the same constructor keywords (NPU-only ones are
+accepted and ignored), `run_test(module, inputs, expected_outputs, rtol, atol,
+max_mismatch_percentage, min_correlation) -> 0 | -1` printing `PASS!` / `failed.`,
+`compile(module) -> artifact`, `load(artifact) -> invoker(*arrays) -> tuple(arrays)`, `unload()`,
+`last_latency_us`.  A "module" here is a `KernelSpec` (what the example's `build_module`
+returns): there is no IR to compile, so `compile` validates the spec and loads the library.
+
+The invoker behaves like the XRT one (xrt.py:742-791): it allocates device buffers per call,
+copies every argument in, runs, copies every buffer back and returns them all as fresh host
+arrays (inputs first, outputs after).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence
+
+import numpy as np
+from ml_dtypes import bfloat16
+
+from . import _lib, layouts
+from ._lib import AwqBackendError
+
+AirBackendError = AwqBackendError  # the reference's exception name
+
+
+@dataclass
+class KernelSpec:
+    """What `build_module` returns: the kernel instance and its compile-time shape parameters
+    (the `-DDIM_*` macros of the AIE kernels become run-time arguments here)."""
+    instance_name: str
+    params: Dict[str, int] = field(default_factory=dict)
+
+    def __str__(self):  # `-p/--print-module-only` prints the resolved plan instead of MLIR
+        items = ", ".join(f"{k}={v}" for k, v in self.params.items())
+        return f"b200.kernel @{self.instance_name}({items})"
+
+
+def _to_dev(a: np.ndarray):
+    import torch
+    a = np.ascontiguousarray(a)
+    if a.dtype == bfloat16:
+        return torch.from_numpy(a.view(np.int16)).cuda().view(torch.bfloat16)
+    return torch.from_numpy(a).cuda()
+
+
+def _to_host(t, like: np.ndarray):
+    import torch
+    if t.dtype == torch.bfloat16:
+        return t.contiguous().view(torch.int16).cpu().numpy().view(bfloat16).reshape(like.shape)
+    return t.cpu().numpy().reshape(like.shape)
+
+
+# ---- one host-level implementation per kernel instance: args are the example's buffers ----------
+def _run_dequant(p, args):
+    from . import ops
+    packed, out = args
+    pq, s, z = layouts.unpack_dequant_tiles(packed, p["n"], p["group_size"], p["herd_n"])
+    y = ops.dequant_1d(_to_dev(pq), _to_dev(s), _to_dev(z), p["n"], p["group_size"])
+    return [y], [1]
+
+
+def _weight_from_gemv_tiles(p, packed, M):
+    from . import ops
+    A_q, A_s, A_z = layouts.unpack_gemv_tiles(packed, M, p["K"], p["GS"], p["M_TILE"], p["K_CHUNK"], p["N_CORES"],
+                                              p.get("M_PER_LAUNCH") or M)
+    return ops.repack_B_to_A(_to_dev(A_q), _to_dev(A_s), _to_dev(A_z), p["GS"])
+
+
+def _run_matvec(p, args):
+    from . import ops
+    packed, x, out = args
+    w = _weight_from_gemv_tiles(p, packed, p["M"])
+    ws = ops.Workspace(w.K, w.N)
+    y = ops.gemv(_to_dev(np.asarray(x).reshape(-1, p["K"])), w, ws)
+    ws.check()
+    return [y], [2]
+
+
+def _run_matvec_add(p, args):
+    from . import ops
+    packed, x, r, out = args
+    w = _weight_from_gemv_tiles(p, packed, p["M"])
+    ws = ops.Workspace(w.K, w.N)
+    y = ops.gemv(_to_dev(np.asarray(x).reshape(-1, p["K"])), w, ws, residual=_to_dev(np.asarray(r).reshape(-1, p["M"])))
+    ws.check()
+    return [y], [3]
+
+
+def _run_swiglu_rms(p, args):
+    from . import ops
+    packed, rms_in, out = args
+    w = _weight_from_gemv_tiles(p, packed, p["M"])  # rows gate/up interleaved -> [K, 2I] interleaved columns
+    ws = ops.Workspace(w.K, w.N)
+    rms_in = np.asarray(rms_in).reshape(2, p["K"])
+    normed = ops.rmsnorm(_to_dev(rms_in[0:1]), _to_dev(rms_in[1]), p.get("eps", 1e-5))
+    y = ops.gateup_swiglu(normed, w, ws)
+    ws.check()
+    return [y], [2]
+
+
+def _run_matmul(p, args):
+    from . import ops
+    A, packed, out = args
+    W_q, W_s, W_z = layouts.unpack_gemm_tiles(packed, p["K"], p["N"], p["GS"], p["N_TILE"], p["K_CHUNK"])
+    w = ops.repack_B_to_A(_to_dev(W_q), _to_dev(W_s), _to_dev(W_z), p["GS"])
+    y = ops.gemm(_to_dev(np.asarray(A).reshape(p["M"], p["K"])), w)
+    return [y], [2]
+
+
+def _run_ffn_int4(p, args):
+    """x, then (qweight, qzeros, scales) of gate/up-interleaved and of down, then `inter` and `out`."""
+    from . import ops
+    x, gq, gz, gs_, dq, dz, ds, inter, out = args
+    H, I, gsz = p["hidden"], p["intermediate"], p["GS"]
+    wgu = ops.AwqWeight.from_numpy(gq, gz, gs_, gsz)
+    wd = ops.AwqWeight.from_numpy(dq, dz, ds, gsz)
+    ws = ops.Workspace(max(H, I), max(2 * I, H))
+    xd = _to_dev(np.asarray(x).reshape(-1, H))
+    it = ops.gateup_swiglu(xd, wgu, ws)  # bf16 intermediate, returned to the caller for checking
+    y = ops.gemv(it, wd, ws)
+    ws.check()
+    return [it, y], [7, 8]
+
+
+def _run_ffn_bf16(p, args):
+    """bf16 FFN examples: x, packed [gate | up | down] weights, then the gate / up / inter buffers
+    (function arguments in the reference, ffn_decode.py:300-303) and the output."""
+    from . import ops
+    x, packed, gate_buf, up_buf, inter_buf, out = args
+    dim, cols = p["dim"], p["num_cols"]
+    unpack = layouts.unpack_ffn_weights_prefill if p["mode"] == "prefill" else layouts.unpack_ffn_weights_decode
+    flat = np.asarray(packed).reshape(3, dim * dim)
+    Wg, Wu, Wd = (unpack(flat[i], dim, cols) for i in range(3))
+    if p["mode"] == "prefill":
+        # that example packs B = W^T column blocks of `W[:, cols]`, and its golden multiplies by W^T
+        Wg, Wu, Wd = (np.ascontiguousarray(w) for w in (Wg, Wu, Wd))
+    xd = _to_dev(np.asarray(x).reshape(-1, dim))
+    g = ops.linear_bf16(xd, _to_dev(Wg))
+    u = ops.linear_bf16(xd, _to_dev(Wu))
+    t = ops.silu_mul(g, u)
+    y = ops.linear_bf16(t, _to_dev(Wd))
+    return [g, u, t, y], [2, 3, 4, 5]
+
+
+_INSTANCES: Dict[str, Callable] = {
+    "ffn_swiglu": _run_ffn_bf16,
+    "dequant": _run_dequant,
+    "matvec_int4_packed": _run_matvec,
+    "matvec_int4_packed_add": _run_matvec_add,
+    "matvec_int4_swiglu_rms": _run_swiglu_rms,
+    "matmul_int4_packed": _run_matmul,
+    "ffn_swiglu_int4": _run_ffn_int4,
+}
+
+
+class B200Backend:
+    """Counterpart of XRTBackend.  Keyword arguments that only steer the AIE compiler are ignored."""
+
+    def __init__(self, verbose: bool = False, n_perf_iters: int = 0, n_warmup_iters: int = 10,
+                 instance_name: str = "", **npu_only_kwargs):
+        self.verbose = verbose
+        self.n_perf_iters = n_perf_iters
+        self.n_warmup_iters = n_warmup_iters
+        self.instance_name = instance_name
+        self.ignored_kwargs = dict(npu_only_kwargs)
+        self.currently_loaded = False
+        self.last_latency_us: Optional[float] = None
+
+    def __del__(self):
+        self.unload()
+
+    def compile(self, module: KernelSpec):
+        if self.currently_loaded:
+            raise AwqBackendError("Cannot compile while an artifact is loaded. Call unload() first.")
+        if not isinstance(module, KernelSpec):
+            raise AwqBackendError(f"expected a KernelSpec from build_module, got {type(module).__name__}")
+        name = module.instance_name or self.instance_name
+        if name not in _INSTANCES:
+            raise AwqBackendError(f"no B200 kernel for instance '{name}' (have: {sorted(_INSTANCES)})")
+        _lib.load()  # the "link" step: fails loudly if libawq_b200.so has not been built
+        return KernelSpec(name, dict(module.params))
+
+    def load(self, artifact: KernelSpec):
+        import torch
+        if self.currently_loaded:
+            raise AwqBackendError("Cannot load while an artifact is loaded. Call unload() first.")
+        if not torch.cuda.is_available():
+            raise AwqBackendError("load() needs a CUDA device; there is no CPU path")
+        fn, params = _INSTANCES[artifact.instance_name], artifact.params
+
+        def invoker(*args):
+            args = [np.asarray(a) for a in args]
+            outs, idx = fn(params, args)
+            if self.n_perf_iters > 0:  # time whole invocations, as xrt.py:768-779 times run.start()+wait2()
+                for _ in range(self.n_warmup_iters):
+                    fn(params, args)
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(self.n_perf_iters):
+                    fn(params, args)
+                e1.record()
+                torch.cuda.synchronize()
+                self.last_latency_us = e0.elapsed_time(e1) * 1e3 / self.n_perf_iters
+            torch.cuda.synchronize()
+            result = [a.copy() for a in args]
+            for t, i in zip(outs, idx):
+                result[i] = _to_host(t, args[i])
+            return tuple(result)
+
+        self.currently_loaded = True
+        return invoker
+
+    def compile_and_load(self, module):
+        return self.load(self.compile(module))
+
+    def unload(self):
+        self.currently_loaded = False
+
+
+class B200Runner:
+    """Counterpart of XRTRunner: compile, run once, compare against the expected outputs."""
+
+    def __init__(self, verbose: bool = False, n_perf_iters: int = 0, n_warmup_iters: int = 10,
+                 perf_flops: Optional[float] = None, report_precision: bool = False, instance_name: str = "",
+                 **npu_only_kwargs):
+        self.verbose = verbose
+        self.n_perf_iters = n_perf_iters
+        self.n_warmup_iters = n_warmup_iters
+        self.perf_flops = perf_flops
+        self.report_precision = report_precision
+        self.instance_name = instance_name
+        self.ignored_kwargs = dict(npu_only_kwargs)
+        self.last_latency_us: Optional[float] = None
+        self.last_outputs: List[np.ndarray] = []
+
+    def run_test(self, mlir_module, inputs: Sequence[np.ndarray], expected_outputs: Sequence[np.ndarray] = (),
+                 stochastic_expected_outputs: Sequence = (), rtol: float = 1e-3, atol: float = 1e-8,
+                 max_mismatch_percentage: float = 0, min_correlation: Optional[float] = None) -> int:
+        if stochastic_expected_outputs:
+            raise AwqBackendError("stochastic_expected_outputs is not used by the int4-AWQ examples")
+        if not expected_outputs:
+            raise AwqBackendError("expected_outputs must not be empty")
+        backend = B200Backend(verbose=self.verbose, n_perf_iters=self.n_perf_iters,
+                              n_warmup_iters=self.n_warmup_iters, instance_name=self.instance_name)
+        placeholders = [np.zeros(o.shape, o.dtype) for o in expected_outputs]
+        invoker = backend.load(backend.compile(mlir_module))
+        actual = invoker(*list(inputs), *placeholders)
+        self.last_latency_us = backend.last_latency_us
+        if self.n_perf_iters > 0 and self.last_latency_us is not None:
+            line = f"Latency (us): {self.last_latency_us:.1f}"
+            if self.perf_flops is not None:
+                line += f" | Throughput: {self.perf_flops / (self.last_latency_us * 1e-6) / 1e9:.6e} GFLOP/s"
+            print(line)
+        backend.unload()
+        self.last_outputs = list(actual[len(inputs):])
+        ok = self._check_outputs(self.last_outputs, list(expected_outputs), rtol, atol, max_mismatch_percentage,
+                                 min_correlation)
+        print("PASS!" if ok else "failed.")
+        return 0 if ok else -1
+
+    def _check_outputs(self, actual_outputs, expected_outputs, rtol, atol, max_mismatch_percentage, min_correlation):
+        """Same acceptance rule as xrt_runner.py:423-521: float outputs by np.isclose on f64 with a
+        mismatch budget and an optional Pearson-correlation floor; integer outputs exactly.  Also
+        prints the rel-L2 error, which is what this library's own tests bound."""
+        if len(actual_outputs) != len(expected_outputs):
+            raise AwqBackendError("number of outputs differs from number of expected outputs")
+        ok = True
+        for i, (act, exp) in enumerate(zip(actual_outputs, expected_outputs)):
+            act = np.reshape(act, exp.shape)
+            if exp.dtype in (np.float16, np.float32, np.float64, bfloat16):
+                a, e = act.astype(np.float64), exp.astype(np.float64)
+                bad = ~np.isclose(a, e, rtol=rtol, atol=atol)
+                allowed = int(e.size * max_mismatch_percentage / 100)
+                rel_l2 = float(np.linalg.norm(a - e) / max(np.linalg.norm(e), 1e-30))
+                print(f"Output {i}: rel-L2 {rel_l2:.3e}, {int(bad.sum())} / {e.size} outside rtol={rtol} atol={atol}")
+                if self.report_precision:
+                    err = np.abs(a - e)
+                    print(f"[precision] Output {i} ({err.size} elements): mean_rel_L1={err.mean() / (np.abs(e).mean() + 1e-30):.3e}"
+                          f" | rel_err max={(err / (np.abs(e) + 1e-30)).max():.3e} | abs_err max={err.max():.3e}")
+                if bad.sum() > allowed:
+                    ok = False
+                    print(f"ERROR: Output {i} does not meet expected output.")
+                    for idx in list(zip(*np.where(bad)))[:20]:
+                        print(f"  Index {idx}: expected={e[idx]}, actual={a[idx]}, diff={abs(a[idx] - e[idx])}")
+                if min_correlation is not None and e.size > 0:
+                    corr = float(np.corrcoef(a.ravel(), e.ravel())[0, 1])
+                    print(f"Output {i} correlation: {corr:.6f} (threshold: {min_correlation})")
+                    if not np.isfinite(corr) or corr < min_correlation:
+                        ok = False
+                        print(f"ERROR: Output {i} correlation {corr:.6f} below threshold {min_correlation}")
+            elif not np.array_equal(act, exp):
+                ok = False
+                print(f"ERROR: Output {i} does not meet expected output ({int((act != exp).sum())} mismatches).")
+        return ok
+
+
+# drop-in names for scripts written against the reference
+XRTRunner = B200Runner
+XRTBackend = B200Backend

@@ -59,16 +59,21 @@ static int check_gemv_args(const char *who, const GemvArgs &a) {
     return AWQ_OK;
 }
 
-static int run_gemv(const char *who, const GemvArgs &a) {
+static int run_gemv(const char *who, GemvArgs a) {
     int rc = check_gemv_args(who, a);
     if (rc || a.B == 0 || a.N == 0) return rc;
+    AWQ_REQUIRE(a.x_format == ACT_BF16 || a.x_format == ACT_F16, "%s: unknown activation format %d", who, a.x_format);
+    AWQ_REQUIRE(a.out_format == ACT_BF16 || a.out_format == ACT_F16, "%s: unknown output format %d", who, a.out_format);
     const int mode = g_decode_mode.load();
     const bool fast_ok = gemv_streamk_supported(a);
-    if (mode == 2 && !fast_ok)
+    if (mode >= 2 && !fast_ok)
         return set_error(AWQ_ERR_UNSUPPORTED,
                          "%s: stream-K kernel needs group 128, K %% 128 == 0, N %% 32 == 0, 16-byte aligned "
                          "pointers and an sm_100 device (K=%d N=%d gs=%d)", who, a.K, a.N, a.group_size);
-    if (mode != 1 && fast_ok) return launch_gemv_streamk(a);
+    if (mode != 1 && fast_ok) {
+        a.native_bf16 = (mode == 3);
+        return launch_gemv_streamk(a);
+    }
     return launch_gemv_generic(a);
 }
 
@@ -80,7 +85,7 @@ extern "C" int awq_b200_version(void) { return 100; }
 extern "C" const char *awq_b200_last_error(void) { return g_error; }
 
 extern "C" int awq_b200_set_decode_kernel(int mode) {
-    AWQ_REQUIRE(mode >= 0 && mode <= 2, "set_decode_kernel: mode must be 0, 1 or 2");
+    AWQ_REQUIRE(mode >= 0 && mode <= 3, "set_decode_kernel: mode must be 0, 1, 2 or 3");
     g_decode_mode.store(mode);
     return AWQ_OK;
 }
@@ -91,9 +96,8 @@ extern "C" int awq_b200_set_gemm_kernel(int mode) {
 }
 
 extern "C" size_t awq_b200_workspace_bytes(int B, int K, int N) {
-    (void)B;
     if (K <= 0 || N <= 0) return 256;
-    return gemv_streamk_workspace_bytes(K, N);
+    return gemv_streamk_workspace_bytes(B, K, N);
 }
 
 extern "C" int awq_b200_workspace_init(void *workspace, size_t workspace_bytes, awq_stream_t stream) {
@@ -109,6 +113,10 @@ extern "C" int awq_b200_workspace_check(const void *workspace, awq_stream_t stre
     if (rc) return rc;
     rc = check_cuda(cudaStreamSynchronize(as_stream(stream)), "workspace_check sync");
     if (rc) return rc;
+    if (flag == 4)
+        return set_error(AWQ_ERR_UNSUPPORTED,
+                         "an activation exceeded the fp16 range (|x| > 65504) and was clamped; select the bf16 "
+                         "activation path with awq_b200_set_decode_kernel(3) and re-initialise the workspace");
     if (flag != 0)
         return set_error(AWQ_ERR_DEVICE_TIMEOUT,
                          "a device-side wait gave up (code %d: 1 = producer waiting for a free stage, "
@@ -116,31 +124,50 @@ extern "C" int awq_b200_workspace_check(const void *workspace, awq_stream_t stre
     return AWQ_OK;
 }
 
+extern "C" int awq_b200_gemv_act(const void *x, int x_format, const int32_t *qweight, const int32_t *qzeros,
+                                 const uint16_t *scales, const uint16_t *residual, void *y, int y_is_f32, int B,
+                                 int K, int N, int group_size, void *workspace, size_t workspace_bytes,
+                                 awq_stream_t stream) {
+    AWQ_REQUIRE(!(y_is_f32 && residual), "gemv: the f32 partial output takes no residual");
+    GemvArgs a{reinterpret_cast<const uint16_t *>(x), qweight, qzeros, scales, residual, y, B, K, N, group_size,
+               y_is_f32 ? EPI_F32 : EPI_BF16, workspace, workspace_bytes, as_stream(stream)};
+    a.x_format = x_format;
+    return run_gemv(y_is_f32 ? "gemv_f32" : "gemv_bf16", a);
+}
+
 extern "C" int awq_b200_gemv_bf16(const uint16_t *x, const int32_t *qweight, const int32_t *qzeros,
                                   const uint16_t *scales, const uint16_t *residual, uint16_t *y, int B, int K,
                                   int N, int group_size, void *workspace, size_t workspace_bytes,
                                   awq_stream_t stream) {
-    GemvArgs a{x, qweight, qzeros, scales, residual, y, B, K, N, group_size, EPI_BF16,
-               workspace, workspace_bytes, as_stream(stream)};
-    return run_gemv("gemv_bf16", a);
+    return awq_b200_gemv_act(x, ACT_BF16, qweight, qzeros, scales, residual, y, 0, B, K, N, group_size, workspace,
+                             workspace_bytes, stream);
 }
 
 extern "C" int awq_b200_gemv_f32(const uint16_t *x, const int32_t *qweight, const int32_t *qzeros,
                                  const uint16_t *scales, float *y, int B, int K, int N, int group_size,
                                  void *workspace, size_t workspace_bytes, awq_stream_t stream) {
-    GemvArgs a{x, qweight, qzeros, scales, nullptr, y, B, K, N, group_size, EPI_F32,
-               workspace, workspace_bytes, as_stream(stream)};
-    return run_gemv("gemv_f32", a);
+    return awq_b200_gemv_act(x, ACT_BF16, qweight, qzeros, scales, nullptr, y, 1, B, K, N, group_size, workspace,
+                             workspace_bytes, stream);
+}
+
+extern "C" int awq_b200_gateup_swiglu_act(const void *x, int x_format, const int32_t *qweight, const int32_t *qzeros,
+                                          const uint16_t *scales, void *out, int out_format, int B, int K, int I,
+                                          int group_size, void *workspace, size_t workspace_bytes,
+                                          awq_stream_t stream) {
+    AWQ_REQUIRE(I >= 0 && I % 4 == 0, "gateup_swiglu: I (%d) must be a multiple of 4", I);
+    GemvArgs a{reinterpret_cast<const uint16_t *>(x), qweight, qzeros, scales, nullptr, out, B, K, 2 * I, group_size,
+               EPI_SWIGLU, workspace, workspace_bytes, as_stream(stream)};
+    a.x_format = x_format;
+    a.out_format = out_format;
+    return run_gemv("gateup_swiglu", a);
 }
 
 extern "C" int awq_b200_gateup_swiglu_bf16(const uint16_t *x, const int32_t *qweight, const int32_t *qzeros,
                                            const uint16_t *scales, uint16_t *out, int B, int K, int I,
                                            int group_size, void *workspace, size_t workspace_bytes,
                                            awq_stream_t stream) {
-    AWQ_REQUIRE(I >= 0 && I % 4 == 0, "gateup_swiglu: I (%d) must be a multiple of 4", I);
-    GemvArgs a{x, qweight, qzeros, scales, nullptr, out, B, K, 2 * I, group_size, EPI_SWIGLU,
-               workspace, workspace_bytes, as_stream(stream)};
-    return run_gemv("gateup_swiglu", a);
+    return awq_b200_gateup_swiglu_act(x, ACT_BF16, qweight, qzeros, scales, out, ACT_BF16, B, K, I, group_size,
+                                      workspace, workspace_bytes, stream);
 }
 
 extern "C" int awq_b200_ffn_decode_bf16(const uint16_t *x, const uint16_t *gamma, float eps,
@@ -151,17 +178,21 @@ extern "C" int awq_b200_ffn_decode_bf16(const uint16_t *x, const uint16_t *gamma
                                         void *workspace, size_t workspace_bytes, awq_stream_t stream) {
     AWQ_REQUIRE(inter, "ffn_decode: inter buffer is required");
     AWQ_REQUIRE(!gamma || normed, "ffn_decode: normed buffer is required with gamma");
+    // The intermediates travel between the three kernels as fp16 (exact for bf16-rounded values
+    // inside the fp16 range): that is the activation format the GEMV kernel multiplies fastest.
     int rc;
-    const uint16_t *xin = x;
+    const void *xin = x;
+    int xfmt = ACT_BF16;
     if (gamma) {
-        if ((rc = awq_b200_rmsnorm_bf16(x, gamma, eps, normed, B, H, stream))) return rc;
+        if ((rc = awq_b200_rmsnorm_act(x, gamma, eps, normed, ACT_F16, B, H, stream))) return rc;
         xin = normed;
+        xfmt = ACT_F16;
     }
-    if ((rc = awq_b200_gateup_swiglu_bf16(xin, qw_gateup, qz_gateup, s_gateup, inter, B, H, I, group_size, workspace,
-                                          workspace_bytes, stream)))
+    if ((rc = awq_b200_gateup_swiglu_act(xin, xfmt, qw_gateup, qz_gateup, s_gateup, inter, ACT_F16, B, H, I, group_size,
+                                         workspace, workspace_bytes, stream)))
         return rc;
-    return awq_b200_gemv_bf16(inter, qw_down, qz_down, s_down, residual, out, B, I, H, group_size, workspace,
-                              workspace_bytes, stream);
+    return awq_b200_gemv_act(inter, ACT_F16, qw_down, qz_down, s_down, residual, out, 0, B, I, H, group_size, workspace,
+                             workspace_bytes, stream);
 }
 
 extern "C" int awq_b200_gemm_bf16(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros,

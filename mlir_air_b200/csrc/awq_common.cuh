@@ -68,6 +68,10 @@ enum Epilogue : int {
     EPI_SWIGLU = 2,  // y bf16 [B, N/2] = swiglu(sum[2i], sum[2i+1])
 };
 
+// 16-bit activation formats.  The stream-K kernel's fastest path wants fp16 activations (an fp16
+// significand holds two nibbles, so one shift serves four nibbles); bf16 inputs are converted once.
+enum ActFormat : int { ACT_BF16 = 0, ACT_F16 = 1 };
+
 struct GemvArgs {
     const uint16_t *x;
     const int32_t *qweight;
@@ -80,6 +84,9 @@ struct GemvArgs {
     void *workspace;
     size_t workspace_bytes;
     cudaStream_t stream;
+    int x_format = ACT_BF16;    // format of x
+    int out_format = ACT_BF16;  // EPI_SWIGLU only: format of the output
+    bool native_bf16 = false;   // stream-K: multiply bf16 activations as they are (no fp16 conversion)
 };
 
 // Generic CUDA-core kernel: any group size, any N % 8 == 0, B <= 64.
@@ -87,7 +94,8 @@ int launch_gemv_generic(const GemvArgs &a);
 // TMA + mma.sync stream-K kernel: group 128, N % 32 == 0, K % 128 == 0, B <= 8.
 bool gemv_streamk_supported(const GemvArgs &a);
 int launch_gemv_streamk(const GemvArgs &a);
-size_t gemv_streamk_workspace_bytes(int K, int N);
+size_t gemv_streamk_scratch_bytes(int N);               // counters + split-K partials
+size_t gemv_streamk_workspace_bytes(int B, int K, int N);  // + room to convert B rows of x to fp16
 size_t gemv_streamk_workspace_clear_bytes();
 
 int launch_gemm_generic(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros,

@@ -29,6 +29,7 @@
 // Epilogues: bf16 (+ residual), f32 (tensor-parallel partial), SwiGLU over interleaved
 // gate/up column pairs (matvec_int4_swiglu_rms.py:511-516 rounding points).
 #include <cudaTypedefs.h>
+#include <cuda_fp16.h>
 
 #include <mutex>
 
@@ -69,13 +70,6 @@ constexpr int SK_MAX_STRIPS = 504;  // N up to 258,048 columns
 constexpr size_t SK_WS_PARTIALS = SK_WS_HEADER + (size_t)SK_MAX_STRIPS * SK_CONSUMER_WARPS * 4;  // 16 KB
 constexpr int SK_MAX_CTAS = 2048;
 
-size_t gemv_streamk_workspace_bytes(int K, int N) {
-    (void)K;
-    const size_t V = (size_t)(N + SK_STRIP - 1) / SK_STRIP;
-    int sms = device_sm_count();
-    if (sms <= 0) sms = 148;
-    return SK_WS_PARTIALS + (V + (size_t)sms * SK_CTAS_PER_SM) * SK_PARTIAL_FLOATS * 4;
-}
 
 // Leading bytes of a workspace (error flag + counters) that must be zero before a launch.
 size_t gemv_streamk_workspace_clear_bytes() { return SK_WS_PARTIALS; }
@@ -85,54 +79,101 @@ __host__ __device__ __forceinline__ long long sk_owner(long long x, long long C,
     return ((x + 1) * C + U - 1) / U - 1;
 }
 
-// One lane's share of a finished strip: 8 consecutive columns (n .. n+7) for batch rows 2t and
-// 2t+1.  v[e][0..3] = (col 2e, row 2t), (col 2e, row 2t+1), (col 2e+1, row 2t), (col 2e+1, row 2t+1).
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t v, uint32_t mask, uint32_t magic) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(v), "r"(mask), "r"(magic));
+    return r;
+}
+
+// R holds one 16-bit half of a packed word for k (low 16 bits) and for k + 1 (high 16 bits):
+// four nibbles each.  Output e is the pair (nibble e at k, nibble e at k + 1) as 16-bit floats.
+//   bf16: 128 + n for every e (three shifts).
+//   fp16: 1024 + n for e = 0, 2 and 1024 + 16 n for e = 1, 3 (one shift); the factor 16 and the
+//         different offset are undone in the per-group fix-up.
+template <bool XH>
+__device__ __forceinline__ void decode4(uint32_t R, uint32_t (&o)[4]) {
+    if (XH) {
+        const uint32_t T = R >> 8;
+        o[0] = lop3_and_or(R, 0x000F000Fu, 0x64006400u);
+        o[1] = lop3_and_or(R, 0x00F000F0u, 0x64006400u);
+        o[2] = lop3_and_or(T, 0x000F000Fu, 0x64006400u);
+        o[3] = lop3_and_or(T, 0x00F000F0u, 0x64006400u);
+    } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[e] = lop3_and_or(R >> (4 * e), 0x000F000Fu, 0x43004300u);
+    }
+}
+
+template <bool XH>
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+    if (XH) {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+            "{%0, %1, %2, %3};"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    } else {
+        mma_bf16_16816(d, a0, a1, a2, a3, b0, b1);
+    }
+}
+
+// bf16-rounded value -> fp16 bits, clamped to the finite fp16 range.
+__device__ __forceinline__ uint16_t bf16_value_to_f16_bits(float v) {
+    v = fminf(fmaxf(v, -65504.f), 65504.f);
+    return __half_as_ushort(__float2half_rn(v));
+}
+
+// One lane's share of a finished strip after the lane exchange: batch row b, and for each
+// 32-column half h of the warp's 64 columns, 8 consecutive columns starting at n + 32 h.
 template <int EPI>
-__device__ __forceinline__ void sk_epilogue(const float (&v)[4][4], const uint16_t *__restrict__ residual,
-                                            void *__restrict__ y_, int B, int N, int n, int row0) {
-    if (n >= N) return;
+__device__ __forceinline__ void sk_epilogue(const float (&own)[2][8], const uint16_t *__restrict__ residual,
+                                            void *__restrict__ y_, int B, int N, int n, int b, int out_f16) {
+    if (b >= B) return;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-        const int b = row0 + h;
-        if (b >= B) continue;
+        const int nh = n + 32 * h;
+        if (nh >= N) continue;
+        const float(&v)[8] = own[h];
         if (EPI == EPI_SWIGLU) {
-            uint32_t o[2];
+            uint16_t o[4];
 #pragma unroll
-            for (int e = 0; e < 4; e += 2)
-                o[e >> 1] = (uint32_t)swiglu_bits(v[e][h], v[e][2 + h]) |
-                            ((uint32_t)swiglu_bits(v[e + 1][h], v[e + 1][2 + h]) << 16);
-            *reinterpret_cast<uint2 *>(reinterpret_cast<uint16_t *>(y_) + (size_t)b * (N >> 1) + (n >> 1)) =
-                make_uint2(o[0], o[1]);
+            for (int i = 0; i < 4; ++i) {
+                o[i] = swiglu_bits(v[2 * i], v[2 * i + 1]);
+                if (out_f16) o[i] = bf16_value_to_f16_bits(bf16_bits_to_f32(o[i]));
+            }
+            *reinterpret_cast<uint2 *>(reinterpret_cast<uint16_t *>(y_) + (size_t)b * (N >> 1) + (nh >> 1)) =
+                make_uint2((uint32_t)o[0] | ((uint32_t)o[1] << 16), (uint32_t)o[2] | ((uint32_t)o[3] << 16));
         } else if (EPI == EPI_F32) {
-            float4 *dst = reinterpret_cast<float4 *>(reinterpret_cast<float *>(y_) + (size_t)b * N + n);
-            dst[0] = make_float4(v[0][h], v[0][2 + h], v[1][h], v[1][2 + h]);
-            dst[1] = make_float4(v[2][h], v[2][2 + h], v[3][h], v[3][2 + h]);
+            float4 *dst = reinterpret_cast<float4 *>(reinterpret_cast<float *>(y_) + (size_t)b * N + nh);
+            dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+            dst[1] = make_float4(v[4], v[5], v[6], v[7]);
         } else {
             float r[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             if (residual) {
-                const uint4 rv = *reinterpret_cast<const uint4 *>(residual + (size_t)b * N + n);
+                const uint4 rv = *reinterpret_cast<const uint4 *>(residual + (size_t)b * N + nh);
                 const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    r[2 * e] = bf16x2_lo(rw[e]);
-                    r[2 * e + 1] = bf16x2_hi(rw[e]);
+                for (int i = 0; i < 4; ++i) {
+                    r[2 * i] = bf16x2_lo(rw[i]);
+                    r[2 * i + 1] = bf16x2_hi(rw[i]);
                 }
             }
             uint32_t o[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) o[e] = pack_bf16x2(v[e][h] + r[2 * e], v[e][2 + h] + r[2 * e + 1]);
-            *reinterpret_cast<uint4 *>(reinterpret_cast<uint16_t *>(y_) + (size_t)b * N + n) =
+            for (int i = 0; i < 4; ++i) o[i] = pack_bf16x2(v[2 * i] + r[2 * i], v[2 * i + 1] + r[2 * i + 1]);
+            *reinterpret_cast<uint4 *>(reinterpret_cast<uint16_t *>(y_) + (size_t)b * N + nh) =
                 make_uint4(o[0], o[1], o[2], o[3]);
         }
     }
 }
 
-template <int EPI>
+template <int EPI, bool XH>
 __global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM)
 gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                     const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmZ,
                     const uint16_t *__restrict__ residual, void *__restrict__ y_, int B, int N, int G,
-                    int V, float *__restrict__ partials, int *__restrict__ counters,
+                    int V, int out_f16, float *__restrict__ partials, int *__restrict__ counters,
                     int *__restrict__ err_flag) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -144,6 +185,7 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     const long long U = (long long)V * G, C = gridDim.x, c = blockIdx.x;
     const long long u0 = c * U / C, u1 = (c + 1) * U / C;
     const int n_units = (int)(u1 - u0);
+    const int v_first = (int)(u0 / G), g_first = (int)(u0 % G);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < SK_STAGES; ++s) {
@@ -162,14 +204,12 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             tma_prefetch_desc(&tmS);
             tma_prefetch_desc(&tmZ);
             const uint64_t stream_policy = l2_policy_evict_first();
+            int v = v_first, g = g_first, slot = 0, round = 0;
             for (int i = 0; i < n_units; ++i) {
-                const int slot = i % SK_STAGES, round = i / SK_STAGES;
                 if (round > 0 && !mbar_wait_bounded(empty_bar(slot), (round - 1) & 1)) {
                     atomicExch(err_flag, 1);
                     break;
                 }
-                const long long u = u0 + i;
-                const int v = (int)(u / G), g = (int)(u % G);
                 const uint32_t st = smem_base + slot * SK_STAGE_BYTES;
                 const uint32_t bar = full_bar(slot);
                 mbar_expect_tx(bar, SK_TX_BYTES);
@@ -183,22 +223,26 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                 for (int bx = 0; bx < SK_STRIP / SK_BOX_COLS; ++bx)
                     tma_load_2d(st + SK_OFF_S + bx * SK_BOX_COLS * 2, &tmS, v * SK_STRIP + bx * SK_BOX_COLS, g, bar);
                 tma_load_2d(st + SK_OFF_Z, &tmZ, v * (SK_STRIP / 8), g, bar);
+                if (++g == G) { g = 0; ++v; }
+                if (++slot == SK_STAGES) { slot = 0; ++round; }
             }
         }
         return;
     }
 
     // ------------------------------ consumers ------------------------------
-    // Warp w owns strip columns [64 w, 64 w + 64); lane (g8, t4) owns packed word g8 of them.
-    const int g8 = lane >> 2, t4 = lane & 3;
-    const uint32_t w_box = (warp >> 2) * SK_WBOX_BYTES;          // which 256-column box
-    const uint32_t chunk = 2 * (warp & 3) + (g8 >> 2);           // 16-byte chunk inside a box row
-    // Rows 2t and 2t+1 of a 16-row k-step; rows +8 share the swizzle (row & 7 unchanged).
-    const uint32_t offA = w_box + (2 * t4) * 128 + ((chunk ^ (2 * t4)) << 4) + (g8 & 3) * 4;
-    const uint32_t offB = w_box + (2 * t4 + 1) * 128 + ((chunk ^ (2 * t4 + 1)) << 4) + (g8 & 3) * 4;
-    const int xm = lane >> 3, xb = lane & 7;  // ldmatrix: matrix index, batch row
-    const uint32_t ONES = 0x3F803F80u;
-    const int col0 = warp * 64 + g8 * 8;      // first of this lane's 8 strip columns
+    // Warp w owns strip columns [64 w, 64 w + 64): two 16-byte chunks (A, B) of every box row.
+    // ldmatrix.trans hands lane (g8, t4) 16-bit half g8 of chunk A / B for rows 2 t4 and 2 t4 + 1
+    // already paired in one register: half g8 = packed word g8 / 2, even (low half) or odd
+    // (high half) columns.  MMA row g8 is that lane's chunk-A column, row g8 + 8 its chunk-B column.
+    const int g8 = lane >> 2, t4 = lane & 3, odd = g8 & 1;
+    const int lm = lane >> 3, lr = lane & 7;  // ldmatrix: matrix index, row within the matrix
+    const uint32_t w_chunk = 2 * (warp & 3) + (lm >> 1);
+    const uint32_t w_off = (warp >> 2) * SK_WBOX_BYTES + ((lm & 1) * 8 + lr) * 128 + ((w_chunk ^ lr) << 4);
+    const uint32_t ONES = XH ? 0x3C003C00u : 0x3F803F80u;
+    const int colw = warp * 64 + (g8 >> 1) * 8;  // first strip column of this lane's 8-column blocks (+32 for B)
+    const uint32_t z_off = SK_OFF_Z + (colw >> 3) * 4 + odd * 2;
+    const uint32_t s_off = SK_OFF_S + (colw + odd) * 2;
     bool failed = false;
 
     float res[4][4];
@@ -207,20 +251,35 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     // Finish the strip segment this warp has been accumulating (strip cur_v).
     auto flush = [&]() {
         const int v = cur_v;
-        const int n = v * SK_STRIP + col0;
+        // lanes g8 and g8 ^ 1 hold the even / odd columns of the same 8-column blocks for batch
+        // rows 2t and 2t+1: swap so that each owns one batch row and 8 consecutive columns.
+        float own[2][8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const float keep = odd ? res[e][2 * h + 1] : res[e][2 * h];
+                const float send = odd ? res[e][2 * h] : res[e][2 * h + 1];
+                const float recv = __shfl_xor_sync(0xffffffffu, send, 4);
+                own[h][2 * e] = odd ? recv : keep;
+                own[h][2 * e + 1] = odd ? keep : recv;
+            }
+        const int b = 2 * t4 + odd;
+        const int n = v * SK_STRIP + colw;
         const long long c_lo = sk_owner((long long)v * G, C, U);
         const long long c_hi = sk_owner((long long)(v + 1) * G - 1, C, U);
         if (c_hi == c_lo) {
-            if (!failed) sk_epilogue<EPI>(res, residual, y_, B, N, n, 2 * t4);
+            if (!failed) sk_epilogue<EPI>(own, residual, y_, B, N, n, b, out_f16);
             return;
         }
         // [slot][warp][batch row][64 columns]
-        float *mine = partials + (size_t)(c + v) * SK_PARTIAL_FLOATS + warp * 512 + g8 * 8;
+        const size_t lane_off = (size_t)warp * 512 + b * 64 + (g8 >> 1) * 8;
+        float *mine = partials + (size_t)(c + v) * SK_PARTIAL_FLOATS + lane_off;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            float4 *dst = reinterpret_cast<float4 *>(mine + (2 * t4 + h) * 64);
-            dst[0] = make_float4(res[0][h], res[0][2 + h], res[1][h], res[1][2 + h]);
-            dst[1] = make_float4(res[2][h], res[2][2 + h], res[3][h], res[3][2 + h]);
+            float4 *dst = reinterpret_cast<float4 *>(mine + 32 * h);
+            dst[0] = make_float4(own[h][0], own[h][1], own[h][2], own[h][3]);
+            dst[1] = make_float4(own[h][4], own[h][5], own[h][6], own[h][7]);
         }
         __threadfence();
         __syncwarp();
@@ -229,29 +288,27 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         old = __shfl_sync(0xffffffffu, old, 0);
         if (old != (int)(c_hi - c_lo)) return;
         __threadfence();
-        float sum[4][4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e)
+        for (int h = 0; h < 2; ++h)
 #pragma unroll
-            for (int q = 0; q < 4; ++q) sum[e][q] = 0.f;
+            for (int i = 0; i < 8; ++i) own[h][i] = 0.f;
         for (long long cc = c_lo; cc <= c_hi; ++cc) {
-            const float *src = partials + (size_t)(cc + v) * SK_PARTIAL_FLOATS + warp * 512 + g8 * 8;
+            const float *src = partials + (size_t)(cc + v) * SK_PARTIAL_FLOATS + lane_off;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                const float4 a = __ldcg(reinterpret_cast<const float4 *>(src + (2 * t4 + h) * 64));
-                const float4 b = __ldcg(reinterpret_cast<const float4 *>(src + (2 * t4 + h) * 64) + 1);
-                sum[0][h] += a.x; sum[0][2 + h] += a.y; sum[1][h] += a.z; sum[1][2 + h] += a.w;
-                sum[2][h] += b.x; sum[2][2 + h] += b.y; sum[3][h] += b.z; sum[3][2 + h] += b.w;
+                const float4 p0 = __ldcg(reinterpret_cast<const float4 *>(src + 32 * h));
+                const float4 p1 = __ldcg(reinterpret_cast<const float4 *>(src + 32 * h) + 1);
+                own[h][0] += p0.x; own[h][1] += p0.y; own[h][2] += p0.z; own[h][3] += p0.w;
+                own[h][4] += p1.x; own[h][5] += p1.y; own[h][6] += p1.z; own[h][7] += p1.w;
             }
         }
         __syncwarp();
         if (lane == 0) counters[v * SK_CONSUMER_WARPS + warp] = 0;  // ready for the next launch
-        if (!failed) sk_epilogue<EPI>(sum, residual, y_, B, N, n, 2 * t4);
+        if (!failed) sk_epilogue<EPI>(own, residual, y_, B, N, n, b, out_f16);
     };
 
+    int v = v_first, g = g_first, slot = 0, round = 0;
     for (int i = 0; i < n_units; ++i) {
-        const long long u = u0 + i;
-        const int v = (int)(u / G);
         if (v != cur_v) {
             if (cur_v >= 0) flush();
             cur_v = v;
@@ -260,70 +317,89 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 #pragma unroll
                 for (int q = 0; q < 4; ++q) res[e][q] = 0.f;
         }
-        const int slot = i % SK_STAGES, round = i / SK_STAGES;
         if (!failed && !mbar_wait_bounded(full_bar(slot), round & 1)) {
             failed = true;
             if (lane == 0) atomicExch(err_flag, 2);
         }
-        if (failed) continue;
-        const uint32_t st = smem_base + slot * SK_STAGE_BYTES;
+        if (!failed) {
+            const uint32_t st = smem_base + slot * SK_STAGE_BYTES;
+            float acc[4][4];
+            float sx[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) acc[e][q] = 0.f;
 
-        float acc[4][4];
-        float sx[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int e = 0; e < 4; ++e)
+            for (int p = 0; p < 4; ++p) {
+                // activations for k-steps 2p and 2p+1: 16-byte chunk q = 4p + matrix index
+                const int q = 4 * p + lm;
+                uint32_t bx[4];
+                ldmatrix_x4(bx, st + SK_OFF_X + (q >> 3) * 1024 + lr * 128 + (((q & 7) ^ lr) << 4));
 #pragma unroll
-            for (int q = 0; q < 4; ++q) acc[e][q] = 0.f;
-
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t R[4];  // chunk A rows 0-7, chunk A rows 8-15, chunk B rows 0-7, chunk B rows 8-15
+                    ldmatrix_x4_trans(R, st + (2 * p + h) * 2048 + w_off);
+                    const uint32_t b0 = bx[2 * h], b1 = bx[2 * h + 1];
+                    mma_16816<XH>(sx, ONES, ONES, ONES, ONES, b0, b1);
+                    uint32_t a_lo[4], a_hi[4], b_lo[4], b_hi[4];
+                    decode4<XH>(R[0], a_lo);
+                    decode4<XH>(R[1], a_hi);
+                    decode4<XH>(R[2], b_lo);
+                    decode4<XH>(R[3], b_hi);
 #pragma unroll
-        for (int p = 0; p < 4; ++p) {
-            // activations for k-steps 2p and 2p+1: 16-byte chunk q = 4p + matrix index
-            const int q = 4 * p + xm;
-            uint32_t bx[4];
-            ldmatrix_x4(bx, st + SK_OFF_X + (q >> 3) * 1024 + xb * 128 + (((q & 7) ^ xb) << 4));
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const uint32_t rb = st + (2 * p + h) * 2048;
-                const uint32_t w0 = lds32(rb + offA);
-                const uint32_t w1 = lds32(rb + offB);
-                const uint32_t w2 = lds32(rb + 1024 + offA);
-                const uint32_t w3 = lds32(rb + 1024 + offB);
-                const uint32_t b0 = bx[2 * h], b1 = bx[2 * h + 1];
-                mma_bf16_16816(sx, ONES, ONES, ONES, ONES, b0, b1);
-                // low halves hold nibbles 0-3 (columns 0,2,4,6), high halves nibbles 4-7
-                // (columns 1,3,5,7); pair rows k and k+1 of the same column in one register
-                const uint32_t lo01 = __byte_perm(w0, w1, 0x5410);
-                const uint32_t hi01 = __byte_perm(w0, w1, 0x7632);
-                const uint32_t lo23 = __byte_perm(w2, w3, 0x5410);
-                const uint32_t hi23 = __byte_perm(w2, w3, 0x7632);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    // MMA row g8 = column 2e of the lane's word, row g8 + 8 = column 2e + 1
-                    mma_bf16_16816(acc[e], nib2_to_bf16x2_biased(lo01 >> (4 * e)),
-                                   nib2_to_bf16x2_biased(hi01 >> (4 * e)), nib2_to_bf16x2_biased(lo23 >> (4 * e)),
-                                   nib2_to_bf16x2_biased(hi23 >> (4 * e)), b0, b1);
+                    for (int e = 0; e < 4; ++e) mma_16816<XH>(acc[e], a_lo[e], b_lo[e], a_hi[e], b_hi[e], b0, b1);
                 }
             }
-        }
 
-        // group fix-up: res += s * (acc - (128 + z) * sum_x)
-        const uint32_t zw = lds32(st + SK_OFF_Z + (col0 >> 3) * 4);
-        const uint4 sv = lds128(st + SK_OFF_S + col0 * 2);
-        const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
-        __syncwarp();
-        if (lane == 0) mbar_arrive(empty_bar(slot));  // all of this warp's reads of the slot are done
+            // group fix-up: res += s * (acc - c * sum_x); the zero point (and, for fp16, the decode
+            // offset and the factor 16 of odd nibbles) live in c and s
+            const uint32_t zA = lds_u16(st + z_off), zB = lds_u16(st + z_off + 16);
+            uint32_t sA[4], sB[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const uint32_t zz = nib2_to_bf16x2_biased(zw >> (4 * e));
-            const float z_even = bf16x2_lo(zz), z_odd = bf16x2_hi(zz);
-            const float s_even = bf16x2_lo(sw[e]), s_odd = bf16x2_hi(sw[e]);
-            res[e][0] = fmaf(s_even, fmaf(-z_even, sx[0], acc[e][0]), res[e][0]);
-            res[e][1] = fmaf(s_even, fmaf(-z_even, sx[1], acc[e][1]), res[e][1]);
-            res[e][2] = fmaf(s_odd, fmaf(-z_odd, sx[0], acc[e][2]), res[e][2]);
-            res[e][3] = fmaf(s_odd, fmaf(-z_odd, sx[1], acc[e][3]), res[e][3]);
+            for (int e = 0; e < 4; ++e) {
+                sA[e] = lds_u16(st + s_off + 4 * e);
+                sB[e] = lds_u16(st + s_off + 64 + 4 * e);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty_bar(slot));  // all of this warp's reads of the slot are done
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                // 128 + z as f32: bits 0x43000000 | z << 16
+                float cA = __uint_as_float(((zA << (16 - 4 * e)) & 0x000F0000u) | 0x43000000u);
+                float cB = __uint_as_float(((zB << (16 - 4 * e)) & 0x000F0000u) | 0x43000000u);
+                float fA = __uint_as_float(sA[e] << 16), fB = __uint_as_float(sB[e] << 16);
+                if (XH) {
+                    if (e & 1) {
+                        cA = fmaf(cA, 16.f, -1024.f);  // 1024 + 16 z
+                        cB = fmaf(cB, 16.f, -1024.f);
+                        fA *= 0.0625f;
+                        fB *= 0.0625f;
+                    } else {
+                        cA += 896.f;  // 1024 + z
+                        cB += 896.f;
+                    }
+                }
+                res[e][0] = fmaf(fA, fmaf(-cA, sx[0], acc[e][0]), res[e][0]);
+                res[e][1] = fmaf(fA, fmaf(-cA, sx[1], acc[e][1]), res[e][1]);
+                res[e][2] = fmaf(fB, fmaf(-cB, sx[0], acc[e][2]), res[e][2]);
+                res[e][3] = fmaf(fB, fmaf(-cB, sx[1], acc[e][3]), res[e][3]);
+            }
         }
+        if (++g == G) { g = 0; ++v; }
+        if (++slot == SK_STAGES) { slot = 0; ++round; }
     }
     if (cur_v >= 0) flush();
+}
+
+// x bf16 -> fp16 (values beyond the fp16 range are clamped and reported through the error flag)
+__global__ void cvt_bf16_to_f16_kernel(const uint16_t *__restrict__ x, uint16_t *__restrict__ xh, size_t n,
+                                       int *__restrict__ err_flag) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = bf16_bits_to_f32(x[i]);
+    if (fabsf(v) > 65504.f && !(v != v)) atomicExch(err_flag, 4);
+    xh[i] = bf16_value_to_f16_bits(v);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -366,12 +442,25 @@ bool gemv_streamk_supported(const GemvArgs &a) {
            (a.N + SK_STRIP - 1) / SK_STRIP <= SK_MAX_STRIPS && device_is_sm100();
 }
 
-template <int EPI>
+size_t gemv_streamk_scratch_bytes(int N) {
+    const size_t V = (size_t)(N + SK_STRIP - 1) / SK_STRIP;
+    int sms = device_sm_count();
+    if (sms <= 0) sms = 148;
+    return SK_WS_PARTIALS + (V + (size_t)sms * SK_CTAS_PER_SM) * SK_PARTIAL_FLOATS * 4;
+}
+
+size_t gemv_streamk_workspace_bytes(int B, int K, int N) {
+    // counters + partial slots + room for B rows of activations converted to fp16
+    const size_t rows = B < 1 ? 1 : (B > 64 ? 64 : B);
+    return gemv_streamk_scratch_bytes(N) + rows * (size_t)(K > 0 ? K : 0) * 2;
+}
+
+template <int EPI, bool XH>
 static int launch_one(const GemvArgs &a, const uint16_t *x, const uint16_t *residual, void *y, int B) {
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(gemv_streamk_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        attr_err = cudaFuncSetAttribute(gemv_streamk_kernel<EPI, XH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         SK_SMEM_BYTES);
     });
     if (attr_err != cudaSuccess) return check_cuda(attr_err, "stream-K gemv: shared memory attribute");
@@ -382,8 +471,8 @@ static int launch_one(const GemvArgs &a, const uint16_t *x, const uint16_t *resi
     if ((rc = encode_tensor_map_2d(&tmW, CU_TENSOR_MAP_DATA_TYPE_INT32, a.qweight, nb, a.K, (uint64_t)nb * 4, 32,
                                    SK_GROUP, CU_TENSOR_MAP_SWIZZLE_128B)))
         return rc;
-    if ((rc = encode_tensor_map_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x, a.K, B, (uint64_t)a.K * 2, 64, 8,
-                                   CU_TENSOR_MAP_SWIZZLE_128B)))
+    if ((rc = encode_tensor_map_2d(&tmX, XH ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x,
+                                   a.K, B, (uint64_t)a.K * 2, 64, 8, CU_TENSOR_MAP_SWIZZLE_128B)))
         return rc;
     if ((rc = encode_tensor_map_2d(&tmS, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a.scales, a.N, G, (uint64_t)a.N * 2,
                                    SK_BOX_COLS, 1, CU_TENSOR_MAP_SWIZZLE_NONE)))
@@ -400,36 +489,51 @@ static int launch_one(const GemvArgs &a, const uint16_t *x, const uint16_t *resi
     int *err_flag = reinterpret_cast<int *>(ws);
     int *counters = reinterpret_cast<int *>(ws + SK_WS_HEADER);
     float *partials = reinterpret_cast<float *>(ws + SK_WS_PARTIALS);
-    gemv_streamk_kernel<EPI><<<ctas, SK_THREADS, SK_SMEM_BYTES, a.stream>>>(tmW, tmX, tmS, tmZ, residual, y, B, a.N,
-                                                                           G, V, partials, counters, err_flag);
+    gemv_streamk_kernel<EPI, XH><<<ctas, SK_THREADS, SK_SMEM_BYTES, a.stream>>>(
+        tmW, tmX, tmS, tmZ, residual, y, B, a.N, G, V, a.out_format == ACT_F16 ? 1 : 0, partials, counters, err_flag);
     return check_cuda(cudaGetLastError(), "stream-K gemv launch");
 }
 
-int launch_gemv_streamk(const GemvArgs &a) {
-    if (!a.workspace || a.workspace_bytes < gemv_streamk_workspace_bytes(a.K, a.N))
-        return set_error(AWQ_ERR_WORKSPACE, "gemv: workspace of %zu bytes needed, %zu given",
-                         gemv_streamk_workspace_bytes(a.K, a.N), a.workspace_bytes);
+template <bool XH>
+static int launch_passes(const GemvArgs &a, const uint16_t *x_all) {
     // more than 8 batch rows: one pass over the weights per 8 rows
     for (int b0 = 0; b0 < a.B; b0 += 8) {
         const int B = a.B - b0 < 8 ? a.B - b0 : 8;
-        const uint16_t *x = a.x + (size_t)b0 * a.K;
+        const uint16_t *x = x_all + (size_t)b0 * a.K;
         const uint16_t *res = a.residual ? a.residual + (size_t)b0 * a.N : nullptr;
         int rc;
         switch (a.epilogue) {
             case EPI_BF16:
-                rc = launch_one<EPI_BF16>(a, x, res, reinterpret_cast<uint16_t *>(a.y) + (size_t)b0 * a.N, B);
+                rc = launch_one<EPI_BF16, XH>(a, x, res, reinterpret_cast<uint16_t *>(a.y) + (size_t)b0 * a.N, B);
                 break;
             case EPI_F32:
-                rc = launch_one<EPI_F32>(a, x, nullptr, reinterpret_cast<float *>(a.y) + (size_t)b0 * a.N, B);
+                rc = launch_one<EPI_F32, XH>(a, x, nullptr, reinterpret_cast<float *>(a.y) + (size_t)b0 * a.N, B);
                 break;
             default:
-                rc = launch_one<EPI_SWIGLU>(a, x, nullptr,
-                                            reinterpret_cast<uint16_t *>(a.y) + (size_t)b0 * (a.N / 2), B);
+                rc = launch_one<EPI_SWIGLU, XH>(a, x, nullptr,
+                                                reinterpret_cast<uint16_t *>(a.y) + (size_t)b0 * (a.N / 2), B);
                 break;
         }
         if (rc) return rc;
     }
     return AWQ_OK;
+}
+
+int launch_gemv_streamk(const GemvArgs &a) {
+    const bool convert = a.x_format == ACT_BF16 && !a.native_bf16;
+    const size_t need = convert ? gemv_streamk_workspace_bytes(a.B, a.K, a.N) : gemv_streamk_scratch_bytes(a.N);
+    if (!a.workspace || a.workspace_bytes < need)
+        return set_error(AWQ_ERR_WORKSPACE, "gemv: workspace of %zu bytes needed, %zu given", need, a.workspace_bytes);
+    if (a.x_format == ACT_F16) return launch_passes<true>(a, a.x);
+    if (a.native_bf16) return launch_passes<false>(a, a.x);
+    // bf16 activations: convert once to fp16 in the workspace, then take the fp16 path
+    uint8_t *ws = reinterpret_cast<uint8_t *>(a.workspace);
+    uint16_t *xh = reinterpret_cast<uint16_t *>(ws + gemv_streamk_scratch_bytes(a.N));
+    const size_t n = (size_t)a.B * a.K;
+    cvt_bf16_to_f16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, a.stream>>>(a.x, xh, n, reinterpret_cast<int *>(ws));
+    int rc = check_cuda(cudaGetLastError(), "activation conversion launch");
+    if (rc) return rc;
+    return launch_passes<true>(a, xh);
 }
 
 }  // namespace awq

@@ -1,6 +1,8 @@
 // Generic CUDA-core kernels: the any-shape decode GEMV / prefill GEMM (used where the
 // specialised kernels' shape rules do not hold, and as an independent cross-check in the
 // tests), RMSNorm, residual-add + RMSNorm, and the once-per-weight layout converters.
+#include <cuda_fp16.h>
+
 #include "awq_common.cuh"
 
 namespace awq {
@@ -17,7 +19,7 @@ __global__ void __launch_bounds__(256)
 gemv_generic_kernel(const uint16_t *__restrict__ x, const uint32_t *__restrict__ qweight,
                     const uint32_t *__restrict__ qzeros, const uint16_t *__restrict__ scales,
                     const uint16_t *__restrict__ residual, void *__restrict__ y_, int B, int K,
-                    int N, int group_size) {
+                    int N, int group_size, int x_f16, int out_f16) {
     __shared__ float red[8][GV_TB][256];
     const int nb = N >> 3;
     const int cx = threadIdx.x & 31, ky = threadIdx.x >> 5;
@@ -53,7 +55,8 @@ gemv_generic_kernel(const uint16_t *__restrict__ x, const uint32_t *__restrict__
 #pragma unroll
                 for (int b = 0; b < GV_TB; ++b) {
                     if (b0 + b < B) {
-                        const float xv = bf16_bits_to_f32(x[(size_t)(b0 + b) * K + k]);
+                        const uint16_t xb = x[(size_t)(b0 + b) * K + k];
+                        const float xv = x_f16 ? __half2float(__ushort_as_half(xb)) : bf16_bits_to_f32(xb);
 #pragma unroll
                         for (int c = 0; c < 8; ++c) acc[b][c] = fmaf(w[c], xv, acc[b][c]);
                     }
@@ -75,9 +78,11 @@ gemv_generic_kernel(const uint16_t *__restrict__ x, const uint32_t *__restrict__
             const int bb = b0 + b;
             if (EPI == EPI_SWIGLU) {
                 const float other = __shfl_xor_sync(0xffffffffu, sum, 1);
-                if (bb < B && n < N && !(col & 1))
-                    reinterpret_cast<uint16_t *>(y_)[(size_t)bb * (N >> 1) + (n >> 1)] =
-                        swiglu_bits(sum, other);
+                if (bb < B && n < N && !(col & 1)) {
+                    uint16_t o = swiglu_bits(sum, other);
+                    if (out_f16) o = __half_as_ushort(__float2half_rn(fminf(fmaxf(bf16_bits_to_f32(o), -65504.f), 65504.f)));
+                    reinterpret_cast<uint16_t *>(y_)[(size_t)bb * (N >> 1) + (n >> 1)] = o;
+                }
             } else if (bb < B && n < N) {
                 if (EPI == EPI_F32) {
                     reinterpret_cast<float *>(y_)[(size_t)bb * N + n] = sum;
@@ -95,18 +100,19 @@ int launch_gemv_generic(const GemvArgs &a) {
     const int blocks = (a.N / 8 + 31) / 32;
     const uint32_t *qw = reinterpret_cast<const uint32_t *>(a.qweight);
     const uint32_t *qz = reinterpret_cast<const uint32_t *>(a.qzeros);
+    const int xf = a.x_format == ACT_F16, of = a.out_format == ACT_F16;
     switch (a.epilogue) {
         case EPI_BF16:
             gemv_generic_kernel<EPI_BF16><<<blocks, 256, 0, a.stream>>>(
-                a.x, qw, qz, a.scales, a.residual, a.y, a.B, a.K, a.N, a.group_size);
+                a.x, qw, qz, a.scales, a.residual, a.y, a.B, a.K, a.N, a.group_size, xf, of);
             break;
         case EPI_F32:
             gemv_generic_kernel<EPI_F32><<<blocks, 256, 0, a.stream>>>(
-                a.x, qw, qz, a.scales, nullptr, a.y, a.B, a.K, a.N, a.group_size);
+                a.x, qw, qz, a.scales, nullptr, a.y, a.B, a.K, a.N, a.group_size, xf, of);
             break;
         default:
             gemv_generic_kernel<EPI_SWIGLU><<<blocks, 256, 0, a.stream>>>(
-                a.x, qw, qz, a.scales, nullptr, a.y, a.B, a.K, a.N, a.group_size);
+                a.x, qw, qz, a.scales, nullptr, a.y, a.B, a.K, a.N, a.group_size, xf, of);
             break;
     }
     return check_cuda(cudaGetLastError(), "generic gemv launch");
@@ -223,7 +229,7 @@ __device__ __forceinline__ float block_sum_256(float v, float *smem) {
 __global__ void __launch_bounds__(256)
 rmsnorm_kernel(const uint16_t *__restrict__ h, const float *__restrict__ partial,
                const uint16_t *__restrict__ gamma, float eps, uint16_t *__restrict__ h_out,
-               uint16_t *__restrict__ normed, int K) {
+               uint16_t *__restrict__ normed, int K, int normed_f16) {
     __shared__ float red[8];
     const size_t row = (size_t)blockIdx.x * K;
     float ss = 0.f;
@@ -245,7 +251,9 @@ rmsnorm_kernel(const uint16_t *__restrict__ h, const float *__restrict__ partial
             v = bf16_bits_to_f32(f32_to_bf16_bits(bf16_bits_to_f32(h[row + k]) + partial[row + k]));
         else
             v = bf16_bits_to_f32(h[row + k]);
-        normed[row + k] = f32_to_bf16_bits((v * rstd) * bf16_bits_to_f32(gamma[k]));
+        uint16_t o = f32_to_bf16_bits((v * rstd) * bf16_bits_to_f32(gamma[k]));
+        if (normed_f16) o = __half_as_ushort(__float2half_rn(fminf(fmaxf(bf16_bits_to_f32(o), -65504.f), 65504.f)));
+        normed[row + k] = o;
     }
 }
 
@@ -333,31 +341,116 @@ __global__ void repack_A_to_B_z_kernel(const uint32_t *__restrict__ qzeros, uint
     A_z[idx] = (uint8_t)awq_nibble(qzeros[g * (M >> 3) + (n >> 3)], n & 7);
 }
 
+// =====================================================================================
+// bf16 sibling path (un-quantised weights): y[M, N] = x[M, K] @ W[N, K]^T, one warp per output
+// column, lanes stride over K with 16-byte loads, f32 accumulate, shuffle reduction.
+// =====================================================================================
+constexpr int LB_ROWS = 8;  // activation rows per pass
+
+__global__ void __launch_bounds__(256)
+linear_bf16_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__ W, uint16_t *__restrict__ y,
+                   int M, int K, int N) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 8 + warp;
+    const int m0 = blockIdx.y * LB_ROWS;
+    if (n >= N) return;
+    float acc[LB_ROWS];
+#pragma unroll
+    for (int r = 0; r < LB_ROWS; ++r) acc[r] = 0.f;
+    for (int k = lane * 8; k < K; k += 256) {
+        const uint4 wv = *reinterpret_cast<const uint4 *>(W + (size_t)n * K + k);
+        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+        for (int r = 0; r < LB_ROWS; ++r) {
+            if (m0 + r >= M) break;
+            const uint4 xv = *reinterpret_cast<const uint4 *>(x + (size_t)(m0 + r) * K + k);
+            const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                acc[r] = fmaf(bf16x2_lo(ww[e]), bf16x2_lo(xw[e]), acc[r]);
+                acc[r] = fmaf(bf16x2_hi(ww[e]), bf16x2_hi(xw[e]), acc[r]);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < LB_ROWS; ++r) {
+        float v = acc[r];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0 && m0 + r < M) y[(size_t)(m0 + r) * N + n] = f32_to_bf16_bits(v);
+    }
+}
+
+// out = bf16(g * sigmoid(g) * u) in f32: the golden form of ffn_swiglu/decode/ffn_decode.py:309-311.
+__global__ void silu_mul_bf16_kernel(const uint16_t *__restrict__ gate, const uint16_t *__restrict__ up,
+                                     uint16_t *__restrict__ out, size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float g = bf16_bits_to_f32(gate[i]), u = bf16_bits_to_f32(up[i]);
+    out[i] = f32_to_bf16_bits(g * (1.0f / (1.0f + expf(-g))) * u);
+}
+
 static inline unsigned blocks_for(size_t n, int threads) { return (unsigned)((n + threads - 1) / threads); }
 
 }  // namespace awq
 
 using namespace awq;
 
-extern "C" int awq_b200_rmsnorm_bf16(const uint16_t *x, const uint16_t *gamma, float eps, uint16_t *out,
-                                     int B, int K, awq_stream_t stream) {
+extern "C" int awq_b200_rmsnorm_act(const uint16_t *x, const uint16_t *gamma, float eps, void *out, int out_format,
+                                    int B, int K, awq_stream_t stream) {
     AWQ_REQUIRE(B >= 0 && K > 0, "rmsnorm: bad size");
+    AWQ_REQUIRE(out_format == ACT_BF16 || out_format == ACT_F16, "rmsnorm: unknown output format %d", out_format);
     if (B == 0) return AWQ_OK;
     AWQ_REQUIRE(x && gamma && out, "rmsnorm: null pointer");
-    rmsnorm_kernel<<<B, 256, 0, as_stream(stream)>>>(x, nullptr, gamma, eps, nullptr, out, K);
+    rmsnorm_kernel<<<B, 256, 0, as_stream(stream)>>>(x, nullptr, gamma, eps, nullptr, reinterpret_cast<uint16_t *>(out),
+                                                     K, out_format == ACT_F16);
     return check_cuda(cudaGetLastError(), "rmsnorm launch");
+}
+
+extern "C" int awq_b200_rmsnorm_bf16(const uint16_t *x, const uint16_t *gamma, float eps, uint16_t *out,
+                                     int B, int K, awq_stream_t stream) {
+    return awq_b200_rmsnorm_act(x, gamma, eps, out, ACT_BF16, B, K, stream);
 }
 
 extern "C" int awq_b200_add_rmsnorm_bf16(const uint16_t *h, const float *partial_sum, const uint16_t *gamma,
                                          float eps, uint16_t *h_out, uint16_t *normed, int B, int K,
                                          awq_stream_t stream) {
+    return awq_b200_add_rmsnorm_act(h, partial_sum, gamma, eps, h_out, normed, ACT_BF16, B, K, stream);
+}
+
+extern "C" int awq_b200_add_rmsnorm_act(const uint16_t *h, const float *partial_sum, const uint16_t *gamma,
+                                        float eps, uint16_t *h_out, void *normed, int normed_format, int B, int K,
+                                        awq_stream_t stream) {
     AWQ_REQUIRE(B >= 0 && K > 0, "add_rmsnorm: bad size");
+    AWQ_REQUIRE(normed_format == ACT_BF16 || normed_format == ACT_F16, "add_rmsnorm: unknown format %d", normed_format);
     if (B == 0) return AWQ_OK;
     AWQ_REQUIRE(h && partial_sum && h_out, "add_rmsnorm: null pointer");
     AWQ_REQUIRE((gamma == nullptr) == (normed == nullptr), "add_rmsnorm: gamma and normed go together");
     AWQ_REQUIRE(h_out != h, "add_rmsnorm: h_out must not alias h");
-    rmsnorm_kernel<<<B, 256, 0, as_stream(stream)>>>(h, partial_sum, gamma, eps, h_out, normed, K);
+    rmsnorm_kernel<<<B, 256, 0, as_stream(stream)>>>(h, partial_sum, gamma, eps, h_out,
+                                                     reinterpret_cast<uint16_t *>(normed), K, normed_format == ACT_F16);
     return check_cuda(cudaGetLastError(), "add_rmsnorm launch");
+}
+
+extern "C" int awq_b200_linear_bf16(const uint16_t *x, const uint16_t *W, uint16_t *y, int M, int K, int N,
+                                    awq_stream_t stream) {
+    AWQ_REQUIRE(M >= 0 && K > 0 && N >= 0, "linear_bf16: bad size");
+    AWQ_REQUIRE(K % 8 == 0, "linear_bf16: K (%d) must be a multiple of 8", K);
+    if (M == 0 || N == 0) return AWQ_OK;
+    AWQ_REQUIRE(x && W && y, "linear_bf16: null pointer");
+    AWQ_REQUIRE(aligned16(x) && aligned16(W), "linear_bf16: x and W must be 16-byte aligned");
+    dim3 grid((N + 7) / 8, (M + LB_ROWS - 1) / LB_ROWS);
+    AWQ_REQUIRE(grid.y <= 65535u, "linear_bf16: M (%d) too large", M);
+    linear_bf16_kernel<<<grid, 256, 0, as_stream(stream)>>>(x, W, y, M, K, N);
+    return check_cuda(cudaGetLastError(), "linear_bf16 launch");
+}
+
+extern "C" int awq_b200_silu_mul_bf16(const uint16_t *gate, const uint16_t *up, uint16_t *out, size_t n,
+                                      awq_stream_t stream) {
+    if (n == 0) return AWQ_OK;
+    AWQ_REQUIRE(gate && up && out, "silu_mul_bf16: null pointer");
+    silu_mul_bf16_kernel<<<blocks_for(n, 256), 256, 0, as_stream(stream)>>>(gate, up, out, n);
+    return check_cuda(cudaGetLastError(), "silu_mul_bf16 launch");
 }
 
 extern "C" int awq_b200_interleave_gate_up(const int32_t *qw_gate, const int32_t *qz_gate,

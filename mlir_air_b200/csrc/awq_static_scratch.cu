@@ -62,13 +62,14 @@ extern "C" int awq_b200_gemv_bf16_static(const uint16_t *x, const int32_t *qweig
     if (rc) return rc;
     GemvArgs a{x, qweight, qzeros, scales, residual, y, B, K, N, group_size, EPI_BF16,
                scratch, STATIC_SCRATCH_BYTES, as_stream(stream)};
+    a.native_bf16 = true;  // multiply the bf16 activations as they are: no conversion buffer needed
     if (!gemv_streamk_supported(a))
         return set_error(AWQ_ERR_UNSUPPORTED,
                          "gemv_static: needs group size 128, K %% 128 == 0, N %% 32 == 0, 16-byte aligned pointers "
                          "and an sm_100 device (K=%d N=%d group=%d)", K, N, group_size);
-    if (gemv_streamk_workspace_bytes(K, N) > STATIC_SCRATCH_BYTES)
+    if (gemv_streamk_scratch_bytes(N) > STATIC_SCRATCH_BYTES)
         return set_error(AWQ_ERR_UNSUPPORTED, "gemv_static: this GPU needs %zu bytes of scratch for N = %d, the built-in "
-                         "array has %zu", gemv_streamk_workspace_bytes(K, N), N, STATIC_SCRATCH_BYTES);
+                         "array has %zu", gemv_streamk_scratch_bytes(N), N, STATIC_SCRATCH_BYTES);
     // The array keeps whatever the previous call left.  The error flag and the strip counters
     // must read zero when the kernel starts, so clear them on the caller's stream first.
     rc = check_cuda(cudaMemsetAsync(scratch, 0, gemv_streamk_workspace_clear_bytes(), as_stream(stream)),

@@ -119,8 +119,9 @@ class DecodeFFNStack:
         max_il = max(l.down.K for l in self.layers)
         bf = dict(dtype=torch.bfloat16, device=device)
         self._h = [torch.empty((max_batch, hidden), **bf) for _ in range(2)]
-        self._normed = torch.empty((max_batch, hidden), **bf)
-        self._inter = torch.empty((max_batch, max_il), **bf)
+        # intermediates between the kernels of a layer are fp16 (the GEMV kernel's fastest input)
+        self._normed = torch.empty((max_batch, hidden), dtype=torch.float16, device=device)
+        self._inter = torch.empty((max_batch, max_il), dtype=torch.float16, device=device)
         self._partial = torch.empty((max_batch, hidden), dtype=torch.float32, device=device)
         self._graphs = {}
         self._pin_in = torch.empty((max_batch, hidden), dtype=torch.bfloat16).pin_memory() if torch.cuda.is_available() else None
@@ -154,16 +155,17 @@ class DecodeFFNStack:
         # allreduce -> residual add fused with the next layer's norm
         x = h
         if self.layers[0].gamma is not None:
-            ops.rmsnorm(h, self.layers[0].gamma, self.eps, out=normed)
+            ops.rmsnorm(h, self.layers[0].gamma, self.eps, out=normed, out_f16=True)
             x = normed
         for idx, l in enumerate(self.layers):
             il = l.down.K
             it = inter.view(-1)[:B * il].view(B, il)
-            ops.gateup_swiglu(x, l.gateup, self.ws, out=it)
-            ops.gemv(it, l.down, self.ws, out=partial, f32_out=True)
+            ops.gateup_swiglu(x, l.gateup, self.ws, out=it, x_f16=x is normed, out_f16=True)
+            ops.gemv(it, l.down, self.ws, out=partial, f32_out=True, x_f16=True)
             torch.distributed.all_reduce(partial, group=self.group)
             nxt = self.layers[idx + 1].gamma if idx + 1 < len(self.layers) else None
-            ops.add_rmsnorm(h, partial, nxt, self.eps, h_out=other, normed=normed if nxt is not None else None)
+            ops.add_rmsnorm(h, partial, nxt, self.eps, h_out=other, normed=normed if nxt is not None else None,
+                            normed_f16=True)
             h, other = other, h
             x = normed if nxt is not None else h
         return h

@@ -158,3 +158,38 @@ def interleave_rows_gate_up(gate_B, up_B):
             m[:, 0::2], m[:, 1::2] = g, u
         out.append(m)
     return tuple(out)
+
+
+# ---------------------------------------------------------------------------------------
+# bf16 FFN examples: one flat buffer [gate | up | down], each matrix cut into `num_cols`
+# partitions (ffn_swiglu/decode/ffn_decode.py:39-45,287-299; ffn_swiglu/prefill/ffn_prefill.py:295-301)
+# ---------------------------------------------------------------------------------------
+def transpose_32bit_words(A, M, K):
+    """A[M, K] row-major -> 32-bit-word-transposed: pairs of k stay together, rows vary fastest."""
+    if M % 16:
+        raise ValueError(f"M must be divisible by 16; got M={M}.")
+    if K % 8:
+        raise ValueError(f"K must be divisible by 8; got K={K}.")
+    return A.reshape(M, K // 2, 2).transpose(1, 0, 2).reshape(-1)
+
+
+def pack_ffn_weights_decode(W, dim, num_cols):
+    dim_m = dim // num_cols
+    return np.concatenate([transpose_32bit_words(W[c * dim_m:(c + 1) * dim_m, :], dim_m, dim) for c in range(num_cols)])
+
+
+def unpack_ffn_weights_decode(flat, dim, num_cols):
+    dim_m = dim // num_cols
+    parts = np.asarray(flat).reshape(num_cols, dim // 2, dim_m, 2)
+    return np.ascontiguousarray(parts.transpose(0, 2, 1, 3)).reshape(dim, dim)
+
+
+def pack_ffn_weights_prefill(W, dim, num_cols):
+    dim_n = dim // num_cols
+    return np.concatenate([W[:, c * dim_n:(c + 1) * dim_n].reshape(-1) for c in range(num_cols)])
+
+
+def unpack_ffn_weights_prefill(flat, dim, num_cols):
+    dim_n = dim // num_cols
+    parts = np.asarray(flat).reshape(num_cols, dim, dim_n)
+    return np.ascontiguousarray(parts.transpose(1, 0, 2)).reshape(dim, dim)

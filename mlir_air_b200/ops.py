@@ -78,14 +78,14 @@ class Workspace:
     """Caller-owned scratch for the decode kernels (strip counters + split-K partials).
     One per stream: calls that share a workspace must not overlap on the GPU."""
 
-    def __init__(self, K: int, N: int, device="cuda"):
-        self.nbytes = int(_lib.load().awq_b200_workspace_bytes(1, int(K), int(N)))
+    def __init__(self, K: int, N: int, device="cuda", batch: int = 64):
+        self.nbytes = int(_lib.load().awq_b200_workspace_bytes(int(batch), int(K), int(N)))
         self.buf = torch.empty(self.nbytes, dtype=torch.uint8, device=device)
         with torch.cuda.device(self.buf.device):
             _lib.call("awq_b200_workspace_init", self.buf.data_ptr(), self.nbytes, _stream())
 
-    def fits(self, K, N):
-        return int(_lib.load().awq_b200_workspace_bytes(1, int(K), int(N))) <= self.nbytes
+    def fits(self, K, N, batch=64):
+        return int(_lib.load().awq_b200_workspace_bytes(int(batch), int(K), int(N))) <= self.nbytes
 
     def check(self):
         """Synchronise and raise if a device-side wait timed out."""
@@ -93,8 +93,16 @@ class Workspace:
             _lib.call("awq_b200_workspace_check", self.buf.data_ptr(), _stream())
 
 
+ACT_BF16, ACT_F16 = 0, 1
+
+
+def _act_dtype(f16: bool):
+    return torch.float16 if f16 else torch.bfloat16
+
+
 def set_decode_kernel(mode: str):
-    _lib.call("awq_b200_set_decode_kernel", {"auto": 0, "generic": 1, "streamk": 2}[mode])
+    """"auto", "generic", "streamk" (fp16 activation path) or "streamk_bf16" (bf16 activations as they are)."""
+    _lib.call("awq_b200_set_decode_kernel", {"auto": 0, "generic": 1, "streamk": 2, "streamk_bf16": 3}[mode])
 
 
 def set_gemm_kernel(mode: str):
@@ -120,8 +128,8 @@ def dequant_1d(packed_q, scales, zeros, n, group_size, out=None):
     return out
 
 
-def _x2d(x, K):
-    _want(x, torch.bfloat16, "x")
+def _x2d(x, K, f16=False):
+    _want(x, _act_dtype(f16), "x")
     if x.dim() == 1:
         x = x.view(1, -1)
     if x.dim() != 2 or x.shape[1] != K:
@@ -129,35 +137,33 @@ def _x2d(x, K):
     return x
 
 
-def gemv(x, w: AwqWeight, ws: Workspace, residual=None, out=None, f32_out=False):
-    """y [B, N] = x [B, K] @ W (+ residual); bf16 with one rounding, or the f32 partial."""
-    x = _x2d(x, w.K)
+def gemv(x, w: AwqWeight, ws: Workspace, residual=None, out=None, f32_out=False, x_f16=False):
+    """y [B, N] = x [B, K] @ W (+ residual); bf16 with one rounding, or the f32 partial.
+    x is bf16, or fp16 (the library's internal activation format) with x_f16."""
+    x = _x2d(x, w.K, x_f16)
     B = x.shape[0]
     if out is None:
         out = torch.empty((B, w.N), dtype=torch.float32 if f32_out else torch.bfloat16, device=x.device)
-    if f32_out:
-        if residual is not None:
-            raise _lib.AwqBackendError("f32 partial output takes no residual")
-        _lib.call("awq_b200_gemv_f32", _ptr(x), _ptr(w.qweight), _ptr(w.qzeros), _ptr(w.scales),
-                  _ptr(_want(out, torch.float32, "out")), B, w.K, w.N, w.group_size, _ptr(ws.buf), ws.nbytes, _stream())
-    else:
-        if residual is not None:
-            _want(residual, torch.bfloat16, "residual")
-        _lib.call("awq_b200_gemv_bf16", _ptr(x), _ptr(w.qweight), _ptr(w.qzeros), _ptr(w.scales), _ptr(residual),
-                  _ptr(_want(out, torch.bfloat16, "out")), B, w.K, w.N, w.group_size, _ptr(ws.buf), ws.nbytes,
-                  _stream())
+    if f32_out and residual is not None:
+        raise _lib.AwqBackendError("f32 partial output takes no residual")
+    if residual is not None:
+        _want(residual, torch.bfloat16, "residual")
+    _want(out, torch.float32 if f32_out else torch.bfloat16, "out")
+    _lib.call("awq_b200_gemv_act", _ptr(x), ACT_F16 if x_f16 else ACT_BF16, _ptr(w.qweight), _ptr(w.qzeros),
+              _ptr(w.scales), _ptr(residual), _ptr(out), 1 if f32_out else 0, B, w.K, w.N, w.group_size, _ptr(ws.buf),
+              ws.nbytes, _stream())
     return out
 
 
-def gateup_swiglu(x, w_gateup: AwqWeight, ws: Workspace, out=None):
+def gateup_swiglu(x, w_gateup: AwqWeight, ws: Workspace, out=None, x_f16=False, out_f16=False):
     """out [B, I] = silu(gate) * up for a gate/up-interleaved [K, 2I] weight."""
-    x = _x2d(x, w_gateup.K)
+    x = _x2d(x, w_gateup.K, x_f16)
     B, I = x.shape[0], w_gateup.N // 2
     if out is None:
-        out = torch.empty((B, I), dtype=torch.bfloat16, device=x.device)
-    _lib.call("awq_b200_gateup_swiglu_bf16", _ptr(x), _ptr(w_gateup.qweight), _ptr(w_gateup.qzeros),
-              _ptr(w_gateup.scales), _ptr(_want(out, torch.bfloat16, "out")), B, w_gateup.K, I, w_gateup.group_size,
-              _ptr(ws.buf), ws.nbytes, _stream())
+        out = torch.empty((B, I), dtype=_act_dtype(out_f16), device=x.device)
+    _lib.call("awq_b200_gateup_swiglu_act", _ptr(x), ACT_F16 if x_f16 else ACT_BF16, _ptr(w_gateup.qweight),
+              _ptr(w_gateup.qzeros), _ptr(w_gateup.scales), _ptr(_want(out, _act_dtype(out_f16), "out")),
+              ACT_F16 if out_f16 else ACT_BF16, B, w_gateup.K, I, w_gateup.group_size, _ptr(ws.buf), ws.nbytes, _stream())
     return out
 
 
@@ -176,41 +182,43 @@ def interleave_gate_up(gate: AwqWeight, up: AwqWeight) -> AwqWeight:
     return AwqWeight(qw, qz, sc, gate.group_size)
 
 
-def rmsnorm(x, gamma, eps=1e-5, out=None):
+def rmsnorm(x, gamma, eps=1e-5, out=None, out_f16=False):
     _want(x, torch.bfloat16, "x")
     x2 = x.view(1, -1) if x.dim() == 1 else x
     if out is None:
-        out = torch.empty_like(x2)
-    _lib.call("awq_b200_rmsnorm_bf16", _ptr(x2), _ptr(_want(gamma, torch.bfloat16, "gamma")), float(eps), _ptr(out),
-              x2.shape[0], x2.shape[1], _stream())
+        out = torch.empty(x2.shape, dtype=_act_dtype(out_f16), device=x.device)
+    _lib.call("awq_b200_rmsnorm_act", _ptr(x2), _ptr(_want(gamma, torch.bfloat16, "gamma")), float(eps),
+              _ptr(_want(out, _act_dtype(out_f16), "out")), ACT_F16 if out_f16 else ACT_BF16, x2.shape[0], x2.shape[1],
+              _stream())
     return out
 
 
-def add_rmsnorm(h, partial_sum, gamma=None, eps=1e-5, h_out=None, normed=None):
+def add_rmsnorm(h, partial_sum, gamma=None, eps=1e-5, h_out=None, normed=None, normed_f16=False):
     """h_out = bf16(h + partial_sum); normed = rmsnorm(h_out, gamma) when gamma is given."""
     _want(h, torch.bfloat16, "h")
     _want(partial_sum, torch.float32, "partial_sum")
     if h_out is None:
         h_out = torch.empty_like(h)
     if gamma is not None and normed is None:
-        normed = torch.empty_like(h)
-    _lib.call("awq_b200_add_rmsnorm_bf16", _ptr(h), _ptr(partial_sum), _ptr(gamma), float(eps), _ptr(h_out),
-              _ptr(normed), h.shape[0], h.shape[1], _stream())
+        normed = torch.empty(h.shape, dtype=_act_dtype(normed_f16), device=h.device)
+    _lib.call("awq_b200_add_rmsnorm_act", _ptr(h), _ptr(partial_sum), _ptr(gamma), float(eps), _ptr(h_out),
+              _ptr(normed), ACT_F16 if normed_f16 else ACT_BF16, h.shape[0], h.shape[1], _stream())
     return h_out, normed
 
 
 def ffn_decode(x, w_gateup: AwqWeight, w_down: AwqWeight, ws: Workspace, gamma=None, eps=1e-5, residual=None,
                normed=None, inter=None, out=None):
-    """out [B, H] = down(swiglu(gateup . norm(x))) (+ residual): one C-ABI call, three kernels."""
+    """out [B, H] = down(swiglu(gateup . norm(x))) (+ residual): one C-ABI call, three kernels.
+    `normed` and `inter` are 16-bit scratch (the library keeps its intermediates there as fp16)."""
     x = _x2d(x, w_gateup.K)
     B, H, I = x.shape[0], w_gateup.K, w_gateup.N // 2
     if w_down.K != I or w_down.N != H:
         raise _lib.AwqBackendError(f"down weight must be [{I}, {H}], got [{w_down.K}, {w_down.N}]")
     dev = x.device
     if gamma is not None and normed is None:
-        normed = torch.empty((B, H), dtype=torch.bfloat16, device=dev)
+        normed = torch.empty((B, H), dtype=torch.float16, device=dev)
     if inter is None:
-        inter = torch.empty((B, I), dtype=torch.bfloat16, device=dev)
+        inter = torch.empty((B, I), dtype=torch.float16, device=dev)
     if out is None:
         out = torch.empty((B, H), dtype=torch.bfloat16, device=dev)
     _lib.call("awq_b200_ffn_decode_bf16", _ptr(x), _ptr(gamma), float(eps), _ptr(w_gateup.qweight),
@@ -229,6 +237,26 @@ def gemm(A, w: AwqWeight, out=None):
         out = torch.empty((A.shape[0], w.N), dtype=torch.bfloat16, device=A.device)
     _lib.call("awq_b200_gemm_bf16", _ptr(A), _ptr(w.qweight), _ptr(w.qzeros), _ptr(w.scales), _ptr(out), A.shape[0],
               w.K, w.N, w.group_size, _stream())
+    return out
+
+
+def linear_bf16(x, W, out=None):
+    """y [M, N] = x [M, K] @ W[N, K]^T with un-quantised bf16 weights (the bf16 sibling path)."""
+    _want(x, torch.bfloat16, "x")
+    _want(W, torch.bfloat16, "W")
+    x2 = x.view(1, -1) if x.dim() == 1 else x
+    if out is None:
+        out = torch.empty((x2.shape[0], W.shape[0]), dtype=torch.bfloat16, device=x.device)
+    _lib.call("awq_b200_linear_bf16", _ptr(x2), _ptr(W), _ptr(out), x2.shape[0], x2.shape[1], W.shape[0], _stream())
+    return out
+
+
+def silu_mul(gate, up, out=None):
+    """out = silu(gate) * up elementwise (bf16 in, f32 math, bf16 out)."""
+    if out is None:
+        out = torch.empty_like(gate)
+    _lib.call("awq_b200_silu_mul_bf16", _ptr(_want(gate, torch.bfloat16, "gate")), _ptr(_want(up, torch.bfloat16, "up")),
+              _ptr(out), gate.numel(), _stream())
     return out
 
 

@@ -116,7 +116,7 @@ def test_interleave_gate_up_exact(ops):
 GEMV_SHAPES = [(1, 512, 256), (3, 1024, 1056), (8, 2048, 4096), (2, 256, 32), (5, 11008, 4096)]
 
 
-@pytest.mark.parametrize("kernel", ["generic", "streamk"])
+@pytest.mark.parametrize("kernel", ["generic", "streamk", "streamk_bf16"])
 @pytest.mark.parametrize("B,K,N", GEMV_SHAPES)
 def test_gemv_vs_oracle(ops, kernel, B, K, N):
     ops.set_decode_kernel(kernel)
@@ -147,7 +147,7 @@ def test_gemv_cfg2_full_size(ops):
     for B in (1, 8):
         x = randn_bf16((B, 4096), seed=B)
         ref = (x.astype(np.float32) @ wf).astype(bfloat16)
-        for kernel in ("streamk", "generic"):
+        for kernel in ("streamk", "streamk_bf16", "generic"):
             ops.set_decode_kernel(kernel)
             y = to_host(ops.gemv(to_dev(x), w, ws))
             assert O.rel_l2(y, ref) <= REL_L2_TOL, (kernel, B)
@@ -172,7 +172,7 @@ def test_gemv_batch_over_8(ops):
     w = dev_weight(qw, qz, s)
     ws = ops.Workspace(1024, 512)
     ref = O.gemv_A_ref(x, qw, qz, s, 128)
-    for kernel in ("streamk", "generic"):
+    for kernel in ("streamk", "streamk_bf16", "generic"):
         ops.set_decode_kernel(kernel)
         assert O.rel_l2(to_host(ops.gemv(to_dev(x), w, ws)), ref) <= REL_L2_TOL
     ws.check()
@@ -226,7 +226,7 @@ def test_swiglu_rms_reference_example_fixture(ops):
     g = load("matvec_int4_swiglu_rms_256x512")
     w = ops.repack_B_to_A(to_dev(g["A_q"]), to_dev(g["A_s"]), to_dev(g["A_z"]), 128)  # [K, 2I] interleaved
     ws = ops.Workspace(w.K, w.N)
-    for kernel in ("generic", "streamk"):
+    for kernel in ("generic", "streamk", "streamk_bf16"):
         ops.set_decode_kernel(kernel)
         normed = ops.rmsnorm(to_dev(g["RMS_in"][0:1]), to_dev(g["RMS_in"][1]), 1e-5)
         y = to_host(ops.gateup_swiglu(normed, w, ws))[0]
@@ -244,7 +244,7 @@ def _ffn_weights(H, I, seed):
     return gate, up, down
 
 
-@pytest.mark.parametrize("kernel", ["generic", "streamk"])
+@pytest.mark.parametrize("kernel", ["generic", "streamk", "streamk_bf16"])
 @pytest.mark.parametrize("B,H,I", [(1, 512, 1408), (4, 1024, 2816), (16, 512, 1024)])
 def test_ffn_decode_vs_oracle(ops, kernel, B, H, I):
     ops.set_decode_kernel(kernel)
@@ -282,6 +282,49 @@ def test_ffn_cfg3_full_size(ops):
         y = to_host(ops.ffn_decode(to_dev(x), wgu, wd, ws))
         assert O.rel_l2(y, ref) <= REL_L2_TOL, B
     ws.check()
+
+
+def test_fp16_activation_formats_agree_with_bf16(ops):
+    """The internal fp16 activation format is exact for bf16 values in range: feeding the same
+    values as fp16 gives the same bits as feeding bf16, for both kernels."""
+    import torch
+    K, N = 1024, 1536
+    qw, qz, s = synth_awq(K, N, 128, seed=31)
+    w = dev_weight(qw, qz, s)
+    ws = ops.Workspace(K, N)
+    x = to_dev(randn_bf16((5, K), seed=32))
+    for kernel in ("streamk", "generic"):
+        ops.set_decode_kernel(kernel)
+        y_b = to_host(ops.gemv(x, w, ws))
+        y_h = to_host(ops.gemv(x.to(torch.float16), w, ws, x_f16=True))
+        assert np.array_equal(bits(y_b), bits(y_h)), kernel
+        t_b = ops.gateup_swiglu(x, w, ws)
+        t_h = ops.gateup_swiglu(x, w, ws, out_f16=True)
+        assert torch.equal(t_b.float(), t_h.float()), kernel
+    n_b = ops.rmsnorm(x, to_dev(randn_bf16(K, seed=33)), 1e-5)
+    n_h = ops.rmsnorm(x, to_dev(randn_bf16(K, seed=33)), 1e-5, out_f16=True)
+    assert torch.equal(n_b.float(), n_h.float())
+    ws.check()
+
+
+def test_fp16_overflow_is_reported_and_bf16_path_handles_it(ops):
+    from mlir_air_b200._lib import AwqBackendError
+    K, N = 256, 512
+    qw, qz, s = synth_awq(K, N, 128, seed=41)
+    w = dev_weight(qw, qz, s)
+    x = randn_bf16((2, K), seed=42)
+    x[0, 3] = bfloat16(1.0e6)  # beyond fp16
+    ref = O.gemv_A_ref(x, qw, qz, s, 128)
+    ops.set_decode_kernel("streamk")
+    ws = ops.Workspace(K, N)
+    ops.gemv(to_dev(x), w, ws)
+    with pytest.raises(AwqBackendError):
+        ws.check()
+    ops.set_decode_kernel("streamk_bf16")
+    ws = ops.Workspace(K, N)
+    y = to_host(ops.gemv(to_dev(x), w, ws))
+    ws.check()
+    assert O.rel_l2(y, ref) <= REL_L2_TOL
 
 
 # ------------------------------------------------------------------ prefill GEMM (row a9)
