@@ -17,6 +17,25 @@ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
 int device_sm_count();
 bool device_is_sm100();
 
+// Launch `kernel` so that it may overlap the tail of the previous kernel in `stream`
+// (programmatic dependent launch); the kernel must call pdl_wait() before touching anything the
+// previous kernel wrote or read.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 #define AWQ_REQUIRE(cond, ...)                                        \
     do {                                                              \
         if (!(cond)) return awq::set_error(AWQ_ERR_INVALID_ARGUMENT, __VA_ARGS__); \

@@ -195,6 +195,7 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         mbar_fence_init();
     }
     __syncthreads();
+    pdl_launch_dependents();
 
     if (warp == SK_CONSUMER_WARPS) {
         // ------------------------------ producer ------------------------------
@@ -204,12 +205,7 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             tma_prefetch_desc(&tmS);
             tma_prefetch_desc(&tmZ);
             const uint64_t stream_policy = l2_policy_evict_first();
-            int v = v_first, g = g_first, slot = 0, round = 0;
-            for (int i = 0; i < n_units; ++i) {
-                if (round > 0 && !mbar_wait_bounded(empty_bar(slot), (round - 1) & 1)) {
-                    atomicExch(err_flag, 1);
-                    break;
-                }
+            auto load_weights = [&](int slot, int v, int g) {
                 const uint32_t st = smem_base + slot * SK_STAGE_BYTES;
                 const uint32_t bar = full_bar(slot);
                 mbar_expect_tx(bar, SK_TX_BYTES);
@@ -217,18 +213,45 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                 for (int bx = 0; bx < SK_STRIP / SK_BOX_COLS; ++bx)
                     tma_load_2d_hint(st + bx * SK_WBOX_BYTES, &tmW, (v * SK_STRIP + bx * SK_BOX_COLS) / 8, g * SK_GROUP,
                                      bar, stream_policy);
-                tma_load_2d(st + SK_OFF_X, &tmX, g * SK_GROUP, 0, bar);
-                tma_load_2d(st + SK_OFF_X + 1024, &tmX, g * SK_GROUP + 64, 0, bar);
 #pragma unroll
                 for (int bx = 0; bx < SK_STRIP / SK_BOX_COLS; ++bx)
                     tma_load_2d(st + SK_OFF_S + bx * SK_BOX_COLS * 2, &tmS, v * SK_STRIP + bx * SK_BOX_COLS, g, bar);
                 tma_load_2d(st + SK_OFF_Z, &tmZ, v * (SK_STRIP / 8), g, bar);
+            };
+            auto load_activations = [&](int slot, int g) {
+                const uint32_t st = smem_base + slot * SK_STAGE_BYTES;
+                tma_load_2d(st + SK_OFF_X, &tmX, g * SK_GROUP, 0, full_bar(slot));
+                tma_load_2d(st + SK_OFF_X + 1024, &tmX, g * SK_GROUP + 64, 0, full_bar(slot));
+            };
+            // The weights do not depend on the previous kernel: fill the ring with them first, and
+            // only then wait for the previous kernel (whose output is this kernel's activations).
+            const int n_first = n_units < SK_STAGES ? n_units : SK_STAGES;
+            int v = v_first, g = g_first;
+            for (int i = 0; i < n_first; ++i) {
+                load_weights(i, v, g);
+                if (++g == G) { g = 0; ++v; }
+            }
+            pdl_wait();
+            g = g_first;
+            for (int i = 0; i < n_first; ++i) {
+                load_activations(i, g);
+                if (++g == G) g = 0;
+            }
+            int slot = 0, round = 1;
+            for (int i = n_first; i < n_units; ++i) {
+                if (!mbar_wait_bounded(empty_bar(slot), (round - 1) & 1)) {
+                    atomicExch(err_flag, 1);
+                    break;
+                }
+                load_weights(slot, v, g);
+                load_activations(slot, g);
                 if (++g == G) { g = 0; ++v; }
                 if (++slot == SK_STAGES) { slot = 0; ++round; }
             }
         }
         return;
     }
+    pdl_wait();  // consumers read and write global memory the previous kernel may still be using
 
     // ------------------------------ consumers ------------------------------
     // Warp w owns strip columns [64 w, 64 w + 64): two 16-byte chunks (A, B) of every box row.
@@ -292,14 +315,31 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         for (int h = 0; h < 2; ++h)
 #pragma unroll
             for (int i = 0; i < 8; ++i) own[h][i] = 0.f;
-        for (long long cc = c_lo; cc <= c_hi; ++cc) {
-            const float *src = partials + (size_t)(cc + v) * SK_PARTIAL_FLOATS + lane_off;
+        // Four slots' loads in flight at a time (the loop is latency-bound otherwise); the adds
+        // stay in CTA order, so the sum does not depend on which warp happens to be last.
+        const int n_slots = (int)(c_hi - c_lo) + 1;
+        const float *src0 = partials + (size_t)(c_lo + v) * SK_PARTIAL_FLOATS + lane_off;
+        for (int s0 = 0; s0 < n_slots; s0 += 4) {
+            float4 p[4][4];
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const float4 p0 = __ldcg(reinterpret_cast<const float4 *>(src + 32 * h));
-                const float4 p1 = __ldcg(reinterpret_cast<const float4 *>(src + 32 * h) + 1);
-                own[h][0] += p0.x; own[h][1] += p0.y; own[h][2] += p0.z; own[h][3] += p0.w;
-                own[h][4] += p1.x; own[h][5] += p1.y; own[h][6] += p1.z; own[h][7] += p1.w;
+            for (int j = 0; j < 4; ++j) {
+                const int sj = s0 + j < n_slots ? s0 + j : n_slots - 1;
+                const float4 *src = reinterpret_cast<const float4 *>(src0 + (size_t)sj * SK_PARTIAL_FLOATS);
+                p[j][0] = __ldcg(src);
+                p[j][1] = __ldcg(src + 1);
+                p[j][2] = __ldcg(src + 8);
+                p[j][3] = __ldcg(src + 9);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (s0 + j >= n_slots) break;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    own[h][0] += p[j][2 * h].x; own[h][1] += p[j][2 * h].y;
+                    own[h][2] += p[j][2 * h].z; own[h][3] += p[j][2 * h].w;
+                    own[h][4] += p[j][2 * h + 1].x; own[h][5] += p[j][2 * h + 1].y;
+                    own[h][6] += p[j][2 * h + 1].z; own[h][7] += p[j][2 * h + 1].w;
+                }
             }
         }
         __syncwarp();
@@ -395,6 +435,8 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 // x bf16 -> fp16 (values beyond the fp16 range are clamped and reported through the error flag)
 __global__ void cvt_bf16_to_f16_kernel(const uint16_t *__restrict__ x, uint16_t *__restrict__ xh, size_t n,
                                        int *__restrict__ err_flag) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const float v = bf16_bits_to_f32(x[i]);
@@ -489,9 +531,10 @@ static int launch_one(const GemvArgs &a, const uint16_t *x, const uint16_t *resi
     int *err_flag = reinterpret_cast<int *>(ws);
     int *counters = reinterpret_cast<int *>(ws + SK_WS_HEADER);
     float *partials = reinterpret_cast<float *>(ws + SK_WS_PARTIALS);
-    gemv_streamk_kernel<EPI, XH><<<ctas, SK_THREADS, SK_SMEM_BYTES, a.stream>>>(
-        tmW, tmX, tmS, tmZ, residual, y, B, a.N, G, V, a.out_format == ACT_F16 ? 1 : 0, partials, counters, err_flag);
-    return check_cuda(cudaGetLastError(), "stream-K gemv launch");
+    return check_cuda(launch_pdl(gemv_streamk_kernel<EPI, XH>, dim3(ctas), dim3(SK_THREADS), SK_SMEM_BYTES, a.stream, tmW,
+                                 tmX, tmS, tmZ, residual, y, B, a.N, G, V, a.out_format == ACT_F16 ? 1 : 0, partials,
+                                 counters, err_flag),
+                      "stream-K gemv launch");
 }
 
 template <bool XH>
@@ -530,8 +573,9 @@ int launch_gemv_streamk(const GemvArgs &a) {
     uint8_t *ws = reinterpret_cast<uint8_t *>(a.workspace);
     uint16_t *xh = reinterpret_cast<uint16_t *>(ws + gemv_streamk_scratch_bytes(a.N));
     const size_t n = (size_t)a.B * a.K;
-    cvt_bf16_to_f16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, a.stream>>>(a.x, xh, n, reinterpret_cast<int *>(ws));
-    int rc = check_cuda(cudaGetLastError(), "activation conversion launch");
+    int rc = check_cuda(launch_pdl(cvt_bf16_to_f16_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, a.stream, a.x,
+                                   xh, n, reinterpret_cast<int *>(ws)),
+                        "activation conversion launch");
     if (rc) return rc;
     return launch_passes<true>(a, xh);
 }

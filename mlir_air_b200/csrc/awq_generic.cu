@@ -4,6 +4,7 @@
 #include <cuda_fp16.h>
 
 #include "awq_common.cuh"
+#include "awq_ptx.cuh"
 
 namespace awq {
 
@@ -226,34 +227,72 @@ __device__ __forceinline__ float block_sum_256(float v, float *smem) {
 
 // normed = bf16((x * rstd) * gamma), rstd = 1 / sqrt(mean(x^2) + eps) with the mean formed
 // in f32 and the rsqrt in f64 as the numpy golden does (matvec_int4_swiglu_rms.py:496-500).
-__global__ void __launch_bounds__(256)
+// One block per row; each thread keeps its (up to RN_PER_THREAD * 8) elements in registers
+// between the two passes, 16 bytes per load.
+constexpr int RN_THREADS = 256;
+constexpr int RN_CHUNKS = 8;  // 16-byte chunks per thread held in registers: rows up to 16384 elements
+
+__global__ void __launch_bounds__(RN_THREADS)
 rmsnorm_kernel(const uint16_t *__restrict__ h, const float *__restrict__ partial,
                const uint16_t *__restrict__ gamma, float eps, uint16_t *__restrict__ h_out,
                uint16_t *__restrict__ normed, int K, int normed_f16) {
     __shared__ float red[8];
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t row = (size_t)blockIdx.x * K;
+    const int n_chunks = K >> 3;  // K % 8 == 0 is required by the launcher
+    float v[RN_CHUNKS][8];
     float ss = 0.f;
-    for (int k = threadIdx.x; k < K; k += 256) {
-        float v = bf16_bits_to_f32(h[row + k]);
-        if (partial) {
-            const uint16_t r = f32_to_bf16_bits(v + partial[row + k]);
-            if (h_out) h_out[row + k] = r;
-            v = bf16_bits_to_f32(r);
+#pragma unroll
+    for (int c = 0; c < RN_CHUNKS; ++c) {
+        const int ch = threadIdx.x + c * RN_THREADS;
+        if (ch < n_chunks) {
+            const uint4 t = *reinterpret_cast<const uint4 *>(h + row + 8 * ch);
+            const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                v[c][2 * e] = bf16x2_lo(w[e]);
+                v[c][2 * e + 1] = bf16x2_hi(w[e]);
+            }
+            if (partial) {
+                const float4 p0 = *reinterpret_cast<const float4 *>(partial + row + 8 * ch);
+                const float4 p1 = *reinterpret_cast<const float4 *>(partial + row + 8 * ch + 4);
+                const float pp[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+                uint32_t o[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    o[e] = pack_bf16x2(v[c][2 * e] + pp[2 * e], v[c][2 * e + 1] + pp[2 * e + 1]);
+                    v[c][2 * e] = bf16x2_lo(o[e]);
+                    v[c][2 * e + 1] = bf16x2_hi(o[e]);
+                }
+                if (h_out) *reinterpret_cast<uint4 *>(h_out + row + 8 * ch) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss = fmaf(v[c][e], v[c][e], ss);
         }
-        ss = fmaf(v, v, ss);
     }
     if (!normed) return;
     const float total = block_sum_256(ss, red);
     const float rstd = (float)(1.0 / sqrt((double)(total / (float)K) + (double)eps));
-    for (int k = threadIdx.x; k < K; k += 256) {
-        float v;
-        if (partial)
-            v = bf16_bits_to_f32(f32_to_bf16_bits(bf16_bits_to_f32(h[row + k]) + partial[row + k]));
-        else
-            v = bf16_bits_to_f32(h[row + k]);
-        uint16_t o = f32_to_bf16_bits((v * rstd) * bf16_bits_to_f32(gamma[k]));
-        if (normed_f16) o = __half_as_ushort(__float2half_rn(fminf(fmaxf(bf16_bits_to_f32(o), -65504.f), 65504.f)));
-        normed[row + k] = o;
+#pragma unroll
+    for (int c = 0; c < RN_CHUNKS; ++c) {
+        const int ch = threadIdx.x + c * RN_THREADS;
+        if (ch < n_chunks) {
+            const uint4 gt = *reinterpret_cast<const uint4 *>(gamma + 8 * ch);
+            const uint32_t gw[4] = {gt.x, gt.y, gt.z, gt.w};
+            uint32_t o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                uint16_t lo = f32_to_bf16_bits((v[c][2 * e] * rstd) * bf16x2_lo(gw[e]));
+                uint16_t hi = f32_to_bf16_bits((v[c][2 * e + 1] * rstd) * bf16x2_hi(gw[e]));
+                if (normed_f16) {
+                    lo = __half_as_ushort(__float2half_rn(fminf(fmaxf(bf16_bits_to_f32(lo), -65504.f), 65504.f)));
+                    hi = __half_as_ushort(__float2half_rn(fminf(fmaxf(bf16_bits_to_f32(hi), -65504.f), 65504.f)));
+                }
+                o[e] = (uint32_t)lo | ((uint32_t)hi << 16);
+            }
+            *reinterpret_cast<uint4 *>(normed + row + 8 * ch) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
     }
 }
 
@@ -399,12 +438,15 @@ using namespace awq;
 extern "C" int awq_b200_rmsnorm_act(const uint16_t *x, const uint16_t *gamma, float eps, void *out, int out_format,
                                     int B, int K, awq_stream_t stream) {
     AWQ_REQUIRE(B >= 0 && K > 0, "rmsnorm: bad size");
+    AWQ_REQUIRE(K % 8 == 0 && K <= RN_THREADS * RN_CHUNKS * 8, "rmsnorm: K (%d) must be a multiple of 8, at most %d", K, RN_THREADS * RN_CHUNKS * 8);
+    AWQ_REQUIRE(aligned16(x) && aligned16(gamma) && aligned16(out), "rmsnorm: pointers must be 16-byte aligned");
     AWQ_REQUIRE(out_format == ACT_BF16 || out_format == ACT_F16, "rmsnorm: unknown output format %d", out_format);
     if (B == 0) return AWQ_OK;
     AWQ_REQUIRE(x && gamma && out, "rmsnorm: null pointer");
-    rmsnorm_kernel<<<B, 256, 0, as_stream(stream)>>>(x, nullptr, gamma, eps, nullptr, reinterpret_cast<uint16_t *>(out),
-                                                     K, out_format == ACT_F16);
-    return check_cuda(cudaGetLastError(), "rmsnorm launch");
+    return check_cuda(launch_pdl(rmsnorm_kernel, dim3(B), dim3(256), 0, as_stream(stream), x, (const float *)nullptr,
+                                 gamma, eps, (uint16_t *)nullptr, reinterpret_cast<uint16_t *>(out), K,
+                                 out_format == ACT_F16 ? 1 : 0),
+                      "rmsnorm launch");
 }
 
 extern "C" int awq_b200_rmsnorm_bf16(const uint16_t *x, const uint16_t *gamma, float eps, uint16_t *out,
@@ -422,14 +464,16 @@ extern "C" int awq_b200_add_rmsnorm_act(const uint16_t *h, const float *partial_
                                         float eps, uint16_t *h_out, void *normed, int normed_format, int B, int K,
                                         awq_stream_t stream) {
     AWQ_REQUIRE(B >= 0 && K > 0, "add_rmsnorm: bad size");
+    AWQ_REQUIRE(K % 8 == 0 && K <= RN_THREADS * RN_CHUNKS * 8, "add_rmsnorm: K (%d) must be a multiple of 8, at most %d", K, RN_THREADS * RN_CHUNKS * 8);
+    AWQ_REQUIRE(aligned16(h) && aligned16(partial_sum) && aligned16(h_out) && aligned16(normed) && aligned16(gamma), "add_rmsnorm: pointers must be 16-byte aligned");
     AWQ_REQUIRE(normed_format == ACT_BF16 || normed_format == ACT_F16, "add_rmsnorm: unknown format %d", normed_format);
     if (B == 0) return AWQ_OK;
     AWQ_REQUIRE(h && partial_sum && h_out, "add_rmsnorm: null pointer");
     AWQ_REQUIRE((gamma == nullptr) == (normed == nullptr), "add_rmsnorm: gamma and normed go together");
     AWQ_REQUIRE(h_out != h, "add_rmsnorm: h_out must not alias h");
-    rmsnorm_kernel<<<B, 256, 0, as_stream(stream)>>>(h, partial_sum, gamma, eps, h_out,
-                                                     reinterpret_cast<uint16_t *>(normed), K, normed_format == ACT_F16);
-    return check_cuda(cudaGetLastError(), "add_rmsnorm launch");
+    return check_cuda(launch_pdl(rmsnorm_kernel, dim3(B), dim3(256), 0, as_stream(stream), h, partial_sum, gamma, eps,
+                                 h_out, reinterpret_cast<uint16_t *>(normed), K, normed_format == ACT_F16 ? 1 : 0),
+                      "add_rmsnorm launch");
 }
 
 extern "C" int awq_b200_linear_bf16(const uint16_t *x, const uint16_t *W, uint16_t *y, int M, int K, int N,

@@ -120,6 +120,16 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Programmatic dependent launch: a kernel launched with programmatic stream serialization may
+// start while its predecessor in the stream is still running.  pdl_wait() returns once the
+// predecessor has completed and its writes are visible; nothing the predecessor produces may be
+// read, and nothing it reads may be overwritten, before that.  pdl_launch_dependents() lets the
+// successor's blocks be scheduled as soon as resources free up.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
