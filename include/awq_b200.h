@@ -63,6 +63,11 @@ const char *awq_b200_last_error(void);
  * Process-wide; for tests. */
 int awq_b200_set_decode_kernel(int mode);
 
+/* Split-K partial sums of the stream-K decode kernel are combined with f32 atomic adds by
+ * default (fastest; the last bits of a result can differ between runs because the order of the
+ * adds is not fixed).  on = 1 sums them in a fixed order instead: bit-reproducible, slower. */
+int awq_b200_set_deterministic(int on);
+
 /* ---- AWQ dequant --------------------------------------------------------------
  * out bf16 [K, N] = bf16_rne((q - z) * s).  Bit-exact with dequant_to_bf16
  * (programming_examples/llms/llama32_1b_int4/awq_repacker.py:57-82),
@@ -103,7 +108,7 @@ int awq_b200_gemv_bf16(const uint16_t *x, const int32_t *qweight, const int32_t 
  * (a plugin interface that carries only inputs and outputs, a serving process that bans
  * cudaMalloc after start-up, plain C hosts without an allocator).  It has no counterpart in
  * the reference.  The kernel's scratch is a fixed array inside the library image, about
- * 7 MB on every GPU that loads the library, held until the process exits; nothing is
+ * 1 MB on every GPU that loads the library, held until the process exits; nothing is
  * allocated or freed by this call.  Limits: N <= 32768, group size 128, K % 128 == 0,
  * N % 32 == 0, 1 <= B <= 64; anything else returns an error rather than falling back.
  * The first call on each device looks up the array's device address, so make that first

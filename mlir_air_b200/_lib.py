@@ -36,6 +36,7 @@ SIGNATURES = {
     "awq_b200_last_error": (c_char_p, []),
     "awq_b200_set_decode_kernel": (c_int, [c_int]),
     "awq_b200_set_gemm_kernel": (c_int, [c_int]),
+    "awq_b200_set_deterministic": (c_int, [c_int]),
     "awq_b200_dequant_bf16": (c_int, [_P, _P, _P, _P, c_int, c_int, c_int, _P]),
     "awq_b200_dequant_1d_bf16": (c_int, [_P, _P, _P, _P, c_int, c_int, _P]),
     "awq_b200_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),

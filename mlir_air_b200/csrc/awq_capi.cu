@@ -12,6 +12,7 @@ namespace awq {
 static thread_local char g_error[512] = "";
 static std::atomic<int> g_decode_mode{0};
 static std::atomic<int> g_gemm_mode{0};
+static std::atomic<int> g_deterministic{0};
 
 int set_error(int code, const char *fmt, ...) {
     va_list ap;
@@ -72,6 +73,7 @@ static int run_gemv(const char *who, GemvArgs a) {
                          "pointers and an sm_100 device (K=%d N=%d gs=%d)", who, a.K, a.N, a.group_size);
     if (mode != 1 && fast_ok) {
         a.native_bf16 = (mode == 3);
+        a.deterministic = g_deterministic.load() != 0;
         return launch_gemv_streamk(a);
     }
     return launch_gemv_generic(a);
@@ -87,6 +89,10 @@ extern "C" const char *awq_b200_last_error(void) { return g_error; }
 extern "C" int awq_b200_set_decode_kernel(int mode) {
     AWQ_REQUIRE(mode >= 0 && mode <= 3, "set_decode_kernel: mode must be 0, 1, 2 or 3");
     g_decode_mode.store(mode);
+    return AWQ_OK;
+}
+extern "C" int awq_b200_set_deterministic(int on) {
+    g_deterministic.store(on ? 1 : 0);
     return AWQ_OK;
 }
 extern "C" int awq_b200_set_gemm_kernel(int mode) {

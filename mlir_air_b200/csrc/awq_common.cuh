@@ -106,6 +106,7 @@ struct GemvArgs {
     int x_format = ACT_BF16;    // format of x
     int out_format = ACT_BF16;  // EPI_SWIGLU only: format of the output
     bool native_bf16 = false;   // stream-K: multiply bf16 activations as they are (no fp16 conversion)
+    bool deterministic = false; // stream-K: sum split-K partials in a fixed order (slower) instead of f32 atomics
 };
 
 // Generic CUDA-core kernel: any group size, any N % 8 == 0, B <= 64.
@@ -113,9 +114,9 @@ int launch_gemv_generic(const GemvArgs &a);
 // TMA + mma.sync stream-K kernel: group 128, N % 32 == 0, K % 128 == 0, B <= 8.
 bool gemv_streamk_supported(const GemvArgs &a);
 int launch_gemv_streamk(const GemvArgs &a);
-size_t gemv_streamk_scratch_bytes(int N);               // counters + split-K partials
+size_t gemv_streamk_scratch_bytes(int N, bool deterministic);  // counters + split-K accumulators / partial slots
 size_t gemv_streamk_workspace_bytes(int B, int K, int N);  // + room to convert B rows of x to fp16
-size_t gemv_streamk_workspace_clear_bytes();
+size_t gemv_streamk_workspace_clear_bytes(int N);
 
 int launch_gemm_generic(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros,
                         const uint16_t *scales, uint16_t *C, int M, int K, int N, int group_size,

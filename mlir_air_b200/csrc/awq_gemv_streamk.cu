@@ -61,18 +61,28 @@ constexpr int SK_PARTIAL_FLOATS = 8 * SK_STRIP;        // one slot: [warp][batch
 static_assert(SK_TX_BYTES <= SK_STAGE_BYTES, "stage too small");
 static_assert(SK_CTAS_PER_SM * (SK_SMEM_BYTES + 1024) <= 228 * 1024, "shared memory budget");
 
-// Workspace: [0, 256) header (int error flag), then a fixed region of sub-strip counters (one per
-// 64 columns), then partial slots.  The layout does not depend on the shape, so one workspace
-// can serve products of different shapes back to back (the counters are all zero between
-// launches).
+// Workspace: [0, 256) header (int error flag); a fixed region of sub-strip counters (one per 64
+// columns); the per-strip f32 accumulators of the fast reduction (strip v at a fixed offset, up
+// to SK_MAX_STRIPS); then, for the deterministic reduction only, one partial slot per (CTA,
+// strip) segment.  Counters and accumulators are all zero between launches (the last arriver
+// resets what it used), and their offsets do not depend on the shape, so one workspace serves
+// products of different shapes back to back.
 constexpr size_t SK_WS_HEADER = 256;
 constexpr int SK_MAX_STRIPS = 504;  // N up to 258,048 columns
-constexpr size_t SK_WS_PARTIALS = SK_WS_HEADER + (size_t)SK_MAX_STRIPS * SK_CONSUMER_WARPS * 4;  // 16 KB
+constexpr size_t SK_WS_ACCUM = SK_WS_HEADER + (size_t)SK_MAX_STRIPS * SK_CONSUMER_WARPS * 4;  // 16 KB
+constexpr size_t SK_WS_PARTIALS = SK_WS_ACCUM + (size_t)SK_MAX_STRIPS * SK_PARTIAL_FLOATS * 4;
 constexpr int SK_MAX_CTAS = 2048;
 
 
-// Leading bytes of a workspace (error flag + counters) that must be zero before a launch.
-size_t gemv_streamk_workspace_clear_bytes() { return SK_WS_PARTIALS; }
+// Leading bytes of a workspace (error flag, counters, accumulators of the strips a product of N
+// columns uses) that must be zero before a launch.
+size_t gemv_streamk_workspace_clear_bytes(int N) {
+    return SK_WS_ACCUM + (size_t)((N + SK_STRIP - 1) / SK_STRIP) * SK_PARTIAL_FLOATS * 4;
+}
+
+__device__ __forceinline__ void red_add_v4(float *addr, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
 
 // CTA that owns unit x when U units are split over C CTAs as [c U / C, (c + 1) U / C).
 __host__ __device__ __forceinline__ long long sk_owner(long long x, long long C, long long U) {
@@ -173,8 +183,8 @@ __global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM)
 gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                     const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmZ,
                     const uint16_t *__restrict__ residual, void *__restrict__ y_, int B, int N, int G,
-                    int V, int out_f16, float *__restrict__ partials, int *__restrict__ counters,
-                    int *__restrict__ err_flag) {
+                    int V, int out_f16, int fast_reduce, float *__restrict__ accum, float *__restrict__ partials,
+                    int *__restrict__ counters, int *__restrict__ err_flag) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t bar_base = smem_base + SK_STAGES * SK_STAGE_BYTES;
@@ -295,50 +305,77 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             if (!failed) sk_epilogue<EPI>(own, residual, y_, B, N, n, b, out_f16);
             return;
         }
-        // [slot][warp][batch row][64 columns]
+        // [warp][batch row][64 columns] inside a strip's accumulator / a CTA's slot
         const size_t lane_off = (size_t)warp * 512 + b * 64 + (g8 >> 1) * 8;
-        float *mine = partials + (size_t)(c + v) * SK_PARTIAL_FLOATS + lane_off;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            float4 *dst = reinterpret_cast<float4 *>(mine + 32 * h);
-            dst[0] = make_float4(own[h][0], own[h][1], own[h][2], own[h][3]);
-            dst[1] = make_float4(own[h][4], own[h][5], own[h][6], own[h][7]);
-        }
-        __threadfence();
-        __syncwarp();
-        int old = 0;
-        if (lane == 0) old = atomicAdd(&counters[v * SK_CONSUMER_WARPS + warp], 1);
-        old = __shfl_sync(0xffffffffu, old, 0);
-        if (old != (int)(c_hi - c_lo)) return;
-        __threadfence();
-#pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-            for (int i = 0; i < 8; ++i) own[h][i] = 0.f;
-        // Four slots' loads in flight at a time (the loop is latency-bound otherwise); the adds
-        // stay in CTA order, so the sum does not depend on which warp happens to be last.
         const int n_slots = (int)(c_hi - c_lo) + 1;
-        const float *src0 = partials + (size_t)(c_lo + v) * SK_PARTIAL_FLOATS + lane_off;
-        for (int s0 = 0; s0 < n_slots; s0 += 4) {
-            float4 p[4][4];
+        if (fast_reduce) {
+            // every contributor adds its partial into the strip's f32 accumulator with vector
+            // reductions at L2; the last one reads the total and leaves the accumulator zero
+            float *acc_ptr = accum + (size_t)v * SK_PARTIAL_FLOATS + lane_off;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int sj = s0 + j < n_slots ? s0 + j : n_slots - 1;
-                const float4 *src = reinterpret_cast<const float4 *>(src0 + (size_t)sj * SK_PARTIAL_FLOATS);
-                p[j][0] = __ldcg(src);
-                p[j][1] = __ldcg(src + 1);
-                p[j][2] = __ldcg(src + 8);
-                p[j][3] = __ldcg(src + 9);
+            for (int h = 0; h < 2; ++h) {
+                red_add_v4(acc_ptr + 32 * h, own[h][0], own[h][1], own[h][2], own[h][3]);
+                red_add_v4(acc_ptr + 32 * h + 4, own[h][4], own[h][5], own[h][6], own[h][7]);
             }
+            __threadfence();
+            __syncwarp();
+            int old = 0;
+            if (lane == 0) old = atomicAdd(&counters[v * SK_CONSUMER_WARPS + warp], 1);
+            old = __shfl_sync(0xffffffffu, old, 0);
+            if (old != n_slots - 1) return;
+            __threadfence();
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                if (s0 + j >= n_slots) break;
+            for (int h = 0; h < 2; ++h) {
+                float4 *src = reinterpret_cast<float4 *>(acc_ptr + 32 * h);
+                const float4 p0 = __ldcg(src), p1 = __ldcg(src + 1);
+                own[h][0] = p0.x; own[h][1] = p0.y; own[h][2] = p0.z; own[h][3] = p0.w;
+                own[h][4] = p1.x; own[h][5] = p1.y; own[h][6] = p1.z; own[h][7] = p1.w;
+                src[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+                src[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        } else {
+            // deterministic: one slot per contributing CTA, summed by the last arriver in CTA order
+            float *mine = partials + (size_t)(c + v) * SK_PARTIAL_FLOATS + lane_off;
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    own[h][0] += p[j][2 * h].x; own[h][1] += p[j][2 * h].y;
-                    own[h][2] += p[j][2 * h].z; own[h][3] += p[j][2 * h].w;
-                    own[h][4] += p[j][2 * h + 1].x; own[h][5] += p[j][2 * h + 1].y;
-                    own[h][6] += p[j][2 * h + 1].z; own[h][7] += p[j][2 * h + 1].w;
+            for (int h = 0; h < 2; ++h) {
+                float4 *dst = reinterpret_cast<float4 *>(mine + 32 * h);
+                dst[0] = make_float4(own[h][0], own[h][1], own[h][2], own[h][3]);
+                dst[1] = make_float4(own[h][4], own[h][5], own[h][6], own[h][7]);
+            }
+            __threadfence();
+            __syncwarp();
+            int old = 0;
+            if (lane == 0) old = atomicAdd(&counters[v * SK_CONSUMER_WARPS + warp], 1);
+            old = __shfl_sync(0xffffffffu, old, 0);
+            if (old != n_slots - 1) return;
+            __threadfence();
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) own[h][i] = 0.f;
+            // four slots' loads in flight at a time (the loop is latency-bound otherwise)
+            const float *src0 = partials + (size_t)(c_lo + v) * SK_PARTIAL_FLOATS + lane_off;
+            for (int s0 = 0; s0 < n_slots; s0 += 4) {
+                float4 p[4][4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int sj = s0 + j < n_slots ? s0 + j : n_slots - 1;
+                    const float4 *src = reinterpret_cast<const float4 *>(src0 + (size_t)sj * SK_PARTIAL_FLOATS);
+                    p[j][0] = __ldcg(src);
+                    p[j][1] = __ldcg(src + 1);
+                    p[j][2] = __ldcg(src + 8);
+                    p[j][3] = __ldcg(src + 9);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (s0 + j >= n_slots) break;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        own[h][0] += p[j][2 * h].x; own[h][1] += p[j][2 * h].y;
+                        own[h][2] += p[j][2 * h].z; own[h][3] += p[j][2 * h].w;
+                        own[h][4] += p[j][2 * h + 1].x; own[h][5] += p[j][2 * h + 1].y;
+                        own[h][6] += p[j][2 * h + 1].z; own[h][7] += p[j][2 * h + 1].w;
+                    }
                 }
             }
         }
@@ -484,8 +521,11 @@ bool gemv_streamk_supported(const GemvArgs &a) {
            (a.N + SK_STRIP - 1) / SK_STRIP <= SK_MAX_STRIPS && device_is_sm100();
 }
 
-size_t gemv_streamk_scratch_bytes(int N) {
+// Scratch without the activation-conversion buffer: fast reduction needs the accumulators of
+// its strips only; the deterministic one also a slot per (CTA, strip) segment.
+size_t gemv_streamk_scratch_bytes(int N, bool deterministic) {
     const size_t V = (size_t)(N + SK_STRIP - 1) / SK_STRIP;
+    if (!deterministic) return SK_WS_ACCUM + V * SK_PARTIAL_FLOATS * 4;
     int sms = device_sm_count();
     if (sms <= 0) sms = 148;
     return SK_WS_PARTIALS + (V + (size_t)sms * SK_CTAS_PER_SM) * SK_PARTIAL_FLOATS * 4;
@@ -494,7 +534,7 @@ size_t gemv_streamk_scratch_bytes(int N) {
 size_t gemv_streamk_workspace_bytes(int B, int K, int N) {
     // counters + partial slots + room for B rows of activations converted to fp16
     const size_t rows = B < 1 ? 1 : (B > 64 ? 64 : B);
-    return gemv_streamk_scratch_bytes(N) + rows * (size_t)(K > 0 ? K : 0) * 2;
+    return gemv_streamk_scratch_bytes(N, true) + rows * (size_t)(K > 0 ? K : 0) * 2;
 }
 
 template <int EPI, bool XH>
@@ -530,10 +570,11 @@ static int launch_one(const GemvArgs &a, const uint16_t *x, const uint16_t *resi
     uint8_t *ws = reinterpret_cast<uint8_t *>(a.workspace);
     int *err_flag = reinterpret_cast<int *>(ws);
     int *counters = reinterpret_cast<int *>(ws + SK_WS_HEADER);
+    float *accum = reinterpret_cast<float *>(ws + SK_WS_ACCUM);
     float *partials = reinterpret_cast<float *>(ws + SK_WS_PARTIALS);
     return check_cuda(launch_pdl(gemv_streamk_kernel<EPI, XH>, dim3(ctas), dim3(SK_THREADS), SK_SMEM_BYTES, a.stream, tmW,
-                                 tmX, tmS, tmZ, residual, y, B, a.N, G, V, a.out_format == ACT_F16 ? 1 : 0, partials,
-                                 counters, err_flag),
+                                 tmX, tmS, tmZ, residual, y, B, a.N, G, V, a.out_format == ACT_F16 ? 1 : 0,
+                                 a.deterministic ? 0 : 1, accum, partials, counters, err_flag),
                       "stream-K gemv launch");
 }
 
@@ -564,14 +605,15 @@ static int launch_passes(const GemvArgs &a, const uint16_t *x_all) {
 
 int launch_gemv_streamk(const GemvArgs &a) {
     const bool convert = a.x_format == ACT_BF16 && !a.native_bf16;
-    const size_t need = convert ? gemv_streamk_workspace_bytes(a.B, a.K, a.N) : gemv_streamk_scratch_bytes(a.N);
+    const size_t xh_off = gemv_streamk_scratch_bytes(a.N, true);
+    const size_t need = convert ? xh_off + (size_t)a.B * a.K * 2 : gemv_streamk_scratch_bytes(a.N, a.deterministic);
     if (!a.workspace || a.workspace_bytes < need)
         return set_error(AWQ_ERR_WORKSPACE, "gemv: workspace of %zu bytes needed, %zu given", need, a.workspace_bytes);
     if (a.x_format == ACT_F16) return launch_passes<true>(a, a.x);
     if (a.native_bf16) return launch_passes<false>(a, a.x);
     // bf16 activations: convert once to fp16 in the workspace, then take the fp16 path
     uint8_t *ws = reinterpret_cast<uint8_t *>(a.workspace);
-    uint16_t *xh = reinterpret_cast<uint16_t *>(ws + gemv_streamk_scratch_bytes(a.N));
+    uint16_t *xh = reinterpret_cast<uint16_t *>(ws + xh_off);
     const size_t n = (size_t)a.B * a.K;
     int rc = check_cuda(launch_pdl(cvt_bf16_to_f16_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, a.stream, a.x,
                                    xh, n, reinterpret_cast<int *>(ws)),

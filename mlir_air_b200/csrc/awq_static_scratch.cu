@@ -5,7 +5,7 @@
 // cudaMalloc once serving has started, or C code that links the .so without any allocator of
 // its own.  For them the scratch of the stream-K decode kernel (strip counters and split-K
 // partials) lives in a fixed array inside the library image instead of a caller-owned
-// workspace.  Every GPU that loads the library holds that array (about 7 MB) until the
+// workspace.  Every GPU that loads the library holds that array (about 1 MB) until the
 // process exits.
 #include <mutex>
 
@@ -13,10 +13,10 @@
 
 namespace awq {
 
-// Room for 64 strips of 512 columns (N <= 32768) on a GPU with up to 192 SMs (two CTAs each):
-// 16 KB of header + counters, then (64 + 2 * 192) partial slots of 16 KB.
+// Room for 64 strips of 512 columns (N <= 32768): 16 KB of header + counters, then one 16 KB
+// f32 accumulator per strip.
 constexpr int STATIC_MAX_N = 32768;
-constexpr size_t STATIC_SCRATCH_BYTES = 16384 + (size_t)(64 + 2 * 192) * 16384;
+constexpr size_t STATIC_SCRATCH_BYTES = 16384 + (size_t)64 * 16384;
 
 static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
 
@@ -67,12 +67,13 @@ extern "C" int awq_b200_gemv_bf16_static(const uint16_t *x, const int32_t *qweig
         return set_error(AWQ_ERR_UNSUPPORTED,
                          "gemv_static: needs group size 128, K %% 128 == 0, N %% 32 == 0, 16-byte aligned pointers "
                          "and an sm_100 device (K=%d N=%d group=%d)", K, N, group_size);
-    if (gemv_streamk_scratch_bytes(N) > STATIC_SCRATCH_BYTES)
-        return set_error(AWQ_ERR_UNSUPPORTED, "gemv_static: this GPU needs %zu bytes of scratch for N = %d, the built-in "
-                         "array has %zu", gemv_streamk_scratch_bytes(N), N, STATIC_SCRATCH_BYTES);
-    // The array keeps whatever the previous call left.  The error flag and the strip counters
-    // must read zero when the kernel starts, so clear them on the caller's stream first.
-    rc = check_cuda(cudaMemsetAsync(scratch, 0, gemv_streamk_workspace_clear_bytes(), as_stream(stream)),
+    if (gemv_streamk_scratch_bytes(N, false) > STATIC_SCRATCH_BYTES)
+        return set_error(AWQ_ERR_UNSUPPORTED, "gemv_static: %zu bytes of scratch are needed for N = %d, the built-in "
+                         "array has %zu", gemv_streamk_scratch_bytes(N, false), N, STATIC_SCRATCH_BYTES);
+    // The array keeps whatever the previous call left.  The error flag, the strip counters and the
+    // strips' accumulators must read zero when the kernel starts, so clear them on the caller's
+    // stream first.
+    rc = check_cuda(cudaMemsetAsync(scratch, 0, gemv_streamk_workspace_clear_bytes(N), as_stream(stream)),
                     "gemv_static: clearing counters");
     if (rc) return rc;
     return launch_gemv_streamk(a);

@@ -42,21 +42,28 @@ def tp_shard_bounds(intermediate: int, tp: int, group_size: int = 128) -> List[T
     return bounds
 
 
-def shard_gateup(w: AwqWeight, i0: int, i1: int) -> AwqWeight:
-    """Columns [2 i0, 2 i1) of a gate/up-interleaved [K, 2I] weight (a column-parallel shard)."""
+def slice_gateup(qweight, qzeros, scales, i0: int, i1: int):
+    """Columns [2 i0, 2 i1) of gate/up-interleaved [K, 2I] tensors (a column-parallel shard).
+    Works on numpy arrays and on torch tensors."""
     if i0 % 4 or i1 % 4:
         raise AwqBackendError("gate/up shard bounds must be multiples of 4")
-    return AwqWeight(w.qweight[:, 2 * i0 // 8:2 * i1 // 8].contiguous(), w.qzeros[:, 2 * i0 // 8:2 * i1 // 8].contiguous(),
-                     w.scales[:, 2 * i0:2 * i1].contiguous(), w.group_size)
+    return qweight[:, 2 * i0 // 8:2 * i1 // 8], qzeros[:, 2 * i0 // 8:2 * i1 // 8], scales[:, 2 * i0:2 * i1]
+
+
+def slice_down(qweight, qzeros, scales, i0: int, i1: int, group_size: int = 128):
+    """Rows [i0, i1) of [I, H] tensors (a row-parallel shard); bounds on group boundaries."""
+    if i0 % group_size or i1 % group_size:
+        raise AwqBackendError("down shard bounds must be multiples of the group size")
+    return qweight[i0:i1], qzeros[i0 // group_size:i1 // group_size], scales[i0 // group_size:i1 // group_size]
+
+
+def shard_gateup(w: AwqWeight, i0: int, i1: int) -> AwqWeight:
+    return AwqWeight(*(t.contiguous() for t in slice_gateup(w.qweight, w.qzeros, w.scales, i0, i1)), w.group_size)
 
 
 def shard_down(w: AwqWeight, i0: int, i1: int) -> AwqWeight:
-    """Rows [i0, i1) of a [I, H] weight (a row-parallel shard); bounds on group boundaries."""
-    gs = w.group_size
-    if i0 % gs or i1 % gs:
-        raise AwqBackendError("down shard bounds must be multiples of the group size")
-    return AwqWeight(w.qweight[i0:i1].contiguous(), w.qzeros[i0 // gs:i1 // gs].contiguous(),
-                     w.scales[i0 // gs:i1 // gs].contiguous(), gs)
+    return AwqWeight(*(t.contiguous() for t in slice_down(w.qweight, w.qzeros, w.scales, i0, i1, w.group_size)),
+                     w.group_size)
 
 
 @dataclass

@@ -105,6 +105,11 @@ def set_decode_kernel(mode: str):
     _lib.call("awq_b200_set_decode_kernel", {"auto": 0, "generic": 1, "streamk": 2, "streamk_bf16": 3}[mode])
 
 
+def set_deterministic(on: bool):
+    """Sum split-K partials in a fixed order (bit-reproducible, slower) instead of f32 atomics."""
+    _lib.call("awq_b200_set_deterministic", 1 if on else 0)
+
+
 def set_gemm_kernel(mode: str):
     _lib.call("awq_b200_set_gemm_kernel", {"auto": 0, "generic": 1, "tc": 2}[mode])
 
