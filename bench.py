@@ -279,7 +279,9 @@ def run_ours(a):
     roofline = {"bound": "hbm", "kernel": "gemv_streamk_kernel<EPI_SWIGLU> (gate/up GEMV + SwiGLU)",
                 "achieved": achieved, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
                 "frac_of_8TBs": achieved / 8000.0, "us_per_launch": gu_us, "bytes_per_launch": gu_bytes / passes,
-                "traffic": None}
+                # dram__bytes_read.sum + dram__bytes_write.sum of one launch at this exact shape
+                # (profiles/gemv_streamk_70b_ffn_layer.md); other shapes were not captured
+                "traffic": 249810432 if (a.hidden, il, B) == (8192, 28672, 8) else None}
     stack_bytes = stack.weight_bytes + a.layers * 4 * B * a.hidden * 2
     stack_gbs = stack_bytes / (ms_step * 1e-3) / 1e9
 
