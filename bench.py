@@ -171,6 +171,11 @@ class ClockSampler:
 # --------------------------------------------------------------------------------------
 # this library
 # --------------------------------------------------------------------------------------
+def _dbg(msg):
+    if os.environ.get("AWQ_BENCH_DEBUG"):
+        print(f"[bench rank {os.environ.get('RANK', '0')}] {msg}", file=sys.stderr, flush=True)
+
+
 def run_ours(a):
     import numpy as np
     import torch
@@ -192,6 +197,7 @@ def run_ours(a):
     assert world == a.gpus or world == 1, f"--gpus {a.gpus} but WORLD_SIZE={world}"
     tp = world
 
+    _dbg("process group ready")
     bounds = ffn.tp_shard_bounds(a.intermediate, tp)[rank]
     layers = [ffn.random_layer(a.hidden, a.intermediate, seed=1000 + l, bounds=bounds) for l in range(a.layers)]
     stack = ffn.DecodeFFNStack(layers, a.hidden, max_batch=max(64, a.batch), group=group)
@@ -213,12 +219,19 @@ def run_ours(a):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    _dbg("weights ready")
+
     def time_steps(batch, steps, warmup):
+        stack._run(batch)
+        torch.cuda.synchronize()
+        _dbg("eager run done")
         stack.capture(batch)
+        _dbg("graph captured")
         stack.load_input(x_dev[:batch] if batch <= B else x_dev.repeat((batch + B - 1) // B, 1)[:batch])
         for _ in range(max(3, warmup)):
             stack.replay(batch)
         sync_all()
+        _dbg("warm-up replays done")
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(steps):
@@ -292,10 +305,19 @@ def run_ours(a):
             ms = time_steps(b, max(3, a.steps // 2), 3)
             batches[str(b)] = {"ms_per_step": ms, "tokens_per_s": b / (ms * 1e-3)}
 
-    if rank != 0:
+    def finish():
+        """Leave without tearing the communicator down: destroying a process group while captured
+        graphs still hold its collectives can block, and there is nothing left to clean up."""
         if world > 1:
+            torch.cuda.synchronize()
             dist.barrier()
-            dist.destroy_process_group()
+            torch.cuda.synchronize()
+            sys.stdout.flush()
+            sys.stderr.flush()
+            os._exit(0)
+
+    if rank != 0:
+        finish()
         return
 
     line = {
@@ -326,9 +348,7 @@ def run_ours(a):
                                 "sample": f"numpy golden on {s['cols']}/{a.intermediate} of one layer's columns, mean of "
                                           f"{reps} runs, scaled to {a.layers} layers"}
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    finish()
 
 
 def main():
