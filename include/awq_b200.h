@@ -196,6 +196,10 @@ int awq_b200_gemm_bf16(const uint16_t *A, const int32_t *qweight, const int32_t 
                        const uint16_t *scales, uint16_t *C, int M, int K, int N, int group_size,
                        awq_stream_t stream);
 
+/* Synchronise `stream` and report whether the tensor-core GEMM gave up on a bounded device-side
+ * wait since the last check (AWQ_ERR_DEVICE_TIMEOUT); the counterpart of xrt.py:204-218. */
+int awq_b200_gemm_check(awq_stream_t stream);
+
 /* Choose the prefill kernel: 0 = automatic, 1 = generic CUDA-core kernel,
  * 2 = tcgen05 tensor-core kernel (AWQ_ERR_UNSUPPORTED where it cannot run). */
 int awq_b200_set_gemm_kernel(int mode);

@@ -220,3 +220,5 @@ extern "C" int awq_b200_gemm_bf16(const uint16_t *A, const int32_t *qweight, con
     if (mode != 1 && tc_ok) return launch_gemm_tc(A, qweight, qzeros, scales, C, M, K, N, group_size, as_stream(stream));
     return launch_gemm_generic(A, qweight, qzeros, scales, C, M, K, N, group_size, as_stream(stream));
 }
+
+extern "C" int awq_b200_gemm_check(awq_stream_t stream) { return gemm_tc_check(as_stream(stream)); }

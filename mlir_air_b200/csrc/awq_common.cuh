@@ -126,4 +126,6 @@ int launch_gemm_tc(const uint16_t *A, const int32_t *qweight, const int32_t *qze
                    const uint16_t *scales, uint16_t *C, int M, int K, int N, int group_size,
                    cudaStream_t stream);
 
+int gemm_tc_check(cudaStream_t stream);
+
 }  // namespace awq

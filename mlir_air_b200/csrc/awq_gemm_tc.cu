@@ -1,10 +1,386 @@
-// Prefill GEMM on tcgen05 tensor cores (placeholder until the kernel lands).
+// Prefill GEMM  C[M, N] = A[M, K] @ W  for AWQ int4 weights on the 5th-generation tensor cores.
+//
+// Compute-bound (2 M K N flops against 0.52 B per weight), so the weights are dequantised once
+// per CTA tile into shared memory as bf16 -- bit-exactly bf16_rne((q - z) s), the same value the
+// dequant kernel writes -- and fed to tcgen05.mma with the accumulator in tensor memory.
+//
+//   tile        128 (M) x 256 (N) per CTA, k-block 64, persistent CTAs, tiles ordered so that
+//               consecutive CTAs share a weight column block (A stays in L2)
+//   warp 0      producer: TMA loads of the A tile (128 x 64 bf16, 128B swizzle), the packed
+//               words (64 k rows x 32 words), scales and zeros of the k-block
+//   warps 4-11  dequant: warp w owns 32 columns, lane p the k rows 2p, 2p+1; nibbles -> bf16 pairs
+//               (128 + q) by LOP3, exact (v - (128 + z)) * s in bf16x2, 4-byte stores into the
+//               K-major 128B-swizzled B tile (bank-conflict free)
+//   warp 1      MMA issuer (one thread): 4 x tcgen05.mma.kind::f16 (M 128, N 256, K 16) per
+//               k-block into one of two 256-column TMEM accumulators; tcgen05.commit releases the
+//               stage and, after the last k-block, hands the accumulator to the epilogue
+//   warps 12-15 epilogue: tcgen05.ld (each warp its 32 TMEM lanes), f32 -> bf16, global stores;
+//               overlaps the next tile's main loop through the second accumulator
+//
+// Every mbarrier wait is bounded; on expiry the kernel records an error and all roles drain, so
+// the tensor memory is always released.
+#include <cudaTypedefs.h>
+#include <cuda_bf16.h>
+
+#include <mutex>
+
 #include "awq_common.cuh"
+#include "awq_ptx.cuh"
 
 namespace awq {
-bool gemm_tc_supported(int, int, int, int) { return false; }
-int launch_gemm_tc(const uint16_t *, const int32_t *, const int32_t *, const uint16_t *, uint16_t *, int, int, int,
-                   int, cudaStream_t) {
-    return set_error(AWQ_ERR_UNSUPPORTED, "tensor-core gemm not built");
+
+int encode_tensor_map_2d(CUtensorMap *map, int dtype, const void *base, uint64_t dim0, uint64_t dim1,
+                         uint64_t stride1_bytes, uint32_t box0, uint32_t box1, int swizzle);
+
+constexpr int TC_BM = 128, TC_BN = 256, TC_BK = 64, TC_GROUP = 128;
+constexpr int TC_STAGES = 3;
+constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;        // 16 KB
+constexpr int TC_B_BYTES = TC_BN * TC_BK * 2;        // 32 KB
+constexpr int TC_W_BYTES = TC_BK * (TC_BN / 8) * 4;  // 8 KB of packed words
+constexpr int TC_S_BYTES = TC_BN * 2;
+constexpr int TC_Z_BYTES = TC_BN / 8 * 4;
+constexpr int TC_OFF_B = TC_A_BYTES;
+constexpr int TC_OFF_W = TC_OFF_B + TC_B_BYTES;
+constexpr int TC_OFF_S = TC_OFF_W + TC_W_BYTES;
+constexpr int TC_OFF_Z = TC_OFF_S + TC_S_BYTES;
+constexpr int TC_STAGE_BYTES = 57 * 1024;
+constexpr int TC_TX_BYTES = TC_A_BYTES + TC_W_BYTES + TC_S_BYTES + TC_Z_BYTES;
+constexpr int TC_TABLE_BYTES = 8 * 32 * 2 * 4;  // per dequant warp: 32 x (zero pair, scale pair)
+constexpr int TC_NUM_BARS = 3 * TC_STAGES + 4;
+constexpr int TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + TC_TABLE_BYTES + TC_NUM_BARS * 8 + 16 + 1024;
+constexpr int TC_THREADS = 512;
+constexpr int TC_DEQUANT_WARP0 = 4, TC_EPI_WARP0 = 12;
+constexpr uint32_t TC_TMEM_COLS = 512;
+static_assert(TC_OFF_Z + TC_Z_BYTES <= TC_STAGE_BYTES, "stage too small");
+static_assert(TC_SMEM_BYTES <= 227 * 1024, "shared memory budget");
+
+__device__ int g_gemm_error;  // 0 = ok; set when a bounded wait gave up
+
+// ---- tcgen05 wrappers -----------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
 }
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// D[tmem] (+)= A[smem] * B[smem], bf16 inputs, f32 accumulate
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// The mbarrier gets one arrival when every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major tile of 128-byte rows, 128B swizzle, 8-row atoms 1024 B apart.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);  // start address
+    d |= (uint64_t)1 << 16;                        // leading byte offset (unused with swizzle, K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset between 8-row atoms
+    d |= (uint64_t)1 << 46;                        // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                        // 128-byte swizzle
+    return d;
+}
+// Instruction descriptor: f32 accumulate, bf16 x bf16, both operands K-major, M 128, N 256.
+constexpr uint32_t TC_IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_BN >> 3) << 17) |
+                              ((uint32_t)(TC_BM >> 4) << 24);
+
+__device__ __forceinline__ uint32_t bf16x2_sub(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
+               const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmZ,
+               uint16_t *__restrict__ C, int M, int N, int K) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t table_base = smem_base + TC_STAGES * TC_STAGE_BYTES;
+    const uint32_t bar_base = table_base + TC_TABLE_BYTES;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_gen + TC_STAGES * TC_STAGE_BYTES + TC_TABLE_BYTES +
+                                                       TC_NUM_BARS * 8);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };                       // TMA landed
+    auto ready_bar = [&](int s) { return bar_base + 8u * (TC_STAGES + s); };        // B tile dequantised
+    auto empty_bar = [&](int s) { return bar_base + 8u * (2 * TC_STAGES + s); };    // MMA done with the stage
+    auto acc_full = [&](int b) { return bar_base + 8u * (3 * TC_STAGES + b); };     // accumulator complete
+    auto acc_empty = [&](int b) { return bar_base + 8u * (3 * TC_STAGES + 2 + b); };  // accumulator drained
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_tiles = (M + TC_BM - 1) / TC_BM, n_tiles = (N + TC_BN - 1) / TC_BN;
+    const int n_tiles_total = m_tiles * n_tiles;
+    const int k_blocks = K / TC_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(ready_bar(s), 8);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full(b), 1);
+            mbar_init(acc_empty(b), 4);
+        }
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), TC_TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------ producer ------------------------------
+        if (lane == 0) {
+            tma_prefetch_desc(&tmA);
+            tma_prefetch_desc(&tmW);
+            tma_prefetch_desc(&tmS);
+            tma_prefetch_desc(&tmZ);
+            int it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < n_tiles_total && ok; t += gridDim.x) {
+                const int m0 = (t % m_tiles) * TC_BM, n0 = (t / m_tiles) * TC_BN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % TC_STAGES, round = it / TC_STAGES;
+                    if (round > 0 && !mbar_wait_bounded(empty_bar(s), (round - 1) & 1)) {
+                        atomicExch(&g_gemm_error, 1);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t st = smem_base + s * TC_STAGE_BYTES;
+                    const int g = (kb * TC_BK) / TC_GROUP;
+                    mbar_expect_tx(full_bar(s), TC_TX_BYTES);
+                    tma_load_2d(st, &tmA, kb * TC_BK, m0, full_bar(s));
+                    tma_load_2d(st + TC_OFF_W, &tmW, n0 / 8, kb * TC_BK, full_bar(s));
+                    tma_load_2d(st + TC_OFF_S, &tmS, n0, g, full_bar(s));
+                    tma_load_2d(st + TC_OFF_Z, &tmZ, n0 / 8, g, full_bar(s));
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            int it = 0, tile_it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < n_tiles_total && ok; t += gridDim.x, ++tile_it) {
+                const int b = tile_it & 1;
+                if (tile_it >= 2 && !mbar_wait_bounded(acc_empty(b), ((tile_it >> 1) - 1) & 1)) {
+                    atomicExch(&g_gemm_error, 2);
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)b * TC_BN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % TC_STAGES, round = it / TC_STAGES;
+                    if (!mbar_wait_bounded(full_bar(s), round & 1) || !mbar_wait_bounded(ready_bar(s), round & 1)) {
+                        atomicExch(&g_gemm_error, 3);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t st = smem_base + s * TC_STAGE_BYTES;
+                    const uint64_t a_desc = umma_desc_sw128(st), b_desc = umma_desc_sw128(st + TC_OFF_B);
+#pragma unroll
+                    for (int k4 = 0; k4 < TC_BK / 16; ++k4)  // 32 bytes of K per MMA inside the swizzled row
+                        umma_bf16(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, TC_IDESC, (kb | k4) ? 1u : 0u);
+                    umma_commit(empty_bar(s));
+                }
+                if (ok) umma_commit(acc_full(b));
+            }
+        }
+    } else if (warp >= TC_DEQUANT_WARP0 && warp < TC_EPI_WARP0) {
+        // ------------------------------ dequant ------------------------------
+        const int w = warp - TC_DEQUANT_WARP0;  // 32-column chunk of the tile
+        const uint32_t tab = table_base + w * 256;  // [32] zero pairs, then [32] scale pairs
+        // first load takes an even row for lanes 0-3 (mod 8) and an odd row for lanes 4-7, so that
+        // the eight lanes of a quarter-warp touch eight different 16-byte bank groups
+        const int r_first = 2 * lane + ((lane >> 2) & 1), r_second = 2 * lane + 1 - ((lane >> 2) & 1);
+        int it = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < n_tiles_total && ok; t += gridDim.x) {
+            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                const int s = it % TC_STAGES, round = it / TC_STAGES;
+                if ((round > 0 && !mbar_wait_bounded(empty_bar(s), (round - 1) & 1)) ||
+                    !mbar_wait_bounded(full_bar(s), round & 1)) {
+                    if (lane == 0) atomicExch(&g_gemm_error, 4);
+                    ok = false;
+                    break;
+                }
+                const uint32_t st = smem_base + s * TC_STAGE_BYTES;
+                // this lane's column of the chunk: 128 + z and s, each duplicated into a bf16 pair
+                {
+                    const int col = 32 * w + lane;
+                    const uint32_t zw = lds32(st + TC_OFF_Z + (col >> 3) * 4);
+                    const uint32_t z = 0x4300u | awq_nibble(zw, col & 7);
+                    const uint32_t sc = lds_u16(st + TC_OFF_S + col * 2);
+                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(tab + lane * 4), "r"(z | (z << 16)) : "memory");
+                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(tab + 128 + lane * 4), "r"(sc | (sc << 16)) : "memory");
+                }
+                __syncwarp();
+                const uint4 wa = lds128(st + TC_OFF_W + r_first * 128 + ((w ^ (r_first & 7)) << 4));
+                const uint4 wb = lds128(st + TC_OFF_W + r_second * 128 + ((w ^ (r_second & 7)) << 4));
+                const bool swapped = (lane >> 2) & 1;  // wa holds the odd row for these lanes
+                const uint32_t we[4] = {swapped ? wb.x : wa.x, swapped ? wb.y : wa.y, swapped ? wb.z : wa.z,
+                                        swapped ? wb.w : wa.w};  // row 2p
+                const uint32_t wo[4] = {swapped ? wa.x : wb.x, swapped ? wa.y : wb.y, swapped ? wa.z : wb.z,
+                                        swapped ? wa.w : wb.w};  // row 2p + 1
+                // B tile: row n (output column), 16-byte chunk (p >> 2) ^ (n & 7), word p & 3
+                const uint32_t b_base = st + TC_OFF_B + (lane & 3) * 4;
+                const int kchunk = lane >> 2;
+#pragma unroll
+                for (int cb = 0; cb < 4; ++cb) {
+                    const uint4 zt0 = lds128(tab + cb * 32), zt1 = lds128(tab + cb * 32 + 16);
+                    const uint4 st0 = lds128(tab + 128 + cb * 32), st1 = lds128(tab + 128 + cb * 32 + 16);
+                    const uint32_t zz[8] = {zt0.x, zt0.y, zt0.z, zt0.w, zt1.x, zt1.y, zt1.z, zt1.w};
+                    const uint32_t ss[8] = {st0.x, st0.y, st0.z, st0.w, st1.x, st1.y, st1.z, st1.w};
+                    const uint32_t lo = __byte_perm(we[cb], wo[cb], 0x5410);  // columns 0, 2, 4, 6
+                    const uint32_t hi = __byte_perm(we[cb], wo[cb], 0x7632);  // columns 1, 3, 5, 7
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+#pragma unroll
+                        for (int par = 0; par < 2; ++par) {
+                            const int c = 2 * e + par;  // column inside the packed word
+                            const uint32_t v = nib2_to_bf16x2_biased((par ? hi : lo) >> (4 * e));
+                            const uint32_t o = bf16x2_mul(bf16x2_sub(v, zz[c]), ss[c]);
+                            const int n = 32 * w + 8 * cb + c;
+                            asm volatile("st.shared.u32 [%0], %1;" ::"r"(b_base + n * 128 + ((kchunk ^ (n & 7)) << 4)),
+                                         "r"(o)
+                                         : "memory");
+                        }
+                    }
+                }
+                fence_async_smem();  // make the generic-proxy stores visible to the tensor core's reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive(ready_bar(s));
+            }
+        }
+    } else if (warp >= TC_EPI_WARP0) {
+        // ------------------------------ epilogue ------------------------------
+        const int q = warp & 3;  // this warp's 32 TMEM lanes
+        int tile_it = 0;
+        for (int t = blockIdx.x; t < n_tiles_total; t += gridDim.x, ++tile_it) {
+            const int b = tile_it & 1;
+            const int m0 = (t % m_tiles) * TC_BM, n0 = (t / m_tiles) * TC_BN;
+            if (!mbar_wait_bounded(acc_full(b), (tile_it >> 1) & 1)) {
+                if (lane == 0) atomicExch(&g_gemm_error, 5);
+                break;
+            }
+            tc_fence_after();
+            const int m = m0 + 32 * q + lane;
+#pragma unroll 1
+            for (int c = 0; c < TC_BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(b * TC_BN + 32 * c), r);
+                tmem_ld_wait();
+                const int n = n0 + 32 * c;
+                if (m < M && n < N) {  // N is a multiple of 32: a 32-column chunk is all inside or all outside
+                    uint32_t o[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) o[i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                    uint4 *dst = reinterpret_cast<uint4 *>(C + (size_t)m * N + n);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty(b));
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TC_TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+bool gemm_tc_supported(int M, int K, int N, int group_size) {
+    return group_size == TC_GROUP && K % TC_GROUP == 0 && N % 32 == 0 && M >= 1 && K > 0 && N > 0 && device_is_sm100();
+}
+
+int launch_gemm_tc(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros, const uint16_t *scales,
+                   uint16_t *C, int M, int K, int N, int group_size, cudaStream_t stream) {
+    (void)group_size;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
+    });
+    if (attr_err != cudaSuccess) return check_cuda(attr_err, "tensor-core gemm: shared memory attribute");
+    const int G = K / TC_GROUP, nb = N / 8;
+    CUtensorMap tmA, tmW, tmS, tmZ;
+    int rc;
+    if ((rc = encode_tensor_map_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, A, K, M, (uint64_t)K * 2, TC_BK, TC_BM,
+                                   CU_TENSOR_MAP_SWIZZLE_128B)))
+        return rc;
+    if ((rc = encode_tensor_map_2d(&tmW, CU_TENSOR_MAP_DATA_TYPE_INT32, qweight, nb, K, (uint64_t)nb * 4, TC_BN / 8, TC_BK,
+                                   CU_TENSOR_MAP_SWIZZLE_128B)))
+        return rc;
+    if ((rc = encode_tensor_map_2d(&tmS, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, scales, N, G, (uint64_t)N * 2, TC_BN, 1,
+                                   CU_TENSOR_MAP_SWIZZLE_NONE)))
+        return rc;
+    if ((rc = encode_tensor_map_2d(&tmZ, CU_TENSOR_MAP_DATA_TYPE_INT32, qzeros, nb, G, (uint64_t)nb * 4, TC_BN / 8, 1,
+                                   CU_TENSOR_MAP_SWIZZLE_NONE)))
+        return rc;
+    const int tiles = ((M + TC_BM - 1) / TC_BM) * ((N + TC_BN - 1) / TC_BN);
+    int ctas = device_sm_count();
+    if (ctas > tiles) ctas = tiles;
+    gemm_tc_kernel<<<ctas, TC_THREADS, TC_SMEM_BYTES, stream>>>(tmA, tmW, tmS, tmZ, C, M, N, K);
+    return check_cuda(cudaGetLastError(), "tensor-core gemm launch");
+}
+
+int gemm_tc_check(cudaStream_t stream) {
+    int flag = 0;
+    int rc = check_cuda(cudaStreamSynchronize(stream), "gemm_check sync");
+    if (rc) return rc;
+    rc = check_cuda(cudaMemcpyFromSymbol(&flag, g_gemm_error, sizeof(int)), "gemm_check read");
+    if (rc) return rc;
+    if (flag != 0) {
+        int zero = 0;
+        cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int));
+        return set_error(AWQ_ERR_DEVICE_TIMEOUT,
+                         "prefill gemm: a device-side wait gave up (role %d: 1 producer, 2/3 MMA issuer, 4 dequant, "
+                         "5 epilogue)", flag);
+    }
+    return AWQ_OK;
+}
+
 }  // namespace awq

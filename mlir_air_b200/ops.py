@@ -265,6 +265,11 @@ def silu_mul(gate, up, out=None):
     return out
 
 
+def gemm_check():
+    """Synchronise and raise if the tensor-core GEMM reported a device-side timeout."""
+    _lib.call("awq_b200_gemm_check", _stream())
+
+
 def repack_B_to_A(A_q, A_s, A_z, group_size=128) -> AwqWeight:
     """mlir-air logical layout (A_q u8 [M, K/2], A_s bf16 [G, M], A_z u8 [G, M]) -> layout A."""
     M, K = A_q.shape[0], A_q.shape[1] * 2

@@ -359,4 +359,39 @@ def test_gemm_vs_oracle(ops, M, K, N):
     for kernel in ("generic", "auto"):
         ops.set_gemm_kernel(kernel)
         c = to_host(ops.gemm(to_dev(A), dev_weight(qw, qz, s)))
+        ops.gemm_check()
         assert O.rel_l2(c, ref) <= REL_L2_TOL, kernel
+
+
+@pytest.mark.parametrize("M,K,N", [(128, 128, 256), (1, 128, 32), (130, 384, 288), (300, 1024, 1056), (512, 2048, 768)])
+def test_gemm_tensor_core_kernel(ops, M, K, N):
+    """The tcgen05 kernel alone: ragged M and N tiles, several tiles per CTA, against both goldens
+    (f32 weights, and the bf16-rounded weights the kernel actually multiplies)."""
+    ops.set_gemm_kernel("tc")
+    qw, qz, s = synth_awq(K, N, 128, seed=3 * M + N)
+    A = randn_bf16((M, K), seed=7)
+    c = to_host(ops.gemm(to_dev(A), dev_weight(qw, qz, s)))
+    ops.gemm_check()
+    ref_f32w = (A.astype(np.float32) @ O.dequant_f32(qw, qz, s, 128)).astype(bfloat16)
+    ref_bf16w = (A.astype(np.float32) @ O.dequant_to_bf16(qw, qz, s, 128).astype(np.float32)).astype(bfloat16)
+    assert O.rel_l2(c, ref_bf16w) <= 3e-3   # same products, f32 summation order only
+    assert O.rel_l2(c, ref_f32w) <= REL_L2_TOL
+
+
+def test_gemm_cfg4_full_size(ops):
+    """BASELINE config 4: [2048, 4096] x [4096, 14336]."""
+    M, K, N = 2048, 4096, 14336
+    qw, qz, s = synth_awq(K, N, 128, seed=0)
+    A = randn_bf16((M, K), seed=1)
+    ops.set_gemm_kernel("tc")
+    c = to_host(ops.gemm(to_dev(A), dev_weight(qw, qz, s)))
+    ops.gemm_check()
+    ref = (A.astype(np.float32) @ O.dequant_f32(qw, qz, s, 128)).astype(bfloat16)
+    assert O.rel_l2(c, ref) <= REL_L2_TOL
+    # identical A rows give identical C rows; a zero A gives exactly zero (size-independent checks)
+    A2 = np.tile(A[:1], (256, 1))
+    c2 = to_host(ops.gemm(to_dev(A2), dev_weight(qw, qz, s)))
+    assert (bits(c2) == bits(c2[:1])).all() and np.array_equal(bits(c2[0]), bits(c[0]))
+    c0 = to_host(ops.gemm(to_dev(np.zeros((128, K), bfloat16)), dev_weight(qw, qz, s)))
+    assert not c0.astype(np.float32).any()
+    ops.gemm_check()
