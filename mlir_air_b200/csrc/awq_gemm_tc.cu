@@ -4,18 +4,23 @@
 // per CTA tile into shared memory as bf16 -- bit-exactly bf16_rne((q - z) s), the same value the
 // dequant kernel writes -- and fed to tcgen05.mma with the accumulator in tensor memory.
 //
-//   tile        128 (M) x 256 (N) per CTA, k-block 64, persistent CTAs, tiles ordered so that
-//               consecutive CTAs share a weight column block (A stays in L2)
+//   tile        MT x 128 (M) x 256 (N) per CTA with MT = 2 (MT = 1 when M <= 128): the two 128-row
+//               accumulators share one dequantised B tile, which halves the dequant work per
+//               flop; k-block 64, persistent CTAs, tiles ordered so that consecutive CTAs share a
+//               weight column block (A stays in L2)
 //   warp 0      producer: TMA loads of the A tile (128 x 64 bf16, 128B swizzle), the packed
 //               words (64 k rows x 32 words), scales and zeros of the k-block
-//   warps 4-11  dequant: warp w owns 32 columns, lane p the k rows 2p, 2p+1; nibbles -> bf16 pairs
-//               (128 + q) by LOP3, exact (v - (128 + z)) * s in bf16x2, 4-byte stores into the
-//               K-major 128B-swizzled B tile (bank-conflict free)
-//   warp 1      MMA issuer (one thread): 4 x tcgen05.mma.kind::f16 (M 128, N 256, K 16) per
-//               k-block into one of two 256-column TMEM accumulators; tcgen05.commit releases the
-//               stage and, after the last k-block, hands the accumulator to the epilogue
+//   warps 4-11  dequant: warp w owns k rows 8w .. 8w+7, lane j packed word j (8 columns); a word
+//               unpacks to four bf16 pairs of adjacent columns (128 + q) by LOP3, exact
+//               (v - (128 + z)) * s in bf16x2, and goes out as ONE 16-byte store: the B tile is
+//               kept N-major ("MN-major", 128B swizzle), which is the order the AWQ word already
+//               has, so nothing is transposed (all shared-memory accesses bank-conflict free)
+//   warp 1      MMA issuer (one thread): 4 x MT tcgen05.mma.kind::f16 (M 128, N 256, K 16) per
+//               k-block into 256-column TMEM accumulators (512 columns: MT = 1 double-buffers them,
+//               MT = 2 uses both for one tile); tcgen05.commit releases the stage and, after the
+//               last k-block, hands the accumulators to the epilogue
 //   warps 12-15 epilogue: tcgen05.ld (each warp its 32 TMEM lanes), f32 -> bf16, global stores;
-//               overlaps the next tile's main loop through the second accumulator
+//               with MT = 1 it overlaps the next tile's main loop
 //
 // Every mbarrier wait is bounded; on expiry the kernel records an error and all roles drain, so
 // the tensor memory is always released.
@@ -34,7 +39,7 @@ int encode_tensor_map_2d(CUtensorMap *map, int dtype, const void *base, uint64_t
 
 constexpr int TC_BM = 128, TC_BN = 256, TC_BK = 64, TC_GROUP = 128;
 constexpr int TC_STAGES = 3;
-constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;        // 16 KB
+constexpr int TC_A_BYTES = 2 * TC_BM * TC_BK * 2;    // 32 KB: room for two 128-row A tiles
 constexpr int TC_B_BYTES = TC_BN * TC_BK * 2;        // 32 KB
 constexpr int TC_W_BYTES = TC_BK * (TC_BN / 8) * 4;  // 8 KB of packed words
 constexpr int TC_S_BYTES = TC_BN * 2;
@@ -43,9 +48,9 @@ constexpr int TC_OFF_B = TC_A_BYTES;
 constexpr int TC_OFF_W = TC_OFF_B + TC_B_BYTES;
 constexpr int TC_OFF_S = TC_OFF_W + TC_W_BYTES;
 constexpr int TC_OFF_Z = TC_OFF_S + TC_S_BYTES;
-constexpr int TC_STAGE_BYTES = 57 * 1024;
-constexpr int TC_TX_BYTES = TC_A_BYTES + TC_W_BYTES + TC_S_BYTES + TC_Z_BYTES;
-constexpr int TC_TABLE_BYTES = 8 * 32 * 2 * 4;  // per dequant warp: 32 x (zero pair, scale pair)
+constexpr int TC_STAGE_BYTES = 73 * 1024;
+constexpr int TC_TABLE_BYTES = 0;
+constexpr int TC_B_NATOM_BYTES = 8 * 1024;  // B tile: 64-column atoms 8 KB apart, 8-row k atoms 1 KB apart
 constexpr int TC_NUM_BARS = 3 * TC_STAGES + 4;
 constexpr int TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + TC_TABLE_BYTES + TC_NUM_BARS * 8 + 16 + 1024;
 constexpr int TC_THREADS = 512;
@@ -106,8 +111,19 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
     d |= (uint64_t)2 << 61;                        // 128-byte swizzle
     return d;
 }
-// Instruction descriptor: f32 accumulate, bf16 x bf16, both operands K-major, M 128, N 256.
-constexpr uint32_t TC_IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_BN >> 3) << 17) |
+// N-major ("MN-major") tile with 128B swizzle: atoms of 64 columns (128 B) x 8 k rows; `lbo`
+// bytes between atoms along N, `sbo` bytes between atoms along K.
+__device__ __forceinline__ uint64_t umma_desc_sw128_nmajor(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((lbo >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// Instruction descriptor: f32 accumulate, bf16 x bf16, A K-major, B N-major, M 128, N 256.
+constexpr uint32_t TC_IDESC = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(TC_BN >> 3) << 17) |
                               ((uint32_t)(TC_BM >> 4) << 24);
 
 __device__ __forceinline__ uint32_t bf16x2_sub(uint32_t a, uint32_t b) {
@@ -121,6 +137,7 @@ __device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
     return r;
 }
 
+template <int MT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
                const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmZ,
@@ -128,8 +145,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t table_base = smem_base + TC_STAGES * TC_STAGE_BYTES;
-    const uint32_t bar_base = table_base + TC_TABLE_BYTES;
+    const uint32_t bar_base = smem_base + TC_STAGES * TC_STAGE_BYTES + TC_TABLE_BYTES;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_gen + TC_STAGES * TC_STAGE_BYTES + TC_TABLE_BYTES +
                                                        TC_NUM_BARS * 8);
     auto full_bar = [&](int s) { return bar_base + 8u * s; };                       // TMA landed
@@ -139,7 +155,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     auto acc_empty = [&](int b) { return bar_base + 8u * (3 * TC_STAGES + 2 + b); };  // accumulator drained
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m_tiles = (M + TC_BM - 1) / TC_BM, n_tiles = (N + TC_BN - 1) / TC_BN;
+    constexpr int NBUF = 2 / MT;  // accumulator buffers
+    constexpr uint32_t TX_BYTES = MT * TC_BM * TC_BK * 2 + TC_W_BYTES + TC_S_BYTES + TC_Z_BYTES;
+    const int m_tiles = (M + MT * TC_BM - 1) / (MT * TC_BM), n_tiles = (N + TC_BN - 1) / TC_BN;
     const int n_tiles_total = m_tiles * n_tiles;
     const int k_blocks = K / TC_BK;
 
@@ -174,7 +192,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             int it = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < n_tiles_total && ok; t += gridDim.x) {
-                const int m0 = (t % m_tiles) * TC_BM, n0 = (t / m_tiles) * TC_BN;
+                const int m0 = (t % m_tiles) * (MT * TC_BM), n0 = (t / m_tiles) * TC_BN;
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % TC_STAGES, round = it / TC_STAGES;
                     if (round > 0 && !mbar_wait_bounded(empty_bar(s), (round - 1) & 1)) {
@@ -184,8 +202,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     }
                     const uint32_t st = smem_base + s * TC_STAGE_BYTES;
                     const int g = (kb * TC_BK) / TC_GROUP;
-                    mbar_expect_tx(full_bar(s), TC_TX_BYTES);
-                    tma_load_2d(st, &tmA, kb * TC_BK, m0, full_bar(s));
+                    mbar_expect_tx(full_bar(s), TX_BYTES);
+                    tma_load_2d(st, &tmA, kb * TC_BK, m0, full_bar(s));  // MT * 128 rows in one box
                     tma_load_2d(st + TC_OFF_W, &tmW, n0 / 8, kb * TC_BK, full_bar(s));
                     tma_load_2d(st + TC_OFF_S, &tmS, n0, g, full_bar(s));
                     tma_load_2d(st + TC_OFF_Z, &tmZ, n0 / 8, g, full_bar(s));
@@ -198,8 +216,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             int it = 0, tile_it = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < n_tiles_total && ok; t += gridDim.x, ++tile_it) {
-                const int b = tile_it & 1;
-                if (tile_it >= 2 && !mbar_wait_bounded(acc_empty(b), ((tile_it >> 1) - 1) & 1)) {
+                const int b = tile_it % NBUF, use = tile_it / NBUF;  // buffer and how often it was used before
+                if (use >= 1 && !mbar_wait_bounded(acc_empty(b), (use - 1) & 1)) {
                     atomicExch(&g_gemm_error, 2);
                     break;
                 }
@@ -214,10 +232,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     }
                     tc_fence_after();
                     const uint32_t st = smem_base + s * TC_STAGE_BYTES;
-                    const uint64_t a_desc = umma_desc_sw128(st), b_desc = umma_desc_sw128(st + TC_OFF_B);
+                    const uint64_t a_desc = umma_desc_sw128(st);
+                    const uint64_t b_desc = umma_desc_sw128_nmajor(st + TC_OFF_B, TC_B_NATOM_BYTES, 1024);
 #pragma unroll
-                    for (int k4 = 0; k4 < TC_BK / 16; ++k4)  // 32 bytes of K per MMA inside the swizzled row
-                        umma_bf16(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, TC_IDESC, (kb | k4) ? 1u : 0u);
+                    for (int k4 = 0; k4 < TC_BK / 16; ++k4)  // A: 32 bytes further in the row; B: two k atoms further
+#pragma unroll
+                        for (int a = 0; a < MT; ++a)  // second 128 rows of A: 16 KB further, next 256 TMEM columns
+                            umma_bf16(d_tmem + a * TC_BN, a_desc + 2 * k4 + a * (16384 >> 4), b_desc + (2048 >> 4) * k4,
+                                      TC_IDESC, (kb | k4) ? 1u : 0u);
                     umma_commit(empty_bar(s));
                 }
                 if (ok) umma_commit(acc_full(b));
@@ -225,11 +247,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
     } else if (warp >= TC_DEQUANT_WARP0 && warp < TC_EPI_WARP0) {
         // ------------------------------ dequant ------------------------------
-        const int w = warp - TC_DEQUANT_WARP0;  // 32-column chunk of the tile
-        const uint32_t tab = table_base + w * 256;  // [32] zero pairs, then [32] scale pairs
-        // first load takes an even row for lanes 0-3 (mod 8) and an odd row for lanes 4-7, so that
-        // the eight lanes of a quarter-warp touch eight different 16-byte bank groups
-        const int r_first = 2 * lane + ((lane >> 2) & 1), r_second = 2 * lane + 1 - ((lane >> 2) & 1);
+        const int w = warp - TC_DEQUANT_WARP0;  // k atom: rows 8w .. 8w+7 of the k-block
+        const int j = lane;                     // packed word: tile columns 8j .. 8j+7
         int it = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < n_tiles_total && ok; t += gridDim.x) {
@@ -242,47 +261,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     break;
                 }
                 const uint32_t st = smem_base + s * TC_STAGE_BYTES;
-                // this lane's column of the chunk: 128 + z and s, each duplicated into a bf16 pair
-                {
-                    const int col = 32 * w + lane;
-                    const uint32_t zw = lds32(st + TC_OFF_Z + (col >> 3) * 4);
-                    const uint32_t z = 0x4300u | awq_nibble(zw, col & 7);
-                    const uint32_t sc = lds_u16(st + TC_OFF_S + col * 2);
-                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(tab + lane * 4), "r"(z | (z << 16)) : "memory");
-                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(tab + 128 + lane * 4), "r"(sc | (sc << 16)) : "memory");
-                }
-                __syncwarp();
-                const uint4 wa = lds128(st + TC_OFF_W + r_first * 128 + ((w ^ (r_first & 7)) << 4));
-                const uint4 wb = lds128(st + TC_OFF_W + r_second * 128 + ((w ^ (r_second & 7)) << 4));
-                const bool swapped = (lane >> 2) & 1;  // wa holds the odd row for these lanes
-                const uint32_t we[4] = {swapped ? wb.x : wa.x, swapped ? wb.y : wa.y, swapped ? wb.z : wa.z,
-                                        swapped ? wb.w : wa.w};  // row 2p
-                const uint32_t wo[4] = {swapped ? wa.x : wb.x, swapped ? wa.y : wb.y, swapped ? wa.z : wb.z,
-                                        swapped ? wa.w : wb.w};  // row 2p + 1
-                // B tile: row n (output column), 16-byte chunk (p >> 2) ^ (n & 7), word p & 3
-                const uint32_t b_base = st + TC_OFF_B + (lane & 3) * 4;
-                const int kchunk = lane >> 2;
+                // this word's eight columns: 128 + z as bf16 pairs, and the scale pairs as stored
+                const uint32_t zw = lds32(st + TC_OFF_Z + j * 4);
+                const uint4 sv = lds128(st + TC_OFF_S + j * 16);
+                const uint32_t ss[4] = {sv.x, sv.y, sv.z, sv.w};
+                uint32_t zz[4];
 #pragma unroll
-                for (int cb = 0; cb < 4; ++cb) {
-                    const uint4 zt0 = lds128(tab + cb * 32), zt1 = lds128(tab + cb * 32 + 16);
-                    const uint4 st0 = lds128(tab + 128 + cb * 32), st1 = lds128(tab + 128 + cb * 32 + 16);
-                    const uint32_t zz[8] = {zt0.x, zt0.y, zt0.z, zt0.w, zt1.x, zt1.y, zt1.z, zt1.w};
-                    const uint32_t ss[8] = {st0.x, st0.y, st0.z, st0.w, st1.x, st1.y, st1.z, st1.w};
-                    const uint32_t lo = __byte_perm(we[cb], wo[cb], 0x5410);  // columns 0, 2, 4, 6
-                    const uint32_t hi = __byte_perm(we[cb], wo[cb], 0x7632);  // columns 1, 3, 5, 7
+                for (int e = 0; e < 4; ++e) zz[e] = nib2_to_bf16x2_biased(zw >> (4 * e));
+                const uint32_t w_src = st + TC_OFF_W + (8 * w) * 128 + (j & 3) * 4;
+                const uint32_t b_dst = st + TC_OFF_B + (j >> 3) * TC_B_NATOM_BYTES + w * 1024;
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
+                for (int r = 0; r < 8; ++r) {  // row k = 8w + r: its swizzle key is r
+                    const uint32_t word = lds32(w_src + r * 128 + (((j >> 2) ^ r) << 4));
+                    uint32_t o[4];
 #pragma unroll
-                        for (int par = 0; par < 2; ++par) {
-                            const int c = 2 * e + par;  // column inside the packed word
-                            const uint32_t v = nib2_to_bf16x2_biased((par ? hi : lo) >> (4 * e));
-                            const uint32_t o = bf16x2_mul(bf16x2_sub(v, zz[c]), ss[c]);
-                            const int n = 32 * w + 8 * cb + c;
-                            asm volatile("st.shared.u32 [%0], %1;" ::"r"(b_base + n * 128 + ((kchunk ^ (n & 7)) << 4)),
-                                         "r"(o)
-                                         : "memory");
-                        }
-                    }
+                    for (int e = 0; e < 4; ++e)  // nibbles e and e + 4 are columns 2e and 2e + 1
+                        o[e] = bf16x2_mul(bf16x2_sub(nib2_to_bf16x2_biased(word >> (4 * e)), zz[e]), ss[e]);
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(b_dst + r * 128 + (((j & 7) ^ r) << 4)),
+                                 "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
+                                 : "memory");
                 }
                 fence_async_smem();  // make the generic-proxy stores visible to the tensor core's reads
                 __syncwarp();
@@ -294,18 +291,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int q = warp & 3;  // this warp's 32 TMEM lanes
         int tile_it = 0;
         for (int t = blockIdx.x; t < n_tiles_total; t += gridDim.x, ++tile_it) {
-            const int b = tile_it & 1;
-            const int m0 = (t % m_tiles) * TC_BM, n0 = (t / m_tiles) * TC_BN;
-            if (!mbar_wait_bounded(acc_full(b), (tile_it >> 1) & 1)) {
+            const int b = tile_it % NBUF, use = tile_it / NBUF;
+            const int m0 = (t % m_tiles) * (MT * TC_BM), n0 = (t / m_tiles) * TC_BN;
+            if (!mbar_wait_bounded(acc_full(b), use & 1)) {
                 if (lane == 0) atomicExch(&g_gemm_error, 5);
                 break;
             }
             tc_fence_after();
-            const int m = m0 + 32 * q + lane;
 #pragma unroll 1
-            for (int c = 0; c < TC_BN / 32; ++c) {
+            for (int ac = 0; ac < MT * (TC_BN / 32); ++ac) {
+                const int a = ac / (TC_BN / 32), c = ac % (TC_BN / 32);
+                const int m = m0 + a * TC_BM + 32 * q + lane;
                 uint32_t r[32];
-                tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(b * TC_BN + 32 * c), r);
+                tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)((b + a) * TC_BN + 32 * c), r);
                 tmem_ld_wait();
                 const int n = n0 + 32 * c;
                 if (m < M && n < N) {  // N is a multiple of 32: a 32-column chunk is all inside or all outside
@@ -342,13 +340,16 @@ int launch_gemm_tc(const uint16_t *A, const int32_t *qweight, const int32_t *qze
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
+        attr_err = cudaFuncSetAttribute(gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
+        if (attr_err == cudaSuccess)
+            attr_err = cudaFuncSetAttribute(gemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
     });
     if (attr_err != cudaSuccess) return check_cuda(attr_err, "tensor-core gemm: shared memory attribute");
     const int G = K / TC_GROUP, nb = N / 8;
     CUtensorMap tmA, tmW, tmS, tmZ;
     int rc;
-    if ((rc = encode_tensor_map_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, A, K, M, (uint64_t)K * 2, TC_BK, TC_BM,
+    const int mt = M > TC_BM ? 2 : 1;  // 128-row accumulators per tile
+    if ((rc = encode_tensor_map_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, A, K, M, (uint64_t)K * 2, TC_BK, mt * TC_BM,
                                    CU_TENSOR_MAP_SWIZZLE_128B)))
         return rc;
     if ((rc = encode_tensor_map_2d(&tmW, CU_TENSOR_MAP_DATA_TYPE_INT32, qweight, nb, K, (uint64_t)nb * 4, TC_BN / 8, TC_BK,
@@ -360,10 +361,13 @@ int launch_gemm_tc(const uint16_t *A, const int32_t *qweight, const int32_t *qze
     if ((rc = encode_tensor_map_2d(&tmZ, CU_TENSOR_MAP_DATA_TYPE_INT32, qzeros, nb, G, (uint64_t)nb * 4, TC_BN / 8, 1,
                                    CU_TENSOR_MAP_SWIZZLE_NONE)))
         return rc;
-    const int tiles = ((M + TC_BM - 1) / TC_BM) * ((N + TC_BN - 1) / TC_BN);
+    const int tiles = ((M + mt * TC_BM - 1) / (mt * TC_BM)) * ((N + TC_BN - 1) / TC_BN);
     int ctas = device_sm_count();
     if (ctas > tiles) ctas = tiles;
-    gemm_tc_kernel<<<ctas, TC_THREADS, TC_SMEM_BYTES, stream>>>(tmA, tmW, tmS, tmZ, C, M, N, K);
+    if (mt == 2)
+        gemm_tc_kernel<2><<<ctas, TC_THREADS, TC_SMEM_BYTES, stream>>>(tmA, tmW, tmS, tmZ, C, M, N, K);
+    else
+        gemm_tc_kernel<1><<<ctas, TC_THREADS, TC_SMEM_BYTES, stream>>>(tmA, tmW, tmS, tmZ, C, M, N, K);
     return check_cuda(cudaGetLastError(), "tensor-core gemm launch");
 }
 
