@@ -6,8 +6,10 @@
 //
 //   tile        MT x 128 (M) x 256 (N) per CTA with MT = 2 (MT = 1 when M <= 128): the two 128-row
 //               accumulators share one dequantised B tile, which halves the dequant work per
-//               flop; k-block 64, persistent CTAs, tiles ordered so that consecutive CTAs share a
-//               weight column block (A stays in L2)
+//               flop; k-block 64.  Scheduling: the CTAs are split evenly over the M blocks and each
+//               owns a contiguous range of 64-column atoms of its M block, walked in sub-tiles
+//               of up to 4 atoms (256 columns), so no SM waits for a partial last wave; CTAs
+//               of different M blocks walk the same columns at the same time (weights from L2)
 //   warp 0      producer: TMA loads of the A tile (128 x 64 bf16, 128B swizzle), the packed
 //               words (64 k rows x 32 words), scales and zeros of the k-block
 //   warps 4-11  dequant: warp w owns k rows 8w .. 8w+7, lane j packed word j (8 columns); a word
@@ -122,9 +124,9 @@ __device__ __forceinline__ uint64_t umma_desc_sw128_nmajor(uint32_t smem_addr, u
     d |= (uint64_t)2 << 61;
     return d;
 }
-// Instruction descriptor: f32 accumulate, bf16 x bf16, A K-major, B N-major, M 128, N 256.
-constexpr uint32_t TC_IDESC = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(TC_BN >> 3) << 17) |
-                              ((uint32_t)(TC_BM >> 4) << 24);
+// Instruction descriptor without its N field (bits 17-22 = N / 8, set per sub-tile): f32
+// accumulate, bf16 x bf16, A K-major, B N-major, M 128.
+constexpr uint32_t TC_IDESC_BASE = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(TC_BM >> 4) << 24);
 
 __device__ __forceinline__ uint32_t bf16x2_sub(uint32_t a, uint32_t b) {
     uint32_t r;
@@ -137,11 +139,36 @@ __device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
     return r;
 }
 
+// The same walk over a CTA's sub-tiles for every warp role.  CTA (ml, p) of ML x P: M blocks
+// ml, ml + ML, ...; in each, atoms [p NA / P, (p + 1) NA / P) in steps of up to 4 (full-width
+// sub-tiles first: 13 atoms -> 4, 4, 4, 1 measured faster than 4, 3, 3, 3).
+struct TileWalk {
+    int ML, m_blocks, a0, a1, mb, a;
+    __device__ __forceinline__ TileWalk(int ml_count, int p_count, int m_block_count, int atoms) {
+        ML = ml_count;
+        m_blocks = m_block_count;
+        const int p = blockIdx.x / ML;
+        a0 = (int)((long long)p * atoms / p_count);
+        a1 = (int)((long long)(p + 1) * atoms / p_count);
+        mb = blockIdx.x % ML;
+        a = a0;
+    }
+    __device__ __forceinline__ bool valid() const { return mb < m_blocks && a0 < a1; }
+    __device__ __forceinline__ int atoms() const { return a1 - a < 4 ? a1 - a : 4; }
+    __device__ __forceinline__ void next() {
+        a += atoms();
+        if (a >= a1) {
+            a = a0;
+            mb += ML;
+        }
+    }
+};
+
 template <int MT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
                const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmZ,
-               uint16_t *__restrict__ C, int M, int N, int K) {
+               uint16_t *__restrict__ C, int M, int N, int K, int ML, int P) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -157,8 +184,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int NBUF = 2 / MT;  // accumulator buffers
     constexpr uint32_t TX_BYTES = MT * TC_BM * TC_BK * 2 + TC_W_BYTES + TC_S_BYTES + TC_Z_BYTES;
-    const int m_tiles = (M + MT * TC_BM - 1) / (MT * TC_BM), n_tiles = (N + TC_BN - 1) / TC_BN;
-    const int n_tiles_total = m_tiles * n_tiles;
+    const int m_blocks = (M + MT * TC_BM - 1) / (MT * TC_BM), n_atoms = (N + 63) / 64;
     const int k_blocks = K / TC_BK;
 
     if (threadIdx.x == 0) {
@@ -191,8 +217,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             tma_prefetch_desc(&tmZ);
             int it = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < n_tiles_total && ok; t += gridDim.x) {
-                const int m0 = (t % m_tiles) * (MT * TC_BM), n0 = (t / m_tiles) * TC_BN;
+            for (TileWalk tw(ML, P, m_blocks, n_atoms); tw.valid() && ok; tw.next()) {
+                const int m0 = tw.mb * (MT * TC_BM), n0 = tw.a * 64;
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % TC_STAGES, round = it / TC_STAGES;
                     if (round > 0 && !mbar_wait_bounded(empty_bar(s), (round - 1) & 1)) {
@@ -215,7 +241,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (lane == 0) {
             int it = 0, tile_it = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < n_tiles_total && ok; t += gridDim.x, ++tile_it) {
+            for (TileWalk tw(ML, P, m_blocks, n_atoms); tw.valid() && ok; tw.next(), ++tile_it) {
+                const uint32_t idesc = TC_IDESC_BASE | ((uint32_t)(tw.atoms() * 64 >> 3) << 17);
                 const int b = tile_it % NBUF, use = tile_it / NBUF;  // buffer and how often it was used before
                 if (use >= 1 && !mbar_wait_bounded(acc_empty(b), (use - 1) & 1)) {
                     atomicExch(&g_gemm_error, 2);
@@ -239,7 +266,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
                         for (int a = 0; a < MT; ++a)  // second 128 rows of A: 16 KB further, next 256 TMEM columns
                             umma_bf16(d_tmem + a * TC_BN, a_desc + 2 * k4 + a * (16384 >> 4), b_desc + (2048 >> 4) * k4,
-                                      TC_IDESC, (kb | k4) ? 1u : 0u);
+                                      idesc, (kb | k4) ? 1u : 0u);
                     umma_commit(empty_bar(s));
                 }
                 if (ok) umma_commit(acc_full(b));
@@ -248,10 +275,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     } else if (warp >= TC_DEQUANT_WARP0 && warp < TC_EPI_WARP0) {
         // ------------------------------ dequant ------------------------------
         const int w = warp - TC_DEQUANT_WARP0;  // k atom: rows 8w .. 8w+7 of the k-block
-        const int j = lane;                     // packed word: tile columns 8j .. 8j+7
         int it = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < n_tiles_total && ok; t += gridDim.x) {
+        for (TileWalk tw(ML, P, m_blocks, n_atoms); tw.valid() && ok; tw.next()) {
+            // a sub-tile of 1 / 2 / 3-4 atoms has 8 / 16 / 32 packed words per row: the warp takes
+            // 4 / 2 / 1 rows at a time so that narrow sub-tiles cost proportionally less
+            const int words = tw.atoms() * 8;
+            const int rows_at_once = words <= 8 ? 4 : (words <= 16 ? 2 : 1);
+            const int lanes_per_row = 32 / rows_at_once;
+            const int j = lane % lanes_per_row;     // packed word: tile columns 8j .. 8j+7
+            const int r_sub = lane / lanes_per_row;
+            const bool active = j < words;
             for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                 const int s = it % TC_STAGES, round = it / TC_STAGES;
                 if ((round > 0 && !mbar_wait_bounded(empty_bar(s), (round - 1) & 1)) ||
@@ -261,6 +295,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     break;
                 }
                 const uint32_t st = smem_base + s * TC_STAGE_BYTES;
+                if (active) {
                 // this word's eight columns: 128 + z as bf16 pairs, and the scale pairs as stored
                 const uint32_t zw = lds32(st + TC_OFF_Z + j * 4);
                 const uint4 sv = lds128(st + TC_OFF_S + j * 16);
@@ -271,7 +306,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 const uint32_t w_src = st + TC_OFF_W + (8 * w) * 128 + (j & 3) * 4;
                 const uint32_t b_dst = st + TC_OFF_B + (j >> 3) * TC_B_NATOM_BYTES + w * 1024;
 #pragma unroll
-                for (int r = 0; r < 8; ++r) {  // row k = 8w + r: its swizzle key is r
+                for (int i = 0; i < 8; ++i) {  // row k = 8w + r: its swizzle key is r
+                    if (i * rows_at_once >= 8) break;
+                    const int r = i * rows_at_once + r_sub;
                     const uint32_t word = lds32(w_src + r * 128 + (((j >> 2) ^ r) << 4));
                     uint32_t o[4];
 #pragma unroll
@@ -280,6 +317,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(b_dst + r * 128 + (((j & 7) ^ r) << 4)),
                                  "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
                                  : "memory");
+                }
                 }
                 fence_async_smem();  // make the generic-proxy stores visible to the tensor core's reads
                 __syncwarp();
@@ -290,17 +328,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // ------------------------------ epilogue ------------------------------
         const int q = warp & 3;  // this warp's 32 TMEM lanes
         int tile_it = 0;
-        for (int t = blockIdx.x; t < n_tiles_total; t += gridDim.x, ++tile_it) {
+        for (TileWalk tw(ML, P, m_blocks, n_atoms); tw.valid(); tw.next(), ++tile_it) {
             const int b = tile_it % NBUF, use = tile_it / NBUF;
-            const int m0 = (t % m_tiles) * (MT * TC_BM), n0 = (t / m_tiles) * TC_BN;
+            const int m0 = tw.mb * (MT * TC_BM), n0 = tw.a * 64;
+            const int chunks = tw.atoms() * 2;  // 32-column chunks in this sub-tile
             if (!mbar_wait_bounded(acc_full(b), use & 1)) {
                 if (lane == 0) atomicExch(&g_gemm_error, 5);
                 break;
             }
             tc_fence_after();
 #pragma unroll 1
-            for (int ac = 0; ac < MT * (TC_BN / 32); ++ac) {
-                const int a = ac / (TC_BN / 32), c = ac % (TC_BN / 32);
+            for (int ac = 0; ac < MT * chunks; ++ac) {
+                const int a = ac / chunks, c = ac % chunks;
                 const int m = m0 + a * TC_BM + 32 * q + lane;
                 uint32_t r[32];
                 tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)((b + a) * TC_BN + 32 * c), r);
@@ -361,13 +400,19 @@ int launch_gemm_tc(const uint16_t *A, const int32_t *qweight, const int32_t *qze
     if ((rc = encode_tensor_map_2d(&tmZ, CU_TENSOR_MAP_DATA_TYPE_INT32, qzeros, nb, G, (uint64_t)nb * 4, TC_BN / 8, 1,
                                    CU_TENSOR_MAP_SWIZZLE_NONE)))
         return rc;
-    const int tiles = ((M + mt * TC_BM - 1) / (mt * TC_BM)) * ((N + TC_BN - 1) / TC_BN);
-    int ctas = device_sm_count();
-    if (ctas > tiles) ctas = tiles;
+    // CTAs: ML lanes over the M blocks times P column ranges per M block
+    const int m_blocks = (M + mt * TC_BM - 1) / (mt * TC_BM), n_atoms = (N + 63) / 64;
+    int sms = device_sm_count();
+    if (sms <= 0) sms = 148;
+    const int ML = m_blocks < sms ? m_blocks : sms;
+    int P = sms / ML;
+    if (P > n_atoms) P = n_atoms;
+    if (P < 1) P = 1;
+    const int ctas = ML * P;
     if (mt == 2)
-        gemm_tc_kernel<2><<<ctas, TC_THREADS, TC_SMEM_BYTES, stream>>>(tmA, tmW, tmS, tmZ, C, M, N, K);
+        gemm_tc_kernel<2><<<ctas, TC_THREADS, TC_SMEM_BYTES, stream>>>(tmA, tmW, tmS, tmZ, C, M, N, K, ML, P);
     else
-        gemm_tc_kernel<1><<<ctas, TC_THREADS, TC_SMEM_BYTES, stream>>>(tmA, tmW, tmS, tmZ, C, M, N, K);
+        gemm_tc_kernel<1><<<ctas, TC_THREADS, TC_SMEM_BYTES, stream>>>(tmA, tmW, tmS, tmZ, C, M, N, K, ML, P);
     return check_cuda(cudaGetLastError(), "tensor-core gemm launch");
 }
 
