@@ -39,6 +39,7 @@ def parse():
     ap.add_argument("--hidden", type=int, default=8192)
     ap.add_argument("--intermediate", type=int, default=28672)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM timing (extra key `prefill`)")
     ap.add_argument("--sweep", action="store_true", help="also time batch 1/8/32/64 (extra key `batches`)")
     return ap.parse_args()
 
@@ -298,6 +299,34 @@ def run_ours(a):
     stack_bytes = stack.weight_bytes + a.layers * 4 * B * a.hidden * 2
     stack_gbs = stack_bytes / (ms_step * 1e-3) / 1e9
 
+    # ---- prefill int4 GEMM (BASELINE configs[3]) on this GPU: extra key, not the headline ----
+    prefill = None
+    if not a.no_prefill:
+        Mp, Kp, Np = 2048, 4096, 14336
+        wp = ffn.random_layer(Kp, Np // 2, seed=7, with_gamma=False).gateup  # a [4096, 14336] AWQ weight
+        Ap = torch.randn((Mp, Kp), device="cuda").to(torch.bfloat16)
+        Cp = torch.empty((Mp, Np), dtype=torch.bfloat16, device="cuda")
+        for _ in range(3):
+            ops.gemm(Ap, wp, Cp)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            ops.gemm(Ap, wp, Cp)
+        e1.record()
+        torch.cuda.synchronize()
+        ops.gemm_check()
+        us = e0.elapsed_time(e1) * 100.0
+        tf = 2.0 * Mp * Kp * Np / us / 1e6
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                pk = float(json.load(f)["bf16_tflops"])
+        except Exception:
+            pk = 1590.0
+        prefill = {"workload": "int4 GEMM [2048 x 4096] x AWQ [4096 x 14336]", "us": us, "tflops": tf,
+                   "frac_of_measured_bf16_peak": tf / pk, "frac_of_2250": tf / 2250.0, "kernel": "gemm_tc_kernel (tcgen05)"}
+        del wp, Ap, Cp
+
     batches = None
     if a.sweep:
         batches = {}
@@ -336,6 +365,8 @@ def run_ours(a):
     }
     if batches:
         line["batches"] = batches
+    if prefill:
+        line["prefill"] = prefill
     if a.gpus == 1 and not a.no_cpu_baseline:
         s = cpu_sample_setup(a)
         cpu_sample_run(a, s)
