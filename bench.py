@@ -40,8 +40,14 @@ def parse():
     ap.add_argument("--intermediate", type=int, default=28672)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM timing (extra key `prefill`)")
+    ap.add_argument("--unfused", action="store_true", help="per-layer kernels instead of the one-launch stack kernel")
     ap.add_argument("--sweep", action="store_true", help="also time batch 1/8/32/64 (extra key `batches`)")
     return ap.parse_args()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per layer of the stack kernel at hidden 8192 / intermediate
+# 28672 / batch 8 (ncu capture of a 2-layer launch, halved); None until captured
+FUSED_TRAFFIC_PER_LAYER = None
 
 
 def workload_name(a):
@@ -201,7 +207,7 @@ def run_ours(a):
     _dbg("process group ready")
     bounds = ffn.tp_shard_bounds(a.intermediate, tp)[rank]
     layers = [ffn.random_layer(a.hidden, a.intermediate, seed=1000 + l, bounds=bounds) for l in range(a.layers)]
-    stack = ffn.DecodeFFNStack(layers, a.hidden, max_batch=max(64, a.batch), group=group)
+    stack = ffn.DecodeFFNStack(layers, a.hidden, max_batch=max(64, a.batch), group=group, fused=not a.unfused)
     B = a.batch
     rng = np.random.default_rng(0)
     x_host = rng.standard_normal((B, a.hidden)).astype(bfloat16)
@@ -290,7 +296,7 @@ def run_ours(a):
     gu_us = e0.elapsed_time(e1) * 1e3 / (reps * len(layers) * passes)
     peak, peak_src = measured_peak_gbs()
     achieved = gu_bytes / passes / (gu_us * 1e-6) / 1e9
-    roofline = {"bound": "hbm", "kernel": "gemv_streamk_kernel<EPI_SWIGLU> (gate/up GEMV + SwiGLU)",
+    gateup_kernel = {"bound": "hbm", "kernel": "gemv_streamk_kernel<EPI_SWIGLU> (gate/up GEMV + SwiGLU)",
                 "achieved": achieved, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
                 "frac_of_8TBs": achieved / 8000.0, "us_per_launch": gu_us, "bytes_per_launch": gu_bytes / passes,
                 # dram__bytes_read.sum + dram__bytes_write.sum of one launch at this exact shape
@@ -298,6 +304,16 @@ def run_ours(a):
                 "traffic": 249810432 if (a.hidden, il, B) == (8192, 28672, 8) else None}
     stack_bytes = stack.weight_bytes + a.layers * 4 * B * a.hidden * 2
     stack_gbs = stack_bytes / (ms_step * 1e-3) / 1e9
+    if stack.uses_fused(B):
+        # the timed region is ONE launch of the stack kernel: its roofline is the step's
+        roofline = {"bound": "hbm", "kernel": "ffn_fused_kernel (all layers of the stack in one launch)",
+                    "achieved": stack_gbs, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": stack_gbs / peak,
+                    "frac_of_8TBs": stack_gbs / 8000.0, "us_per_launch": ms_step * 1e3, "bytes_per_launch": stack_bytes,
+                    # dram bytes of a 2-layer launch scaled by the layer count (profiles/ffn_fused_70b_stack.md)
+                    "traffic": FUSED_TRAFFIC_PER_LAYER * a.layers
+                    if FUSED_TRAFFIC_PER_LAYER and (a.hidden, il, B) == (8192, 28672, 8) else None}
+    else:
+        roofline = gateup_kernel
 
     # ---- prefill int4 GEMM (BASELINE configs[3]) on this GPU: extra key, not the headline ----
     prefill = None
@@ -354,12 +370,14 @@ def run_ours(a):
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
         "config": {"workload": workload_name(a), "parallelism": f"tp{tp}", "l2": "inputs_exceed_l2 (weights streamed once per step)",
-                   "launch": "one CUDA graph per step"},
+                   "launch": ("one CUDA graph per step: one launch of the stack kernel" if stack.uses_fused(B)
+                              else "one CUDA graph per step")},
         "clocks": clocks,
         "e2e": {"value": B / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": io_bytes,
                 "d2h_bytes_per_step": io_bytes},
         "gpu_launches": stack.launches_per_step(B) * a.steps,
         "roofline": roofline,
+        "gateup_kernel": gateup_kernel,
         "stack_hbm": {"achieved": stack_gbs, "unit": "GB/s", "frac": stack_gbs / peak, "frac_of_8TBs": stack_gbs / 8000.0,
                       "bytes_per_step_per_gpu": stack_bytes},
     }

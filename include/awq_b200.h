@@ -188,6 +188,46 @@ int awq_b200_ffn_decode_bf16(const uint16_t *x, const uint16_t *gamma, float eps
                              uint16_t *out, int B, int H, int I, int group_size, void *workspace,
                              size_t workspace_bytes, awq_stream_t stream);
 
+/* ---- whole decode FFN stack in one launch ---------------------------------------------------
+ * For l in 0 .. n_layers-1:  h <- bf16(h + down_l(swiglu(gateup_l . RMSNorm(h, gamma_l, eps)))),
+ * h starting as x and ending in out; batch B <= 8.  The single-launch form of the decode
+ * block's FFN (llms/llama32_1b_int4/multi_launch_builder/o_gemv_ffn_int4_fused.py:4-30: RMS,
+ * gate/up + SwiGLU, down + residual in ONE launch, intermediates staying on chip) applied to
+ * the layer loop of llms/llama32_1b_int4/llama32_1b_int4_inference.py:445-455, with the same
+ * rounding points as awq_b200_ffn_decode_bf16 called once per layer.
+ *
+ * The weights are described once by a plan: tensor maps written to `plan` (device memory,
+ * 128-byte aligned, awq_b200_ffn_stack_plan_bytes(n_layers) bytes).  The pointer arguments of
+ * awq_b200_ffn_stack_plan are HOST arrays of n_layers DEVICE pointers (layout A, gate/up
+ * interleaved, gamma bf16 [H]); it copies synchronously, so call it outside stream capture.
+ * The plan stays valid as long as the weights do not move.
+ *
+ * decode: `inter` is 16-bit [B, I] scratch; `workspace` holds at least
+ * awq_b200_ffn_stack_workspace_bytes(n_layers) bytes prepared by awq_b200_workspace_init.
+ * x may alias out.  All CTAs of the launch wait for one another on counters in the workspace,
+ * so the stream must be the only user of that workspace, and the launch takes two CTAs per
+ * SM: run nothing else on the device that could keep them from becoming resident together.
+ * Split-K sums use f32 atomics (run-to-run differences in the last bits, like the default
+ * decode kernel).  Needs group 128, H % 128 == 0, I % 128 == 0; AWQ_ERR_UNSUPPORTED otherwise.
+ * Device-side waits are bounded; awq_b200_workspace_check reports a timeout. */
+/* Tuning of the stack kernel; a negative value leaves a setting as it is.
+ * lookahead_units: 36 KB units per half-CTA that are prefetched into L2 ahead of the
+ *   shared-memory ring (default 2, 0 = off, at most 64; 2 units on 148 SMs are 21 MB of L2).
+ * split_per_1024: the kernel runs one CTA per SM made of two independent halves; the SM's units
+ *   of a phase are cut between them at split / 1024 (default 512 = even). */
+int awq_b200_set_ffn_stack_tuning(int lookahead_units, int split_per_1024);
+size_t awq_b200_ffn_stack_plan_bytes(int n_layers);
+size_t awq_b200_ffn_stack_workspace_bytes(int n_layers);
+int awq_b200_ffn_stack_plan(void *plan, size_t plan_bytes, int n_layers,
+                            const int32_t *const *qw_gateup, const int32_t *const *qz_gateup,
+                            const uint16_t *const *s_gateup, const int32_t *const *qw_down,
+                            const int32_t *const *qz_down, const uint16_t *const *s_down,
+                            const uint16_t *const *gamma, int H, int I, int group_size);
+int awq_b200_ffn_stack_decode_bf16(const void *plan, int n_layers, const uint16_t *x,
+                                   uint16_t *out, uint16_t *inter, float eps, int B, int H, int I,
+                                   int group_size, void *workspace, size_t workspace_bytes,
+                                   awq_stream_t stream);
+
 /* ---- prefill GEMM ----------------------------------------------------------------------
  * C bf16 [M, N] = bf16(A[M, K] @ W), f32 accumulate.  Replaces
  * matmul_int4_bf16_packed_f32 / zero_vectorized_f32_mn / f32_to_bf16_mn

@@ -201,6 +201,38 @@ extern "C" int awq_b200_ffn_decode_bf16(const uint16_t *x, const uint16_t *gamma
                              workspace_bytes, stream);
 }
 
+extern "C" int awq_b200_set_ffn_stack_tuning(int lookahead_units, int split_per_1024) {
+    if (lookahead_units >= 0) ffn_fused_set_lookahead(lookahead_units);
+    if (split_per_1024 >= 0) ffn_fused_set_split(split_per_1024);
+    return AWQ_OK;
+}
+extern "C" size_t awq_b200_ffn_stack_plan_bytes(int n_layers) { return ffn_fused_plan_bytes(n_layers); }
+extern "C" size_t awq_b200_ffn_stack_workspace_bytes(int n_layers) { return ffn_fused_workspace_bytes(n_layers); }
+
+extern "C" int awq_b200_ffn_stack_plan(void *plan, size_t plan_bytes, int n_layers, const int32_t *const *qw_gateup,
+                                       const int32_t *const *qz_gateup, const uint16_t *const *s_gateup,
+                                       const int32_t *const *qw_down, const int32_t *const *qz_down,
+                                       const uint16_t *const *s_down, const uint16_t *const *gamma, int H, int I,
+                                       int group_size) {
+    AWQ_REQUIRE(qw_gateup && qz_gateup && s_gateup && qw_down && qz_down && s_down && gamma, "ffn_stack_plan: null array");
+    return ffn_fused_plan(plan, plan_bytes, n_layers, qw_gateup, qz_gateup, s_gateup, qw_down, qz_down, s_down, gamma, H, I,
+                          group_size);
+}
+
+extern "C" int awq_b200_ffn_stack_decode_bf16(const void *plan, int n_layers, const uint16_t *x, uint16_t *out,
+                                              uint16_t *inter, float eps, int B, int H, int I, int group_size,
+                                              void *workspace, size_t workspace_bytes, awq_stream_t stream) {
+    AWQ_REQUIRE(n_layers >= 1 && B >= 0 && H > 0 && I > 0, "ffn_stack_decode: bad size");
+    if (B == 0) return AWQ_OK;
+    AWQ_REQUIRE(plan && x && out && inter, "ffn_stack_decode: null pointer");
+    AWQ_REQUIRE(aligned16(x) && aligned16(out) && aligned16(inter), "ffn_stack_decode: pointers must be 16-byte aligned");
+    if (!ffn_fused_supported(B, H, I, group_size))
+        return set_error(AWQ_ERR_UNSUPPORTED,
+                         "ffn_stack_decode: needs B <= 8, group 128, H and I multiples of 128 (B=%d H=%d I=%d gs=%d)", B, H, I,
+                         group_size);
+    return launch_ffn_fused(plan, n_layers, x, out, inter, eps, B, H, I, workspace, workspace_bytes, as_stream(stream));
+}
+
 extern "C" int awq_b200_gemm_bf16(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros,
                                   const uint16_t *scales, uint16_t *C, int M, int K, int N, int group_size,
                                   awq_stream_t stream) {

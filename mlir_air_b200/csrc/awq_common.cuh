@@ -128,4 +128,17 @@ int launch_gemm_tc(const uint16_t *A, const int32_t *qweight, const int32_t *qze
 
 int gemm_tc_check(cudaStream_t stream);
 
+// Fused decode FFN stack (awq_ffn_fused.cu)
+size_t ffn_fused_plan_bytes(int n_layers);
+void ffn_fused_set_lookahead(int units);
+void ffn_fused_set_split(int per_1024);
+size_t ffn_fused_workspace_bytes(int n_layers);
+bool ffn_fused_supported(int B, int H, int I, int group_size);
+int ffn_fused_plan(void *plan_dev, size_t plan_bytes, int n_layers, const int32_t *const *qw_gateup,
+                   const int32_t *const *qz_gateup, const uint16_t *const *s_gateup, const int32_t *const *qw_down,
+                   const int32_t *const *qz_down, const uint16_t *const *s_down, const uint16_t *const *gamma, int H, int I,
+                   int group_size);
+int launch_ffn_fused(const void *plan_dev, int n_layers, const uint16_t *x, uint16_t *out, uint16_t *inter, float eps, int B,
+                     int H, int I, void *workspace, size_t workspace_bytes, cudaStream_t stream);
+
 }  // namespace awq

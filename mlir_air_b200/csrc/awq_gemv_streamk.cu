@@ -35,147 +35,14 @@
 
 #include "awq_common.cuh"
 #include "awq_ptx.cuh"
+#include "awq_streamk.cuh"
 
 namespace awq {
-
-constexpr int SK_STRIP = 512;                 // columns per unit
-constexpr int SK_BOX_COLS = 256;              // columns per 128-byte-wide TMA box
-constexpr int SK_GROUP = 128;
-constexpr int SK_CONSUMER_WARPS = SK_STRIP / 64;
-constexpr int SK_THREADS = SK_CONSUMER_WARPS * 32 + 32;
-constexpr int SK_CTAS_PER_SM = 2;
-constexpr int SK_STAGES = 3;
-constexpr int SK_WBOX_BYTES = SK_GROUP * 128;          // 128 k rows x 32 packed words
-constexpr int SK_W_BYTES = (SK_STRIP / SK_BOX_COLS) * SK_WBOX_BYTES;
-constexpr int SK_X_BYTES = 2 * 1024;                   // two boxes of 8 batch rows x 64 k (bf16)
-constexpr int SK_S_BYTES = SK_STRIP * 2;
-constexpr int SK_Z_BYTES = SK_STRIP / 8 * 4;
-constexpr int SK_TX_BYTES = SK_W_BYTES + SK_X_BYTES + SK_S_BYTES + SK_Z_BYTES;
-constexpr int SK_OFF_X = SK_W_BYTES;
-constexpr int SK_OFF_S = SK_OFF_X + SK_X_BYTES;
-constexpr int SK_OFF_Z = SK_OFF_S + SK_S_BYTES;
-constexpr int SK_STAGE_BYTES = 36 * 1024;
-constexpr int SK_BAR_BYTES = 2 * SK_STAGES * 8 + 16;
-constexpr int SK_SMEM_BYTES = SK_STAGES * SK_STAGE_BYTES + SK_BAR_BYTES + 1024;
-constexpr int SK_PARTIAL_FLOATS = 8 * SK_STRIP;        // one slot: [warp][batch 8][64 columns]
-static_assert(SK_TX_BYTES <= SK_STAGE_BYTES, "stage too small");
-static_assert(SK_CTAS_PER_SM * (SK_SMEM_BYTES + 1024) <= 228 * 1024, "shared memory budget");
-
-// Workspace: [0, 256) header (int error flag); a fixed region of sub-strip counters (one per 64
-// columns); the per-strip f32 accumulators of the fast reduction (strip v at a fixed offset, up
-// to SK_MAX_STRIPS); then, for the deterministic reduction only, one partial slot per (CTA,
-// strip) segment.  Counters and accumulators are all zero between launches (the last arriver
-// resets what it used), and their offsets do not depend on the shape, so one workspace serves
-// products of different shapes back to back.
-constexpr size_t SK_WS_HEADER = 256;
-constexpr int SK_MAX_STRIPS = 504;  // N up to 258,048 columns
-constexpr size_t SK_WS_ACCUM = SK_WS_HEADER + (size_t)SK_MAX_STRIPS * SK_CONSUMER_WARPS * 4;  // 16 KB
-constexpr size_t SK_WS_PARTIALS = SK_WS_ACCUM + (size_t)SK_MAX_STRIPS * SK_PARTIAL_FLOATS * 4;
-constexpr int SK_MAX_CTAS = 2048;
-
 
 // Leading bytes of a workspace (error flag, counters, accumulators of the strips a product of N
 // columns uses) that must be zero before a launch.
 size_t gemv_streamk_workspace_clear_bytes(int N) {
     return SK_WS_ACCUM + (size_t)((N + SK_STRIP - 1) / SK_STRIP) * SK_PARTIAL_FLOATS * 4;
-}
-
-__device__ __forceinline__ void red_add_v4(float *addr, float a, float b, float c, float d) {
-    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
-
-// CTA that owns unit x when U units are split over C CTAs as [c U / C, (c + 1) U / C).
-__host__ __device__ __forceinline__ long long sk_owner(long long x, long long C, long long U) {
-    return ((x + 1) * C + U - 1) / U - 1;
-}
-
-__device__ __forceinline__ uint32_t lop3_and_or(uint32_t v, uint32_t mask, uint32_t magic) {
-    uint32_t r;
-    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(v), "r"(mask), "r"(magic));
-    return r;
-}
-
-// R holds one 16-bit half of a packed word for k (low 16 bits) and for k + 1 (high 16 bits):
-// four nibbles each.  Output e is the pair (nibble e at k, nibble e at k + 1) as 16-bit floats.
-//   bf16: 128 + n for every e (three shifts).
-//   fp16: 1024 + n for e = 0, 2 and 1024 + 16 n for e = 1, 3 (one shift); the factor 16 and the
-//         different offset are undone in the per-group fix-up.
-template <bool XH>
-__device__ __forceinline__ void decode4(uint32_t R, uint32_t (&o)[4]) {
-    if (XH) {
-        const uint32_t T = R >> 8;
-        o[0] = lop3_and_or(R, 0x000F000Fu, 0x64006400u);
-        o[1] = lop3_and_or(R, 0x00F000F0u, 0x64006400u);
-        o[2] = lop3_and_or(T, 0x000F000Fu, 0x64006400u);
-        o[3] = lop3_and_or(T, 0x00F000F0u, 0x64006400u);
-    } else {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) o[e] = lop3_and_or(R >> (4 * e), 0x000F000Fu, 0x43004300u);
-    }
-}
-
-template <bool XH>
-__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                          uint32_t b0, uint32_t b1) {
-    if (XH) {
-        asm volatile(
-            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
-            "{%0, %1, %2, %3};"
-            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-    } else {
-        mma_bf16_16816(d, a0, a1, a2, a3, b0, b1);
-    }
-}
-
-// bf16-rounded value -> fp16 bits, clamped to the finite fp16 range.
-__device__ __forceinline__ uint16_t bf16_value_to_f16_bits(float v) {
-    v = fminf(fmaxf(v, -65504.f), 65504.f);
-    return __half_as_ushort(__float2half_rn(v));
-}
-
-// One lane's share of a finished strip after the lane exchange: batch row b, and for each
-// 32-column half h of the warp's 64 columns, 8 consecutive columns starting at n + 32 h.
-template <int EPI>
-__device__ __forceinline__ void sk_epilogue(const float (&own)[2][8], const uint16_t *__restrict__ residual,
-                                            void *__restrict__ y_, int B, int N, int n, int b, int out_f16) {
-    if (b >= B) return;
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const int nh = n + 32 * h;
-        if (nh >= N) continue;
-        const float(&v)[8] = own[h];
-        if (EPI == EPI_SWIGLU) {
-            uint16_t o[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                o[i] = swiglu_bits(v[2 * i], v[2 * i + 1]);
-                if (out_f16) o[i] = bf16_value_to_f16_bits(bf16_bits_to_f32(o[i]));
-            }
-            *reinterpret_cast<uint2 *>(reinterpret_cast<uint16_t *>(y_) + (size_t)b * (N >> 1) + (nh >> 1)) =
-                make_uint2((uint32_t)o[0] | ((uint32_t)o[1] << 16), (uint32_t)o[2] | ((uint32_t)o[3] << 16));
-        } else if (EPI == EPI_F32) {
-            float4 *dst = reinterpret_cast<float4 *>(reinterpret_cast<float *>(y_) + (size_t)b * N + nh);
-            dst[0] = make_float4(v[0], v[1], v[2], v[3]);
-            dst[1] = make_float4(v[4], v[5], v[6], v[7]);
-        } else {
-            float r[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            if (residual) {
-                const uint4 rv = *reinterpret_cast<const uint4 *>(residual + (size_t)b * N + nh);
-                const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    r[2 * i] = bf16x2_lo(rw[i]);
-                    r[2 * i + 1] = bf16x2_hi(rw[i]);
-                }
-            }
-            uint32_t o[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) o[i] = pack_bf16x2(v[2 * i] + r[2 * i], v[2 * i + 1] + r[2 * i + 1]);
-            *reinterpret_cast<uint4 *>(reinterpret_cast<uint16_t *>(y_) + (size_t)b * N + nh) =
-                make_uint4(o[0], o[1], o[2], o[3]);
-        }
-    }
 }
 
 template <int EPI, bool XH>
@@ -268,14 +135,8 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     // ldmatrix.trans hands lane (g8, t4) 16-bit half g8 of chunk A / B for rows 2 t4 and 2 t4 + 1
     // already paired in one register: half g8 = packed word g8 / 2, even (low half) or odd
     // (high half) columns.  MMA row g8 is that lane's chunk-A column, row g8 + 8 its chunk-B column.
-    const int g8 = lane >> 2, t4 = lane & 3, odd = g8 & 1;
-    const int lm = lane >> 3, lr = lane & 7;  // ldmatrix: matrix index, row within the matrix
-    const uint32_t w_chunk = 2 * (warp & 3) + (lm >> 1);
-    const uint32_t w_off = (warp >> 2) * SK_WBOX_BYTES + ((lm & 1) * 8 + lr) * 128 + ((w_chunk ^ lr) << 4);
-    const uint32_t ONES = XH ? 0x3C003C00u : 0x3F803F80u;
-    const int colw = warp * 64 + (g8 >> 1) * 8;  // first strip column of this lane's 8-column blocks (+32 for B)
-    const uint32_t z_off = SK_OFF_Z + (colw >> 3) * 4 + odd * 2;
-    const uint32_t s_off = SK_OFF_S + (colw + odd) * 2;
+    const SkLane lane_geo(warp, lane);
+    const int g8 = lane_geo.g8, t4 = lane_geo.t4, odd = lane_geo.odd, colw = lane_geo.colw;
     bool failed = false;
 
     float res[4][4];
@@ -284,19 +145,8 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     // Finish the strip segment this warp has been accumulating (strip cur_v).
     auto flush = [&]() {
         const int v = cur_v;
-        // lanes g8 and g8 ^ 1 hold the even / odd columns of the same 8-column blocks for batch
-        // rows 2t and 2t+1: swap so that each owns one batch row and 8 consecutive columns.
         float own[2][8];
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const float keep = odd ? res[e][2 * h + 1] : res[e][2 * h];
-                const float send = odd ? res[e][2 * h] : res[e][2 * h + 1];
-                const float recv = __shfl_xor_sync(0xffffffffu, send, 4);
-                own[h][2 * e] = odd ? recv : keep;
-                own[h][2 * e + 1] = odd ? keep : recv;
-            }
+        sk_lane_exchange(res, odd, own);
         const int b = 2 * t4 + odd;
         const int n = v * SK_STRIP + colw;
         const long long c_lo = sk_owner((long long)v * G, C, U);
@@ -399,69 +249,7 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             if (lane == 0) atomicExch(err_flag, 2);
         }
         if (!failed) {
-            const uint32_t st = smem_base + slot * SK_STAGE_BYTES;
-            float acc[4][4];
-            float sx[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-#pragma unroll
-                for (int q = 0; q < 4; ++q) acc[e][q] = 0.f;
-
-#pragma unroll
-            for (int p = 0; p < 4; ++p) {
-                // activations for k-steps 2p and 2p+1: 16-byte chunk q = 4p + matrix index
-                const int q = 4 * p + lm;
-                uint32_t bx[4];
-                ldmatrix_x4(bx, st + SK_OFF_X + (q >> 3) * 1024 + lr * 128 + (((q & 7) ^ lr) << 4));
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    uint32_t R[4];  // chunk A rows 0-7, chunk A rows 8-15, chunk B rows 0-7, chunk B rows 8-15
-                    ldmatrix_x4_trans(R, st + (2 * p + h) * 2048 + w_off);
-                    const uint32_t b0 = bx[2 * h], b1 = bx[2 * h + 1];
-                    mma_16816<XH>(sx, ONES, ONES, ONES, ONES, b0, b1);
-                    uint32_t a_lo[4], a_hi[4], b_lo[4], b_hi[4];
-                    decode4<XH>(R[0], a_lo);
-                    decode4<XH>(R[1], a_hi);
-                    decode4<XH>(R[2], b_lo);
-                    decode4<XH>(R[3], b_hi);
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) mma_16816<XH>(acc[e], a_lo[e], b_lo[e], a_hi[e], b_hi[e], b0, b1);
-                }
-            }
-
-            // group fix-up: res += s * (acc - c * sum_x); the zero point (and, for fp16, the decode
-            // offset and the factor 16 of odd nibbles) live in c and s
-            const uint32_t zA = lds_u16(st + z_off), zB = lds_u16(st + z_off + 16);
-            uint32_t sA[4], sB[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                sA[e] = lds_u16(st + s_off + 4 * e);
-                sB[e] = lds_u16(st + s_off + 64 + 4 * e);
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(empty_bar(slot));  // all of this warp's reads of the slot are done
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                // 128 + z as f32: bits 0x43000000 | z << 16
-                float cA = __uint_as_float(((zA << (16 - 4 * e)) & 0x000F0000u) | 0x43000000u);
-                float cB = __uint_as_float(((zB << (16 - 4 * e)) & 0x000F0000u) | 0x43000000u);
-                float fA = __uint_as_float(sA[e] << 16), fB = __uint_as_float(sB[e] << 16);
-                if (XH) {
-                    if (e & 1) {
-                        cA = fmaf(cA, 16.f, -1024.f);  // 1024 + 16 z
-                        cB = fmaf(cB, 16.f, -1024.f);
-                        fA *= 0.0625f;
-                        fB *= 0.0625f;
-                    } else {
-                        cA += 896.f;  // 1024 + z
-                        cB += 896.f;
-                    }
-                }
-                res[e][0] = fmaf(fA, fmaf(-cA, sx[0], acc[e][0]), res[e][0]);
-                res[e][1] = fmaf(fA, fmaf(-cA, sx[1], acc[e][1]), res[e][1]);
-                res[e][2] = fmaf(fB, fmaf(-cB, sx[0], acc[e][2]), res[e][2]);
-                res[e][3] = fmaf(fB, fmaf(-cB, sx[1], acc[e][3]), res[e][3]);
-            }
+            sk_consume_unit<XH>(smem_base + slot * SK_STAGE_BYTES, lane_geo, res, empty_bar(slot), lane);
         }
         if (++g == G) { g = 0; ++v; }
         if (++slot == SK_STAGES) { slot = 0; ++round; }

@@ -112,7 +112,7 @@ class DecodeFFNStack:
     """
 
     def __init__(self, layers: Sequence[FFNLayer], hidden: int, max_batch: int = 64, eps: float = 1e-5,
-                 group=None, device="cuda"):
+                 group=None, device="cuda", fused: bool = True):
         self.layers = list(layers)
         self.hidden = hidden
         self.eps = eps
@@ -131,11 +131,35 @@ class DecodeFFNStack:
         self._inter = torch.empty((max_batch, max_il), dtype=torch.float16, device=device)
         self._partial = torch.empty((max_batch, hidden), dtype=torch.float32, device=device)
         self._graphs = {}
+        # one launch for the whole stack where the fused kernel applies: one GPU, every layer with
+        # a norm weight, one shape, group 128, batch <= 8 (larger batches take the per-layer kernels)
+        self.plan = None
+        if fused and self.tp == 1 and self._fusable():
+            self.plan = ops.FFNStackPlan([l.gateup for l in self.layers], [l.down for l in self.layers],
+                                         [l.gamma for l in self.layers])
+            if self.plan.workspace_bytes() > self.ws.nbytes:
+                self.plan = None
         self._pin_in = torch.empty((max_batch, hidden), dtype=torch.bfloat16).pin_memory() if torch.cuda.is_available() else None
         self._pin_out = torch.empty((max_batch, hidden), dtype=torch.bfloat16).pin_memory() if torch.cuda.is_available() else None
 
+    def _fusable(self) -> bool:
+        l0 = self.layers[0]
+        il = l0.down.K
+        if l0.gateup.group_size != 128 or self.hidden % 128 or il % 128:
+            return False
+        for l in self.layers:
+            if l.gamma is None or l.gateup.K != self.hidden or l.gateup.N != 2 * il or l.down.K != il or \
+                    l.down.N != self.hidden or l.gateup.group_size != 128 or l.down.group_size != 128:
+                return False
+        return True
+
+    def uses_fused(self, batch: int) -> bool:
+        return self.plan is not None and batch <= 8
+
     # kernels launched per step (this library's own), for accounting
     def launches_per_step(self, batch: int) -> int:
+        if self.uses_fused(batch):
+            return 1
         passes = (batch + 7) // 8  # the decode kernels take 8 rows per launch
         n = len(self.layers)
         if self.tp == 1:
@@ -151,6 +175,8 @@ class DecodeFFNStack:
         holding the result."""
         h, other = self._h[0][:B], self._h[1][:B]
         normed, inter, partial = self._normed[:B], self._inter, self._partial[:B]
+        if self.uses_fused(B):
+            return ops.ffn_stack_decode(self.plan, h, self.ws, eps=self.eps, inter=inter, out=other)
         if self.tp == 1:
             for l in self.layers:
                 il = l.down.K

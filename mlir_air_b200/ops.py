@@ -4,7 +4,7 @@ memory and streams only; no operator here has a PyTorch implementation."""
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional
+from typing import Optional, Sequence
 
 import torch
 
@@ -230,6 +230,68 @@ def ffn_decode(x, w_gateup: AwqWeight, w_down: AwqWeight, ws: Workspace, gamma=N
               _ptr(w_gateup.qzeros), _ptr(w_gateup.scales), _ptr(w_down.qweight), _ptr(w_down.qzeros),
               _ptr(w_down.scales), _ptr(residual), _ptr(normed), _ptr(inter), _ptr(out), B, H, I, w_gateup.group_size,
               _ptr(ws.buf), ws.nbytes, _stream())
+    return out
+
+
+class FFNStackPlan:
+    """Tensor maps of a decode FFN layer stack in device memory, for ffn_stack_decode.
+    `gateups`, `downs`: one AwqWeight per layer (gate/up interleaved [H, 2I], down [I, H]);
+    `gammas`: one bf16 [H] tensor per layer.  Keeps references to the weights it describes."""
+
+    def __init__(self, gateups: Sequence[AwqWeight], downs: Sequence[AwqWeight], gammas: Sequence[torch.Tensor]):
+        import ctypes
+        n = len(gateups)
+        if n == 0 or len(downs) != n or len(gammas) != n:
+            raise _lib.AwqBackendError("FFNStackPlan: one gate/up weight, one down weight and one gamma per layer")
+        self.n_layers = n
+        self.H, self.I, self.group_size = gateups[0].K, gateups[0].N // 2, gateups[0].group_size
+        for gu, d, g in zip(gateups, downs, gammas):
+            if (gu.K, gu.N, d.K, d.N, gu.group_size, d.group_size) != (self.H, 2 * self.I, self.I, self.H, self.group_size,
+                                                                         self.group_size):
+                raise _lib.AwqBackendError("FFNStackPlan: all layers must have the same shape and group size")
+            _want(g, torch.bfloat16, "gamma")
+            if g.numel() != self.H:
+                raise _lib.AwqBackendError(f"FFNStackPlan: gamma must have {self.H} elements")
+        self._keep = (list(gateups), list(downs), list(gammas))
+        dev = gateups[0].qweight.device
+        lib = _lib.load()
+        self.nbytes = int(lib.awq_b200_ffn_stack_plan_bytes(n))
+        self.buf = torch.empty(self.nbytes + 128, dtype=torch.uint8, device=dev)
+        self.ptr = (self.buf.data_ptr() + 127) // 128 * 128
+        arr = ctypes.c_void_p * n
+
+        def ptrs(ts):
+            return arr(*[t.data_ptr() for t in ts])
+
+        with torch.cuda.device(dev):
+            _lib.call("awq_b200_ffn_stack_plan", self.ptr, self.nbytes, n, ptrs([w.qweight for w in gateups]),
+                      ptrs([w.qzeros for w in gateups]), ptrs([w.scales for w in gateups]), ptrs([w.qweight for w in downs]),
+                      ptrs([w.qzeros for w in downs]), ptrs([w.scales for w in downs]), ptrs(list(gammas)), self.H, self.I,
+                      self.group_size)
+
+    def workspace_bytes(self) -> int:
+        return int(_lib.load().awq_b200_ffn_stack_workspace_bytes(self.n_layers))
+
+
+def set_ffn_stack_tuning(lookahead_units: int = -1, split_per_1024: int = -1):
+    """Tuning of the one-launch stack kernel (negative = keep): units per half-CTA prefetched into
+    L2 ahead of the ring, and where an SM's unit range is cut between the CTA's two halves."""
+    _lib.call("awq_b200_set_ffn_stack_tuning", int(lookahead_units), int(split_per_1024))
+
+
+def ffn_stack_decode(plan: FFNStackPlan, x, ws: Workspace, eps=1e-5, inter=None, out=None):
+    """out [B, H] = the whole layer stack applied to x [B <= 8, H], ONE kernel launch."""
+    x = _x2d(x, plan.H)
+    B = x.shape[0]
+    if inter is None:
+        inter = torch.empty((B, plan.I), dtype=torch.float16, device=x.device)
+    if out is None:
+        out = torch.empty((B, plan.H), dtype=torch.bfloat16, device=x.device)
+    _want(out, torch.bfloat16, "out")
+    if inter.numel() < B * plan.I or inter.element_size() != 2:
+        raise _lib.AwqBackendError("ffn_stack_decode: inter must hold B * I 16-bit elements")
+    _lib.call("awq_b200_ffn_stack_decode_bf16", plan.ptr, plan.n_layers, _ptr(x), _ptr(out), _ptr(inter), float(eps), B,
+              plan.H, plan.I, plan.group_size, _ptr(ws.buf), ws.nbytes, _stream())
     return out
 
 

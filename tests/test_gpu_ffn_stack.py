@@ -1,0 +1,131 @@
+"""GPU parity of the one-launch decode FFN stack (awq_b200_ffn_stack_decode_bf16) against the
+numpy oracle (the layer chain of o_gemv_ffn_int4_multi.py:9-12 repeated over the layers) and
+against the per-layer kernels."""
+import numpy as np
+import pytest
+from ml_dtypes import bfloat16
+
+from oracle import awq_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+REL_L2_TOL = 1e-2  # BASELINE north_star tolerance for GEMV / FFN outputs
+
+
+@pytest.fixture(scope="module")
+def ops():
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from mlir_air_b200 import ops as _ops
+    _ops.set_decode_kernel("auto")
+    _ops.set_deterministic(False)
+    return _ops
+
+
+def _layers_np(H, I, L, seed):
+    from gpu_util import synth_awq
+    out = []
+    for l in range(L):
+        gate = synth_awq(H, I, 128, seed=seed + 10 * l)
+        up = synth_awq(H, I, 128, seed=seed + 10 * l + 1)
+        down = synth_awq(I, H, 128, seed=seed + 10 * l + 2, scale_lo=0.0005, scale_hi=0.004)
+        gamma = (np.random.default_rng(seed + 10 * l + 3).standard_normal(H) * 0.1 + 1.0).astype(bfloat16)
+        out.append((gate, up, down, gamma))
+    return out
+
+
+def _plan(ops, layers_np):
+    from gpu_util import dev_weight, to_dev
+    gus, downs, gammas = [], [], []
+    for gate, up, down, gamma in layers_np:
+        gus.append(ops.interleave_gate_up(dev_weight(*gate), dev_weight(*up)))
+        downs.append(dev_weight(*down))
+        gammas.append(to_dev(gamma))
+    return ops.FFNStackPlan(gus, downs, gammas), gus, downs, gammas
+
+
+def _oracle_stack(x, layers_np):
+    h = x
+    for gate, up, down, gamma in layers_np:
+        h = O.ffn_layer_A_ref(h, gamma, gate, up, down, 128)
+    return h
+
+
+@pytest.mark.parametrize("B,H,I,L", [(1, 512, 1408, 2), (4, 1024, 2816, 3), (8, 512, 1024, 4), (3, 2048, 5632, 2)])
+def test_stack_vs_oracle(ops, B, H, I, L):
+    from gpu_util import randn_bf16, to_dev, to_host
+    layers_np = _layers_np(H, I, L, seed=H + I)
+    plan, gus, downs, gammas = _plan(ops, layers_np)
+    ws = ops.Workspace(max(H, I), max(2 * I, H))
+    assert plan.workspace_bytes() <= ws.nbytes
+    x = randn_bf16((B, H), seed=5)
+    ref = _oracle_stack(x, layers_np)
+    y = to_host(ops.ffn_stack_decode(plan, to_dev(x), ws))
+    ws.check()
+    assert y.shape == (B, H)
+    assert O.rel_l2(y, ref) <= REL_L2_TOL
+    # the same through the per-layer entry point
+    h = to_dev(x)
+    for l in range(L):
+        h = ops.ffn_decode(h, gus[l], downs[l], ws, gamma=gammas[l], residual=h)
+    # two correct f32 summation orders differ by bf16 rounding flips that later layers amplify
+    assert O.rel_l2(y, to_host(h)) <= 5e-3
+    # a second call on the same workspace (state reset by the launcher), output aliasing the input
+    hx = to_dev(x)
+    ops.ffn_stack_decode(plan, hx, ws, out=hx)
+    ws.check()
+    assert O.rel_l2(to_host(hx), ref) <= REL_L2_TOL
+
+
+def test_stack_llama70b_dims_matches_per_layer_kernels(ops):
+    """BASELINE config 5 dims (hidden 8192, intermediate 28672), 3 layers, batch 8 and 1: the
+    fused launch against the same stack run layer by layer, eager and as a replayed CUDA graph."""
+    import torch
+    from mlir_air_b200 import ffn
+    H, I, L = 8192, 28672, 3
+    layers = [ffn.random_layer(H, I, seed=l) for l in range(L)]
+    fused = ffn.DecodeFFNStack(layers, H, max_batch=16)
+    plain = ffn.DecodeFFNStack(layers, H, max_batch=16, fused=False)
+    assert fused.uses_fused(8) and not fused.uses_fused(16) and not plain.uses_fused(8)
+    assert fused.launches_per_step(8) == 1
+    for B in (8, 1):
+        x = (torch.randn((B, H), device="cuda") * 0.5).to(torch.bfloat16)
+        a = fused.step(x).float()
+        b = plain.step(x).float()
+        fused.check()
+        plain.check()
+        assert torch.isfinite(a).all()
+        rel = float((a - b).norm() / b.norm())
+        assert rel <= 5e-3, (B, rel)
+        fused.load_input(x)
+        g1 = fused.replay(B).float().clone()
+        fused.load_input(x)
+        g2 = fused.replay(B).float().clone()
+        fused.check()
+        assert float((g1 - b).norm() / b.norm()) <= 5e-3
+        assert float((g2 - b).norm() / b.norm()) <= 5e-3
+    # a batch the fused kernel does not take goes through the per-layer kernels
+    x = (torch.randn((16, H), device="cuda") * 0.5).to(torch.bfloat16)
+    rel = float((fused.step(x).float() - plain.step(x).float()).norm() / plain.step(x).float().norm())
+    assert rel <= 5e-3
+
+
+def test_stack_rejects_what_it_cannot_run(ops):
+    import torch
+    from gpu_util import dev_weight, synth_awq, to_dev
+    from mlir_air_b200._lib import AwqBackendError
+    H, I = 512, 1024
+    layers_np = _layers_np(H, I, 1, seed=1)
+    plan, *_ = _plan(ops, layers_np)
+    ws = ops.Workspace(I, 2 * I)
+    x = torch.zeros((9, H), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(AwqBackendError):
+        ops.ffn_stack_decode(plan, x, ws)  # more than 8 rows
+    with pytest.raises(AwqBackendError):  # group size 64
+        g64 = dev_weight(*synth_awq(H, 2 * I, 64, seed=2), gs=64)
+        d64 = dev_weight(*synth_awq(I, H, 64, seed=3), gs=64)
+        ops.FFNStackPlan([g64], [d64], [to_dev(layers_np[0][3])])
+    # an empty batch is a no-op
+    out = ops.ffn_stack_decode(plan, torch.zeros((0, H), dtype=torch.bfloat16, device="cuda"), ws)
+    assert out.shape == (0, H)
