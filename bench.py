@@ -46,8 +46,8 @@ def parse():
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per layer of the stack kernel at hidden 8192 / intermediate
-# 28672 / batch 8 (ncu capture of a 2-layer launch, halved); None until captured
-FUSED_TRAFFIC_PER_LAYER = None
+# 28672 / batch 8: ncu capture of a 2-layer launch, halved (profiles/ffn_fused_70b_stack.md)
+FUSED_TRAFFIC_PER_LAYER = 370400128
 
 
 def workload_name(a):
