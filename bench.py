@@ -41,6 +41,8 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM timing (extra key `prefill`)")
     ap.add_argument("--unfused", action="store_true", help="per-layer kernels instead of the one-launch stack kernel")
+    ap.add_argument("--peer-exchange", action="store_true",
+                    help="tensor parallel: partials read from peer memory + flag words instead of an NCCL allreduce per layer")
     ap.add_argument("--sweep", action="store_true", help="also time batch 1/8/32/64 (extra key `batches`)")
     return ap.parse_args()
 
@@ -207,7 +209,8 @@ def run_ours(a):
     _dbg("process group ready")
     bounds = ffn.tp_shard_bounds(a.intermediate, tp)[rank]
     layers = [ffn.random_layer(a.hidden, a.intermediate, seed=1000 + l, bounds=bounds) for l in range(a.layers)]
-    stack = ffn.DecodeFFNStack(layers, a.hidden, max_batch=max(64, a.batch), group=group, fused=not a.unfused)
+    stack = ffn.DecodeFFNStack(layers, a.hidden, max_batch=max(64, a.batch), group=group, fused=not a.unfused,
+                               peer_push=a.peer_exchange)
     B = a.batch
     rng = np.random.default_rng(0)
     x_host = rng.standard_normal((B, a.hidden)).astype(bfloat16)
@@ -369,7 +372,10 @@ def run_ours(a):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps, "warmup": max(3, a.warmup),
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": workload_name(a), "parallelism": f"tp{tp}", "l2": "inputs_exceed_l2 (weights streamed once per step)",
+        "config": {"workload": workload_name(a), "parallelism": f"tp{tp}",
+                   "exchange": ("none" if tp == 1 else "peer loads from every rank's send buffer + flag words"
+                                if stack.peers is not None and B <= 8 else "NCCL allreduce per layer"),
+                   "l2": "inputs_exceed_l2 (weights streamed once per step)",
                    "launch": ("one CUDA graph per step: one launch of the stack kernel" if stack.uses_fused(B)
                               else "one CUDA graph per step")},
         "clocks": clocks,

@@ -188,6 +188,37 @@ int awq_b200_ffn_decode_bf16(const uint16_t *x, const uint16_t *gamma, float eps
                              uint16_t *out, int B, int H, int I, int group_size, void *workspace,
                              size_t workspace_bytes, awq_stream_t stream);
 
+/* ---- tensor-parallel hand-over over peer memory (no collective call) ----------------------
+ * The reference has no multi-GPU form of this path; its only inter-GPU mechanism is a
+ * symmetric heap with peer loads/stores and flag words (runtime_lib/airgpu/symmetric_heap.cpp:172-312,
+ * test/gpu/multi_gpu/handwritten/allgather.mlir:19-41), which is the model for this pair.
+ *
+ * awq_b200_gemv_f32_push: this rank's down projection, y f32 [B, N] = x[B, K] @ W_shard, B <= 8,
+ * written to y, which must be memory the other ranks have mapped (this rank's send buffer).  When
+ * the launch's last sub-strip is stored the kernel issues one system-scope fence and adds 1 to
+ * peer_flags[r][rank] on every rank r (uint32 [16] per rank: [0, 8) arrivals per sender, [8] used
+ * by the receiver).  peer_flags is a HOST array of n_ranks device pointers valid on this GPU
+ * (peer mappings; entry `rank` is this rank's own flag block).
+ *
+ * awq_b200_tp_reduce_add_rmsnorm_act: waits (bounded, about a second; a timeout is reported by
+ * awq_b200_workspace_check on `workspace`) until every rank has signalled its
+ * [B, K] partial in `flags` (this rank's flag block), then reads the partials with peer loads
+ * (peer_partials: HOST array of n_ranks device pointers to the ranks' send buffers):
+ * h_out = bf16(h + sum_r partial_r) in rank order and, when gamma != NULL, normed =
+ * RMSNorm(h_out); the last block clears the 9 flag words.  A send buffer + flag block may be
+ * reused once the reduce that followed it has itself been followed by this rank's next push (two
+ * of them used alternately are enough for a layer loop).  The kernels of different GPUs wait for
+ * one another: every rank must enqueue the same sequence. */
+int awq_b200_gemv_f32_push(const void *x, int x_format, const int32_t *qweight,
+                           const int32_t *qzeros, const uint16_t *scales, float *y, int B, int K,
+                           int N, int group_size, void *const *peer_flags, int n_ranks, int rank,
+                           void *workspace, size_t workspace_bytes, awq_stream_t stream);
+int awq_b200_tp_reduce_add_rmsnorm_act(const uint16_t *h, const void *const *peer_partials,
+                                       uint32_t *flags, int n_ranks, const uint16_t *gamma,
+                                       float eps, uint16_t *h_out, void *normed,
+                                       int normed_format, int B, int K, void *workspace,
+                                       awq_stream_t stream);
+
 /* ---- whole decode FFN stack in one launch ---------------------------------------------------
  * For l in 0 .. n_layers-1:  h <- bf16(h + down_l(swiglu(gateup_l . RMSNorm(h, gamma_l, eps)))),
  * h starting as x and ending in out; batch B <= 8.  The single-launch form of the decode

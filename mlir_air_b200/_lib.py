@@ -54,6 +54,8 @@ SIGNATURES = {
     "awq_b200_gateup_swiglu_bf16": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P, c_size_t, _P]),
     "awq_b200_interleave_gate_up": (c_int, [_P] * 9 + [c_int, c_int, c_int, _P]),
     "awq_b200_ffn_decode_bf16": (c_int, [_P, _P, c_float] + [_P] * 10 + [c_int, c_int, c_int, c_int, _P, c_size_t, _P]),
+    "awq_b200_gemv_f32_push": (c_int, [_P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P, c_int, c_int, _P, c_size_t, _P]),
+    "awq_b200_tp_reduce_add_rmsnorm_act": (c_int, [_P, _P, _P, c_int, _P, c_float, _P, _P, c_int, c_int, c_int, _P, _P]),
     "awq_b200_set_ffn_stack_tuning": (c_int, [c_int, c_int]),
     "awq_b200_ffn_stack_plan_bytes": (c_size_t, [c_int]),
     "awq_b200_ffn_stack_workspace_bytes": (c_size_t, [c_int]),

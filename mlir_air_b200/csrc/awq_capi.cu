@@ -156,6 +156,37 @@ extern "C" int awq_b200_gemv_f32(const uint16_t *x, const int32_t *qweight, cons
                              workspace_bytes, stream);
 }
 
+extern "C" int awq_b200_gemv_f32_push(const void *x, int x_format, const int32_t *qweight, const int32_t *qzeros,
+                                      const uint16_t *scales, float *y, int B, int K, int N, int group_size,
+                                      void *const *peer_flags, int n_ranks, int rank, void *workspace,
+                                      size_t workspace_bytes, awq_stream_t stream) {
+    AWQ_REQUIRE(n_ranks >= 1 && n_ranks <= TP_MAX_RANKS && rank >= 0 && rank < n_ranks, "gemv_f32_push: rank %d of %d", rank,
+                n_ranks);
+    AWQ_REQUIRE(peer_flags, "gemv_f32_push: null peer array");
+    AWQ_REQUIRE(B >= 1 && B <= 8, "gemv_f32_push: 1..8 batch rows");
+    PeerPush push{};
+    push.n = n_ranks;
+    push.rank = rank;
+    for (int r = 0; r < n_ranks; ++r) {
+        AWQ_REQUIRE(peer_flags[r], "gemv_f32_push: null flag pointer for rank %d", r);
+        push.flag[r] = reinterpret_cast<unsigned int *>(peer_flags[r]);
+    }
+    GemvArgs a{reinterpret_cast<const uint16_t *>(x), qweight, qzeros, scales, nullptr, y, B, K, N, group_size,
+               EPI_F32_PUSH, workspace, workspace_bytes, as_stream(stream)};
+    a.x_format = x_format;
+    a.push = &push;
+    int rc = check_gemv_args("gemv_f32_push", a);
+    if (rc) return rc;
+    AWQ_REQUIRE(x_format == ACT_BF16 || x_format == ACT_F16, "gemv_f32_push: unknown activation format %d", x_format);
+    AWQ_REQUIRE(aligned16(y), "gemv_f32_push: y must be 16-byte aligned");
+    if (!gemv_streamk_supported(a))
+        return set_error(AWQ_ERR_UNSUPPORTED, "gemv_f32_push: needs group 128, K %% 128 == 0, N %% 32 == 0 (K=%d N=%d gs=%d)", K,
+                         N, group_size);
+    a.native_bf16 = g_decode_mode.load() == 3;
+    a.deterministic = g_deterministic.load() != 0;
+    return launch_gemv_streamk(a);
+}
+
 extern "C" int awq_b200_gateup_swiglu_act(const void *x, int x_format, const int32_t *qweight, const int32_t *qzeros,
                                           const uint16_t *scales, void *out, int out_format, int B, int K, int I,
                                           int group_size, void *workspace, size_t workspace_bytes,

@@ -85,6 +85,21 @@ enum Epilogue : int {
     EPI_BF16 = 0,    // y bf16 [B, N] = bf16(sum (+ residual))
     EPI_F32 = 1,     // y f32  [B, N] = sum
     EPI_SWIGLU = 2,  // y bf16 [B, N/2] = swiglu(sum[2i], sum[2i+1])
+    EPI_F32_PUSH = 3,  // EPI_F32 into this rank's send buffer, then every tensor-parallel rank is signalled
+};
+
+// Tensor-parallel hand-over through peer memory.  A rank writes its f32 partial [B, N] into its own
+// send buffer and adds 1 per finished sub-strip to entry `rank` of every rank's arrival counters
+// (flag[r]: uint32 words on rank r, mapped into this GPU's address space); the receivers read the
+// partials with peer loads.
+constexpr int TP_MAX_RANKS = 8;
+struct PeerPush {
+    unsigned int *flag[TP_MAX_RANKS];
+    int n, rank;
+};
+struct PeerPartials {
+    const float *partial[TP_MAX_RANKS];  // rank r's send buffer [B, K], mapped into this GPU's address space
+    int n;
 };
 
 // 16-bit activation formats.  The stream-K kernel's fastest path wants fp16 activations (an fp16
@@ -107,6 +122,7 @@ struct GemvArgs {
     int out_format = ACT_BF16;  // EPI_SWIGLU only: format of the output
     bool native_bf16 = false;   // stream-K: multiply bf16 activations as they are (no fp16 conversion)
     bool deterministic = false; // stream-K: sum split-K partials in a fixed order (slower) instead of f32 atomics
+    const PeerPush *push = nullptr;  // EPI_F32_PUSH only
 };
 
 // Generic CUDA-core kernel: any group size, any N % 8 == 0, B <= 64.
@@ -127,6 +143,10 @@ int launch_gemm_tc(const uint16_t *A, const int32_t *qweight, const int32_t *qze
                    cudaStream_t stream);
 
 int gemm_tc_check(cudaStream_t stream);
+int gemv_push_arrivals_per_rank(int N);  // arrivals a rank signals per EPI_F32_PUSH launch of N columns
+int launch_tp_reduce_add_rmsnorm(const uint16_t *h, const PeerPartials &parts, unsigned int *flags, int expected,
+                                 const uint16_t *gamma, float eps, uint16_t *h_out, uint16_t *normed, int normed_f16, int B,
+                                 int K, int *err_flag, cudaStream_t stream);
 
 // Fused decode FFN stack (awq_ffn_fused.cu)
 size_t ffn_fused_plan_bytes(int n_layers);

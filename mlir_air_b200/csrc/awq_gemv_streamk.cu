@@ -51,7 +51,7 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                     const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmZ,
                     const uint16_t *__restrict__ residual, void *__restrict__ y_, int B, int N, int G,
                     int V, int out_f16, int fast_reduce, float *__restrict__ accum, float *__restrict__ partials,
-                    int *__restrict__ counters, int *__restrict__ err_flag) {
+                    int *__restrict__ counters, int *__restrict__ err_flag, const PeerPush push) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t bar_base = smem_base + SK_STAGES * SK_STAGE_BYTES;
@@ -153,6 +153,7 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         const long long c_hi = sk_owner((long long)(v + 1) * G - 1, C, U);
         if (c_hi == c_lo) {
             if (!failed) sk_epilogue<EPI>(own, residual, y_, B, N, n, b, out_f16);
+            if (EPI == EPI_F32_PUSH && !failed) sk_push_signal(push, err_flag + 8, V * SK_CONSUMER_WARPS, lane);
             return;
         }
         // [warp][batch row][64 columns] inside a strip's accumulator / a CTA's slot
@@ -232,6 +233,7 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         __syncwarp();
         if (lane == 0) counters[v * SK_CONSUMER_WARPS + warp] = 0;  // ready for the next launch
         if (!failed) sk_epilogue<EPI>(own, residual, y_, B, N, n, b, out_f16);
+        if (EPI == EPI_F32_PUSH && !failed) sk_push_signal(push, err_flag + 8, V * SK_CONSUMER_WARPS, lane);
     };
 
     int v = v_first, g = g_first, slot = 0, round = 0;
@@ -303,6 +305,12 @@ int encode_tensor_map_2d(CUtensorMap *map, int dtype, const void *base, uint64_t
     return AWQ_OK;
 }
 
+// A rank signals once per EPI_F32_PUSH launch, when its last sub-strip is stored.
+int gemv_push_arrivals_per_rank(int N) {
+    (void)N;
+    return 1;
+}
+
 bool gemv_streamk_supported(const GemvArgs &a) {
     return a.group_size == SK_GROUP && a.K % SK_GROUP == 0 && a.N % 32 == 0 && a.B >= 1 && a.K > 0 && a.N > 0 &&
            aligned16(a.x) && aligned16(a.qweight) && aligned16(a.qzeros) && aligned16(a.scales) &&
@@ -362,7 +370,8 @@ static int launch_one(const GemvArgs &a, const uint16_t *x, const uint16_t *resi
     float *partials = reinterpret_cast<float *>(ws + SK_WS_PARTIALS);
     return check_cuda(launch_pdl(gemv_streamk_kernel<EPI, XH>, dim3(ctas), dim3(SK_THREADS), SK_SMEM_BYTES, a.stream, tmW,
                                  tmX, tmS, tmZ, residual, y, B, a.N, G, V, a.out_format == ACT_F16 ? 1 : 0,
-                                 a.deterministic ? 0 : 1, accum, partials, counters, err_flag),
+                                 a.deterministic ? 0 : 1, accum, partials, counters, err_flag,
+                                 a.push ? *a.push : PeerPush{}),
                       "stream-K gemv launch");
 }
 
@@ -380,6 +389,10 @@ static int launch_passes(const GemvArgs &a, const uint16_t *x_all) {
                 break;
             case EPI_F32:
                 rc = launch_one<EPI_F32, XH>(a, x, nullptr, reinterpret_cast<float *>(a.y) + (size_t)b0 * a.N, B);
+                break;
+            case EPI_F32_PUSH:  // one pass only: the receivers expect one launch worth of arrivals
+                rc = a.B <= 8 && a.push ? launch_one<EPI_F32_PUSH, XH>(a, x, nullptr, a.y, B)
+                                        : set_error(AWQ_ERR_UNSUPPORTED, "gemv push: at most 8 batch rows");
                 break;
             default:
                 rc = launch_one<EPI_SWIGLU, XH>(a, x, nullptr,

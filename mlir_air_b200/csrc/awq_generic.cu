@@ -296,6 +296,108 @@ rmsnorm_kernel(const uint16_t *__restrict__ h, const float *__restrict__ partial
     }
 }
 
+// Tensor-parallel hand-over without a collective call: every rank's down projection has written its
+// f32 partial [B, K] into its own send buffer and counted its finished sub-strips in flags[rank] on
+// every rank (EPI_F32_PUSH).  One block per batch row waits for all ranks (bounded), then reads the
+// partials with peer loads: h_out = bf16(h + sum over ranks in rank order) and, with gamma, its
+// RMSNorm.  The last block to finish clears the counters for the slot's next use.
+// flags: [0, 8) arrivals per rank, [8] blocks done.
+__device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int *p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(RN_THREADS)
+tp_reduce_add_rmsnorm_kernel(const uint16_t *__restrict__ h, const PeerPartials parts, unsigned int *flags,
+                             unsigned int expected, const uint16_t *__restrict__ gamma, float eps,
+                             uint16_t *__restrict__ h_out, uint16_t *__restrict__ normed, int K, int normed_f16,
+                             int *err_flag) {
+    __shared__ float red[8];
+    const int n_ranks = parts.n;
+    pdl_launch_dependents();
+    pdl_wait();
+    int ok = 1;
+    if ((int)threadIdx.x < n_ranks) {
+        const long long t0 = clock64();
+        while (ld_acquire_sys_u32(flags + threadIdx.x) < expected) {
+            if (clock64() - t0 > (1ll << 31)) {
+                ok = 0;
+                break;
+            }
+            __nanosleep(100);
+        }
+    }
+    if (!__syncthreads_and(ok)) {
+        if (threadIdx.x == 0) atomicExch(err_flag, 5);
+        return;
+    }
+    const size_t row = (size_t)blockIdx.x * K;
+    const int n_chunks = K >> 3;
+    float v[RN_CHUNKS][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < RN_CHUNKS; ++c) {
+        const int ch = threadIdx.x + c * RN_THREADS;
+        if (ch < n_chunks) {
+            float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int r = 0; r < TP_MAX_RANKS; ++r) {
+                if (r >= n_ranks) break;
+                const float *src = parts.partial[r] + row + 8 * ch;
+                const float4 p0 = __ldcg(reinterpret_cast<const float4 *>(src));
+                const float4 p1 = __ldcg(reinterpret_cast<const float4 *>(src + 4));
+                sum[0] += p0.x; sum[1] += p0.y; sum[2] += p0.z; sum[3] += p0.w;
+                sum[4] += p1.x; sum[5] += p1.y; sum[6] += p1.z; sum[7] += p1.w;
+            }
+            const uint4 t = *reinterpret_cast<const uint4 *>(h + row + 8 * ch);
+            const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+            uint32_t o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                o[e] = pack_bf16x2(bf16x2_lo(w[e]) + sum[2 * e], bf16x2_hi(w[e]) + sum[2 * e + 1]);
+                v[c][2 * e] = bf16x2_lo(o[e]);
+                v[c][2 * e + 1] = bf16x2_hi(o[e]);
+            }
+            *reinterpret_cast<uint4 *>(h_out + row + 8 * ch) = make_uint4(o[0], o[1], o[2], o[3]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss = fmaf(v[c][e], v[c][e], ss);
+        }
+    }
+    if (normed) {
+        const float total = block_sum_256(ss, red);
+        const float rstd = (float)(1.0 / sqrt((double)(total / (float)K) + (double)eps));
+#pragma unroll
+        for (int c = 0; c < RN_CHUNKS; ++c) {
+            const int ch = threadIdx.x + c * RN_THREADS;
+            if (ch < n_chunks) {
+                const uint4 gt = *reinterpret_cast<const uint4 *>(gamma + 8 * ch);
+                const uint32_t gw[4] = {gt.x, gt.y, gt.z, gt.w};
+                uint32_t o[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    uint16_t lo = f32_to_bf16_bits((v[c][2 * e] * rstd) * bf16x2_lo(gw[e]));
+                    uint16_t hi = f32_to_bf16_bits((v[c][2 * e + 1] * rstd) * bf16x2_hi(gw[e]));
+                    if (normed_f16) {
+                        lo = __half_as_ushort(__float2half_rn(fminf(fmaxf(bf16_bits_to_f32(lo), -65504.f), 65504.f)));
+                        hi = __half_as_ushort(__float2half_rn(fminf(fmaxf(bf16_bits_to_f32(hi), -65504.f), 65504.f)));
+                    }
+                    o[e] = (uint32_t)lo | ((uint32_t)hi << 16);
+                }
+                *reinterpret_cast<uint4 *>(normed + row + 8 * ch) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+        }
+    }
+    // every block has passed its wait once all of them count here: the last one clears the slot
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (atomicAdd(flags + 8, 1u) == gridDim.x - 1) {
+            for (int r = 0; r < 9; ++r) flags[r] = 0u;
+            __threadfence_system();
+        }
+    }
+}
+
 // =====================================================================================
 // Layout converters (once per weight; clarity over speed).
 // =====================================================================================
@@ -431,6 +533,14 @@ __global__ void silu_mul_bf16_kernel(const uint16_t *__restrict__ gate, const ui
 
 static inline unsigned blocks_for(size_t n, int threads) { return (unsigned)((n + threads - 1) / threads); }
 
+int launch_tp_reduce_add_rmsnorm(const uint16_t *h, const PeerPartials &parts, unsigned int *flags, int expected,
+                                 const uint16_t *gamma, float eps, uint16_t *h_out, uint16_t *normed, int normed_f16, int B,
+                                 int K, int *err_flag, cudaStream_t stream) {
+    return check_cuda(launch_pdl(tp_reduce_add_rmsnorm_kernel, dim3(B), dim3(RN_THREADS), 0, stream, h, parts, flags,
+                                 (unsigned int)expected, gamma, eps, h_out, normed, K, normed_f16, err_flag),
+                      "tp_reduce_add_rmsnorm launch");
+}
+
 }  // namespace awq
 
 using namespace awq;
@@ -474,6 +584,29 @@ extern "C" int awq_b200_add_rmsnorm_act(const uint16_t *h, const float *partial_
     return check_cuda(launch_pdl(rmsnorm_kernel, dim3(B), dim3(256), 0, as_stream(stream), h, partial_sum, gamma, eps,
                                  h_out, reinterpret_cast<uint16_t *>(normed), K, normed_format == ACT_F16 ? 1 : 0),
                       "add_rmsnorm launch");
+}
+
+extern "C" int awq_b200_tp_reduce_add_rmsnorm_act(const uint16_t *h, const void *const *peer_partials, uint32_t *flags, int n_ranks,
+                                                  const uint16_t *gamma, float eps, uint16_t *h_out, void *normed,
+                                                  int normed_format, int B, int K, void *workspace, awq_stream_t stream) {
+    AWQ_REQUIRE(B >= 0 && B <= 8 && K > 0, "tp_reduce_add_rmsnorm: B must be 0..8");
+    AWQ_REQUIRE(n_ranks >= 1 && n_ranks <= TP_MAX_RANKS, "tp_reduce_add_rmsnorm: 1..%d ranks", TP_MAX_RANKS);
+    AWQ_REQUIRE(K % 8 == 0 && K <= RN_THREADS * RN_CHUNKS * 8, "tp_reduce_add_rmsnorm: K (%d) must be a multiple of 8, at most %d", K, RN_THREADS * RN_CHUNKS * 8);
+    AWQ_REQUIRE(normed_format == ACT_BF16 || normed_format == ACT_F16, "tp_reduce_add_rmsnorm: unknown format %d", normed_format);
+    if (B == 0) return AWQ_OK;
+    AWQ_REQUIRE(h && peer_partials && flags && h_out && workspace, "tp_reduce_add_rmsnorm: null pointer");
+    PeerPartials parts{};
+    parts.n = n_ranks;
+    for (int r = 0; r < n_ranks; ++r) {
+        AWQ_REQUIRE(peer_partials[r] && aligned16(peer_partials[r]), "tp_reduce_add_rmsnorm: bad partial pointer of rank %d", r);
+        parts.partial[r] = reinterpret_cast<const float *>(peer_partials[r]);
+    }
+    AWQ_REQUIRE((gamma == nullptr) == (normed == nullptr), "tp_reduce_add_rmsnorm: gamma and normed go together");
+    AWQ_REQUIRE(aligned16(h) && aligned16(h_out) && aligned16(normed) && aligned16(gamma), "tp_reduce_add_rmsnorm: pointers must be 16-byte aligned");
+    AWQ_REQUIRE(h_out != h, "tp_reduce_add_rmsnorm: h_out must not alias h");
+    return launch_tp_reduce_add_rmsnorm(h, parts, flags, gemv_push_arrivals_per_rank(K), gamma, eps, h_out,
+                                        reinterpret_cast<uint16_t *>(normed), normed_format == ACT_F16 ? 1 : 0, B, K,
+                                        reinterpret_cast<int *>(workspace), as_stream(stream));
 }
 
 extern "C" int awq_b200_linear_bf16(const uint16_t *x, const uint16_t *W, uint16_t *y, int M, int K, int N,

@@ -119,7 +119,7 @@ __device__ __forceinline__ void sk_epilogue(const float (&own)[2][8], const uint
             }
             *reinterpret_cast<uint2 *>(reinterpret_cast<uint16_t *>(y_) + (size_t)b * (N >> 1) + (nh >> 1)) =
                 make_uint2((uint32_t)o[0] | ((uint32_t)o[1] << 16), (uint32_t)o[2] | ((uint32_t)o[3] << 16));
-        } else if (EPI == EPI_F32) {
+        } else if (EPI == EPI_F32 || EPI == EPI_F32_PUSH) {
             float4 *dst = reinterpret_cast<float4 *>(reinterpret_cast<float *>(y_) + (size_t)b * N + nh);
             dst[0] = make_float4(v[0], v[1], v[2], v[3]);
             dst[1] = make_float4(v[4], v[5], v[6], v[7]);
@@ -143,6 +143,23 @@ __device__ __forceinline__ void sk_epilogue(const float (&own)[2][8], const uint
     }
 }
 
+
+// After a warp has stored a finished sub-strip with EPI_F32_PUSH.  Sub-strips are counted on this
+// GPU first (`local_done`, zero between launches); the warp that finishes the launch's last one makes
+// everything visible to the other GPUs with ONE system-scope fence (the fence is cumulative: it
+// orders the other warps' stores, which it has observed through the counter, too) and adds 1 to its
+// entry of every rank's arrival counters.  A system-scope fence per sub-strip costs 9 us per launch.
+__device__ __forceinline__ void sk_push_signal(const PeerPush &push, int *local_done, int total, int lane) {
+    __threadfence();
+    __syncwarp();
+    int last = 0;
+    if (lane == 0) last = atomicAdd(local_done, 1) == total - 1;
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (!last) return;
+    __threadfence_system();
+    if (lane == 0) *local_done = 0;
+    if (lane < push.n) atomicAdd_system(push.flag[lane] + push.rank, 1u);
+}
 
 // Per-lane geometry of a consumer warp.  Warp w owns strip columns [64 w, 64 w + 64): two
 // 16-byte chunks (A, B) of every box row.  ldmatrix.trans hands lane (g8, t4) 16-bit half g8 of

@@ -112,7 +112,7 @@ class DecodeFFNStack:
     """
 
     def __init__(self, layers: Sequence[FFNLayer], hidden: int, max_batch: int = 64, eps: float = 1e-5,
-                 group=None, device="cuda", fused: bool = True):
+                 group=None, device="cuda", fused: bool = True, peer_push: bool = False):
         self.layers = list(layers)
         self.hidden = hidden
         self.eps = eps
@@ -131,6 +131,14 @@ class DecodeFFNStack:
         self._inter = torch.empty((max_batch, max_il), dtype=torch.float16, device=device)
         self._partial = torch.empty((max_batch, hidden), dtype=torch.float32, device=device)
         self._graphs = {}
+        # tensor parallel, optional: partials are read from the peers' send buffers (two slots used
+        # alternately) instead of going through an allreduce call, for batches the push kernel takes;
+        # off by default, NCCL's allreduce measured faster at 2 and 4 ranks
+        self.peers = None
+        if peer_push and self.tp > 1 and hidden % 128 == 0 and all(l.down.group_size == 128 and l.down.K % 128 == 0
+                                                                    for l in self.layers):
+            from .peer import PeerBuffers
+            self.peers = PeerBuffers(group, 2, 8 * hidden * 4, device)
         # one launch for the whole stack where the fused kernel applies: one GPU, every layer with
         # a norm weight, one shape, group 128, batch <= 8 (larger batches take the per-layer kernels)
         self.plan = None
@@ -190,15 +198,21 @@ class DecodeFFNStack:
         if self.layers[0].gamma is not None:
             ops.rmsnorm(h, self.layers[0].gamma, self.eps, out=normed, out_f16=True)
             x = normed
+        push = self.peers is not None and B <= 8
         for idx, l in enumerate(self.layers):
             il = l.down.K
             it = inter.view(-1)[:B * il].view(B, il)
             ops.gateup_swiglu(x, l.gateup, self.ws, out=it, x_f16=x is normed, out_f16=True)
-            ops.gemv(it, l.down, self.ws, out=partial, f32_out=True, x_f16=True)
-            torch.distributed.all_reduce(partial, group=self.group)
             nxt = self.layers[idx + 1].gamma if idx + 1 < len(self.layers) else None
-            ops.add_rmsnorm(h, partial, nxt, self.eps, h_out=other, normed=normed if nxt is not None else None,
-                            normed_f16=True)
+            if push:
+                ops.gemv_f32_push(it, l.down, self.ws, self.peers, idx & 1, x_f16=True)
+                ops.tp_reduce_add_rmsnorm(h, self.peers, idx & 1, self.ws, nxt, self.eps, h_out=other,
+                                          normed=normed if nxt is not None else None, normed_f16=True)
+            else:
+                ops.gemv(it, l.down, self.ws, out=partial, f32_out=True, x_f16=True)
+                torch.distributed.all_reduce(partial, group=self.group)
+                ops.add_rmsnorm(h, partial, nxt, self.eps, h_out=other, normed=normed if nxt is not None else None,
+                                normed_f16=True)
             h, other = other, h
             x = normed if nxt is not None else h
         return h
@@ -215,11 +229,13 @@ class DecodeFFNStack:
         """Capture the stack for batch B into a CUDA graph (after one eager warm-up run)."""
         if B in self._graphs:
             return self._graphs[B]
+        keep = self._h[0][:B].clone()  # the warm-up run may end in the input buffer
         self._run(B)
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             out = self._run(B)
+        self._h[0][:B].copy_(keep)
         self._graphs[B] = (g, out)
         return self._graphs[B]
 

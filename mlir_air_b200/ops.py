@@ -233,6 +233,30 @@ def ffn_decode(x, w_gateup: AwqWeight, w_down: AwqWeight, ws: Workspace, gamma=N
     return out
 
 
+def gemv_f32_push(x, w: AwqWeight, ws: Workspace, peers, slot: int, x_f16=False):
+    """This rank's f32 partial x @ w written to its send slot, every rank signalled
+    (`peers`: mlir_air_b200.peer.PeerBuffers); B <= 8."""
+    x = _x2d(x, w.K, x_f16)
+    _lib.call("awq_b200_gemv_f32_push", _ptr(x), ACT_F16 if x_f16 else ACT_BF16, _ptr(w.qweight), _ptr(w.qzeros),
+              _ptr(w.scales), peers.local_send(slot), x.shape[0], w.K, w.N, w.group_size, peers.flag_array(slot),
+              peers.world, peers.rank, _ptr(ws.buf), ws.nbytes, _stream())
+
+
+def tp_reduce_add_rmsnorm(h, peers, slot: int, ws: Workspace, gamma=None, eps=1e-5, h_out=None, normed=None,
+                          normed_f16=False):
+    """Wait for every rank's partial in `slot`, h_out = bf16(h + sum of the partials in rank order),
+    and with gamma the RMSNorm of h_out."""
+    _want(h, torch.bfloat16, "h")
+    if h_out is None:
+        h_out = torch.empty_like(h)
+    if gamma is not None and normed is None:
+        normed = torch.empty(h.shape, dtype=_act_dtype(normed_f16), device=h.device)
+    _lib.call("awq_b200_tp_reduce_add_rmsnorm_act", _ptr(h), peers.send_array(slot), peers.local_flags(slot),
+              peers.world, _ptr(gamma), float(eps), _ptr(h_out), _ptr(normed), ACT_F16 if normed_f16 else ACT_BF16,
+              h.shape[0], h.shape[1], _ptr(ws.buf), _stream())
+    return h_out, normed
+
+
 class FFNStackPlan:
     """Tensor maps of a decode FFN layer stack in device memory, for ffn_stack_decode.
     `gateups`, `downs`: one AwqWeight per layer (gate/up interleaved [H, 2I], down [I, H]);

@@ -1,0 +1,90 @@
+"""Tensor-parallel decode stack on 2 GPUs: the peer-memory hand-over (awq_b200_gemv_f32_push +
+awq_b200_tp_reduce_add_rmsnorm_act) against the NCCL allreduce path and the unsharded numpy oracle.
+Needs two GPUs; skipped otherwise."""
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+from ml_dtypes import bfloat16
+
+from oracle import awq_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, H, I, L, B, out):
+    import torch.distributed as dist
+    from gpu_util import synth_awq, to_dev, to_host
+    from mlir_air_b200 import ffn, ops
+    from mlir_air_b200.ops import AwqWeight
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        group = dist.group.WORLD
+        i0, i1 = ffn.tp_shard_bounds(I, world)[rank]
+        layers, full = [], []
+        for l in range(L):
+            gate = synth_awq(H, I, 128, seed=10 * l)
+            up = synth_awq(H, I, 128, seed=10 * l + 1)
+            down = synth_awq(I, H, 128, seed=10 * l + 2, scale_lo=0.0005, scale_hi=0.004)
+            gamma = (np.random.default_rng(10 * l + 3).standard_normal(H) * 0.1 + 1.0).astype(bfloat16)
+            full.append((gate, up, down, gamma))
+            gu = ops.interleave_gate_up(AwqWeight.from_numpy(*gate, 128), AwqWeight.from_numpy(*up, 128))
+            layers.append(ffn.FFNLayer(ffn.shard_gateup(gu, i0, i1), ffn.shard_down(AwqWeight.from_numpy(*down, 128), i0, i1),
+                                       to_dev(gamma)))
+        x = np.random.default_rng(7).standard_normal((B, H)).astype(bfloat16)
+        push = ffn.DecodeFFNStack(layers, H, max_batch=8, group=group, peer_push=True)
+        nccl = ffn.DecodeFFNStack(layers, H, max_batch=8, group=group)
+        assert push.peers is not None and nccl.peers is None
+        y_push = to_host(push.step(to_dev(x)))
+        y_push2 = to_host(push.step(to_dev(x)))  # the slots and flags are reusable
+        push.check()
+        y_nccl = to_host(nccl.step(to_dev(x)))
+        nccl.check()
+        # replayed as a CUDA graph, twice
+        push.load_input(to_dev(x))
+        g1 = to_host(push.replay(B).clone())
+        push.load_input(to_dev(x))
+        g2 = to_host(push.replay(B).clone())
+        push.check()
+        h = x
+        for gate, up, down, gamma in full:
+            h = O.ffn_layer_A_ref(h, gamma, gate, up, down, 128)
+        out[rank] = dict(how=push.peers.how, oracle=O.rel_l2(y_push, h), again=O.rel_l2(y_push2, h),
+                         vs_nccl=O.rel_l2(y_push, y_nccl), graph1=O.rel_l2(g1, h), graph2=O.rel_l2(g2, h),
+                         nccl_oracle=O.rel_l2(y_nccl, h))
+        torch.cuda.synchronize()
+        dist.barrier()
+    except Exception:  # noqa: BLE001 -- show it before the hard exit below
+        import traceback
+        traceback.print_exc()
+    finally:
+        # captured graphs hold the communicator's collectives: leave without tearing it down
+        os._exit(0 if rank in out else 1)
+
+
+@pytest.mark.parametrize("B,H,I,L", [(8, 1024, 2816, 3), (1, 2048, 5632, 2)])
+def test_tp2_push_matches_nccl_and_oracle(B, H, I, L):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        out = mgr.dict()
+        port = 29600 + (os.getpid() + H) % 300
+        procs = [ctx.Process(target=_worker, args=(r, 2, port, H, I, L, B, out)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(300)
+        for p in procs:
+            if p.is_alive():
+                p.kill()
+        assert all(p.exitcode == 0 for p in procs), dict(out)
+        res = dict(out)
+    assert len(res) == 2, res
+    for r, d in res.items():
+        assert d["oracle"] <= 1e-2 and d["again"] <= 1e-2 and d["graph1"] <= 1e-2 and d["graph2"] <= 1e-2, res
+        assert d["vs_nccl"] <= 5e-3, res
