@@ -284,6 +284,18 @@ int awq_b200_linear_bf16(const uint16_t *x, const uint16_t *W, uint16_t *y, int 
 int awq_b200_silu_mul_bf16(const uint16_t *gate, const uint16_t *up, uint16_t *out, size_t n,
                            awq_stream_t stream);
 
+/* ---- half-split rotary embedding -----------------------------------------------------------
+ * out[b, h, i] = x[i] cos[i] - x[i + d/2] sin[i]; out[b, h, i + d/2] = x[i] sin[i] + x[i + d/2] cos[i]
+ * for every head h of d = head_dim values, f32 arithmetic, one bf16 rounding: rope_halfsplit.cc as
+ * linked by llms/llama32_1b_int4/multi_launch_builder/rms_qkv_int4_rope_multi.py:237-333, golden
+ * _rope_ref (:533-551).  x and out are [B, n_heads * head_dim] with row strides in elements (so Q
+ * and K can be rotated in place inside one [B, Nq + 2 Nkv] projection output); lut is bf16
+ * [B, head_dim], one row [cos_0 .. cos_{d/2-1} | sin_0 .. sin_{d/2-1}] per token
+ * (llama32_1b/llama32_1b_weights.py:395-440).  out may alias x. */
+int awq_b200_rope_halfsplit_bf16(const uint16_t *x, size_t x_stride, const uint16_t *lut,
+                                 uint16_t *out, size_t out_stride, int B, int n_heads,
+                                 int head_dim, awq_stream_t stream);
+
 /* ---- layout converters (once per weight) ------------------------------------------------
  * Layout B is mlir-air's logical form (matvec_int4_packed.py:346-350):
  *   A_q uint8 [M, K/2] (low nibble = even k), A_s bf16 [K/gs, M], A_z uint8 [K/gs, M], M = N.

@@ -101,6 +101,32 @@ def _run_swiglu_rms(p, args):
     return [y], [2]
 
 
+def _run_rms_qkv_rope(p, args):
+    """The 13-argument ABI of rms_qkv_int4_rope_multi.py:17-31: x_in, norm_w, normed, wq_packed, q,
+    wk_packed, k, wv_packed, v, lut_q, lut_k, q_roped, k_roped.  Q, K and V are one GEMV over the
+    concatenated weight; RoPE rotates the Q and K parts of its output."""
+    import torch
+    from . import ops
+    x_in, norm_w, _, wq_p, _, wk_p, _, wv_p, _, lut_q, lut_k, _, _ = args
+    emb, kv, hd = p["emb_dim"], p["kv_dim"], p["head_dim"]
+    tile = dict(K=emb, GS=p["GS"], M_TILE=p["M_TILE"], K_CHUNK=p["K_CHUNK"], N_CORES=p["N_CORES"])
+    ws_ = [_weight_from_gemv_tiles(tile, wq_p, emb), _weight_from_gemv_tiles(tile, wk_p, kv),
+           _weight_from_gemv_tiles(tile, wv_p, kv)]
+    w = ops.AwqWeight(torch.cat([t.qweight for t in ws_], 1).contiguous(), torch.cat([t.qzeros for t in ws_], 1).contiguous(),
+                      torch.cat([t.scales for t in ws_], 1).contiguous(), p["GS"])
+    ws = ops.Workspace(w.K, w.N)
+    normed = ops.rmsnorm(_to_dev(np.asarray(x_in).reshape(1, emb)), _to_dev(np.asarray(norm_w)), p.get("eps", 1e-5))
+    qkv = ops.gemv(normed, w, ws)
+    ws.check()
+    q, k, v = qkv[:, :emb].clone(), qkv[:, emb:emb + kv].clone(), qkv[:, emb + kv:].clone()
+    # the reference tiles one LUT row over the heads (:676-677); a token's row is its first head's
+    lut_row_q = _to_dev(np.asarray(lut_q).reshape(-1, hd)[0:1])
+    lut_row_k = _to_dev(np.asarray(lut_k).reshape(-1, hd)[0:1])
+    q_r = ops.rope_halfsplit(qkv[:, :emb], lut_row_q, p["n_heads"], hd, out=torch.empty_like(q))
+    k_r = ops.rope_halfsplit(qkv[:, emb:emb + kv], lut_row_k, p["n_kv_heads"], hd, out=torch.empty_like(k))
+    return [normed, q, k, v, q_r, k_r], [2, 4, 6, 8, 11, 12]
+
+
 def _run_matmul(p, args):
     from . import ops
     A, packed, out = args
@@ -152,6 +178,7 @@ _INSTANCES: Dict[str, Callable] = {
     "matvec_int4_packed_add": _run_matvec_add,
     "matvec_int4_swiglu_rms": _run_swiglu_rms,
     "matmul_int4_packed": _run_matmul,
+    "rms_qkv_int4_rope": _run_rms_qkv_rope,
     "ffn_swiglu_int4": _run_ffn_int4,
 }
 

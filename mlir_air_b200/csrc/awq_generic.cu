@@ -399,6 +399,43 @@ tp_reduce_add_rmsnorm_kernel(const uint16_t *__restrict__ h, const PeerPartials 
 }
 
 // =====================================================================================
+// Half-split RoPE (rope_halfsplit.cc; golden rms_qkv_int4_rope_multi.py:533-551): for every head of
+// head_dim values, out[i] = x[i] cos[i] - x[i + half] sin[i], out[i + half] = x[i] sin[i] +
+// x[i + half] cos[i], in f32 with one bf16 rounding; the LUT row of a token is [cos_0.. | sin_0..].
+// One thread per pair of 8 + 8 values (16-byte loads).
+// =====================================================================================
+__global__ void rope_halfsplit_kernel(const uint16_t *__restrict__ x, size_t x_stride, const uint16_t *__restrict__ lut,
+                                      uint16_t *__restrict__ out, size_t out_stride, int B, int n_heads, int head_dim) {
+    const int half = head_dim >> 1, chunks = half >> 3;  // 16-byte chunks in a half head
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t total = (size_t)B * n_heads * chunks;
+    if (idx >= total) return;
+    const int c = (int)(idx % chunks);
+    const int head = (int)((idx / chunks) % n_heads);
+    const int b = (int)(idx / ((size_t)chunks * n_heads));
+    const uint16_t *xr = x + (size_t)b * x_stride + (size_t)head * head_dim + 8 * c;
+    const uint16_t *lr = lut + (size_t)b * head_dim + 8 * c;
+    const uint4 a4 = *reinterpret_cast<const uint4 *>(xr), b4 = *reinterpret_cast<const uint4 *>(xr + half);
+    const uint4 c4 = *reinterpret_cast<const uint4 *>(lr), s4 = *reinterpret_cast<const uint4 *>(lr + half);
+    const uint32_t x1[4] = {a4.x, a4.y, a4.z, a4.w}, x2[4] = {b4.x, b4.y, b4.z, b4.w};
+    const uint32_t cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+    uint32_t o1[4], o2[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float a_lo = bf16x2_lo(x1[e]), a_hi = bf16x2_hi(x1[e]), b_lo = bf16x2_lo(x2[e]), b_hi = bf16x2_hi(x2[e]);
+        const float c_lo = bf16x2_lo(cs[e]), c_hi = bf16x2_hi(cs[e]), s_lo = bf16x2_lo(sn[e]), s_hi = bf16x2_hi(sn[e]);
+        // products and sums formed separately in f32, as numpy does (no fused multiply-add)
+        o1[e] = pack_bf16x2(__fsub_rn(__fmul_rn(a_lo, c_lo), __fmul_rn(b_lo, s_lo)),
+                            __fsub_rn(__fmul_rn(a_hi, c_hi), __fmul_rn(b_hi, s_hi)));
+        o2[e] = pack_bf16x2(__fadd_rn(__fmul_rn(a_lo, s_lo), __fmul_rn(b_lo, c_lo)),
+                            __fadd_rn(__fmul_rn(a_hi, s_hi), __fmul_rn(b_hi, c_hi)));
+    }
+    uint16_t *orow = out + (size_t)b * out_stride + (size_t)head * head_dim + 8 * c;
+    *reinterpret_cast<uint4 *>(orow) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+    *reinterpret_cast<uint4 *>(orow + half) = make_uint4(o2[0], o2[1], o2[2], o2[3]);
+}
+
+// =====================================================================================
 // Layout converters (once per weight; clarity over speed).
 // =====================================================================================
 // [K, I] gate + [K, I] up -> [K, 2I] with column 2i = gate_i, 2i + 1 = up_i.
@@ -607,6 +644,21 @@ extern "C" int awq_b200_tp_reduce_add_rmsnorm_act(const uint16_t *h, const void 
     return launch_tp_reduce_add_rmsnorm(h, parts, flags, gemv_push_arrivals_per_rank(K), gamma, eps, h_out,
                                         reinterpret_cast<uint16_t *>(normed), normed_format == ACT_F16 ? 1 : 0, B, K,
                                         reinterpret_cast<int *>(workspace), as_stream(stream));
+}
+
+extern "C" int awq_b200_rope_halfsplit_bf16(const uint16_t *x, size_t x_stride, const uint16_t *lut, uint16_t *out,
+                                            size_t out_stride, int B, int n_heads, int head_dim, awq_stream_t stream) {
+    AWQ_REQUIRE(B >= 0 && n_heads >= 0 && head_dim > 0, "rope: bad size");
+    AWQ_REQUIRE(head_dim % 16 == 0, "rope: head_dim (%d) must be a multiple of 16", head_dim);
+    if (B == 0 || n_heads == 0) return AWQ_OK;
+    AWQ_REQUIRE(x && lut && out, "rope: null pointer");
+    AWQ_REQUIRE(x_stride >= (size_t)n_heads * head_dim && out_stride >= (size_t)n_heads * head_dim, "rope: row stride too small");
+    AWQ_REQUIRE(aligned16(x) && aligned16(lut) && aligned16(out) && x_stride % 8 == 0 && out_stride % 8 == 0,
+                "rope: pointers and row strides must be 16-byte aligned");
+    const size_t total = (size_t)B * n_heads * (head_dim / 16);
+    rope_halfsplit_kernel<<<blocks_for(total, 256), 256, 0, as_stream(stream)>>>(x, x_stride, lut, out, out_stride, B, n_heads,
+                                                                                  head_dim);
+    return check_cuda(cudaGetLastError(), "rope launch");
 }
 
 extern "C" int awq_b200_linear_bf16(const uint16_t *x, const uint16_t *W, uint16_t *y, int M, int K, int N,

@@ -331,6 +331,27 @@ def gemm(A, w: AwqWeight, out=None):
     return out
 
 
+def rope_halfsplit(x, lut, n_heads: int, head_dim: int, out=None):
+    """Half-split RoPE of x [B, >= n_heads * head_dim] (a column slice of a wider projection output
+    is fine: the row stride is passed on) with one LUT row [cos | sin] per token; in place by default."""
+    _want(lut, torch.bfloat16, "lut")
+    if out is None:
+        out = x
+    for name, t in (("x", x), ("out", out)):
+        if not t.is_cuda or t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1 or \
+                t.shape[1] < n_heads * head_dim:
+            raise _lib.AwqBackendError(f"rope: {name} must be a CUDA bf16 [B, >= n_heads * head_dim] tensor with unit "
+                                       "column stride")
+    if out.shape[0] != x.shape[0] or lut.shape != (x.shape[0], head_dim):
+        raise _lib.AwqBackendError(f"rope: out must have {x.shape[0]} rows and lut must be [{x.shape[0]}, {head_dim}]")
+    # the stride of a one-row tensor is arbitrary (0 after numpy's None indexing): it is never used
+    xs = x.stride(0) if x.shape[0] > 1 else n_heads * head_dim
+    os_ = out.stride(0) if out.shape[0] > 1 else n_heads * head_dim
+    _lib.call("awq_b200_rope_halfsplit_bf16", x.data_ptr(), xs, _ptr(lut), out.data_ptr(), os_, x.shape[0], n_heads,
+              head_dim, _stream())
+    return out
+
+
 def linear_bf16(x, W, out=None):
     """y [M, N] = x [M, K] @ W[N, K]^T with un-quantised bf16 weights (the bf16 sibling path)."""
     _want(x, torch.bfloat16, "x")

@@ -384,6 +384,48 @@ def ffn_layer_A_ref(h, gamma, gate, up, down, group_size, eps=1e-5):
     return ffn_A_ref(h, gate, up, down, group_size, gamma=gamma, eps=eps, residual=h)
 
 
+def rms_norm_1d_ref(x, weight, eps=1e-5):
+    """bf16(x / sqrt(mean(x^2) + eps) * w): the RMSNorm golden of the QKV block
+    (rms_qkv_int4_rope_multi.py:527-530); x may be [K] or [B, K]."""
+    xf = np.asarray(x).astype(np.float32)
+    rms = np.sqrt(np.mean(xf ** 2, axis=-1, keepdims=True) + np.float32(eps))
+    return (xf / rms * np.asarray(weight).astype(np.float32)).astype(bfloat16)
+
+
+def rope_lut_ref(head_dim, rope_base, seq_len, dtype=bfloat16):
+    """[seq_len, head_dim] rows [cos(pos f_i) | sin(pos f_i)], f_i = base^(-2i / head_dim), formed in
+    f64 (llama32_1b/llama32_1b_weights.py:395-440)."""
+    inv_freq = 1.0 / (float(rope_base) ** (np.arange(0, head_dim, 2, dtype=np.float64) / head_dim))
+    ang = np.outer(np.arange(seq_len, dtype=np.float64), inv_freq)
+    return np.concatenate([np.cos(ang), np.sin(ang)], axis=1).astype(dtype)
+
+
+def rope_halfsplit_ref(x_flat, lut_flat, head_dim):
+    """Half-split RoPE over consecutive heads of head_dim values, one LUT row per head
+    (rms_qkv_int4_rope_multi.py:533-551): f32 arithmetic, one bf16 rounding."""
+    half = head_dim // 2
+    x = np.asarray(x_flat).astype(np.float32).reshape(-1, head_dim)
+    lut = np.asarray(lut_flat).astype(np.float32).reshape(-1, head_dim)
+    c, s_ = lut[:, :half], lut[:, half:]
+    x1, x2 = x[:, :half], x[:, half:]
+    out = np.empty_like(x)
+    out[:, :half] = x1 * c - x2 * s_
+    out[:, half:] = x1 * s_ + x2 * c
+    return out.astype(bfloat16).reshape(np.asarray(x_flat).shape)
+
+
+def rms_qkv_rope_A_ref(x, norm_w, wq, wk, wv, lut_rows, n_heads, n_kv_heads, head_dim, group_size, eps=1e-5):
+    """The QKV block for a batch: normed = rmsnorm(x); q, k, v = bf16(normed @ W) with layout-A weights;
+    RoPE on q and k with one LUT row per token.  Returns (q_roped, k_roped, v)."""
+    normed = rms_norm_1d_ref(x, norm_w, eps)
+    q, k, v = (gemv_A_ref(normed, *w, group_size) for w in (wq, wk, wv))
+    B = normed.shape[0]
+    lut_rows = np.asarray(lut_rows).reshape(B, head_dim)
+    q_r = rope_halfsplit_ref(q, np.repeat(lut_rows, n_heads, axis=0), head_dim)
+    k_r = rope_halfsplit_ref(k, np.repeat(lut_rows, n_kv_heads, axis=0), head_dim)
+    return q_r, k_r, v
+
+
 def rel_l2(actual, expected):
     a = np.asarray(actual).astype(np.float64).ravel()
     e = np.asarray(expected).astype(np.float64).ravel()

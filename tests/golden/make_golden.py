@@ -76,6 +76,10 @@ def main():
     mm = _import_from(os.path.join(pe, "matrix_multiplication", "int4_awq"), "matmul_int4_packed")
     dq = _import_from(os.path.join(pe, "dequant_awq"), "dequant_awq")
     fd = _import_from(os.path.join(pe, "ffn_swiglu", "decode"), "ffn_decode")
+    for extra in ("llms", os.path.join("llms", "llama32_1b"), os.path.join("llms", "llama32_1b_int4")):
+        sys.path.insert(0, os.path.join(pe, extra))
+    qkv = _import_from(os.path.join(pe, "llms", "llama32_1b_int4", "multi_launch_builder"), "rms_qkv_int4_rope_multi")
+    lw = _import_from(os.path.join(pe, "llms", "llama32_1b"), "llama32_1b_weights")
 
     def save(name, **arrs):
         out = {}
@@ -103,6 +107,34 @@ def main():
     qweight, qzeros, scales, nibs, z_nibs = rp._gen_synthetic_awq(192, 48, 64, seed=7)
     save("awq_repacker_gs64", qweight=qweight, qzeros=qzeros, scales=scales, nibs=nibs,
          z_nibs=z_nibs, w_dense=rp.dequant_to_bf16(qweight, qzeros, scales, 64))
+
+    # --- rms_qkv_int4_rope_multi.py: RMSNorm -> Q/K/V int4 GEMVs -> half-split RoPE on Q and K, its
+    #     __main__ data recipe (:640-687) at a small shape, positions 0..3 of the reference's LUT ---
+    EMB, KVD, NH, NKV, HD = 256, 64, 4, 1, 64
+    np.random.seed(42)
+    x_in = np.random.uniform(-1.0, 1.0, (EMB,)).astype(bfloat16)
+    norm_w = np.random.uniform(0.5, 1.5, (EMB,)).astype(bfloat16)
+
+    def gen_awq_weights(m, k, gs):
+        unp = np.random.randint(0, 16, size=(m, k), dtype=np.uint8)
+        a_q = (unp[:, 0::2] | (unp[:, 1::2] << 4)).astype(np.uint8)
+        a_s = np.random.uniform(0.005, 0.02, size=(k // gs, m)).astype(bfloat16)
+        a_z = np.random.randint(7, 9, size=(k // gs, m), dtype=np.uint8)
+        return a_q, a_s, a_z
+
+    wq, wk, wv = gen_awq_weights(EMB, EMB, 128), gen_awq_weights(KVD, EMB, 128), gen_awq_weights(KVD, EMB, 128)
+    cfg = lw.LlamaConfig()
+    cfg.head_dim = HD
+    lut = lw.generate_rope_lut(cfg, seq_len=4, dtype=bfloat16)
+    normed = qkv._rms_norm_ref(x_in, norm_w)
+    q_ref, k_ref, v_ref = (mv.cpu_reference(*w, normed) for w in (wq, wk, wv))
+    pos = 3
+    lut_q = np.tile(lut[pos], (NH, 1)).flatten().astype(bfloat16)
+    lut_k = np.tile(lut[pos], (NKV, 1)).flatten().astype(bfloat16)
+    save("rms_qkv_int4_rope_256", x_in=x_in, norm_w=norm_w, wq_q=wq[0], wq_s=wq[1], wq_z=wq[2], wk_q=wk[0], wk_s=wk[1],
+         wk_z=wk[2], wv_q=wv[0], wv_s=wv[1], wv_z=wv[2], lut=lut, pos=np.array(pos), normed=normed, q=q_ref, k=k_ref,
+         v=v_ref, q_roped=qkv._rope_ref(q_ref, lut_q, HD), k_roped=qkv._rope_ref(k_ref, lut_k, HD),
+         rope_base=np.array(cfg.rope_base))
 
     # --- the example scripts' seeded inputs (np.random.seed(42)), small shapes ---
     def gemv_inputs(M, K, GS, residual=False, rms=False):

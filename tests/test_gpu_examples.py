@@ -24,6 +24,7 @@ CASES = [
     ("matrix_multiplication.int4_awq.matmul_int4_packed", []),                    # 64 x 128 x 128
     ("matrix_multiplication.int4_awq.matmul_int4_packed", ["--m", "32", "--k", "2048", "--n", "2048"]),
     ("llms.llama32_1b_int4.awq_repacker", []),
+    ("llms.llama32_1b_int4.multi_launch_builder.rms_qkv_int4_rope_multi", []),   # emb 2048, kv 512, 32/8 heads of 64
 ]
 
 
