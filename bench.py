@@ -43,6 +43,7 @@ def parse():
     ap.add_argument("--unfused", action="store_true", help="per-layer kernels instead of the one-launch stack kernel")
     ap.add_argument("--peer-exchange", action="store_true",
                     help="tensor parallel: partials read from peer memory + flag words instead of an NCCL allreduce per layer")
+    ap.add_argument("--no-replicas", action="store_true", help="N > 1: skip the data-parallel measurement (extra key `replicas`)")
     ap.add_argument("--sweep", action="store_true", help="also time batch 1/8/32/64 (extra key `batches`)")
     return ap.parse_args()
 
@@ -346,6 +347,29 @@ def run_ours(a):
                    "frac_of_measured_bf16_peak": tf / pk, "frac_of_2250": tf / 2250.0, "kernel": "gemm_tc_kernel (tcgen05)"}
         del wp, Ap, Cp
 
+    # ---- the other way to use N GPUs (extra key, not the headline): every rank holds the whole stack
+    #      and decodes its own batch; no exchange at all, per-GPU work fixed ("weak" scaling) ----
+    replicas = None
+    if world > 1 and not a.no_replicas:
+        full = [ffn.random_layer(a.hidden, a.intermediate, seed=1000 + l) for l in range(a.layers)]
+        rstack = ffn.DecodeFFNStack(full, a.hidden, max_batch=max(8, B), fused=not a.unfused)
+        rstack.capture(B)
+        rstack.load_input(x_dev)
+        for _ in range(3):
+            rstack.replay(B)
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(a.steps):
+            rstack.replay(B)
+        e1.record()
+        sync_all()
+        rms = max_over_ranks(e0.elapsed_time(e1)) / a.steps
+        rstack.check()
+        replicas = {"value": world * B / (rms * 1e-3), "unit": UNIT, "ms_per_step": rms, "scaling": "weak",
+                    "global_batch": world * B, "parallelism": f"{world} replicas of the whole stack, no exchange"}
+        del rstack, full
+
     batches = None
     if a.sweep:
         batches = {}
@@ -387,6 +411,8 @@ def run_ours(a):
         "stack_hbm": {"achieved": stack_gbs, "unit": "GB/s", "frac": stack_gbs / peak, "frac_of_8TBs": stack_gbs / 8000.0,
                       "bytes_per_step_per_gpu": stack_bytes},
     }
+    if replicas:
+        line["replicas"] = replicas
     if batches:
         line["batches"] = batches
     if prefill:
