@@ -171,7 +171,23 @@ def _run_ffn_bf16(p, args):
     return [g, u, t, y], [2, 3, 4, 5]
 
 
+def _run_matvec_bf16(p, args):
+    """A bf16 [M, K], B bf16 [K], C bf16 [M] (matrix_vector_multiplication/bf16/matvec.py)."""
+    from . import ops
+    A, B, out = args
+    y = ops.linear_bf16(_to_dev(np.asarray(B).reshape(1, p["K"])), _to_dev(np.asarray(A).reshape(p["M"], p["K"])))
+    return [y], [2]
+
+
+def _run_silu_and_mul(p, args):
+    from . import ops
+    gate, up, out = args
+    return [ops.silu_mul(_to_dev(np.asarray(gate).reshape(-1)), _to_dev(np.asarray(up).reshape(-1)))], [2]
+
+
 _INSTANCES: Dict[str, Callable] = {
+    "matvec_bf16": _run_matvec_bf16,
+    "silu_and_mul": _run_silu_and_mul,
     "ffn_swiglu": _run_ffn_bf16,
     "dequant": _run_dequant,
     "matvec_int4_packed": _run_matvec,

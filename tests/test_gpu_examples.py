@@ -24,7 +24,10 @@ CASES = [
     ("matrix_multiplication.int4_awq.matmul_int4_packed", []),                    # 64 x 128 x 128
     ("matrix_multiplication.int4_awq.matmul_int4_packed", ["--m", "32", "--k", "2048", "--n", "2048"]),
     ("llms.llama32_1b_int4.awq_repacker", []),
-    ("llms.llama32_1b_int4.multi_launch_builder.rms_qkv_int4_rope_multi", []),   # emb 2048, kv 512, 32/8 heads of 64
+    ("llms.llama32_1b_int4.multi_launch_builder.rms_qkv_int4_rope_multi", []),
+    ("matrix_vector_multiplication.bf16.matvec", []),                            # 2048 x 8192, bf16 sibling
+    ("matrix_vector_multiplication.bf16.matvec", ["--m", "512", "--k", "2048", "--perf-iters", "3"]),
+    ("silu_and_mul.silu_and_mul", []),                                            # n = 65536   # emb 2048, kv 512, 32/8 heads of 64
 ]
 
 
