@@ -407,11 +407,7 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
                     // counter; the one that completes the count reads the total and leaves both zero
                     const size_t lane_off = (size_t)cw * 512 + b * 64 + (g8 >> 1) * 8;
                     float *acc_ptr = a.accum + (size_t)v * SK_PARTIAL_FLOATS + lane_off;
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        red_add_v4(acc_ptr + 32 * h, own[h][0], own[h][1], own[h][2], own[h][3]);
-                        red_add_v4(acc_ptr + 32 * h + 4, own[h][4], own[h][5], own[h][6], own[h][7]);
-                    }
+                    sk_red_partial(acc_ptr, own, lane);
                     __threadfence();
                     __syncwarp();
                     int old = 0;

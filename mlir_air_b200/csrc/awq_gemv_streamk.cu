@@ -163,11 +163,7 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             // every contributor adds its partial into the strip's f32 accumulator with vector
             // reductions at L2; the last one reads the total and leaves the accumulator zero
             float *acc_ptr = accum + (size_t)v * SK_PARTIAL_FLOATS + lane_off;
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                red_add_v4(acc_ptr + 32 * h, own[h][0], own[h][1], own[h][2], own[h][3]);
-                red_add_v4(acc_ptr + 32 * h + 4, own[h][4], own[h][5], own[h][6], own[h][7]);
-            }
+            sk_red_partial(acc_ptr, own, lane);
             __threadfence();
             __syncwarp();
             int old = 0;

@@ -144,6 +144,28 @@ __device__ __forceinline__ void sk_epilogue(const float (&own)[2][8], const uint
 }
 
 
+// Add a lane's partial (own[h][0..7] = 8 consecutive columns at acc_ptr + 32 h) into the strip's f32
+// accumulator with vector reductions at L2.  Lanes L and L ^ 8 hold neighbouring 32-byte sectors;
+// they swap half a sector first so that each reduction instruction carries whole sectors (the two
+// 16-byte pieces of a sector travel in the same instruction) instead of 32 half sectors.
+__device__ __forceinline__ void sk_red_partial(float *acc_ptr, const float (&own)[2][8], int lane) {
+    const bool upper = (lane & 8) != 0;  // this lane's sector is the second of the pair
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float recv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) recv[i] = __shfl_xor_sync(0xffffffffu, upper ? own[h][i] : own[h][4 + i], 8);
+        float *mine = acc_ptr + 32 * h;  // this lane's sector; the partner's is 8 floats away
+        if (!upper) {
+            red_add_v4(mine, own[h][0], own[h][1], own[h][2], own[h][3]);      // first half of the lower sector
+            red_add_v4(mine + 8, recv[0], recv[1], recv[2], recv[3]);          // first half of the upper sector
+        } else {
+            red_add_v4(mine - 4, recv[0], recv[1], recv[2], recv[3]);          // second half of the lower sector
+            red_add_v4(mine + 4, own[h][4], own[h][5], own[h][6], own[h][7]);  // second half of the upper sector
+        }
+    }
+}
+
 // After a warp has stored a finished sub-strip with EPI_F32_PUSH.  Sub-strips are counted on this
 // GPU first (`local_done`, zero between launches); the warp that finishes the launch's last one makes
 // everything visible to the other GPUs with ONE system-scope fence (the fence is cumulative: it
