@@ -267,6 +267,17 @@ int awq_b200_gemm_bf16(const uint16_t *A, const int32_t *qweight, const int32_t 
                        const uint16_t *scales, uint16_t *C, int M, int K, int N, int group_size,
                        awq_stream_t stream);
 
+/* The same GEMM with the decode block's epilogues, for token batches too large for the GEMV kernel
+ * (M = batch, the batched-decode golden of matmul_int4_packed.py:97-105):
+ *   swiglu != 0: W is gate/up column-interleaved [K, N]; C bf16 [M, N/2] = swiglu(bf16(sum_2i), bf16(sum_2i+1))
+ *                with the rounding points of matvec_int4_swiglu_rms.py:511-516;
+ *   residual != NULL: C bf16 [M, N] = bf16(sum + residual), residual bf16 [M, N] joining the f32 sum
+ *                before the one rounding (matvec_int4_packed_add.py:313-319).
+ * Tensor-core kernel only (AWQ_ERR_UNSUPPORTED where it does not apply). */
+int awq_b200_gemm_fused_bf16(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros,
+                             const uint16_t *scales, const uint16_t *residual, uint16_t *C, int swiglu,
+                             int M, int K, int N, int group_size, awq_stream_t stream);
+
 /* Synchronise `stream` and report whether the tensor-core GEMM gave up on a bounded device-side
  * wait since the last check (AWQ_ERR_DEVICE_TIMEOUT); the counterpart of xrt.py:204-218. */
 int awq_b200_gemm_check(awq_stream_t stream);

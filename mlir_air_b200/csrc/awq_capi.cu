@@ -284,4 +284,20 @@ extern "C" int awq_b200_gemm_bf16(const uint16_t *A, const int32_t *qweight, con
     return launch_gemm_generic(A, qweight, qzeros, scales, C, M, K, N, group_size, as_stream(stream));
 }
 
+extern "C" int awq_b200_gemm_fused_bf16(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros,
+                                        const uint16_t *scales, const uint16_t *residual, uint16_t *C, int swiglu, int M,
+                                        int K, int N, int group_size, awq_stream_t stream) {
+    AWQ_REQUIRE(M >= 0 && K > 0 && N > 0 && group_size > 0, "gemm_fused: bad size");
+    AWQ_REQUIRE(!(swiglu && residual), "gemm_fused: SwiGLU and residual do not combine");
+    if (M == 0) return AWQ_OK;
+    AWQ_REQUIRE(A && qweight && qzeros && scales && C, "gemm_fused: null pointer");
+    AWQ_REQUIRE(aligned16(A) && aligned16(scales) && aligned16(qweight) && aligned16(qzeros) && aligned16(C) &&
+                    aligned16(residual), "gemm_fused: pointers must be 16-byte aligned");
+    if (!gemm_tc_supported(M, K, N, group_size) || g_gemm_mode.load() == 1)
+        return set_error(AWQ_ERR_UNSUPPORTED, "gemm_fused: needs the tensor-core kernel (group 128, K %% 128 == 0, N %% 32 == 0; "
+                         "M=%d K=%d N=%d gs=%d)", M, K, N, group_size);
+    return launch_gemm_tc(A, qweight, qzeros, scales, C, M, K, N, group_size, as_stream(stream),
+                          swiglu ? GEMM_EPI_SWIGLU : (residual ? GEMM_EPI_RESIDUAL : GEMM_EPI_BF16), residual);
+}
+
 extern "C" int awq_b200_gemm_check(awq_stream_t stream) { return gemm_tc_check(as_stream(stream)); }

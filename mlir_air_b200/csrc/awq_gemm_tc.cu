@@ -41,6 +41,7 @@ int encode_tensor_map_2d(CUtensorMap *map, int dtype, const void *base, uint64_t
 
 constexpr int TC_BM = 128, TC_BN = 256, TC_BK = 64, TC_GROUP = 128;
 constexpr int TC_STAGES = 3;
+constexpr int TC_PREFETCH = 12;  // k-blocks of packed words requested into L2 ahead of the ring
 constexpr int TC_A_BYTES = 2 * TC_BM * TC_BK * 2;    // 32 KB: room for two 128-row A tiles
 constexpr int TC_B_BYTES = TC_BN * TC_BK * 2;        // 32 KB
 constexpr int TC_W_BYTES = TC_BK * (TC_BN / 8) * 4;  // 8 KB of packed words
@@ -99,6 +100,9 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
           "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr)
         : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap *map, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -168,7 +172,7 @@ template <int MT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
                const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmZ,
-               uint16_t *__restrict__ C, int M, int N, int K, int ML, int P) {
+               uint16_t *__restrict__ C, const uint16_t *__restrict__ R, int epi, int M, int N, int K, int ML, int P) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -219,7 +223,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             bool ok = true;
             for (TileWalk tw(ML, P, m_blocks, n_atoms); tw.valid() && ok; tw.next()) {
                 const int m0 = tw.mb * (MT * TC_BM), n0 = tw.a * 64;
+                // With few rows (decode batches) the packed words come from HBM, not L2, and three 8 KB
+                // boxes in flight per SM cannot cover that latency: ask L2 for them TC_PREFETCH k-blocks ahead.
+                for (int kb = 0; kb < TC_PREFETCH && kb < k_blocks; ++kb) tma_prefetch_l2_2d(&tmW, n0 / 8, kb * TC_BK);
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    if (kb + TC_PREFETCH < k_blocks) tma_prefetch_l2_2d(&tmW, n0 / 8, (kb + TC_PREFETCH) * TC_BK);
                     const int s = it % TC_STAGES, round = it / TC_STAGES;
                     if (round > 0 && !mbar_wait_bounded(empty_bar(s), (round - 1) & 1)) {
                         atomicExch(&g_gemm_error, 1);
@@ -346,12 +354,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 tmem_ld_wait();
                 const int n = n0 + 32 * c;
                 if (m < M && n < N) {  // N is a multiple of 32: a 32-column chunk is all inside or all outside
-                    uint32_t o[16];
+                    if (epi == GEMM_EPI_SWIGLU) {
+                        // columns 2i / 2i + 1 are gate_i / up_i: bf16 sums, SwiGLU, bf16 (the decode kernel's
+                        // rounding points); 16 outputs per lane into C [M, N / 2]
+                        uint32_t o[8];
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) o[i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-                    uint4 *dst = reinterpret_cast<uint4 *>(C + (size_t)m * N + n);
+                        for (int i = 0; i < 8; ++i)
+                            o[i] = (uint32_t)swiglu_bits(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1])) |
+                                   ((uint32_t)swiglu_bits(__uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])) << 16);
+                        uint4 *dst = reinterpret_cast<uint4 *>(C + (size_t)m * (N >> 1) + (n >> 1));
+                        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+                        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+                    } else {
+                        uint32_t o[16];
+                        if (epi == GEMM_EPI_RESIDUAL) {  // the residual joins the f32 sum before the one rounding
+                            const uint4 *rs = reinterpret_cast<const uint4 *>(R + (size_t)m * N + n);
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                            for (int i4 = 0; i4 < 4; ++i4) {
+                                const uint4 rv = rs[i4];
+                                const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+                                for (int e = 0; e < 4; ++e)
+                                    o[4 * i4 + e] = pack_bf16x2(__uint_as_float(r[8 * i4 + 2 * e]) + bf16x2_lo(rw[e]),
+                                                                __uint_as_float(r[8 * i4 + 2 * e + 1]) + bf16x2_hi(rw[e]));
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i)
+                                o[i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                        }
+                        uint4 *dst = reinterpret_cast<uint4 *>(C + (size_t)m * N + n);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                    }
                 }
             }
             tc_fence_before();
@@ -374,7 +409,8 @@ bool gemm_tc_supported(int M, int K, int N, int group_size) {
 }
 
 int launch_gemm_tc(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros, const uint16_t *scales,
-                   uint16_t *C, int M, int K, int N, int group_size, cudaStream_t stream) {
+                   uint16_t *C, int M, int K, int N, int group_size, cudaStream_t stream, int epilogue,
+                   const uint16_t *residual) {
     (void)group_size;
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
@@ -410,9 +446,9 @@ int launch_gemm_tc(const uint16_t *A, const int32_t *qweight, const int32_t *qze
     if (P < 1) P = 1;
     const int ctas = ML * P;
     if (mt == 2)
-        gemm_tc_kernel<2><<<ctas, TC_THREADS, TC_SMEM_BYTES, stream>>>(tmA, tmW, tmS, tmZ, C, M, N, K, ML, P);
+        gemm_tc_kernel<2><<<ctas, TC_THREADS, TC_SMEM_BYTES, stream>>>(tmA, tmW, tmS, tmZ, C, residual, epilogue, M, N, K, ML, P);
     else
-        gemm_tc_kernel<1><<<ctas, TC_THREADS, TC_SMEM_BYTES, stream>>>(tmA, tmW, tmS, tmZ, C, M, N, K, ML, P);
+        gemm_tc_kernel<1><<<ctas, TC_THREADS, TC_SMEM_BYTES, stream>>>(tmA, tmW, tmS, tmZ, C, residual, epilogue, M, N, K, ML, P);
     return check_cuda(cudaGetLastError(), "tensor-core gemm launch");
 }
 

@@ -319,11 +319,22 @@ def ffn_stack_decode(plan: FFNStackPlan, x, ws: Workspace, eps=1e-5, inter=None,
     return out
 
 
-def gemm(A, w: AwqWeight, out=None):
-    """C [M, N] = A [M, K] @ W, f32 accumulate, bf16 out (prefill)."""
+def gemm(A, w: AwqWeight, out=None, residual=None, swiglu=False):
+    """C [M, N] = A [M, K] @ W, f32 accumulate, bf16 out (prefill).  With `residual` [M, N] the sum is
+    bf16(acc + residual); with `swiglu` W is gate/up-interleaved and C is [M, N/2]."""
     _want(A, torch.bfloat16, "A")
     if A.dim() != 2 or A.shape[1] != w.K:
         raise _lib.AwqBackendError(f"A must be [M, {w.K}], got {tuple(A.shape)}")
+    if residual is not None or swiglu:
+        n_out = w.N // 2 if swiglu else w.N
+        if out is None:
+            out = torch.empty((A.shape[0], n_out), dtype=torch.bfloat16, device=A.device)
+        _want(out, torch.bfloat16, "out")
+        if residual is not None:
+            _want(residual, torch.bfloat16, "residual")
+        _lib.call("awq_b200_gemm_fused_bf16", _ptr(A), _ptr(w.qweight), _ptr(w.qzeros), _ptr(w.scales), _ptr(residual),
+                  _ptr(out), 1 if swiglu else 0, A.shape[0], w.K, w.N, w.group_size, _stream())
+        return out
     if out is None:
         out = torch.empty((A.shape[0], w.N), dtype=torch.bfloat16, device=A.device)
     _lib.call("awq_b200_gemm_bf16", _ptr(A), _ptr(w.qweight), _ptr(w.qzeros), _ptr(w.scales), _ptr(out), A.shape[0],

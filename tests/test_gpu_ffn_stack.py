@@ -129,3 +129,53 @@ def test_stack_rejects_what_it_cannot_run(ops):
     # an empty batch is a no-op
     out = ops.ffn_stack_decode(plan, torch.zeros((0, H), dtype=torch.bfloat16, device="cuda"), ws)
     assert out.shape == (0, H)
+
+
+@pytest.mark.parametrize("M,K,N", [(64, 1024, 2816), (32, 512, 1024), (200, 1024, 512)])
+def test_gemm_epilogues_vs_oracle(ops, M, K, N):
+    """Tensor-core GEMM with the decode block's epilogues (batched-decode golden, M = batch):
+    residual joined before the one rounding; SwiGLU over interleaved gate/up pairs."""
+    from gpu_util import dev_weight, randn_bf16, synth_awq, to_dev, to_host
+    ops.set_gemm_kernel("tc")
+    try:
+        A = randn_bf16((M, K), seed=1)
+        w = synth_awq(K, N, 128, seed=2)
+        R = randn_bf16((M, N), seed=3)
+        y = to_host(ops.gemm(to_dev(A), dev_weight(*w), residual=to_dev(R)))
+        ops.gemm_check()
+        assert O.rel_l2(y, O.gemv_A_ref(A, *w, 128, residual=R)) <= REL_L2_TOL
+        gate, up = synth_awq(K, N // 2, 128, seed=4), synth_awq(K, N // 2, 128, seed=5)
+        wgu = ops.interleave_gate_up(dev_weight(*gate), dev_weight(*up))
+        t = to_host(ops.gemm(to_dev(A), wgu, swiglu=True))
+        ops.gemm_check()
+        assert t.shape == (M, N // 2)
+        assert O.rel_l2(t, O.gateup_swiglu_A_ref(A, gate, up, 128)) <= REL_L2_TOL
+    finally:
+        ops.set_gemm_kernel("auto")
+
+
+def test_stack_large_batch_takes_the_gemm_path(ops):
+    """Batch 40 and 64 on one GPU: two tensor-core GEMMs per layer; same results as one GEMV pass per
+    8 rows (the path batch 16 takes) and as the oracle."""
+    import torch
+    from gpu_util import randn_bf16, to_dev, to_host
+    from mlir_air_b200 import ffn
+    H, I, L = 1024, 2816, 2
+    layers_np = _layers_np(H, I, L, seed=77)
+    plan, gus, downs, gammas = _plan(ops, layers_np)
+    stack = ffn.DecodeFFNStack([ffn.FFNLayer(g, d, gm) for g, d, gm in zip(gus, downs, gammas)], H, max_batch=64)
+    assert stack.uses_gemm(40) and stack.uses_gemm(64) and not stack.uses_gemm(32)
+    assert stack.launches_per_step(64) == 3 * L
+    for B in (40, 64):
+        x = randn_bf16((B, H), seed=B)
+        y = to_host(stack.step(to_dev(x)))
+        ops.gemm_check()
+        assert O.rel_l2(y, _oracle_stack(x, layers_np)) <= REL_L2_TOL
+        # the GEMV path on the same rows, 16 at a time
+        parts = [to_host(stack.step(to_dev(x[i:i + 8]))) for i in range(0, B, 8)]
+        # the GEMM multiplies bf16-rounded weights, the GEMV keeps (q - z) s in f32: both inside the bar
+        assert O.rel_l2(y, np.concatenate(parts, 0)) <= REL_L2_TOL
+        stack.load_input(to_dev(x))
+        g1 = to_host(stack.replay(B).clone())
+        assert O.rel_l2(g1, _oracle_stack(x, layers_np)) <= REL_L2_TOL
+    stack.check()

@@ -97,6 +97,7 @@ def test_stack_launch_accounting():
     s = ffn.DecodeFFNStack.__new__(ffn.DecodeFFNStack)
     s.layers, s.tp, s.plan = [None] * 80, 1, None
     assert s.launches_per_step(8) == 240 and s.launches_per_step(16) == 80 * 5
+    s.uses_gemm = lambda batch: False
     s.plan = object()  # with a fused plan: one launch for up to 8 rows, per-layer kernels beyond
     assert s.launches_per_step(8) == 1 and s.launches_per_step(16) == 80 * 5
     s.plan = None
