@@ -4,7 +4,7 @@
     python bench.py --gpus N --steps K --warmup W            # this library, TP = N
     python bench.py --impl reference --gpus N ...            # the numpy golden path on host cores
 
-Workload (BASELINE.json configs[4]): hidden 8192, intermediate 28672, 80 random-init AWQ-int4
+Workload (the fifth configuration of the benchmark definition): hidden 8192, intermediate 28672, 80 random-init AWQ-int4
 layers (group 128, scales ~U(0.001, 0.02)), residual add per layer, batch 8 tokens by default;
 TP = N with one allreduce after each down projection.  One step = one pass of the whole stack
 over one token batch.  Prints ONE JSON line (see the keys below).
@@ -49,7 +49,7 @@ def parse():
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per layer of the stack kernel at hidden 8192 / intermediate
-# 28672 / batch 8: ncu capture of a 2-layer launch, halved (profiles/ffn_fused_70b_stack.md)
+# 28672 / batch 8: ncu capture of a 2-layer launch, halved (the committed ncu summary of that kernel)
 FUSED_TRAFFIC_PER_LAYER = 370400128
 
 
@@ -304,7 +304,7 @@ def run_ours(a):
                 "achieved": achieved, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
                 "frac_of_8TBs": achieved / 8000.0, "us_per_launch": gu_us, "bytes_per_launch": gu_bytes / passes,
                 # dram__bytes_read.sum + dram__bytes_write.sum of one launch at this exact shape
-                # (profiles/gemv_streamk_70b_ffn_layer.md); other shapes were not captured
+                # (the committed ncu summary of that kernel); other shapes were not captured
                 "traffic": 249810432 if (a.hidden, il, B) == (8192, 28672, 8) else None}
     stack_bytes = stack.weight_bytes + a.layers * 4 * B * a.hidden * 2
     stack_gbs = stack_bytes / (ms_step * 1e-3) / 1e9
@@ -313,13 +313,13 @@ def run_ours(a):
         roofline = {"bound": "hbm", "kernel": "ffn_fused_kernel (all layers of the stack in one launch)",
                     "achieved": stack_gbs, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": stack_gbs / peak,
                     "frac_of_8TBs": stack_gbs / 8000.0, "us_per_launch": ms_step * 1e3, "bytes_per_launch": stack_bytes,
-                    # dram bytes of a 2-layer launch scaled by the layer count (profiles/ffn_fused_70b_stack.md)
+                    # dram bytes of a 2-layer launch scaled by the layer count
                     "traffic": FUSED_TRAFFIC_PER_LAYER * a.layers
                     if FUSED_TRAFFIC_PER_LAYER and (a.hidden, il, B) == (8192, 28672, 8) else None}
     else:
         roofline = gateup_kernel
 
-    # ---- prefill int4 GEMM (BASELINE configs[3]) on this GPU: extra key, not the headline ----
+    # ---- prefill int4 GEMM (the fourth configuration: 2048 x 4096 x 14336) on this GPU: extra key, not the headline ----
     prefill = None
     if not a.no_prefill:
         Mp, Kp, Np = 2048, 4096, 14336

@@ -80,7 +80,7 @@ class FFNLayer:
 
 def random_layer(hidden: int, intermediate: int, seed: int, device="cuda", group_size: int = 128,
                  bounds: Optional[Tuple[int, int]] = None, with_gamma: bool = True) -> FFNLayer:
-    """Random-init AWQ layer with the BASELINE distributions (nibbles and zeros uniform 0..15,
+    """Random-init AWQ layer with the benchmark's distributions (nibbles and zeros uniform 0..15,
     scales ~U(0.001, 0.02), gamma ~ 1 + 0.1 N(0,1)), generated on the device.  With `bounds`
     only the [i0, i1) shard of the intermediate dimension is generated."""
     gen = torch.Generator(device=device)

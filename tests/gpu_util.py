@@ -21,7 +21,7 @@ def to_host(t):
 
 
 def synth_awq(K, N, gs=128, seed=0, scale_lo=0.001, scale_hi=0.02):
-    """Seeded layout-A tensors with BASELINE's distributions: nibbles and zero nibbles
+    """Seeded layout-A tensors with the benchmark's distributions: nibbles and zero nibbles
     uniform 0..15, scales ~U(lo, hi) rounded to bf16."""
     rng = np.random.default_rng(seed)
     nibs = rng.integers(0, 16, size=(K, N), dtype=np.uint8)

@@ -12,7 +12,7 @@ PE = "mlir_air_b200.programming_examples."
 
 CASES = [
     ("dequant_awq.dequant_awq", []),                                              # N=1024, gs=128, herd 4
-    ("dequant_awq.dequant_awq", ["--hf", "2048", "2048"]),                        # BASELINE config 1
+    ("dequant_awq.dequant_awq", ["--hf", "2048", "2048"]),                        # benchmark configuration 1
     ("matrix_vector_multiplication.int4_awq.matvec_int4_packed", []),            # 2048 x 2048 (lit shape)
     ("matrix_vector_multiplication.int4_awq.matvec_int4_packed", ["--k", "8192", "--k-chunk", "2048"]),
     ("matrix_vector_multiplication.int4_awq.matvec_int4_packed", ["--m", "1024", "--k", "512", "--batch", "8"]),

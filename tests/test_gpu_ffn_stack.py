@@ -9,7 +9,7 @@ from oracle import awq_oracle as O
 
 pytestmark = pytest.mark.gpu
 
-REL_L2_TOL = 1e-2  # BASELINE north_star tolerance for GEMV / FFN outputs
+REL_L2_TOL = 1e-2  # the benchmark definition's tolerance for GEMV / FFN outputs
 
 
 @pytest.fixture(scope="module")
@@ -79,7 +79,7 @@ def test_stack_vs_oracle(ops, B, H, I, L):
 
 
 def test_stack_llama70b_dims_matches_per_layer_kernels(ops):
-    """BASELINE config 5 dims (hidden 8192, intermediate 28672), 3 layers, batch 8 and 1: the
+    """Benchmark configuration 5 dims (hidden 8192, intermediate 28672), 3 layers, batch 8 and 1: the
     fused launch against the same stack run layer by layer, eager and as a replayed CUDA graph."""
     import torch
     from mlir_air_b200 import ffn

@@ -12,7 +12,7 @@ from gpu_util import to_dev, to_host, synth_awq, dev_weight, randn_bf16
 
 pytestmark = pytest.mark.gpu
 
-REL_L2_TOL = 1e-2  # BASELINE north_star tolerance for GEMV / GEMM / FFN outputs
+REL_L2_TOL = 1e-2  # the benchmark definition's tolerance for GEMV / GEMM / FFN outputs
 
 
 @pytest.fixture(scope="module")
@@ -139,7 +139,7 @@ def test_gemv_vs_oracle(ops, kernel, B, K, N):
 
 
 def test_gemv_cfg2_full_size(ops):
-    """BASELINE config 2: [B, 4096] x [4096, 11008], B = 1 and 8."""
+    """Benchmark configuration 2: [B, 4096] x [4096, 11008], B = 1 and 8."""
     qw, qz, s = synth_awq(4096, 11008, 128, seed=0)
     wf = O.dequant_f32(qw, qz, s, 128)
     w = dev_weight(qw, qz, s)
@@ -275,7 +275,7 @@ def test_ffn_decode_vs_oracle(ops, kernel, B, H, I):
 
 
 def test_ffn_cfg3_full_size(ops):
-    """BASELINE config 3: hidden 4096, intermediate 11008, batch 1 / 4 / 16."""
+    """Benchmark configuration 3: hidden 4096, intermediate 11008, batch 1 / 4 / 16."""
     H, I = 4096, 11008
     gate, up, down = _ffn_weights(H, I, seed=0)
     wgu = ops.interleave_gate_up(dev_weight(*gate), dev_weight(*up))
@@ -379,7 +379,7 @@ def test_gemm_tensor_core_kernel(ops, M, K, N):
 
 
 def test_gemm_cfg4_full_size(ops):
-    """BASELINE config 4: [2048, 4096] x [4096, 14336]."""
+    """Benchmark configuration 4: [2048, 4096] x [4096, 14336]."""
     M, K, N = 2048, 4096, 14336
     qw, qz, s = synth_awq(K, N, 128, seed=0)
     A = randn_bf16((M, K), seed=1)
