@@ -397,7 +397,10 @@ def run_ours(a):
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
         "config": {"workload": workload_name(a), "parallelism": f"tp{tp}",
-                   "exchange": ("none" if tp == 1 else "peer loads from every rank's send buffer + flag words"
+                   "exchange": ("none" if tp == 1 else
+                                "inside the stack kernel: f32 partials in peer-mapped send buffers, flag words, peer loads"
+                                if stack.uses_fused(B) else
+                                "peer loads from every rank's send buffer + flag words"
                                 if stack.peers is not None and B <= 8 else "NCCL allreduce per layer"),
                    "l2": "inputs_exceed_l2 (weights streamed once per step)",
                    "launch": ("one CUDA graph per step: one launch of the stack kernel" if stack.uses_fused(B)

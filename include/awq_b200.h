@@ -259,6 +259,25 @@ int awq_b200_ffn_stack_decode_bf16(const void *plan, int n_layers, const uint16_
                                    int group_size, void *workspace, size_t workspace_bytes,
                                    awq_stream_t stream);
 
+/* The same launch for tensor-parallel ranks (one process per GPU): the plan describes this rank's
+ * shards (gate/up columns [H, 2 I_local], down rows [I_local, H], cut as in the per-layer path),
+ * and after each layer's down projection the ranks exchange their f32 partials inside the kernel:
+ * a rank writes its partial into its own send slot, signals every rank's flag words once per layer
+ * (one system-scope fence), and the reduce phase reads all ranks' partials with peer loads, in
+ * rank order.  peer_base: HOST array of n_ranks device pointers to the ranks' buffers mapped into
+ * this GPU's address space (entry `rank` is this rank's own); a buffer holds two slots of
+ * slot_stride bytes, each an f32 [8, H] partial followed at flag_offset by 16 uint32 flag words,
+ * zero when first used and owned by this entry point afterwards (the counters are never reset, the
+ * last word of slot 0 counts launches).  Every rank must make the same sequence of calls, and the
+ * kernels of the ranks wait for one another (bounded; awq_b200_workspace_check reports a timeout).
+ * No counterpart in the reference, whose only inter-GPU mechanism is its symmetric heap
+ * (runtime_lib/airgpu/symmetric_heap.cpp:172-312). */
+int awq_b200_ffn_stack_decode_tp_bf16(const void *plan, int n_layers, const uint16_t *x,
+                                      uint16_t *out, uint16_t *inter, float eps, int B, int H,
+                                      int I_local, int group_size, void *const *peer_base,
+                                      size_t slot_stride, size_t flag_offset, int n_ranks, int rank,
+                                      void *workspace, size_t workspace_bytes, awq_stream_t stream);
+
 /* ---- prefill GEMM ----------------------------------------------------------------------
  * C bf16 [M, N] = bf16(A[M, K] @ W), f32 accumulate.  Replaces
  * matmul_int4_bf16_packed_f32 / zero_vectorized_f32_mn / f32_to_bf16_mn

@@ -264,6 +264,36 @@ extern "C" int awq_b200_ffn_stack_decode_bf16(const void *plan, int n_layers, co
     return launch_ffn_fused(plan, n_layers, x, out, inter, eps, B, H, I, workspace, workspace_bytes, as_stream(stream));
 }
 
+extern "C" int awq_b200_ffn_stack_decode_tp_bf16(const void *plan, int n_layers, const uint16_t *x, uint16_t *out,
+                                                 uint16_t *inter, float eps, int B, int H, int I_local, int group_size,
+                                                 void *const *peer_base, size_t slot_stride, size_t flag_offset,
+                                                 int n_ranks, int rank, void *workspace, size_t workspace_bytes,
+                                                 awq_stream_t stream) {
+    AWQ_REQUIRE(n_layers >= 1 && B >= 0 && H > 0 && I_local > 0, "ffn_stack_decode_tp: bad size");
+    AWQ_REQUIRE(n_ranks >= 2 && n_ranks <= TP_MAX_RANKS && rank >= 0 && rank < n_ranks, "ffn_stack_decode_tp: rank %d of %d", rank,
+                n_ranks);
+    if (B == 0) return AWQ_OK;
+    AWQ_REQUIRE(plan && x && out && inter && peer_base, "ffn_stack_decode_tp: null pointer");
+    AWQ_REQUIRE(aligned16(x) && aligned16(out) && aligned16(inter), "ffn_stack_decode_tp: pointers must be 16-byte aligned");
+    AWQ_REQUIRE(flag_offset >= (size_t)8 * H * sizeof(float) && slot_stride >= flag_offset + 64 && slot_stride % 16 == 0 &&
+                    flag_offset % 16 == 0, "ffn_stack_decode_tp: a slot holds an f32 [8, H] partial and 16 flag words behind it");
+    if (!ffn_fused_supported(B, H, I_local, group_size))
+        return set_error(AWQ_ERR_UNSUPPORTED,
+                         "ffn_stack_decode_tp: needs B <= 8, group 128, H and I multiples of 128 (B=%d H=%d I=%d gs=%d)", B, H,
+                         I_local, group_size);
+    FusedPeers peers{};
+    peers.n = n_ranks;
+    peers.rank = rank;
+    peers.slot_stride = slot_stride;
+    peers.flag_offset = flag_offset;
+    for (int r = 0; r < n_ranks; ++r) {
+        AWQ_REQUIRE(peer_base[r] && aligned16(peer_base[r]), "ffn_stack_decode_tp: bad buffer pointer of rank %d", r);
+        peers.base[r] = peer_base[r];
+    }
+    return launch_ffn_fused(plan, n_layers, x, out, inter, eps, B, H, I_local, workspace, workspace_bytes, as_stream(stream),
+                            &peers);
+}
+
 extern "C" int awq_b200_gemm_bf16(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros,
                                   const uint16_t *scales, uint16_t *C, int M, int K, int N, int group_size,
                                   awq_stream_t stream) {

@@ -161,7 +161,15 @@ int ffn_fused_plan(void *plan_dev, size_t plan_bytes, int n_layers, const int32_
                    const int32_t *const *qz_gateup, const uint16_t *const *s_gateup, const int32_t *const *qw_down,
                    const int32_t *const *qz_down, const uint16_t *const *s_down, const uint16_t *const *gamma, int H, int I,
                    int group_size);
+// Peer-mapped buffers of the tensor-parallel stack kernel: base[r] is rank r's buffer (two slots
+// of `slot_stride` bytes: an f32 [8, H] partial, then at `flag_offset` 16 uint32 flag words).
+struct FusedPeers {
+    void *base[TP_MAX_RANKS];
+    size_t slot_stride, flag_offset;
+    int n, rank;
+};
 int launch_ffn_fused(const void *plan_dev, int n_layers, const uint16_t *x, uint16_t *out, uint16_t *inter, float eps, int B,
-                     int H, int I, void *workspace, size_t workspace_bytes, cudaStream_t stream);
+                     int H, int I, void *workspace, size_t workspace_bytes, cudaStream_t stream,
+                     const FusedPeers *peers = nullptr);
 
 }  // namespace awq

@@ -64,6 +64,11 @@ __device__ __forceinline__ int ld_acquire_gpu(const int *p) {
     asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int *p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
 // Wait until *ctr >= target; gives up after about a second.
@@ -117,7 +122,16 @@ struct FusedArgs {
     float *accum;   // per-strip split-K accumulators (zero between uses)
     int *counters;  // per sub-strip counters of the k groups added so far (zero between uses)
     int *err_flag;
-    int *state;     // done_gu, done_d, ..., then sumsq[(n_layers + 1) * 8]
+    int *state;     // done_gu, done_d, done_r, ..., then sumsq[(n_layers + 1) * 8]
+    // Tensor parallelism (tp_n > 1): this rank holds a shard of every layer (gate/up columns, down
+    // rows); the down phase leaves an f32 partial [8, H] in this rank's send slot l & 1, the ranks
+    // tell one another through flag words, and the reduce phase reads all ranks' partials with peer loads.
+    int tp_n, tp_rank;
+    float *partial[2];                         // this rank's send slots
+    const float *peer_partial[2][TP_MAX_RANKS];  // every rank's send slots, mapped into this GPU's address space
+    unsigned int *peer_flags[2][TP_MAX_RANKS];   // rank r's arrival counters [TP_MAX_RANKS] of slot s (never reset)
+    unsigned int *flags[2];                    // this rank's arrival counters of slot s
+    unsigned int *epoch;                       // launches so far on this rank (the counters' base)
 };
 
 // The unit range [u0, u1) of one half in one phase: the SM's range [s U / S, (s + 1) U / S), cut.
@@ -186,7 +200,8 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
     // phase 0: gate/up, K = H, N = 2I; phase 1: down, K = I, N = H
     const int G0 = H / SK_GROUP, V0 = (2 * I + SK_STRIP - 1) / SK_STRIP;
     const int G1 = I / SK_GROUP, V1 = (H + SK_STRIP - 1) / SK_STRIP;
-    int *done_gu = a.state, *done_d = a.state + 1;
+    int *done_gu = a.state, *done_d = a.state + 1, *done_r = a.state + 2;
+    const bool tp = a.tp_n > 1;
     float *sumsq = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(a.state) + FF_STATE_HEADER);
 
     if (role == 1 && lane == 0) {  // each loader sets up its half's barriers
@@ -300,8 +315,12 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
                 cur.next();
             }
             // the phase's activations exist once every sub-strip of the previous phase is finalised
-            const int target = p ? (l + 1) * V0 * SK_CONSUMER_WARPS : B + l * V1 * SK_CONSUMER_WARPS;
-            if (!wait_count(p ? done_gu : done_d, target)) {
+            // (tensor parallel: a gate/up phase waits for the reduce phase of the previous layer instead,
+            // which every normaliser warp of the launch counts in done_r)
+            const bool after_reduce = tp && !p && l > 0;
+            const int target = after_reduce ? l * 2 * (int)gridDim.x
+                                            : (p ? (l + 1) * V0 * SK_CONSUMER_WARPS : B + l * V1 * SK_CONSUMER_WARPS);
+            if (!wait_count(after_reduce ? done_r : (p ? done_gu : done_d), target)) {
                 atomicExch(a.err_flag, 3);
                 return;
             }
@@ -330,6 +349,7 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
         // the 128B-swizzled [8 x 64] box pair put them; bf16 rounding, then the fp16 form
         const int r = lane >> 2, q4 = lane & 3;
         int slot = 0, round = 0;
+        const unsigned int epoch0 = tp ? *a.epoch : 0u;  // every warp reads it before anything of this launch ends
         for (int l = 0; l < a.n_layers; ++l) {
             for (int p = 0; p < 2; ++p) {
                 long long u0, u1;
@@ -371,8 +391,79 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
                     }
                     if (++slot == SK_STAGES) { slot = 0; ++round; }
                 }
+                if (tp && p) {
+                    // ---- reduce phase: h <- bf16(h + sum over ranks of the down partials), in rank order ----
+                    const int sl = l & 1;
+                    // slot sl has been used (l >> 1) + 1 times in this launch and by every earlier launch
+                    const unsigned int uses_per_launch = (unsigned int)(sl ? a.n_layers / 2 : (a.n_layers + 1) / 2);
+                    const unsigned int expected = epoch0 * uses_per_launch + (unsigned int)(l >> 1) + 1u;
+                    int good = 1;
+                    if (lane < a.tp_n) {
+                        const long long t0 = clock64();
+                        while (ld_acquire_sys_u32(a.flags[sl] + lane) < expected) {
+                            if (clock64() - t0 > (1ll << 31)) {
+                                good = 0;
+                                break;
+                            }
+                            __nanosleep(64);
+                        }
+                    }
+                    if (!__all_sync(0xffffffffu, good)) {
+                        if (lane == 0) atomicExch(a.err_flag, 6);
+                        return;
+                    }
+                    const uint16_t *hres = l == 0 ? a.x : a.out;
+                    const long long W = 2 * (long long)gridDim.x, gw = 2 * (long long)blockIdx.x + half;
+                    const long long chunks = (long long)B * (H >> 3);  // 8 values each, rows 0 .. B-1
+                    const long long c0 = gw * chunks / W, c1 = (gw + 1) * chunks / W;
+                    const int row_first = (int)(c0 / (H >> 3));
+                    // squares for row_first and for the next row; a slice that spans more rows (tiny grids)
+                    // adds every chunk's squares on its own
+                    const bool two_rows = c1 <= c0 || (int)((c1 - 1) / (H >> 3)) - row_first <= 1;
+                    float ss0 = 0.f, ss1 = 0.f;
+                    for (long long c = c0 + lane; c < c1; c += 32) {
+                        const size_t e = (size_t)c * 8;
+                        float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                        for (int rk = 0; rk < a.tp_n; ++rk) {
+                            const float *src = a.peer_partial[sl][rk] + e;
+                            const float4 p0 = __ldcg(reinterpret_cast<const float4 *>(src));
+                            const float4 p1 = __ldcg(reinterpret_cast<const float4 *>(src + 4));
+                            sum[0] += p0.x; sum[1] += p0.y; sum[2] += p0.z; sum[3] += p0.w;
+                            sum[4] += p1.x; sum[5] += p1.y; sum[6] += p1.z; sum[7] += p1.w;
+                        }
+                        const uint4 hv = __ldcg(reinterpret_cast<const uint4 *>(hres + e));
+                        const uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w};
+                        uint32_t o[4];
+                        float ss = 0.f;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            o[i] = pack_bf16x2(bf16x2_lo(hw[i]) + sum[2 * i], bf16x2_hi(hw[i]) + sum[2 * i + 1]);
+                            const float lo = bf16x2_lo(o[i]), hi = bf16x2_hi(o[i]);
+                            ss = fmaf(lo, lo, ss);
+                            ss = fmaf(hi, hi, ss);
+                        }
+                        *reinterpret_cast<uint4 *>(a.out + e) = make_uint4(o[0], o[1], o[2], o[3]);
+                        const int row = (int)(c / (H >> 3));
+                        if (!two_rows) atomicAdd(sumsq + (size_t)(l + 1) * 8 + row, ss);
+                        else if (row == row_first) ss0 += ss;
+                        else ss1 += ss;
+                    }
+#pragma unroll
+                    for (int o_ = 16; o_ > 0; o_ >>= 1) {
+                        ss0 += __shfl_xor_sync(0xffffffffu, ss0, o_);
+                        ss1 += __shfl_xor_sync(0xffffffffu, ss1, o_);
+                    }
+                    if (lane == 0 && c1 > c0 && two_rows) {
+                        atomicAdd(sumsq + (size_t)(l + 1) * 8 + row_first, ss0);
+                        if (row_first + 1 < B) atomicAdd(sumsq + (size_t)(l + 1) * 8 + row_first + 1, ss1);
+                    }
+                    __threadfence();
+                    __syncwarp();
+                    if (lane == 0) atomicAdd(done_r, 1);
+                }
             }
         }
+        if (tp && blockIdx.x == 0 && half == 0 && lane == 0) *a.epoch = epoch0 + 1u;
         return;
     }
 
@@ -430,6 +521,20 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
                 if (failed) return;
                 if (!p) {
                     sk_epilogue<EPI_SWIGLU>(own, nullptr, a.inter, B, N, n, b, 1);
+                } else if (tp) {
+                    // this rank's partial goes to its send slot; the warp that completes the phase on this
+                    // GPU makes it visible to the other GPUs (one cumulative system-scope fence) and
+                    // counts this rank in on every rank
+                    sk_epilogue<EPI_F32>(own, nullptr, a.partial[l & 1], B, N, n, b, 0);
+                    __threadfence();
+                    __syncwarp();
+                    int last = 0;
+                    if (lane == 0) last = atomicAdd(done_d, 1) + 1 == B + (l + 1) * V1 * SK_CONSUMER_WARPS;
+                    if (__shfl_sync(0xffffffffu, last, 0)) {
+                        __threadfence_system();
+                        if (lane < a.tp_n) atomicAdd_system(a.peer_flags[l & 1][lane] + a.tp_rank, 1u);
+                    }
+                    return;
                 } else {
                     // hidden state: bf16(sum + residual), and its squares for the next layer's RMSNorm
                     float ss = 0.f;
@@ -556,7 +661,7 @@ int ffn_fused_plan(void *plan_dev, size_t plan_bytes, int n_layers, const int32_
 }
 
 int launch_ffn_fused(const void *plan_dev, int n_layers, const uint16_t *x, uint16_t *out, uint16_t *inter, float eps, int B,
-                     int H, int I, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
+                     int H, int I, void *workspace, size_t workspace_bytes, cudaStream_t stream, const FusedPeers *peers) {
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] {
@@ -599,6 +704,31 @@ int launch_ffn_fused(const void *plan_dev, int n_layers, const uint16_t *x, uint
     a.I = I;
     a.lookahead = g_ffn_lookahead;
     a.split = g_ffn_split;
+    a.tp_n = 1;
+    a.tp_rank = 0;
+    a.epoch = nullptr;
+    for (int sl = 0; sl < 2; ++sl) {
+        a.partial[sl] = nullptr;
+        a.flags[sl] = nullptr;
+        for (int r = 0; r < TP_MAX_RANKS; ++r) {
+            a.peer_partial[sl][r] = nullptr;
+            a.peer_flags[sl][r] = nullptr;
+        }
+    }
+    if (peers && peers->n > 1) {
+        a.tp_n = peers->n;
+        a.tp_rank = peers->rank;
+        for (int sl = 0; sl < 2; ++sl) {
+            for (int r = 0; r < peers->n; ++r) {
+                uint8_t *base = reinterpret_cast<uint8_t *>(peers->base[r]) + (size_t)sl * peers->slot_stride;
+                a.peer_partial[sl][r] = reinterpret_cast<const float *>(base);
+                a.peer_flags[sl][r] = reinterpret_cast<unsigned int *>(base + peers->flag_offset);
+            }
+            a.partial[sl] = const_cast<float *>(a.peer_partial[sl][peers->rank]);
+            a.flags[sl] = a.peer_flags[sl][peers->rank];
+        }
+        a.epoch = a.flags[0] + 15;  // the last word of slot 0's flag block
+    }
     a.accum = reinterpret_cast<float *>(ws + SK_WS_ACCUM);
     a.counters = reinterpret_cast<int *>(ws + SK_WS_HEADER);
     a.err_flag = reinterpret_cast<int *>(ws);

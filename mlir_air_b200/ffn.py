@@ -142,11 +142,15 @@ class DecodeFFNStack:
         # one launch for the whole stack where the fused kernel applies: one GPU, every layer with
         # a norm weight, one shape, group 128, batch <= 8 (larger batches take the per-layer kernels)
         self.plan = None
-        if fused and self.tp == 1 and self._fusable():
+        self.plan_peers = None
+        if fused and self._fusable():
             self.plan = ops.FFNStackPlan([l.gateup for l in self.layers], [l.down for l in self.layers],
                                          [l.gamma for l in self.layers])
             if self.plan.workspace_bytes() > self.ws.nbytes:
                 self.plan = None
+            elif self.tp > 1:  # the ranks exchange their partials inside the launch, through these buffers
+                from .peer import PeerBuffers
+                self.plan_peers = PeerBuffers(group, 2, 8 * hidden * 4, device)
         self._pin_in = torch.empty((max_batch, hidden), dtype=torch.bfloat16).pin_memory() if torch.cuda.is_available() else None
         self._pin_out = torch.empty((max_batch, hidden), dtype=torch.bfloat16).pin_memory() if torch.cuda.is_available() else None
 
@@ -198,6 +202,8 @@ class DecodeFFNStack:
         h, other = self._h[0][:B], self._h[1][:B]
         normed, inter, partial = self._normed[:B], self._inter, self._partial[:B]
         if self.uses_fused(B):
+            if self.tp > 1:
+                return ops.ffn_stack_decode_tp(self.plan, h, self.ws, self.plan_peers, eps=self.eps, inter=inter, out=other)
             return ops.ffn_stack_decode(self.plan, h, self.ws, eps=self.eps, inter=inter, out=other)
         if self.uses_gemm(B):
             nb = self._normed[:B].view(torch.bfloat16)  # the GEMM's A operand is bf16

@@ -319,6 +319,24 @@ def ffn_stack_decode(plan: FFNStackPlan, x, ws: Workspace, eps=1e-5, inter=None,
     return out
 
 
+def ffn_stack_decode_tp(plan: FFNStackPlan, x, ws: Workspace, peers, eps=1e-5, inter=None, out=None):
+    """The one-launch stack on this rank's shards, with the partials exchanged through `peers`
+    (mlir_air_b200.peer.PeerBuffers with two slots of 8 * H * 4 bytes, used by nothing else)."""
+    x = _x2d(x, plan.H)
+    B = x.shape[0]
+    if inter is None:
+        inter = torch.empty((B, plan.I), dtype=torch.float16, device=x.device)
+    if out is None:
+        out = torch.empty((B, plan.H), dtype=torch.bfloat16, device=x.device)
+    _want(out, torch.bfloat16, "out")
+    if inter.numel() < B * plan.I or inter.element_size() != 2:
+        raise _lib.AwqBackendError("ffn_stack_decode_tp: inter must hold B * I 16-bit elements")
+    _lib.call("awq_b200_ffn_stack_decode_tp_bf16", plan.ptr, plan.n_layers, _ptr(x), _ptr(out), _ptr(inter), float(eps), B,
+              plan.H, plan.I, plan.group_size, peers.base_array(), peers.stride, peers.recv_bytes, peers.world, peers.rank,
+              _ptr(ws.buf), ws.nbytes, _stream())
+    return out
+
+
 def gemm(A, w: AwqWeight, out=None, residual=None, swiglu=False):
     """C [M, N] = A [M, K] @ W, f32 accumulate, bf16 out (prefill).  With `residual` [M, N] the sum is
     bf16(acc + residual); with `swiglu` W is gate/up-interleaved and C is [M, N/2]."""

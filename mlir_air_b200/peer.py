@@ -82,6 +82,10 @@ class PeerBuffers:
         self._recv_arrays = [arr(*[p + s * self.stride for p in self.ptrs]) for s in range(n_slots)]
         self._flag_arrays = [arr(*[p + s * self.stride + self.recv_bytes for p in self.ptrs]) for s in range(n_slots)]
 
+    def base_array(self):
+        """ctypes array of every rank's buffer base (argument peer_base)."""
+        return self._recv_arrays[0]
+
     def send_array(self, slot: int):
         """ctypes array of every rank's send-buffer pointer for `slot` (argument peer_partials)."""
         return self._recv_arrays[slot]

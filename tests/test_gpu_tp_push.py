@@ -1,5 +1,6 @@
 """Tensor-parallel decode stack on 2 GPUs: the peer-memory hand-over (awq_b200_gemv_f32_push +
-awq_b200_tp_reduce_add_rmsnorm_act) against the NCCL allreduce path and the unsharded numpy oracle.
+awq_b200_tp_reduce_add_rmsnorm_act) and the one-launch tensor-parallel stack
+(awq_b200_ffn_stack_decode_tp_bf16) against the NCCL allreduce path and the unsharded numpy oracle.
 Needs two GPUs; skipped otherwise."""
 import os
 
@@ -36,9 +37,10 @@ def _worker(rank, world, port, H, I, L, B, out):
             layers.append(ffn.FFNLayer(ffn.shard_gateup(gu, i0, i1), ffn.shard_down(AwqWeight.from_numpy(*down, 128), i0, i1),
                                        to_dev(gamma)))
         x = np.random.default_rng(7).standard_normal((B, H)).astype(bfloat16)
-        push = ffn.DecodeFFNStack(layers, H, max_batch=8, group=group, peer_push=True)
-        nccl = ffn.DecodeFFNStack(layers, H, max_batch=8, group=group)
-        assert push.peers is not None and nccl.peers is None
+        push = ffn.DecodeFFNStack(layers, H, max_batch=8, group=group, peer_push=True, fused=False)
+        nccl = ffn.DecodeFFNStack(layers, H, max_batch=8, group=group, fused=False)
+        one = ffn.DecodeFFNStack(layers, H, max_batch=8, group=group)  # the whole stack in one launch per rank
+        assert push.peers is not None and nccl.peers is None and one.uses_fused(B) and one.plan_peers is not None
         y_push = to_host(push.step(to_dev(x)))
         y_push2 = to_host(push.step(to_dev(x)))  # the slots and flags are reusable
         push.check()
@@ -50,12 +52,20 @@ def _worker(rank, world, port, H, I, L, B, out):
         push.load_input(to_dev(x))
         g2 = to_host(push.replay(B).clone())
         push.check()
+        y_one = to_host(one.step(to_dev(x)))
+        y_one2 = to_host(one.step(to_dev(x)))  # the flag counters run on from launch to launch
+        one.load_input(to_dev(x))
+        y_one3 = to_host(one.replay(B).clone())
+        one.load_input(to_dev(x))
+        y_one4 = to_host(one.replay(B).clone())
+        one.check()
         h = x
         for gate, up, down, gamma in full:
             h = O.ffn_layer_A_ref(h, gamma, gate, up, down, 128)
         out[rank] = dict(how=push.peers.how, oracle=O.rel_l2(y_push, h), again=O.rel_l2(y_push2, h),
                          vs_nccl=O.rel_l2(y_push, y_nccl), graph1=O.rel_l2(g1, h), graph2=O.rel_l2(g2, h),
-                         nccl_oracle=O.rel_l2(y_nccl, h))
+                         nccl_oracle=O.rel_l2(y_nccl, h), one=O.rel_l2(y_one, h), one2=O.rel_l2(y_one2, h),
+                         one3=O.rel_l2(y_one3, h), one4=O.rel_l2(y_one4, h), one_vs_nccl=O.rel_l2(y_one, y_nccl))
         torch.cuda.synchronize()
         dist.barrier()
     except Exception:  # noqa: BLE001 -- show it before the hard exit below
@@ -88,3 +98,4 @@ def test_tp2_push_matches_nccl_and_oracle(B, H, I, L):
     for r, d in res.items():
         assert d["oracle"] <= 1e-2 and d["again"] <= 1e-2 and d["graph1"] <= 1e-2 and d["graph2"] <= 1e-2, res
         assert d["vs_nccl"] <= 5e-3, res
+        assert max(d["one"], d["one2"], d["one3"], d["one4"]) <= 1e-2 and d["one_vs_nccl"] <= 5e-3, res
