@@ -15,8 +15,8 @@
 //    activations exist.
 //  * A phase's activations exist when every 64-column sub-strip of the previous phase has been
 //    finalised; finalising warps count up `done_gu` / `done_d` in global memory (release), the
-//    producers wait for the count (acquire, bounded).  All CTAs of the launch are resident
-//    (grid <= 2 per SM), so the wait cannot starve anybody.
+//    loaders wait for the count (acquire, bounded).  All CTAs of the launch are resident
+//    (one per SM), so the wait cannot starve anybody.
 //  * RMSNorm has no phase of its own.  The warp that finalises a down sub-strip adds the squares
 //    of its new hidden values to the layer's per-row sum; a gate/up unit's stage receives the raw
 //    8 x 128 hidden values and the 128 norm weights of its k range by TMA with the weights, and
@@ -25,6 +25,12 @@
 //  * The loader also prefetches into L2, a few units ahead of the ring and across phase and
 //    layer boundaries (weights depend on nothing), so HBM keeps streaming while a phase change
 //    waits for the slowest CTA; the ring then refills from L2.
+//  * Tensor-parallel ranks run the same launch on their shards.  A down phase then ends with the
+//    rank's f32 partial in its own peer-mapped send slot; the warp that completes the phase issues one
+//    system-scope fence and counts the rank in on every rank's flag words; the normaliser warps of
+//    all CTAs wait for all ranks, read the partials with peer loads in rank order, update the hidden
+//    state and the next layer's sums of squares, and count themselves in for the next gate/up phase.
+//    Kernels of different GPUs wait for one another here, never two launches on one GPU.
 //  * Rounding points are those of the separate kernels: bf16 normed activations, bf16 gate and
 //    up sums before SwiGLU, bf16 SwiGLU output, bf16 hidden state.
 #include <cudaTypedefs.h>
