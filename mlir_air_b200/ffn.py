@@ -137,8 +137,7 @@ class DecodeFFNStack:
         self.peers = None
         if peer_push and self.tp > 1 and hidden % 128 == 0 and all(l.down.group_size == 128 and l.down.K % 128 == 0
                                                                     for l in self.layers):
-            from .peer import PeerBuffers
-            self.peers = PeerBuffers(group, 2, 8 * hidden * 4, device)
+            self.peers = self._peer_buffers_or_none(group, 8 * hidden * 4, device)
         # one launch for the whole stack where the fused kernel applies: one GPU, every layer with
         # a norm weight, one shape, group 128, batch <= 8 (larger batches take the per-layer kernels)
         self.plan = None
@@ -149,10 +148,29 @@ class DecodeFFNStack:
             if self.plan.workspace_bytes() > self.ws.nbytes:
                 self.plan = None
             elif self.tp > 1:  # the ranks exchange their partials inside the launch, through these buffers
-                from .peer import PeerBuffers
-                self.plan_peers = PeerBuffers(group, 2, 8 * hidden * 4, device)
+                self.plan_peers = self._peer_buffers_or_none(group, 8 * hidden * 4, device)
+                if self.plan_peers is None:
+                    self.plan = None  # every rank falls back to the per-layer kernels + NCCL together
         self._pin_in = torch.empty((max_batch, hidden), dtype=torch.bfloat16).pin_memory() if torch.cuda.is_available() else None
         self._pin_out = torch.empty((max_batch, hidden), dtype=torch.bfloat16).pin_memory() if torch.cuda.is_available() else None
+
+    @staticmethod
+    def _peer_buffers_or_none(group, recv_bytes, device):
+        """Peer-mapped buffers, or None on EVERY rank if mapping failed on any (the ranks must take the
+        same path, so they agree through one allreduce)."""
+        import warnings
+        from .peer import PeerBuffers
+        peers, err = None, None
+        try:
+            peers = PeerBuffers(group, 2, recv_bytes, device)
+        except Exception as e:  # noqa: BLE001 -- whatever the mapping raised, the answer is the NCCL path
+            err = e
+        ok = torch.tensor([1 if peers is not None else 0], dtype=torch.int32, device=device)
+        torch.distributed.all_reduce(ok, op=torch.distributed.ReduceOp.MIN, group=group)
+        if int(ok.item()) == 0:
+            warnings.warn(f"peer-mapped buffers are not available ({err!r}); tensor-parallel ranks use NCCL per layer")
+            return None
+        return peers
 
     def _fusable(self) -> bool:
         l0 = self.layers[0]
