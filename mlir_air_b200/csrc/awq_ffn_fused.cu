@@ -512,15 +512,7 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
                     old = __shfl_sync(0xffffffffu, old, 0);
                     if (old + seg_groups != G) return;
                     __threadfence();
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        float4 *src = reinterpret_cast<float4 *>(acc_ptr + 32 * h);
-                        const float4 p0 = __ldcg(src), p1 = __ldcg(src + 1);
-                        own[h][0] = p0.x; own[h][1] = p0.y; own[h][2] = p0.z; own[h][3] = p0.w;
-                        own[h][4] = p1.x; own[h][5] = p1.y; own[h][6] = p1.z; own[h][7] = p1.w;
-                        src[0] = make_float4(0.f, 0.f, 0.f, 0.f);
-                        src[1] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    }
+                    sk_take_accum(acc_ptr, own);
                     __syncwarp();
                     if (lane == 0) a.counters[v * SK_CONSUMER_WARPS + cw] = 0;  // ready for the next phase
                 }
@@ -545,12 +537,16 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
                     // hidden state: bf16(sum + residual), and its squares for the next layer's RMSNorm
                     float ss = 0.f;
                     if (b < B) {
+                        // both residual loads before the first store (`out` is the residual from layer 1 on)
+                        uint4 rres[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
+#pragma unroll
+                        for (int h = 0; h < 2; ++h)
+                            if (n + 32 * h < N) rres[h] = __ldcg(reinterpret_cast<const uint4 *>(residual + (size_t)b * N + n + 32 * h));
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
                             const int nh = n + 32 * h;
                             if (nh >= N) continue;
-                            const uint4 rv = __ldcg(reinterpret_cast<const uint4 *>(residual + (size_t)b * N + nh));
-                            const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+                            const uint32_t rw[4] = {rres[h].x, rres[h].y, rres[h].z, rres[h].w};
                             uint32_t o[4];
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {

@@ -171,15 +171,7 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             old = __shfl_sync(0xffffffffu, old, 0);
             if (old != n_slots - 1) return;
             __threadfence();
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                float4 *src = reinterpret_cast<float4 *>(acc_ptr + 32 * h);
-                const float4 p0 = __ldcg(src), p1 = __ldcg(src + 1);
-                own[h][0] = p0.x; own[h][1] = p0.y; own[h][2] = p0.z; own[h][3] = p0.w;
-                own[h][4] = p1.x; own[h][5] = p1.y; own[h][6] = p1.z; own[h][7] = p1.w;
-                src[0] = make_float4(0.f, 0.f, 0.f, 0.f);
-                src[1] = make_float4(0.f, 0.f, 0.f, 0.f);
-            }
+            sk_take_accum(acc_ptr, own);
         } else {
             // deterministic: one slot per contributing CTA, summed by the last arriver in CTA order
             float *mine = partials + (size_t)(c + v) * SK_PARTIAL_FLOATS + lane_off;

@@ -166,6 +166,23 @@ __device__ __forceinline__ void sk_red_partial(float *acc_ptr, const float (&own
     }
 }
 
+// The last contributor takes the strip's total out of the accumulator and leaves zeros: all four
+// loads are issued before the first store (a store to the same address between them would make the
+// second pair wait for a whole round trip more).
+__device__ __forceinline__ void sk_take_accum(float *acc_ptr, float (&own)[2][8]) {
+    float4 *s0 = reinterpret_cast<float4 *>(acc_ptr), *s1 = reinterpret_cast<float4 *>(acc_ptr + 32);
+    const float4 a0 = __ldcg(s0), a1 = __ldcg(s0 + 1), b0 = __ldcg(s1), b1 = __ldcg(s1 + 1);
+    own[0][0] = a0.x; own[0][1] = a0.y; own[0][2] = a0.z; own[0][3] = a0.w;
+    own[0][4] = a1.x; own[0][5] = a1.y; own[0][6] = a1.z; own[0][7] = a1.w;
+    own[1][0] = b0.x; own[1][1] = b0.y; own[1][2] = b0.z; own[1][3] = b0.w;
+    own[1][4] = b1.x; own[1][5] = b1.y; own[1][6] = b1.z; own[1][7] = b1.w;
+    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+    s0[0] = z;
+    s0[1] = z;
+    s1[0] = z;
+    s1[1] = z;
+}
+
 // After a warp has stored a finished sub-strip with EPI_F32_PUSH.  Sub-strips are counted on this
 // GPU first (`local_done`, zero between launches); the warp that finishes the launch's last one makes
 // everything visible to the other GPUs with ONE system-scope fence (the fence is cumulative: it
