@@ -365,12 +365,23 @@ static int launch_one(const GemvArgs &a, const uint16_t *x, const uint16_t *resi
 
 template <bool XH>
 static int launch_passes(const GemvArgs &a, const uint16_t *x_all) {
-    // more than 8 batch rows: one pass over the weights per 8 rows
-    for (int b0 = 0; b0 < a.B; b0 += 8) {
-        const int B = a.B - b0 < 8 ? a.B - b0 : 8;
+    // more than 8 batch rows: up to 16 rows per pass over the weights with the multi-row kernel
+    // (fp16 activations, f32-atomic reduction), else one pass per 8 rows
+    int B = 0;
+    for (int b0 = 0; b0 < a.B; b0 += B) {
+        const int left = a.B - b0;
         const uint16_t *x = x_all + (size_t)b0 * a.K;
         const uint16_t *res = a.residual ? a.residual + (size_t)b0 * a.N : nullptr;
         int rc;
+        B = left < 16 ? left : 16;
+        if (XH && B > 8 && gemv_streamk_mb_supported(a, B)) {
+            void *yb = a.epilogue == EPI_F32      ? (void *)(reinterpret_cast<float *>(a.y) + (size_t)b0 * a.N)
+                       : a.epilogue == EPI_SWIGLU ? (void *)(reinterpret_cast<uint16_t *>(a.y) + (size_t)b0 * (a.N / 2))
+                                                  : (void *)(reinterpret_cast<uint16_t *>(a.y) + (size_t)b0 * a.N);
+            if ((rc = launch_gemv_streamk_mb(a, x, a.epilogue == EPI_BF16 ? res : nullptr, yb, B))) return rc;
+            continue;
+        }
+        B = left < 8 ? left : 8;
         switch (a.epilogue) {
             case EPI_BF16:
                 rc = launch_one<EPI_BF16, XH>(a, x, res, reinterpret_cast<uint16_t *>(a.y) + (size_t)b0 * a.N, B);

@@ -395,3 +395,31 @@ def test_gemm_cfg4_full_size(ops):
     c0 = to_host(ops.gemm(to_dev(np.zeros((128, K), bfloat16)), dev_weight(qw, qz, s)))
     assert not c0.astype(np.float32).any()
     ops.gemm_check()
+
+
+@pytest.mark.parametrize("B", [9, 12, 16, 27])
+def test_gemv_multi_row_pass(ops, B):
+    """9-16 rows share one pass over the weights (two 8-row tiles per decoded fragment); 27 rows are
+    16 + 11.  All three epilogues, a partial last strip (N = 1312), against the oracle and against
+    the same rows taken 8 at a time."""
+    K, N = 1024, 1312
+    qw, qz, s = synth_awq(K, N, 128, seed=31)
+    x = randn_bf16((B, K), seed=32)
+    r = randn_bf16((B, N), seed=33)
+    w = dev_weight(qw, qz, s)
+    ws = ops.Workspace(K, N)
+    ops.set_decode_kernel("streamk")
+    try:
+        y = to_host(ops.gemv(to_dev(x), w, ws, residual=to_dev(r)))
+        assert O.rel_l2(y, O.gemv_A_ref(x, qw, qz, s, 128, residual=r)) <= REL_L2_TOL
+        y8 = np.concatenate([to_host(ops.gemv(to_dev(x[i:i + 8]), w, ws, residual=to_dev(r[i:i + 8]))) for i in range(0, B, 8)])
+        assert O.rel_l2(y, y8) <= 2e-3
+        yf = to_host(ops.gemv(to_dev(x), w, ws, f32_out=True))
+        assert yf.dtype == np.float32 and O.rel_l2(yf, x.astype(np.float32) @ O.dequant_f32(qw, qz, s, 128)) <= 2e-3
+        gate, up = synth_awq(K, 640, 128, seed=34), synth_awq(K, 640, 128, seed=35)
+        wgu = ops.interleave_gate_up(dev_weight(*gate), dev_weight(*up))
+        t = to_host(ops.gateup_swiglu(to_dev(x), wgu, ws))
+        assert O.rel_l2(t, O.gateup_swiglu_A_ref(x, gate, up, 128)) <= REL_L2_TOL
+    finally:
+        ops.set_decode_kernel("auto")
+    ws.check()
