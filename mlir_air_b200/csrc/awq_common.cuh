@@ -130,7 +130,7 @@ int launch_gemv_generic(const GemvArgs &a);
 // TMA + mma.sync stream-K kernel: group 128, N % 32 == 0, K % 128 == 0, B <= 8.
 bool gemv_streamk_supported(const GemvArgs &a);
 int launch_gemv_streamk(const GemvArgs &a);
-bool gemv_streamk_mb_supported(const GemvArgs &a, int B);  // multi-row pass (9..16 rows, awq_gemv_streamk_mb.cu)
+bool gemv_streamk_mb_supported(const GemvArgs &a, int B);  // multi-row pass (9..32 rows, awq_gemv_streamk_mb.cu)
 int launch_gemv_streamk_mb(const GemvArgs &a, const uint16_t *x, const uint16_t *residual, void *y, int B);
 size_t gemv_streamk_scratch_bytes(int N, bool deterministic);  // counters + split-K accumulators / partial slots
 size_t gemv_streamk_workspace_bytes(int B, int K, int N);  // + room to convert B rows of x to fp16

@@ -365,7 +365,7 @@ static int launch_one(const GemvArgs &a, const uint16_t *x, const uint16_t *resi
 
 template <bool XH>
 static int launch_passes(const GemvArgs &a, const uint16_t *x_all) {
-    // more than 8 batch rows: up to 16 rows per pass over the weights with the multi-row kernel
+    // more than 8 batch rows: up to 32 rows per pass over the weights with the multi-row kernel
     // (fp16 activations, f32-atomic reduction), else one pass per 8 rows
     int B = 0;
     for (int b0 = 0; b0 < a.B; b0 += B) {
@@ -373,7 +373,7 @@ static int launch_passes(const GemvArgs &a, const uint16_t *x_all) {
         const uint16_t *x = x_all + (size_t)b0 * a.K;
         const uint16_t *res = a.residual ? a.residual + (size_t)b0 * a.N : nullptr;
         int rc;
-        B = left < 16 ? left : 16;
+        B = left < 32 ? left : 32;
         if (XH && B > 8 && gemv_streamk_mb_supported(a, B)) {
             void *yb = a.epilogue == EPI_F32      ? (void *)(reinterpret_cast<float *>(a.y) + (size_t)b0 * a.N)
                        : a.epilogue == EPI_SWIGLU ? (void *)(reinterpret_cast<uint16_t *>(a.y) + (size_t)b0 * (a.N / 2))

@@ -1,12 +1,14 @@
-// Decode GEMV / gate-up SwiGLU for 9 to 16 batch rows per weight pass.
+// Decode GEMV / gate-up SwiGLU for 9 to 32 batch rows per weight pass.
 //
 // The 8-row stream-K kernel (awq_gemv_streamk.cu) spends its time on the nibble decode (integer
 // ALU); the MMAs are cheap.  For more rows the decoded fragments are therefore reused: a unit's
-// weights are decoded once and multiplied with T = 2 activation tiles of 8 rows, each tile with its
-// own accumulators.  That costs registers (36 per tile and thread: 145 with two tiles), so this
-// variant runs one CTA of 8 consumer warps per SM with a 5-stage ring instead of two CTAs with 3
-// stages.  (Four tiles need more than the 168 registers a thread can have when one scheduler of the
-// SM hosts three of the CTA's nine warps; the kernel is written for any T but only T = 2 is built.)
+// weights are decoded once and multiplied with T = 2 or 4 activation tiles of 8 rows, each tile with
+// its own accumulators.  That costs registers (36 per tile and thread), so this variant runs one CTA
+// of 8 consumer warps per SM with a 5-stage ring instead of two CTAs with 3 stages.  With T = 4 there
+// is no producer warp: a ninth warp would put three warps on one of the SM's four schedulers and cap
+// every thread at 168 registers, so lane 0 of consumer warp 0 issues the TMA copies itself, between
+// its units, whenever a stage has been released (and blocks for a release only when the unit it is
+// about to consume has not been requested yet).
 // Units, stage layout (with T activation tiles), decode, split-K reduction with f32 vector
 // atomics and epilogues are those of the 8-row kernel; strip v, tile t uses accumulator and counter
 // slot v T + t.  fp16 activations only (bf16 inputs are converted by the caller), no deterministic
@@ -38,8 +40,13 @@ struct MbCfg {
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 };
 
+template <int T>
+__host__ __device__ constexpr bool mb_fold() { return T > 2; }  // the producer's work is folded into consumer warp 0
+template <int T>
+__host__ __device__ constexpr int mb_threads() { return mb_fold<T>() ? SK_CONSUMER_WARPS * 32 : SK_THREADS; }
+
 template <int EPI, int T>
-__global__ void __launch_bounds__(SK_THREADS, 1)
+__global__ void __launch_bounds__(mb_threads<T>(), 1)
 gemv_streamk_mb_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                        const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmZ,
                        const uint16_t *__restrict__ residual, void *__restrict__ y_, int B, int N, int G, int V,
@@ -67,62 +74,84 @@ gemv_streamk_mb_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_con
     __syncthreads();
     pdl_launch_dependents();
 
-    if (warp == SK_CONSUMER_WARPS) {
-        // ------------------------------ producer ------------------------------
+    constexpr bool FOLD = mb_fold<T>();
+    const uint64_t stream_policy = l2_policy_evict_first();
+    auto load_weights = [&](int slot, int v, int g) {
+        const uint32_t st = smem_base + slot * Cfg::STAGE_BYTES;
+        const uint32_t bar = full_bar(slot);
+        mbar_expect_tx(bar, Cfg::TX_BYTES);
+#pragma unroll
+        for (int bx = 0; bx < SK_STRIP / SK_BOX_COLS; ++bx)
+            tma_load_2d_hint(st + bx * SK_WBOX_BYTES, &tmW, (v * SK_STRIP + bx * SK_BOX_COLS) / 8, g * SK_GROUP, bar,
+                             stream_policy);
+#pragma unroll
+        for (int bx = 0; bx < SK_STRIP / SK_BOX_COLS; ++bx)
+            tma_load_2d(st + Cfg::OFF_S + bx * SK_BOX_COLS * 2, &tmS, v * SK_STRIP + bx * SK_BOX_COLS, g, bar);
+        tma_load_2d(st + Cfg::OFF_Z, &tmZ, v * (SK_STRIP / 8), g, bar);
+    };
+    auto load_activations = [&](int slot, int g) {  // rows beyond B read as zero
+        const uint32_t st = smem_base + slot * Cfg::STAGE_BYTES;
+#pragma unroll
+        for (int t = 0; t < T; ++t) {
+            tma_load_2d(st + Cfg::OFF_X + t * SK_X_BYTES, &tmX, g * SK_GROUP, 8 * t, full_bar(slot));
+            tma_load_2d(st + Cfg::OFF_X + t * SK_X_BYTES + 1024, &tmX, g * SK_GROUP + 64, 8 * t, full_bar(slot));
+        }
+    };
+    // what the issuing thread has requested so far: unit number, its strip / group, ring position
+    int iss_n = 0, iss_v = v_first, iss_g = g_first, iss_slot = 0, iss_round = 0;
+    auto issue_prologue = [&]() {
+        // weights first (they do not depend on the previous kernel), then its output
+        tma_prefetch_desc(&tmW);
+        tma_prefetch_desc(&tmX);
+        tma_prefetch_desc(&tmS);
+        tma_prefetch_desc(&tmZ);
+        const int n_first = n_units < Cfg::STAGES ? n_units : Cfg::STAGES;
+        int v = v_first, g = g_first;
+        for (int i = 0; i < n_first; ++i) {
+            load_weights(i, v, g);
+            if (++g == G) { g = 0; ++v; }
+        }
+        pdl_wait();
+        int g2 = g_first;
+        for (int i = 0; i < n_first; ++i) {
+            load_activations(i, g2);
+            if (++g2 == G) g2 = 0;
+        }
+        iss_n = n_first;
+        iss_v = v;
+        iss_g = g;
+        iss_slot = n_first % Cfg::STAGES;
+        iss_round = n_first / Cfg::STAGES;
+    };
+    // request the next unit into its stage; `must`: block (bounded) until the stage is released
+    auto issue_next = [&](bool must) -> bool {
+        const uint32_t parity = (uint32_t)(iss_round - 1) & 1u;
+        if (must) {
+            if (!mbar_wait_bounded(empty_bar(iss_slot), parity)) {
+                atomicExch(err_flag, 1);
+                return false;
+            }
+        } else if (!mbar_try_wait(empty_bar(iss_slot), parity)) {
+            return false;
+        }
+        load_weights(iss_slot, iss_v, iss_g);
+        load_activations(iss_slot, iss_g);
+        ++iss_n;
+        if (++iss_g == G) { iss_g = 0; ++iss_v; }
+        if (++iss_slot == Cfg::STAGES) { iss_slot = 0; ++iss_round; }
+        return true;
+    };
+
+    if (!FOLD && warp == SK_CONSUMER_WARPS) {
+        // ------------------------------ producer warp ------------------------------
         if (lane == 0) {
-            tma_prefetch_desc(&tmW);
-            tma_prefetch_desc(&tmX);
-            tma_prefetch_desc(&tmS);
-            tma_prefetch_desc(&tmZ);
-            const uint64_t stream_policy = l2_policy_evict_first();
-            auto load_weights = [&](int slot, int v, int g) {
-                const uint32_t st = smem_base + slot * Cfg::STAGE_BYTES;
-                const uint32_t bar = full_bar(slot);
-                mbar_expect_tx(bar, Cfg::TX_BYTES);
-#pragma unroll
-                for (int bx = 0; bx < SK_STRIP / SK_BOX_COLS; ++bx)
-                    tma_load_2d_hint(st + bx * SK_WBOX_BYTES, &tmW, (v * SK_STRIP + bx * SK_BOX_COLS) / 8, g * SK_GROUP,
-                                     bar, stream_policy);
-#pragma unroll
-                for (int bx = 0; bx < SK_STRIP / SK_BOX_COLS; ++bx)
-                    tma_load_2d(st + Cfg::OFF_S + bx * SK_BOX_COLS * 2, &tmS, v * SK_STRIP + bx * SK_BOX_COLS, g, bar);
-                tma_load_2d(st + Cfg::OFF_Z, &tmZ, v * (SK_STRIP / 8), g, bar);
-            };
-            auto load_activations = [&](int slot, int g) {  // rows beyond B read as zero
-                const uint32_t st = smem_base + slot * Cfg::STAGE_BYTES;
-#pragma unroll
-                for (int t = 0; t < T; ++t) {
-                    tma_load_2d(st + Cfg::OFF_X + t * SK_X_BYTES, &tmX, g * SK_GROUP, 8 * t, full_bar(slot));
-                    tma_load_2d(st + Cfg::OFF_X + t * SK_X_BYTES + 1024, &tmX, g * SK_GROUP + 64, 8 * t, full_bar(slot));
-                }
-            };
-            // weights first (they do not depend on the previous kernel), then its output
-            const int n_first = n_units < Cfg::STAGES ? n_units : Cfg::STAGES;
-            int v = v_first, g = g_first;
-            for (int i = 0; i < n_first; ++i) {
-                load_weights(i, v, g);
-                if (++g == G) { g = 0; ++v; }
-            }
-            pdl_wait();
-            g = g_first;
-            for (int i = 0; i < n_first; ++i) {
-                load_activations(i, g);
-                if (++g == G) g = 0;
-            }
-            int slot = 0, round = 1;
-            for (int i = n_first; i < n_units; ++i) {
-                if (!mbar_wait_bounded(empty_bar(slot), (round - 1) & 1)) {
-                    atomicExch(err_flag, 1);
-                    break;
-                }
-                load_weights(slot, v, g);
-                load_activations(slot, g);
-                if (++g == G) { g = 0; ++v; }
-                if (++slot == Cfg::STAGES) { slot = 0; ++round; }
+            issue_prologue();
+            while (iss_n < n_units && issue_next(true)) {
             }
         }
         return;
     }
+    if (FOLD && threadIdx.x == 0) issue_prologue();
     pdl_wait();  // consumers read and write global memory the previous kernel may still be using
 
     // ------------------------------ consumers ------------------------------
@@ -179,6 +208,11 @@ gemv_streamk_mb_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_con
                     for (int q = 0; q < 4; ++q) res[t][e][q] = 0.f;
         }
         ++seg_groups;
+        if (FOLD && threadIdx.x == 0 && !failed) {
+            // refill whatever has been released; the unit about to be consumed must have been requested
+            while (iss_n < n_units && issue_next(iss_n <= i)) {
+            }
+        }
         if (!failed && !mbar_wait_bounded(full_bar(slot), round & 1)) {
             failed = true;
             if (lane == 0) atomicExch(err_flag, 2);
@@ -292,7 +326,7 @@ static int launch_mb(const GemvArgs &a, const uint16_t *x, const uint16_t *resid
     if (ctas <= 0) ctas = 148;
     if ((long long)ctas > U) ctas = (int)U;
     uint8_t *ws = reinterpret_cast<uint8_t *>(a.workspace);
-    return check_cuda(launch_pdl(gemv_streamk_mb_kernel<EPI, T>, dim3(ctas), dim3(SK_THREADS), Cfg::SMEM_BYTES, a.stream, tmW,
+    return check_cuda(launch_pdl(gemv_streamk_mb_kernel<EPI, T>, dim3(ctas), dim3(mb_threads<T>()), Cfg::SMEM_BYTES, a.stream, tmW,
                                  tmX, tmS, tmZ, residual, y, B, a.N, G, V, a.out_format == ACT_F16 ? 1 : 0,
                                  reinterpret_cast<float *>(ws + SK_WS_ACCUM), reinterpret_cast<int *>(ws + SK_WS_HEADER),
                                  reinterpret_cast<int *>(ws)),
@@ -309,17 +343,17 @@ static int launch_mb_epi(const GemvArgs &a, const uint16_t *x, const uint16_t *r
     }
 }
 
-// Can B rows (9 <= B <= 16) go through one pass of this kernel?
+// Can B rows (9 <= B <= 32) go through one pass of this kernel?
 bool gemv_streamk_mb_supported(const GemvArgs &a, int B) {
     const int V = (a.N + SK_STRIP - 1) / SK_STRIP;
-    const int T = 2;
-    return B > 8 && B <= 16 && !a.deterministic && a.epilogue != EPI_F32_PUSH && V * T <= SK_MAX_STRIPS &&
+    const int T = B > 16 ? 4 : 2;
+    return B > 8 && B <= 32 && !a.deterministic && a.epilogue != EPI_F32_PUSH && V * T <= SK_MAX_STRIPS &&
            a.workspace_bytes >= SK_WS_PARTIALS;
 }
 
-// x: fp16 [B, K] (already converted), 9 <= B <= 16.
+// x: fp16 [B, K] (already converted), 9 <= B <= 32.
 int launch_gemv_streamk_mb(const GemvArgs &a, const uint16_t *x, const uint16_t *residual, void *y, int B) {
-    return launch_mb_epi<2>(a, x, residual, y, B);
+    return B > 16 ? launch_mb_epi<4>(a, x, residual, y, B) : launch_mb_epi<2>(a, x, residual, y, B);
 }
 
 }  // namespace awq

@@ -397,10 +397,10 @@ def test_gemm_cfg4_full_size(ops):
     ops.gemm_check()
 
 
-@pytest.mark.parametrize("B", [9, 12, 16, 27])
+@pytest.mark.parametrize("B", [9, 12, 16, 17, 27, 32, 45])
 def test_gemv_multi_row_pass(ops, B):
-    """9-16 rows share one pass over the weights (two 8-row tiles per decoded fragment); 27 rows are
-    16 + 11.  All three epilogues, a partial last strip (N = 1312), against the oracle and against
+    """9-16 rows share one pass over the weights with two 8-row tiles per decoded fragment, 17-32 rows
+    with four; 45 rows are 32 + 13.  All three epilogues, a partial last strip (N = 1312), against the oracle and against
     the same rows taken 8 at a time."""
     K, N = 1024, 1312
     qw, qz, s = synth_awq(K, N, 128, seed=31)
