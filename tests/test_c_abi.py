@@ -1,0 +1,71 @@
+"""The C ABI without a GPU: every function declared in include/awq_b200.h is exported by the library
+and bound in mlir_air_b200/_lib.py, and argument errors come back as status codes with a message
+before anything touches the device."""
+import ctypes
+import os
+import re
+
+from mlir_air_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "awq_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(awq_b200_\w+)\s*\(", text)))
+
+
+def test_header_library_and_binding_agree():
+    names = _declared()
+    assert len(names) >= 35
+    lib = _lib.load()
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in the header but not exported"
+        assert n in _lib.SIGNATURES, f"{n} has no ctypes prototype"
+    assert sorted(_lib.SIGNATURES) == names, "a bound symbol is missing from the header"
+    assert lib.awq_b200_version() >= 100
+
+
+def _err(rc):
+    assert rc != 0
+    msg = _lib.last_error()
+    assert msg
+    return rc, msg
+
+
+def test_argument_errors_need_no_gpu():
+    lib = _lib.load()
+    p = ctypes.c_void_p(256)  # a non-null, 16-byte aligned value that is never dereferenced
+    INV, UNS = _lib.AWQ_ERR_INVALID_ARGUMENT, _lib.AWQ_ERR_UNSUPPORTED
+    # dequant / gemv: shapes
+    assert _err(lib.awq_b200_dequant_bf16(p, p, p, p, 100, 64, 128, None))[0] == INV       # K not a multiple of the group
+    assert _err(lib.awq_b200_gemv_bf16(p, p, p, p, None, p, 1, 256, 12, 128, p, 1 << 20, None))[0] == INV  # N % 8
+    assert _err(lib.awq_b200_gemv_bf16(p, p, p, p, None, p, 65, 256, 64, 128, p, 1 << 20, None))[0] == INV  # batch > 64
+    assert _err(lib.awq_b200_gemv_bf16(None, p, p, p, None, p, 1, 256, 64, 128, p, 1 << 20, None))[0] == INV  # null x
+    # rope
+    rc, msg = _err(lib.awq_b200_rope_halfsplit_bf16(p, 256, p, p, 256, 1, 4, 40, None))
+    assert rc == INV and "head_dim" in msg
+    assert _err(lib.awq_b200_rope_halfsplit_bf16(p, 100, p, p, 256, 2, 4, 64, None))[0] == INV  # row stride too small
+    # one-launch stack: plan and decode
+    arr = (ctypes.c_void_p * 1)(256)
+    assert _err(lib.awq_b200_ffn_stack_plan(p, 1 << 20, 0, arr, arr, arr, arr, arr, arr, arr, 512, 1024, 128))[0] == INV
+    assert _err(lib.awq_b200_ffn_stack_plan(p, 1 << 20, 1, None, arr, arr, arr, arr, arr, arr, 512, 1024, 128))[0] == INV
+    assert lib.awq_b200_ffn_stack_plan_bytes(3) == 3 * lib.awq_b200_ffn_stack_plan_bytes(1) > 0
+    assert lib.awq_b200_ffn_stack_workspace_bytes(80) > lib.awq_b200_ffn_stack_workspace_bytes(1) > 0
+    assert lib.awq_b200_ffn_stack_decode_bf16(p, 1, p, p, p, 1e-5, 0, 512, 1024, 128, p, 1 << 20, None) == 0  # empty batch
+    assert _err(lib.awq_b200_ffn_stack_decode_bf16(None, 1, p, p, p, 1e-5, 1, 512, 1024, 128, p, 1 << 20, None))[0] == INV
+    assert _err(lib.awq_b200_ffn_stack_decode_bf16(p, 1, p, p, p, 1e-5, 9, 512, 1024, 128, p, 1 << 20, None))[0] == UNS
+    # tensor-parallel entry points
+    assert _err(lib.awq_b200_ffn_stack_decode_tp_bf16(p, 1, p, p, p, 1e-5, 1, 512, 1024, 128, arr, 1 << 16, 1 << 15, 1, 0, p,
+                                                      1 << 20, None))[0] == INV  # a single rank is not tensor parallel
+    assert _err(lib.awq_b200_ffn_stack_decode_tp_bf16(p, 1, p, p, p, 1e-5, 1, 512, 1024, 128, arr, 64, 0, 2, 0, p, 1 << 20,
+                                                      None))[0] == INV  # slots too small for an [8, H] partial
+    assert _err(lib.awq_b200_gemv_f32_push(p, 0, p, p, p, p, 9, 256, 64, 128, arr, 2, 0, p, 1 << 20, None))[0] == INV
+    assert _err(lib.awq_b200_tp_reduce_add_rmsnorm_act(p, arr, p, 9, None, 1e-5, p, None, 0, 1, 512, p, None))[0] == INV
+    # fused GEMM epilogues
+    rc, msg = _err(lib.awq_b200_gemm_fused_bf16(p, p, p, p, p, p, 1, 64, 256, 512, 128, None))
+    assert rc == INV and "do not combine" in msg
+    # knobs
+    assert _err(lib.awq_b200_set_decode_kernel(7))[0] == INV
+    assert lib.awq_b200_set_decode_kernel(0) == 0 and lib.awq_b200_set_ffn_stack_tuning(-1, -1) == 0
