@@ -62,18 +62,40 @@ def _run_dequant(p, args):
     return [y], [1]
 
 
-def _weight_from_gemv_tiles(p, packed, M):
+def _resident(p, slot, build):
+    """`build()`, or what an earlier call built for argument `slot` when the caller declared that
+    argument static (KernelCache.load_and_run: written on first use, resident afterwards)."""
+    if slot is None or slot not in p.get("__static__", ()):
+        return build()
+    store = p["__resident__"]
+    if slot not in store:
+        store[slot] = build()
+    return store[slot]
+
+
+def _weight_from_gemv_tiles(p, packed, M, slot=None):
     from . import ops
-    A_q, A_s, A_z = layouts.unpack_gemv_tiles(packed, M, p["K"], p["GS"], p["M_TILE"], p["K_CHUNK"], p["N_CORES"],
-                                              p.get("M_PER_LAUNCH") or M)
-    return ops.repack_B_to_A(_to_dev(A_q), _to_dev(A_s), _to_dev(A_z), p["GS"])
+
+    def build():
+        A_q, A_s, A_z = layouts.unpack_gemv_tiles(packed, M, p["K"], p["GS"], p["M_TILE"], p["K_CHUNK"], p["N_CORES"],
+                                                  p.get("M_PER_LAUNCH") or M)
+        return ops.repack_B_to_A(_to_dev(A_q), _to_dev(A_s), _to_dev(A_z), p["GS"])
+
+    return _resident(p, slot, build)
+
+
+def _workspace(p, K, N):
+    from . import ops
+    if "__resident__" in p:
+        return _resident(dict(p, __static__=("ws",)), "ws", lambda: ops.Workspace(K, N))
+    return ops.Workspace(K, N)
 
 
 def _run_matvec(p, args):
     from . import ops
     packed, x, out = args
-    w = _weight_from_gemv_tiles(p, packed, p["M"])
-    ws = ops.Workspace(w.K, w.N)
+    w = _weight_from_gemv_tiles(p, packed, p["M"], slot=0)
+    ws = _workspace(p, w.K, w.N)
     y = ops.gemv(_to_dev(np.asarray(x).reshape(-1, p["K"])), w, ws)
     ws.check()
     return [y], [2]
@@ -82,8 +104,8 @@ def _run_matvec(p, args):
 def _run_matvec_add(p, args):
     from . import ops
     packed, x, r, out = args
-    w = _weight_from_gemv_tiles(p, packed, p["M"])
-    ws = ops.Workspace(w.K, w.N)
+    w = _weight_from_gemv_tiles(p, packed, p["M"], slot=0)
+    ws = _workspace(p, w.K, w.N)
     y = ops.gemv(_to_dev(np.asarray(x).reshape(-1, p["K"])), w, ws, residual=_to_dev(np.asarray(r).reshape(-1, p["M"])))
     ws.check()
     return [y], [3]
@@ -92,8 +114,8 @@ def _run_matvec_add(p, args):
 def _run_swiglu_rms(p, args):
     from . import ops
     packed, rms_in, out = args
-    w = _weight_from_gemv_tiles(p, packed, p["M"])  # rows gate/up interleaved -> [K, 2I] interleaved columns
-    ws = ops.Workspace(w.K, w.N)
+    w = _weight_from_gemv_tiles(p, packed, p["M"], slot=0)  # rows gate/up interleaved -> [K, 2I] interleaved columns
+    ws = _workspace(p, w.K, w.N)
     rms_in = np.asarray(rms_in).reshape(2, p["K"])
     normed = ops.rmsnorm(_to_dev(rms_in[0:1]), _to_dev(rms_in[1]), p.get("eps", 1e-5))
     y = ops.gateup_swiglu(normed, w, ws)
@@ -110,11 +132,17 @@ def _run_rms_qkv_rope(p, args):
     x_in, norm_w, _, wq_p, _, wk_p, _, wv_p, _, lut_q, lut_k, _, _ = args
     emb, kv, hd = p["emb_dim"], p["kv_dim"], p["head_dim"]
     tile = dict(K=emb, GS=p["GS"], M_TILE=p["M_TILE"], K_CHUNK=p["K_CHUNK"], N_CORES=p["N_CORES"])
-    ws_ = [_weight_from_gemv_tiles(tile, wq_p, emb), _weight_from_gemv_tiles(tile, wk_p, kv),
-           _weight_from_gemv_tiles(tile, wv_p, kv)]
-    w = ops.AwqWeight(torch.cat([t.qweight for t in ws_], 1).contiguous(), torch.cat([t.qzeros for t in ws_], 1).contiguous(),
-                      torch.cat([t.scales for t in ws_], 1).contiguous(), p["GS"])
-    ws = ops.Workspace(w.K, w.N)
+
+    def build_qkv():
+        ws_ = [_weight_from_gemv_tiles(tile, wq_p, emb), _weight_from_gemv_tiles(tile, wk_p, kv),
+               _weight_from_gemv_tiles(tile, wv_p, kv)]
+        return ops.AwqWeight(torch.cat([t.qweight for t in ws_], 1).contiguous(),
+                             torch.cat([t.qzeros for t in ws_], 1).contiguous(),
+                             torch.cat([t.scales for t in ws_], 1).contiguous(), p["GS"])
+
+    # resident when all three weight arguments (3, 5, 7) are declared static
+    w = _resident(p, 3 if {3, 5, 7} <= set(p.get("__static__", ())) else None, build_qkv)
+    ws = _workspace(p, w.K, w.N)
     normed = ops.rmsnorm(_to_dev(np.asarray(x_in).reshape(1, emb)), _to_dev(np.asarray(norm_w)), p.get("eps", 1e-5))
     qkv = ops.gemv(normed, w, ws)
     ws.check()
@@ -175,8 +203,20 @@ def _run_matvec_bf16(p, args):
     """A bf16 [M, K], B bf16 [K], C bf16 [M] (matrix_vector_multiplication/bf16/matvec.py)."""
     from . import ops
     A, B, out = args
-    y = ops.linear_bf16(_to_dev(np.asarray(B).reshape(1, p["K"])), _to_dev(np.asarray(A).reshape(p["M"], p["K"])))
+    y = ops.linear_bf16(_to_dev(np.asarray(B).reshape(1, p["K"])),
+                        _resident(p, 0, lambda: _to_dev(np.asarray(A).reshape(p["M"], p["K"]))))
     return [y], [2]
+
+
+def _run_swiglu_rms_bf16(p, args):
+    """A bf16 [M, K] (gate/up rows interleaved), RMS_in bf16 [2, K], D bf16 [M/2]
+    (decode_ffn_swiglu/matvec_swiglu_rms.py)."""
+    from . import ops
+    A, rms_in, out = args
+    rms_in = np.asarray(rms_in).reshape(2, p["K"])
+    normed = ops.rmsnorm(_to_dev(rms_in[0:1]), _to_dev(rms_in[1]), p.get("eps", 1e-5))
+    gu = ops.linear_bf16(normed, _resident(p, 0, lambda: _to_dev(np.asarray(A).reshape(p["M"], p["K"]))))
+    return [ops.silu_mul(gu[0, 0::2].contiguous(), gu[0, 1::2].contiguous())], [2]
 
 
 def _run_silu_and_mul(p, args):
@@ -188,6 +228,7 @@ def _run_silu_and_mul(p, args):
 _INSTANCES: Dict[str, Callable] = {
     "matvec_bf16": _run_matvec_bf16,
     "silu_and_mul": _run_silu_and_mul,
+    "matvec_swiglu_rms": _run_swiglu_rms_bf16,
     "ffn_swiglu": _run_ffn_bf16,
     "dequant": _run_dequant,
     "matvec_int4_packed": _run_matvec,

@@ -27,6 +27,8 @@ CASES = [
     ("llms.llama32_1b_int4.multi_launch_builder.rms_qkv_int4_rope_multi", []),
     ("matrix_vector_multiplication.bf16.matvec", []),                            # 2048 x 8192, bf16 sibling
     ("matrix_vector_multiplication.bf16.matvec", ["--m", "512", "--k", "2048", "--perf-iters", "3"]),
+    ("decode_ffn_swiglu.matvec_swiglu_rms", []),                                 # 16384 x 2048, bf16 fused sibling
+    ("decode_ffn_swiglu.matvec_swiglu_rms", ["--m", "512", "--k", "1024"]),
     ("silu_and_mul.silu_and_mul", []),                                            # n = 65536   # emb 2048, kv 512, 32/8 heads of 64
 ]
 
