@@ -262,16 +262,20 @@ int awq_b200_ffn_stack_decode_bf16(const void *plan, int n_layers, const uint16_
 /* The same launch for tensor-parallel ranks (one process per GPU): the plan describes this rank's
  * shards (gate/up columns [H, 2 I_local], down rows [I_local, H], cut as in the per-layer path),
  * and after each layer's down projection the ranks exchange their f32 partials inside the kernel:
- * a rank writes its partial into its own send slot, signals every rank's flag words once per layer
- * (one system-scope fence), and the reduce phase reads all ranks' partials with peer loads, in
- * rank order.  peer_base: HOST array of n_ranks device pointers to the ranks' buffers mapped into
- * this GPU's address space (entry `rank` is this rank's own); a buffer holds two slots of
- * slot_stride bytes, each an f32 [8, H] partial followed at flag_offset by 16 uint32 flag words,
- * zero when first used and owned by this entry point afterwards (the counters are never reset, the
- * last word of slot 0 counts launches).  Every rank must make the same sequence of calls, and the
+ * the warp that finishes a 64-column piece of the partial stores it into the receive area of
+ * every rank as 8-byte words that carry the value and the exchange's number together (no fence, no
+ * flag), and on every rank one warp per piece polls the words of all ranks, adds them in rank
+ * order and writes the new hidden state.  peer_base: HOST array of n_ranks device pointers to the
+ * ranks' buffers mapped into this GPU's address space (entry `rank` is this rank's own); a buffer
+ * holds two slots of slot_stride bytes, each a receive area of at least
+ * awq_b200_ffn_stack_tp_slot_bytes(H, n_ranks) bytes followed at flag_offset by 16 uint32 words,
+ * all zero when first used and owned by this entry point afterwards (nothing is ever reset; the
+ * last word behind slot 0 counts launches).  Every call on these buffers must have the same n_layers.
+ * Every rank must make the same sequence of calls, and the
  * kernels of the ranks wait for one another (bounded; awq_b200_workspace_check reports a timeout).
  * No counterpart in the reference, whose only inter-GPU mechanism is its symmetric heap
  * (runtime_lib/airgpu/symmetric_heap.cpp:172-312). */
+size_t awq_b200_ffn_stack_tp_slot_bytes(int H, int n_ranks);
 int awq_b200_ffn_stack_decode_tp_bf16(const void *plan, int n_layers, const uint16_t *x,
                                       uint16_t *out, uint16_t *inter, float eps, int B, int H,
                                       int I_local, int group_size, void *const *peer_base,

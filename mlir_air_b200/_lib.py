@@ -59,6 +59,7 @@ SIGNATURES = {
     "awq_b200_set_ffn_stack_tuning": (c_int, [c_int, c_int]),
     "awq_b200_ffn_stack_plan_bytes": (c_size_t, [c_int]),
     "awq_b200_ffn_stack_workspace_bytes": (c_size_t, [c_int]),
+    "awq_b200_ffn_stack_tp_slot_bytes": (c_size_t, [c_int, c_int]),
     "awq_b200_ffn_stack_plan": (c_int, [_P, c_size_t, c_int] + [_P] * 7 + [c_int, c_int, c_int]),
     "awq_b200_ffn_stack_decode_bf16": (c_int, [_P, c_int, _P, _P, _P, c_float, c_int, c_int, c_int, c_int, _P, c_size_t, _P]),
     "awq_b200_ffn_stack_decode_tp_bf16": (c_int, [_P, c_int, _P, _P, _P, c_float, c_int, c_int, c_int, c_int, _P, c_size_t,

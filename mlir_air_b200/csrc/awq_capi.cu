@@ -239,6 +239,7 @@ extern "C" int awq_b200_set_ffn_stack_tuning(int lookahead_units, int split_per_
 }
 extern "C" size_t awq_b200_ffn_stack_plan_bytes(int n_layers) { return ffn_fused_plan_bytes(n_layers); }
 extern "C" size_t awq_b200_ffn_stack_workspace_bytes(int n_layers) { return ffn_fused_workspace_bytes(n_layers); }
+extern "C" size_t awq_b200_ffn_stack_tp_slot_bytes(int H, int n_ranks) { return ffn_fused_tp_slot_bytes(H, n_ranks); }
 
 extern "C" int awq_b200_ffn_stack_plan(void *plan, size_t plan_bytes, int n_layers, const int32_t *const *qw_gateup,
                                        const int32_t *const *qz_gateup, const uint16_t *const *s_gateup,
@@ -275,8 +276,10 @@ extern "C" int awq_b200_ffn_stack_decode_tp_bf16(const void *plan, int n_layers,
     if (B == 0) return AWQ_OK;
     AWQ_REQUIRE(plan && x && out && inter && peer_base, "ffn_stack_decode_tp: null pointer");
     AWQ_REQUIRE(aligned16(x) && aligned16(out) && aligned16(inter), "ffn_stack_decode_tp: pointers must be 16-byte aligned");
-    AWQ_REQUIRE(flag_offset >= (size_t)8 * H * sizeof(float) && slot_stride >= flag_offset + 64 && slot_stride % 16 == 0 &&
-                    flag_offset % 16 == 0, "ffn_stack_decode_tp: a slot holds an f32 [8, H] partial and 16 flag words behind it");
+    AWQ_REQUIRE(flag_offset >= ffn_fused_tp_slot_bytes(H, n_ranks) && slot_stride >= flag_offset + 64 && slot_stride % 16 == 0 &&
+                    flag_offset % 16 == 0,
+                "ffn_stack_decode_tp: a slot holds awq_b200_ffn_stack_tp_slot_bytes(H, n_ranks) = %zu bytes and 16 flag words "
+                "behind them", ffn_fused_tp_slot_bytes(H, n_ranks));
     if (!ffn_fused_supported(B, H, I_local, group_size))
         return set_error(AWQ_ERR_UNSUPPORTED,
                          "ffn_stack_decode_tp: needs B <= 8, group 128, H and I multiples of 128 (B=%d H=%d I=%d gs=%d)", B, H,

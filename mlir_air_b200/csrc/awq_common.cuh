@@ -158,6 +158,7 @@ size_t ffn_fused_plan_bytes(int n_layers);
 void ffn_fused_set_lookahead(int units);
 void ffn_fused_set_split(int per_1024);
 size_t ffn_fused_workspace_bytes(int n_layers);
+size_t ffn_fused_tp_slot_bytes(int H, int n_ranks);
 bool ffn_fused_supported(int B, int H, int I, int group_size);
 int ffn_fused_plan(void *plan_dev, size_t plan_bytes, int n_layers, const int32_t *const *qw_gateup,
                    const int32_t *const *qz_gateup, const uint16_t *const *s_gateup, const int32_t *const *qw_down,

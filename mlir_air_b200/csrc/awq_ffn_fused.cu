@@ -25,12 +25,14 @@
 //  * The loader also prefetches into L2, a few units ahead of the ring and across phase and
 //    layer boundaries (weights depend on nothing), so HBM keeps streaming while a phase change
 //    waits for the slowest CTA; the ring then refills from L2.
-//  * Tensor-parallel ranks run the same launch on their shards.  A down phase then ends with the
-//    rank's f32 partial in its own peer-mapped send slot; the warp that completes the phase issues one
-//    system-scope fence and counts the rank in on every rank's flag words; the normaliser warps of
-//    all CTAs wait for all ranks, read the partials with peer loads in rank order, update the hidden
-//    state and the next layer's sums of squares, and count themselves in for the next gate/up phase.
-//    Kernels of different GPUs wait for one another here, never two launches on one GPU.
+//  * Tensor-parallel ranks run the same launch on their shards.  The warp that finishes a down
+//    sub-strip then stores its f32 partial sums straight into the receive area of every rank
+//    (its own included) as 8-byte words, value and the exchange's tag together, so a word is
+//    either absent or complete and needs no fence and no flag of its own.  On every rank one
+//    normaliser warp per sub-strip polls the words of all ranks, adds them in rank order (every
+//    rank gets the same bits), and ends the sub-strip exactly as a single GPU does: residual,
+//    bf16 hidden state, squares for the next RMSNorm, the phase counter.  Kernels of different
+//    GPUs wait for one another here, never two launches on one GPU.
 //  * Rounding points are those of the separate kernels: bf16 normed activations, bf16 gate and
 //    up sums before SwiGLU, bf16 SwiGLU output, bf16 hidden state.
 #include <cudaTypedefs.h>
@@ -68,11 +70,6 @@ __host__ __device__ constexpr size_t ff_state_bytes(int n_layers) {
 __device__ __forceinline__ int ld_acquire_gpu(const int *p) {
     int v;
     asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int *p) {
-    unsigned int v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
@@ -128,17 +125,25 @@ struct FusedArgs {
     float *accum;   // per-strip split-K accumulators (zero between uses)
     int *counters;  // per sub-strip counters of the k groups added so far (zero between uses)
     int *err_flag;
-    int *state;     // done_gu, done_d, done_r, ..., then sumsq[(n_layers + 1) * 8]
+    int *state;     // done_gu, done_d, ..., then sumsq[(n_layers + 1) * 8]
     // Tensor parallelism (tp_n > 1): this rank holds a shard of every layer (gate/up columns, down
-    // rows); the down phase leaves an f32 partial [8, H] in this rank's send slot l & 1, the ranks
-    // tell one another through flag words, and the reduce phase reads all ranks' partials with peer loads.
+    // rows).  Receive area of rank r, slot s: for every source rank and every 64-column sub-strip of
+    // the hidden state 16 x 32 words of (tag << 32 | f32 bits), laid out so that a warp's store and
+    // load instructions touch 256 consecutive bytes.  Successive exchanges alternate between the slots.
     int tp_n, tp_rank;
-    float *partial[2];                         // this rank's send slots
-    const float *peer_partial[2][TP_MAX_RANKS];  // every rank's send slots, mapped into this GPU's address space
-    unsigned int *peer_flags[2][TP_MAX_RANKS];   // rank r's arrival counters [TP_MAX_RANKS] of slot s (never reset)
-    unsigned int *flags[2];                    // this rank's arrival counters of slot s
-    unsigned int *epoch;                       // launches so far on this rank (the counters' base)
+    unsigned long long *ll_recv[2][TP_MAX_RANKS];  // every rank's receive slots, mapped into this GPU's address space
+    unsigned int *epoch;                           // launches so far on this rank (base of the tags), in peer memory
 };
+constexpr int FF_LL_WORDS = 16 * 32;  // words of one sub-strip from one rank
+
+__device__ __forceinline__ void st_relaxed_sys_u64(unsigned long long *p, unsigned long long v) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_relaxed_sys_u64(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
 
 // The unit range [u0, u1) of one half in one phase: the SM's range [s U / S, (s + 1) U / S), cut.
 __device__ __forceinline__ void ff_range(long long U, int half, int split, long long &u0, long long &u1) {
@@ -186,6 +191,42 @@ struct UnitCursor {
     }
 };
 
+// End of a down sub-strip: lane's 2 x 8 finished sums of batch row b at columns n + 32 h + i.
+// hidden state = bf16(sum + residual), its squares go to the next layer's RMSNorm sums.  `res0`,
+// `res1`: the residual values, loaded by the caller (before it waited for the sums).
+__device__ __forceinline__ void ff_down_epilogue(const float (&own)[2][8], const uint4 (&rres)[2], uint16_t *out, float *sumsq_next,
+                                                 int B, int N, int n, int b, int lane) {
+    float ss = 0.f;
+    if (b < B) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int nh = n + 32 * h;
+            if (nh >= N) continue;
+            const uint32_t rw[4] = {rres[h].x, rres[h].y, rres[h].z, rres[h].w};
+            uint32_t o[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                o[i] = pack_bf16x2(own[h][2 * i] + bf16x2_lo(rw[i]), own[h][2 * i + 1] + bf16x2_hi(rw[i]));
+                const float lo = bf16x2_lo(o[i]), hi = bf16x2_hi(o[i]);
+                ss = fmaf(lo, lo, ss);
+                ss = fmaf(hi, hi, ss);
+            }
+            *reinterpret_cast<uint4 *>(out + (size_t)b * N + nh) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+    // lanes with the same batch row differ in bits 3 and 4
+    ss += __shfl_xor_sync(0xffffffffu, ss, 8);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 16);
+    if (lane < 8 && b < B) atomicAdd(sumsq_next + b, ss);
+}
+__device__ __forceinline__ void ff_load_residual(uint4 (&rres)[2], const uint16_t *residual, int B, int N, int n, int b) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        rres[h] = make_uint4(0u, 0u, 0u, 0u);
+        if (b < B && n + 32 * h < N) rres[h] = __ldcg(reinterpret_cast<const uint4 *>(residual + (size_t)b * N + n + 32 * h));
+    }
+}
+
 __global__ void __launch_bounds__(FF_THREADS, 1)
 ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant__ CUtensorMap tmH0,
                  const __grid_constant__ CUtensorMap tmH, const FusedArgs a) {
@@ -206,8 +247,11 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
     // phase 0: gate/up, K = H, N = 2I; phase 1: down, K = I, N = H
     const int G0 = H / SK_GROUP, V0 = (2 * I + SK_STRIP - 1) / SK_STRIP;
     const int G1 = I / SK_GROUP, V1 = (H + SK_STRIP - 1) / SK_STRIP;
-    int *done_gu = a.state, *done_d = a.state + 1, *done_r = a.state + 2;
+    int *done_gu = a.state, *done_d = a.state + 1;
     const bool tp = a.tp_n > 1;
+    // tensor parallel: exchanges so far on these buffers (all launches run the same number of layers); every
+    // warp reads the count before anything of this launch can end
+    const unsigned int exch0 = tp ? *a.epoch * (unsigned int)a.n_layers : 0u;
     float *sumsq = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(a.state) + FF_STATE_HEADER);
 
     if (role == 1 && lane == 0) {  // each loader sets up its half's barriers
@@ -321,12 +365,9 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
                 cur.next();
             }
             // the phase's activations exist once every sub-strip of the previous phase is finalised
-            // (tensor parallel: a gate/up phase waits for the reduce phase of the previous layer instead,
-            // which every normaliser warp of the launch counts in done_r)
-            const bool after_reduce = tp && !p && l > 0;
-            const int target = after_reduce ? l * 2 * (int)gridDim.x
-                                            : (p ? (l + 1) * V0 * SK_CONSUMER_WARPS : B + l * V1 * SK_CONSUMER_WARPS);
-            if (!wait_count(after_reduce ? done_r : (p ? done_gu : done_d), target)) {
+            // (tensor parallel: a down sub-strip is finalised by the warp that added up all ranks' sums)
+            const int target = p ? (l + 1) * V0 * SK_CONSUMER_WARPS : B + l * V1 * SK_CONSUMER_WARPS;
+            if (!wait_count(p ? done_gu : done_d, target)) {
                 atomicExch(a.err_flag, 3);
                 return;
             }
@@ -355,7 +396,6 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
         // the 128B-swizzled [8 x 64] box pair put them; bf16 rounding, then the fp16 form
         const int r = lane >> 2, q4 = lane & 3;
         int slot = 0, round = 0;
-        const unsigned int epoch0 = tp ? *a.epoch : 0u;  // every warp reads it before anything of this launch ends
         for (int l = 0; l < a.n_layers; ++l) {
             for (int p = 0; p < 2; ++p) {
                 long long u0, u1;
@@ -398,78 +438,56 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
                     if (++slot == SK_STAGES) { slot = 0; ++round; }
                 }
                 if (tp && p) {
-                    // ---- reduce phase: h <- bf16(h + sum over ranks of the down partials), in rank order ----
-                    const int sl = l & 1;
-                    // slot sl has been used (l >> 1) + 1 times in this launch and by every earlier launch
-                    const unsigned int uses_per_launch = (unsigned int)(sl ? a.n_layers / 2 : (a.n_layers + 1) / 2);
-                    const unsigned int expected = epoch0 * uses_per_launch + (unsigned int)(l >> 1) + 1u;
-                    int good = 1;
-                    if (lane < a.tp_n) {
-                        const long long t0 = clock64();
-                        while (ld_acquire_sys_u32(a.flags[sl] + lane) < expected) {
-                            if (clock64() - t0 > (1ll << 31)) {
-                                good = 0;
-                                break;
-                            }
-                            __nanosleep(64);
-                        }
-                    }
-                    if (!__all_sync(0xffffffffu, good)) {
-                        if (lane == 0) atomicExch(a.err_flag, 6);
-                        return;
-                    }
+                    // ---- this layer's exchange: sub-strips gw, gw + W, ... of the hidden state are ended here ----
+                    const unsigned int tag = exch0 + (unsigned int)l + 1u;
+                    const int sl = (int)((exch0 + (unsigned int)l) & 1u);
+                    const int n_sub = V1 * SK_CONSUMER_WARPS;
                     const uint16_t *hres = l == 0 ? a.x : a.out;
-                    const long long W = 2 * (long long)gridDim.x, gw = 2 * (long long)blockIdx.x + half;
-                    const long long chunks = (long long)B * (H >> 3);  // 8 values each, rows 0 .. B-1
-                    const long long c0 = gw * chunks / W, c1 = (gw + 1) * chunks / W;
-                    const int row_first = (int)(c0 / (H >> 3));
-                    // squares for row_first and for the next row; a slice that spans more rows (tiny grids)
-                    // adds every chunk's squares on its own
-                    const bool two_rows = c1 <= c0 || (int)((c1 - 1) / (H >> 3)) - row_first <= 1;
-                    float ss0 = 0.f, ss1 = 0.f;
-                    for (long long c = c0 + lane; c < c1; c += 32) {
-                        const size_t e = (size_t)c * 8;
-                        float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                        for (int rk = 0; rk < a.tp_n; ++rk) {
-                            const float *src = a.peer_partial[sl][rk] + e;
-                            const float4 p0 = __ldcg(reinterpret_cast<const float4 *>(src));
-                            const float4 p1 = __ldcg(reinterpret_cast<const float4 *>(src + 4));
-                            sum[0] += p0.x; sum[1] += p0.y; sum[2] += p0.z; sum[3] += p0.w;
-                            sum[4] += p1.x; sum[5] += p1.y; sum[6] += p1.z; sum[7] += p1.w;
-                        }
-                        const uint4 hv = __ldcg(reinterpret_cast<const uint4 *>(hres + e));
-                        const uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w};
-                        uint32_t o[4];
-                        float ss = 0.f;
+                    const int W = 2 * (int)gridDim.x, gw = 2 * (int)blockIdx.x + half;
+                    for (int sub = gw; sub < n_sub; sub += W) {
+                        const SkLane sg(sub % SK_CONSUMER_WARPS, lane);
+                        const int sb = 2 * sg.t4 + sg.odd, n = (sub / SK_CONSUMER_WARPS) * SK_STRIP + sg.colw;
+                        uint4 rres[2];
+                        ff_load_residual(rres, hres, B, H, n, sb);
+                        float own[2][8];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            o[i] = pack_bf16x2(bf16x2_lo(hw[i]) + sum[2 * i], bf16x2_hi(hw[i]) + sum[2 * i + 1]);
-                            const float lo = bf16x2_lo(o[i]), hi = bf16x2_hi(o[i]);
-                            ss = fmaf(lo, lo, ss);
-                            ss = fmaf(hi, hi, ss);
-                        }
-                        *reinterpret_cast<uint4 *>(a.out + e) = make_uint4(o[0], o[1], o[2], o[3]);
-                        const int row = (int)(c / (H >> 3));
-                        if (!two_rows) atomicAdd(sumsq + (size_t)(l + 1) * 8 + row, ss);
-                        else if (row == row_first) ss0 += ss;
-                        else ss1 += ss;
-                    }
+                        for (int h = 0; h < 2; ++h)
 #pragma unroll
-                    for (int o_ = 16; o_ > 0; o_ >>= 1) {
-                        ss0 += __shfl_xor_sync(0xffffffffu, ss0, o_);
-                        ss1 += __shfl_xor_sync(0xffffffffu, ss1, o_);
+                            for (int i = 0; i < 8; ++i) own[h][i] = 0.f;
+                        bool good = true;
+                        const long long t0 = clock64();
+                        for (int rk = 0; rk < a.tp_n && good; ++rk) {
+                            const unsigned long long *src =
+                                a.ll_recv[sl][a.tp_rank] + ((size_t)rk * n_sub + sub) * FF_LL_WORDS + lane;
+                            unsigned long long w[16];
+                            bool all;
+                            do {
+#pragma unroll
+                                for (int i = 0; i < 16; ++i) w[i] = ld_relaxed_sys_u64(src + i * 32);
+                                all = true;
+#pragma unroll
+                                for (int i = 0; i < 16; ++i) all = all && (unsigned int)(w[i] >> 32) == tag;
+                                all = __all_sync(0xffffffffu, all);
+                                if (!all && clock64() - t0 > (1ll << 31)) good = false;
+                            } while (!all && good);
+                            if (good) {
+#pragma unroll
+                                for (int i = 0; i < 16; ++i) own[i >> 3][i & 7] += __uint_as_float((unsigned int)w[i]);
+                            }
+                        }
+                        if (!good) {
+                            if (lane == 0) atomicExch(a.err_flag, 6);
+                            return;
+                        }
+                        ff_down_epilogue(own, rres, a.out, sumsq + (size_t)(l + 1) * 8, B, H, n, sb, lane);
+                        __threadfence();
+                        __syncwarp();
+                        if (lane == 0) atomicAdd(done_d, 1);
                     }
-                    if (lane == 0 && c1 > c0 && two_rows) {
-                        atomicAdd(sumsq + (size_t)(l + 1) * 8 + row_first, ss0);
-                        if (row_first + 1 < B) atomicAdd(sumsq + (size_t)(l + 1) * 8 + row_first + 1, ss1);
-                    }
-                    __threadfence();
-                    __syncwarp();
-                    if (lane == 0) atomicAdd(done_r, 1);
                 }
             }
         }
-        if (tp && blockIdx.x == 0 && half == 0 && lane == 0) *a.epoch = epoch0 + 1u;
+        if (tp && blockIdx.x == 0 && half == 0 && lane == 0) *a.epoch = exch0 / (unsigned int)a.n_layers + 1u;
         return;
     }
 
@@ -520,48 +538,23 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
                 if (!p) {
                     sk_epilogue<EPI_SWIGLU>(own, nullptr, a.inter, B, N, n, b, 1);
                 } else if (tp) {
-                    // this rank's partial goes to its send slot; the warp that completes the phase on this
-                    // GPU makes it visible to the other GPUs (one cumulative system-scope fence) and
-                    // counts this rank in on every rank
-                    sk_epilogue<EPI_F32>(own, nullptr, a.partial[l & 1], B, N, n, b, 0);
-                    __threadfence();
-                    __syncwarp();
-                    int last = 0;
-                    if (lane == 0) last = atomicAdd(done_d, 1) + 1 == B + (l + 1) * V1 * SK_CONSUMER_WARPS;
-                    if (__shfl_sync(0xffffffffu, last, 0)) {
-                        __threadfence_system();
-                        if (lane < a.tp_n) atomicAdd_system(a.peer_flags[l & 1][lane] + a.tp_rank, 1u);
+                    // this rank's sums of the sub-strip go to every rank, value and tag in one 8-byte word; the
+                    // warp that collects the sub-strip on each rank ends it
+                    const unsigned long long tag = (unsigned long long)(exch0 + (unsigned int)l + 1u) << 32;
+                    const int sl = (int)((exch0 + (unsigned int)l) & 1u);
+                    const size_t w0 = ((size_t)a.tp_rank * (V1 * SK_CONSUMER_WARPS) + v * SK_CONSUMER_WARPS + cw) * FF_LL_WORDS + lane;
+                    for (int rk = 0; rk < a.tp_n; ++rk) {
+                        unsigned long long *dst = a.ll_recv[sl][(a.tp_rank + rk) % a.tp_n] + w0;  // own rank first, then round the ring
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            st_relaxed_sys_u64(dst + i * 32, tag | (unsigned long long)__float_as_uint(own[i >> 3][i & 7]));
                     }
                     return;
                 } else {
                     // hidden state: bf16(sum + residual), and its squares for the next layer's RMSNorm
-                    float ss = 0.f;
-                    if (b < B) {
-                        // both residual loads before the first store (`out` is the residual from layer 1 on)
-                        uint4 rres[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
-#pragma unroll
-                        for (int h = 0; h < 2; ++h)
-                            if (n + 32 * h < N) rres[h] = __ldcg(reinterpret_cast<const uint4 *>(residual + (size_t)b * N + n + 32 * h));
-#pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            const int nh = n + 32 * h;
-                            if (nh >= N) continue;
-                            const uint32_t rw[4] = {rres[h].x, rres[h].y, rres[h].z, rres[h].w};
-                            uint32_t o[4];
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                o[i] = pack_bf16x2(own[h][2 * i] + bf16x2_lo(rw[i]), own[h][2 * i + 1] + bf16x2_hi(rw[i]));
-                                const float lo = bf16x2_lo(o[i]), hi = bf16x2_hi(o[i]);
-                                ss = fmaf(lo, lo, ss);
-                                ss = fmaf(hi, hi, ss);
-                            }
-                            *reinterpret_cast<uint4 *>(a.out + (size_t)b * N + nh) = make_uint4(o[0], o[1], o[2], o[3]);
-                        }
-                    }
-                    // lanes with the same batch row differ in bits 3 and 4
-                    ss += __shfl_xor_sync(0xffffffffu, ss, 8);
-                    ss += __shfl_xor_sync(0xffffffffu, ss, 16);
-                    if (lane < 8 && b < B) atomicAdd(sumsq + (size_t)(l + 1) * 8 + b, ss);
+                    uint4 rres[2];
+                    ff_load_residual(rres, residual, B, N, n, b);
+                    ff_down_epilogue(own, rres, a.out, sumsq + (size_t)(l + 1) * 8, B, N, n, b, lane);
                 }
                 __threadfence();
                 __syncwarp();
@@ -609,6 +602,11 @@ void ffn_fused_set_split(int per_1024) { g_ffn_split = per_1024 < 0 ? 0 : (per_1
 size_t ffn_fused_plan_bytes(int n_layers) { return (size_t)(n_layers > 0 ? n_layers : 0) * sizeof(FusedLayer); }
 
 size_t ffn_fused_workspace_bytes(int n_layers) { return FF_STATE_OFF + ff_state_bytes(n_layers); }
+
+// Receive area of one slot: for each rank and each 64-column sub-strip of the hidden state 16 x 32 words.
+size_t ffn_fused_tp_slot_bytes(int H, int n_ranks) {
+    return (size_t)(n_ranks > 0 ? n_ranks : 0) * ((H + SK_STRIP - 1) / SK_STRIP) * SK_CONSUMER_WARPS * FF_LL_WORDS * 8;
+}
 
 bool ffn_fused_supported(int B, int H, int I, int group_size) {
     return group_size == SK_GROUP && B >= 1 && B <= 8 && H > 0 && I > 0 && H % SK_GROUP == 0 && I % SK_GROUP == 0 &&
@@ -709,27 +707,20 @@ int launch_ffn_fused(const void *plan_dev, int n_layers, const uint16_t *x, uint
     a.tp_n = 1;
     a.tp_rank = 0;
     a.epoch = nullptr;
-    for (int sl = 0; sl < 2; ++sl) {
-        a.partial[sl] = nullptr;
-        a.flags[sl] = nullptr;
-        for (int r = 0; r < TP_MAX_RANKS; ++r) {
-            a.peer_partial[sl][r] = nullptr;
-            a.peer_flags[sl][r] = nullptr;
-        }
-    }
+    for (int sl = 0; sl < 2; ++sl)
+        for (int r = 0; r < TP_MAX_RANKS; ++r) a.ll_recv[sl][r] = nullptr;
     if (peers && peers->n > 1) {
+        if (peers->flag_offset < ffn_fused_tp_slot_bytes(H, peers->n))
+            return set_error(AWQ_ERR_INVALID_ARGUMENT, "ffn_stack_decode_tp: a slot must hold %zu bytes for %d ranks and H = %d",
+                             ffn_fused_tp_slot_bytes(H, peers->n), peers->n, H);
         a.tp_n = peers->n;
         a.tp_rank = peers->rank;
-        for (int sl = 0; sl < 2; ++sl) {
-            for (int r = 0; r < peers->n; ++r) {
-                uint8_t *base = reinterpret_cast<uint8_t *>(peers->base[r]) + (size_t)sl * peers->slot_stride;
-                a.peer_partial[sl][r] = reinterpret_cast<const float *>(base);
-                a.peer_flags[sl][r] = reinterpret_cast<unsigned int *>(base + peers->flag_offset);
-            }
-            a.partial[sl] = const_cast<float *>(a.peer_partial[sl][peers->rank]);
-            a.flags[sl] = a.peer_flags[sl][peers->rank];
-        }
-        a.epoch = a.flags[0] + 15;  // the last word of slot 0's flag block
+        for (int sl = 0; sl < 2; ++sl)
+            for (int r = 0; r < peers->n; ++r)
+                a.ll_recv[sl][r] = reinterpret_cast<unsigned long long *>(reinterpret_cast<uint8_t *>(peers->base[r]) +
+                                                                          (size_t)sl * peers->slot_stride);
+        // the last word of the flag block behind this rank's slot 0
+        a.epoch = reinterpret_cast<unsigned int *>(reinterpret_cast<uint8_t *>(peers->base[peers->rank]) + peers->flag_offset) + 15;
     }
     a.accum = reinterpret_cast<float *>(ws + SK_WS_ACCUM);
     a.counters = reinterpret_cast<int *>(ws + SK_WS_HEADER);

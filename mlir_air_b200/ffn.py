@@ -148,7 +148,7 @@ class DecodeFFNStack:
             if self.plan.workspace_bytes() > self.ws.nbytes:
                 self.plan = None
             elif self.tp > 1:  # the ranks exchange their partials inside the launch, through these buffers
-                self.plan_peers = self._peer_buffers_or_none(group, 8 * hidden * 4, device)
+                self.plan_peers = self._peer_buffers_or_none(group, ops.ffn_stack_tp_slot_bytes(hidden, self.tp), device)
                 if self.plan_peers is None:
                     self.plan = None  # every rank falls back to the per-layer kernels + NCCL together
         self._pin_in = torch.empty((max_batch, hidden), dtype=torch.bfloat16).pin_memory() if torch.cuda.is_available() else None

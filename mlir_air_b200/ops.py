@@ -319,9 +319,14 @@ def ffn_stack_decode(plan: FFNStackPlan, x, ws: Workspace, eps=1e-5, inter=None,
     return out
 
 
+def ffn_stack_tp_slot_bytes(H: int, n_ranks: int) -> int:
+    return int(_lib.load().awq_b200_ffn_stack_tp_slot_bytes(int(H), int(n_ranks)))
+
+
 def ffn_stack_decode_tp(plan: FFNStackPlan, x, ws: Workspace, peers, eps=1e-5, inter=None, out=None):
     """The one-launch stack on this rank's shards, with the partials exchanged through `peers`
-    (mlir_air_b200.peer.PeerBuffers with two slots of 8 * H * 4 bytes, used by nothing else)."""
+    (mlir_air_b200.peer.PeerBuffers with two slots of ffn_stack_tp_slot_bytes(H, world) bytes, used by
+    nothing else and always with the same number of layers)."""
     x = _x2d(x, plan.H)
     B = x.shape[0]
     if inter is None:
