@@ -398,7 +398,7 @@ def run_ours(a):
         "data": "synthetic",
         "config": {"workload": workload_name(a), "parallelism": f"tp{tp}",
                    "exchange": ("none" if tp == 1 else
-                                "inside the stack kernel: f32 partials in peer-mapped send buffers, flag words, peer loads"
+                                "inside the stack kernel: f32 partials stored into every rank's peer-mapped receive area as value+tag words, polled and added in rank order"
                                 if stack.uses_fused(B) else
                                 "peer loads from every rank's send buffer + flag words"
                                 if stack.peers is not None and B <= 8 else "NCCL allreduce per layer"),

@@ -468,7 +468,9 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
 #pragma unroll
                                 for (int i = 0; i < 16; ++i) all = all && (unsigned int)(w[i] >> 32) == tag;
                                 all = __all_sync(0xffffffffu, all);
-                                if (!all && clock64() - t0 > (1ll << 31)) good = false;
+                                // the lanes must leave together: one lane's clock decides for the warp
+                                const bool late = __shfl_sync(0xffffffffu, clock64() - t0 > (1ll << 31) ? 1 : 0, 0) != 0;
+                                if (!all && late) good = false;
                             } while (!all && good);
                             if (good) {
 #pragma unroll
