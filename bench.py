@@ -42,7 +42,7 @@ def parse():
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM timing (extra key `prefill`)")
     ap.add_argument("--unfused", action="store_true", help="per-layer kernels instead of the one-launch stack kernel")
     ap.add_argument("--peer-exchange", action="store_true",
-                    help="tensor parallel: partials read from peer memory + flag words instead of an NCCL allreduce per layer")
+                    help="tensor parallel with the per-layer kernels: partials read from peer memory + flag words instead of an NCCL allreduce per layer")
     ap.add_argument("--no-replicas", action="store_true", help="N > 1: skip the data-parallel measurement (extra key `replicas`)")
     ap.add_argument("--sweep", action="store_true", help="also time batch 1/8/32/64 (extra key `batches`)")
     return ap.parse_args()
