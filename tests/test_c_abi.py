@@ -60,7 +60,15 @@ def test_argument_errors_need_no_gpu():
     assert _err(lib.awq_b200_ffn_stack_decode_tp_bf16(p, 1, p, p, p, 1e-5, 1, 512, 1024, 128, arr, 1 << 16, 1 << 15, 1, 0, p,
                                                       1 << 20, None))[0] == INV  # a single rank is not tensor parallel
     assert _err(lib.awq_b200_ffn_stack_decode_tp_bf16(p, 1, p, p, p, 1e-5, 1, 512, 1024, 128, arr, 64, 0, 2, 0, p, 1 << 20,
-                                                      None))[0] == INV  # slots too small for an [8, H] partial
+                                                      None))[0] == INV  # slots too small for the receive area
+    # receive area of one slot: per rank and 64-column sub-strip of the hidden state 16 x 32 words of 8 bytes
+    assert lib.awq_b200_ffn_stack_tp_slot_bytes(8192, 8) == 8 * (8192 // 64) * 16 * 32 * 8
+    assert lib.awq_b200_ffn_stack_tp_slot_bytes(1000, 2) == 2 * 2 * 8 * 16 * 32 * 8  # strips of 512 columns, rounded up
+    two = (ctypes.c_void_p * 2)(256, 512)
+    need = lib.awq_b200_ffn_stack_tp_slot_bytes(512, 2)
+    rc, msg = _err(lib.awq_b200_ffn_stack_decode_tp_bf16(p, 1, p, p, p, 1e-5, 1, 512, 1024, 128, two, need + 240, need - 16, 2, 0,
+                                                         p, 1 << 20, None))
+    assert rc == INV and "tp_slot_bytes" in msg
     assert _err(lib.awq_b200_gemv_f32_push(p, 0, p, p, p, p, 9, 256, 64, 128, arr, 2, 0, p, 1 << 20, None))[0] == INV
     assert _err(lib.awq_b200_tp_reduce_add_rmsnorm_act(p, arr, p, 9, None, 1e-5, p, None, 0, 1, 512, p, None))[0] == INV
     # fused GEMM epilogues
