@@ -148,8 +148,37 @@ class ClockSampler:
         self.samples = []
         self._stop = threading.Event()
         self._t = threading.Thread(target=self._loop, daemon=True)
+        self.source = "nvidia-smi"
+
+    def _nvml_loop(self):
+        """Read-only NVML queries every 2 ms (a timed region of 100 ms gets tens of samples; one
+        nvidia-smi process per sample gets one or two).  Returns False if NVML is not usable."""
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            reasons_of = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+            mx = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+            pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
+            reasons_of(h)
+        except Exception:
+            return False
+        self.source = "nvml"
+        bits = (0x8, 0x40, 0x20, 0x4)  # hw_slowdown, hw_thermal_slowdown, sw_thermal_slowdown, sw_power_cap
+        while not self._stop.is_set():
+            try:
+                r = int(reasons_of(h))
+                self.samples.append([str(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)), str(mx)] +
+                                    ["Active" if r & b else "Not Active" for b in bits])
+            except Exception:
+                pass
+            self._stop.wait(0.002)
+        return True
 
     def _loop(self):
+        if self._nvml_loop():
+            return
         while not self._stop.is_set():
             try:
                 out = subprocess.run(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
@@ -175,7 +204,7 @@ class ClockSampler:
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(self.samples)}
+                "reasons": reasons, "samples": len(self.samples), "source": self.source}
 
 
 # --------------------------------------------------------------------------------------
