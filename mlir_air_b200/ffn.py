@@ -108,11 +108,15 @@ class DecodeFFNStack:
     forward_host(x)  host array in, host array out: pinned H2D, one CUDA-graph replay of the
                      whole stack, D2H -- the call a serving loop makes per token batch.
     With `group` (a torch.distributed process group) the layers are this rank's shards and
-    each layer ends in one allreduce of the f32 down-projection partials.
+    each layer ends in one exchange of the f32 down-projection partials: inside the one-launch
+    kernel for batches it takes, an allreduce per layer otherwise.  `align_ranks`: the one-launch
+    kernels of the ranks wait for one another with a limit of about a second, so a one-element
+    allreduce is enqueued in front of each launch (also inside the captured graph); it makes the
+    ranks' kernels start together however far apart the host threads are.
     """
 
     def __init__(self, layers: Sequence[FFNLayer], hidden: int, max_batch: int = 64, eps: float = 1e-5,
-                 group=None, device="cuda", fused: bool = True, peer_push: bool = False):
+                 group=None, device="cuda", fused: bool = True, peer_push: bool = False, align_ranks: bool = True):
         self.layers = list(layers)
         self.hidden = hidden
         self.eps = eps
@@ -142,6 +146,7 @@ class DecodeFFNStack:
         # a norm weight, one shape, group 128, batch <= 8 (larger batches take the per-layer kernels)
         self.plan = None
         self.plan_peers = None
+        self._align = torch.zeros(1, dtype=torch.int32, device=device) if align_ranks and self.tp > 1 else None
         if fused and self._fusable():
             self.plan = ops.FFNStackPlan([l.gateup for l in self.layers], [l.down for l in self.layers],
                                          [l.gamma for l in self.layers])
@@ -221,6 +226,8 @@ class DecodeFFNStack:
         normed, inter, partial = self._normed[:B], self._inter, self._partial[:B]
         if self.uses_fused(B):
             if self.tp > 1:
+                if self._align is not None:
+                    torch.distributed.all_reduce(self._align, group=self.group)
                 return ops.ffn_stack_decode_tp(self.plan, h, self.ws, self.plan_peers, eps=self.eps, inter=inter, out=other)
             return ops.ffn_stack_decode(self.plan, h, self.ws, eps=self.eps, inter=inter, out=other)
         if self.uses_gemm(B):
