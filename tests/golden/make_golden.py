@@ -60,7 +60,8 @@ def _import_from(path, modname):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("MLIR_AIR_SRC"), required="MLIR_AIR_SRC" not in os.environ,
+                    help="checkout of mlir-air (or set MLIR_AIR_SRC)")
     ap.add_argument("--out", default=os.path.dirname(os.path.abspath(__file__)))
     ap.add_argument("--big", action="store_true",
                     help="also replay the reference's 2048x2048 GEMV test shape (about 15 s)")
