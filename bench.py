@@ -44,13 +44,20 @@ def parse():
     ap.add_argument("--peer-exchange", action="store_true",
                     help="tensor parallel with the per-layer kernels: partials read from peer memory + flag words instead of an NCCL allreduce per layer")
     ap.add_argument("--no-replicas", action="store_true", help="N > 1: skip the data-parallel measurement (extra key `replicas`)")
-    ap.add_argument("--sweep", action="store_true", help="also time batch 1/8/32/64 (extra key `batches`)")
+    ap.add_argument("--sweep", action="store_true", help="time the batch sweep (extra key `batches`) on all layers instead of 16")
+    ap.add_argument("--no-configs", action="store_true",
+                    help="skip the extra keys dequant_cfg1 / gemv_cfg2 / ffn_cfg3 / batches (the other configurations of the benchmark definition)")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle comparison of the timed path (key `parity`)")
     return ap.parse_args()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per layer of the stack kernel at hidden 8192 / intermediate
-# 28672 / batch 8: ncu capture of a 2-layer launch, halved (the committed ncu summary of that kernel)
-FUSED_TRAFFIC_PER_LAYER = 370400128
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu summaries, keyed by
+# (kernel, hidden, intermediate per rank, batch).  The stack kernel's figure is per layer (a 2-layer
+# capture, halved) and is scaled by the layer count; shapes that were not captured report null.
+NCU_TRAFFIC = {
+    ("ffn_fused_kernel", 8192, 28672, 8): {"bytes_per_layer": 370400128, "source": "profiles/ffn_fused_70b_stack.md"},
+    ("gemv_streamk_kernel<EPI_SWIGLU>", 8192, 28672, 8): {"bytes": 249810432, "source": "profiles/gemv_streamk_70b_ffn_layer.md"},
+}
 
 
 def workload_name(a):
@@ -111,25 +118,40 @@ def cpu_threads():
         return os.cpu_count() or 1
 
 
+def use_all_host_cores():
+    """Give the BLAS pool every host core, whatever the launcher put in OMP_NUM_THREADS (torchrun
+    sets it to 1).  Returns the object that keeps the limit alive."""
+    try:
+        import numpy  # noqa: F401  (loads BLAS so the pool exists)
+        from threadpoolctl import threadpool_limits
+        return threadpool_limits(limits=os.cpu_count() or 1)
+    except Exception:
+        return None
+
+
 def run_reference(a):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    import numpy  # noqa: F401  (loads BLAS so threadpool_info sees it)
+    _pool = use_all_host_cores()  # noqa: F841
     s = cpu_sample_setup(a)
     for _ in range(min(a.warmup, 1)):
         cpu_sample_run(a, s)
     times = [cpu_sample_run(a, s) for _ in range(max(1, a.steps))]
     per = sum(times) / len(times)
     v = cpu_tokens_per_s(a, per, s["cols"])
+    factor = (a.intermediate / s["cols"]) * a.layers
     sample = (f"numpy golden (dequant + f32 matmul + SwiGLU + residual) on {s['cols']}/{a.intermediate} of one layer's "
-              f"columns per step, scaled to {a.layers} layers")
+              f"columns per step; value and ms_per_step are EXTRAPOLATED by {factor:g} (x {a.intermediate / s['cols']:g} columns, "
+              f"x {a.layers} layers)")
     line = {
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps,
         "warmup": a.warmup, "ms_per_step": per * 1e3 * (a.intermediate / s["cols"]) * a.layers,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload_name(a), "parallelism": "host cores"},
-        "cpu_baseline": {"value": v, "unit": UNIT, "cores": cpu_threads(), "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": v, "unit": UNIT, "cores": cpu_threads(), "kind": "port", "sample": sample,
+                         "extrapolated": True, "extrapolation_factor": factor, "measured_ms_per_sample": per * 1e3},
+        "extrapolated": True, "extrapolation_factor": factor, "measured_ms_per_sample": per * 1e3,
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -213,6 +235,144 @@ class ClockSampler:
 def _dbg(msg):
     if os.environ.get("AWQ_BENCH_DEBUG"):
         print(f"[bench rank {os.environ.get('RANK', '0')}] {msg}", file=sys.stderr, flush=True)
+
+
+# --------------------------------------------------------------------------------------
+# the other configurations of the benchmark definition (extra keys) and the parity check
+# --------------------------------------------------------------------------------------
+def _graph_us(torch, enqueue, launches, reps=20, warm=3):
+    """Device time per launch of `enqueue()` (which enqueues `launches` kernels on distinct data)
+    captured in one CUDA graph and replayed `reps` times after `warm` replays."""
+    enqueue()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        enqueue()
+    for _ in range(warm):
+        g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (reps * launches)
+
+
+def _hbm_entry(us, nbytes, peak):
+    gbs = nbytes / (us * 1e-6) / 1e9
+    return {"us": us, "bytes": int(nbytes), "achieved_gbs": gbs, "frac_of_measured": gbs / peak, "frac_of_8TBs": gbs / 8000.0}
+
+
+def time_other_configs(a, torch, ops, ffn, peak):
+    """dequant 2048 x 2048, decode GEMV 4096 x 11008 (batch 1, 8), decode FFN 4096 / 11008 (batch 1, 4, 16):
+    graph replays over weight copies totalling more than twice the L2, so every launch streams from HBM."""
+    l2 = int(torch.cuda.get_device_properties(torch.cuda.current_device()).L2_cache_size)
+    out = {"l2_bytes": l2, "timing": "CUDA graph of one launch per weight copy, copies total > 2 x L2, 20 replays after 3"}
+    # ---- configuration 1: dequant of a 2048 x 2048 weight ----
+    K = N = 2048
+    per = K * N * BYTES_PER_WEIGHT + K * N * 2
+    copies = int(2 * l2 // per) + 2
+    ws_ = [ffn.random_layer(K, N // 2, seed=50 + i, with_gamma=False).gateup for i in range(copies)]
+    outs = [torch.empty((K, N), dtype=torch.bfloat16, device="cuda") for _ in range(copies)]
+    us = _graph_us(torch, lambda: [ops.dequant(w, o) for w, o in zip(ws_, outs)], copies)
+    out["dequant_cfg1"] = dict(_hbm_entry(us, per, peak), workload="AWQ dequant 2048 x 2048 -> bf16", copies=copies,
+                               kernel="dequant_kernel")
+    del ws_, outs
+    # ---- configuration 2: decode GEMV 4096 x 11008 ----
+    K, N = 4096, 11008
+    copies = int(2 * l2 // (K * N * BYTES_PER_WEIGHT)) + 2
+    ws_ = [ffn.random_layer(K, N // 2, seed=80 + i, with_gamma=False).gateup for i in range(copies)]
+    wsp = ops.Workspace(K, N)
+    g2 = {}
+    for B in (1, 8):
+        x = torch.randn((B, K), device="cuda").to(torch.bfloat16)
+        ys = [torch.empty((B, N), dtype=torch.bfloat16, device="cuda") for _ in range(copies)]
+        us = _graph_us(torch, lambda: [ops.gemv(x, w, wsp, out=y) for w, y in zip(ws_, ys)], copies)
+        g2[str(B)] = _hbm_entry(us, K * N * BYTES_PER_WEIGHT + B * K * 2 + B * N * 2, peak)
+    wsp.check()
+    out["gemv_cfg2"] = {"workload": "decode GEMV [B x 4096] x AWQ [4096 x 11008], one awq_b200_gemv_bf16 call per weight "
+                                    "(bf16 activations converted to fp16 by a small kernel in front of each GEMV)",
+                        "copies": copies, "batch": g2}
+    del ws_
+    # ---- configuration 3: decode SwiGLU FFN 4096 / 11008 ----
+    H, I = 4096, 11008
+    per = 3 * H * I * BYTES_PER_WEIGHT
+    nl = int(2 * l2 // per) + 2
+    layers = [ffn.random_layer(H, I, seed=300 + i) for i in range(nl)]
+    st = ffn.DecodeFFNStack(layers, H, max_batch=16)
+    g3 = {}
+    for B in (1, 4, 16):
+        x = torch.randn((B, H), device="cuda").to(torch.bfloat16)
+        st.capture(B)
+        st.load_input(x)
+        for _ in range(3):
+            st.replay(B)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(20):
+            st.replay(B)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (20 * nl)
+        g3[str(B)] = dict(_hbm_entry(us, per + 4 * B * H * 2, peak), tokens_per_s=B / (us * 1e-6),
+                          path="one launch of the stack kernel for all layers" if st.uses_fused(B) else "per-layer kernels")
+    st.check()
+    out["ffn_cfg3"] = {"workload": f"decode SwiGLU FFN hidden 4096 / intermediate 11008 with RMSNorm and residual, {nl} distinct "
+                                   "layers back to back, time per layer", "layers": nl, "batch": g3}
+    del st, layers
+    torch.cuda.empty_cache()
+    return out
+
+
+def parity_check(a, torch, ops, ffn, group, rank, world):
+    """The path the timed region uses (DecodeFFNStack with this run's group, exchange and kernels) on a
+    small seeded stack whose weights also exist on the host, compared on rank 0 with the unsharded
+    numpy oracle.  Outside every timed region."""
+    import numpy as np
+    from ml_dtypes import bfloat16
+    from oracle import awq_oracle as O  # the checker only
+    H, I, L, B, gs = 1024, 2816, 4, min(8, a.batch), 128
+    i0, i1 = ffn.tp_shard_bounds(I, world)[rank]
+
+    def synth(K, N, seed, lo=0.001, hi=0.02):
+        r = np.random.default_rng(seed)
+        return (O.pack_awq_int32(r.integers(0, 16, (K, N), dtype=np.uint8)),
+                O.pack_awq_int32(r.integers(0, 16, (K // gs, N), dtype=np.uint8)), r.uniform(lo, hi, (K // gs, N)).astype(bfloat16))
+
+    def dev16(v):
+        return torch.from_numpy(np.ascontiguousarray(v).view(np.int16)).cuda().view(torch.bfloat16)
+
+    full, layers = [], []
+    for l in range(L):
+        gate, up, down = synth(H, I, 900 + 10 * l), synth(H, I, 901 + 10 * l), synth(I, H, 902 + 10 * l, 0.0005, 0.004)
+        gamma = (np.random.default_rng(903 + 10 * l).standard_normal(H) * 0.1 + 1.0).astype(bfloat16)
+        full.append((gate, up, down, gamma))
+        gu = ops.interleave_gate_up(ops.AwqWeight.from_numpy(*gate, gs), ops.AwqWeight.from_numpy(*up, gs))
+        layers.append(ffn.FFNLayer(ffn.shard_gateup(gu, i0, i1), ffn.shard_down(ops.AwqWeight.from_numpy(*down, gs), i0, i1),
+                                   dev16(gamma)))
+    x = np.random.default_rng(899).standard_normal((B, H)).astype(bfloat16)
+    st = ffn.DecodeFFNStack(layers, H, max_batch=8, group=group, fused=not a.unfused, peer_push=a.peer_exchange)
+    y_eager = st.step(dev16(x))
+    st.load_input(dev16(x))
+    y_graph = st.replay(B).clone()
+    st.check()
+    res = None
+    if rank == 0:
+        ref = x
+        for gate, up, down, gamma in full:
+            ref = O.ffn_layer_A_ref(ref, gamma, gate, up, down, gs)
+        host = lambda t: t.contiguous().view(torch.int16).cpu().numpy().view(bfloat16)  # noqa: E731
+        e1, e2 = O.rel_l2(host(y_eager), ref), O.rel_l2(host(y_graph), ref)
+        res = {"rel_l2": max(e1, e2), "rel_l2_eager": e1, "rel_l2_graph_replay": e2, "tolerance": 1e-2,
+               "dims": f"hidden {H}, intermediate {I}, {L} layers, batch {B}, tp{world}",
+               "path": ("one-launch stack kernel" + (" with the in-kernel exchange" if world > 1 else "")) if st.uses_fused(B)
+               else "per-layer kernels", "oracle": "oracle.awq_oracle.ffn_layer_A_ref, unsharded"}
+    del st, layers
+    return res
+
 
 
 def run_ours(a):
@@ -334,7 +494,8 @@ def run_ours(a):
                 "frac_of_8TBs": achieved / 8000.0, "us_per_launch": gu_us, "bytes_per_launch": gu_bytes / passes,
                 # dram__bytes_read.sum + dram__bytes_write.sum of one launch at this exact shape
                 # (the committed ncu summary of that kernel); other shapes were not captured
-                "traffic": 249810432 if (a.hidden, il, B) == (8192, 28672, 8) else None}
+                "traffic": (NCU_TRAFFIC.get(("gemv_streamk_kernel<EPI_SWIGLU>", a.hidden, il, B)) or {}).get("bytes"),
+                "traffic_source": (NCU_TRAFFIC.get(("gemv_streamk_kernel<EPI_SWIGLU>", a.hidden, il, B)) or {}).get("source")}
     stack_bytes = stack.weight_bytes + a.layers * 4 * B * a.hidden * 2
     stack_gbs = stack_bytes / (ms_step * 1e-3) / 1e9
     if stack.uses_fused(B):
@@ -343,8 +504,9 @@ def run_ours(a):
                     "achieved": stack_gbs, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": stack_gbs / peak,
                     "frac_of_8TBs": stack_gbs / 8000.0, "us_per_launch": ms_step * 1e3, "bytes_per_launch": stack_bytes,
                     # dram bytes of a 2-layer launch scaled by the layer count
-                    "traffic": FUSED_TRAFFIC_PER_LAYER * a.layers
-                    if FUSED_TRAFFIC_PER_LAYER and (a.hidden, il, B) == (8192, 28672, 8) else None}
+                    "traffic": (lambda t: t["bytes_per_layer"] * a.layers if t else None)(
+                        NCU_TRAFFIC.get(("ffn_fused_kernel", a.hidden, il, B))),
+                    "traffic_source": (NCU_TRAFFIC.get(("ffn_fused_kernel", a.hidden, il, B)) or {}).get("source")}
     else:
         roofline = gateup_kernel
 
@@ -399,12 +561,35 @@ def run_ours(a):
                     "global_batch": world * B, "parallelism": f"{world} replicas of the whole stack, no exchange"}
         del rstack, full
 
+    # ---- the batch sweep of configuration 5 (1 / 8 / 32 / 64 tokens) on a shorter stack unless --sweep ----
     batches = None
-    if a.sweep:
-        batches = {}
+    if not a.no_configs or a.sweep:
+        nl = a.layers if a.sweep else min(a.layers, 16)
+        sub = stack if nl == a.layers else ffn.DecodeFFNStack(layers[:nl], a.hidden, max_batch=64, group=group,
+                                                              fused=not a.unfused, peer_push=a.peer_exchange)
+        keep_stack = stack
+        stack = sub
+        batches = {"layers": nl, "note": "ms per step of a stack of `layers` layers; bytes = this rank's weights + activations"}
         for b in (1, 8, 32, 64):
             ms = time_steps(b, max(3, a.steps // 2), 3)
-            batches[str(b)] = {"ms_per_step": ms, "tokens_per_s": b / (ms * 1e-3)}
+            by = sub.weight_bytes + nl * 4 * b * a.hidden * 2
+            batches[str(b)] = {"ms_per_step": ms, "us_per_layer": ms * 1e3 / nl, "tokens_per_s": b / (ms * 1e-3),
+                               "achieved_gbs": by / (ms * 1e-3) / 1e9, "frac_of_measured": by / (ms * 1e-3) / 1e9 / peak,
+                               "frac_of_8TBs": by / (ms * 1e-3) / 1e9 / 8000.0}
+        sub.check()
+        stack = keep_stack
+        if sub is not stack:
+            del sub
+
+    # ---- configurations 1-3 of the benchmark definition on this GPU (rank 0 of a multi-GPU run skips them) ----
+    other = None
+    if not a.no_configs and world == 1:
+        other = time_other_configs(a, torch, ops, ffn, peak)
+
+    # ---- oracle parity of the timed path, outside the timed region, at every N ----
+    parity = None
+    if not a.no_parity:
+        parity = parity_check(a, torch, ops, ffn, group, rank, world)
 
     def finish():
         """Leave without tearing the communicator down: destroying a process group while captured
@@ -447,9 +632,15 @@ def run_ours(a):
         line["replicas"] = replicas
     if batches:
         line["batches"] = batches
+    if other:
+        line.update({k: v for k, v in other.items() if k.endswith(("cfg1", "cfg2", "cfg3"))})
+        line["configs_timing"] = {"l2_bytes": other["l2_bytes"], "method": other["timing"]}
+    if parity:
+        line["parity"] = parity
     if prefill:
         line["prefill"] = prefill
     if a.gpus == 1 and not a.no_cpu_baseline:
+        _pool = use_all_host_cores()  # noqa: F841
         s = cpu_sample_setup(a)
         cpu_sample_run(a, s)
         reps, t_acc = 0, 0.0
@@ -457,10 +648,21 @@ def run_ours(a):
             t_acc += cpu_sample_run(a, s)
             reps += 1
         v = cpu_tokens_per_s(a, t_acc / reps, s["cols"])
+        factor = (a.intermediate / s["cols"]) * a.layers
         line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cpu_threads(), "kind": "port",
                                 "sample": f"numpy golden on {s['cols']}/{a.intermediate} of one layer's columns, mean of "
-                                          f"{reps} runs, scaled to {a.layers} layers"}
+                                          f"{reps} runs; value EXTRAPOLATED by {factor:g} to {a.layers} whole layers",
+                                "extrapolated": True, "extrapolation_factor": factor,
+                                "measured_ms_per_sample": t_acc / reps * 1e3}
     print(json.dumps(line), flush=True)
+    if parity and not parity["rel_l2"] <= parity["tolerance"]:
+        print(f"parity check failed: rel-L2 {parity['rel_l2']:.3e} against the oracle exceeds {parity['tolerance']}",
+              file=sys.stderr, flush=True)
+        if world > 1:
+            torch.cuda.synchronize()
+            dist.barrier()
+            os._exit(3)
+        sys.exit(3)
     finish()
 
 

@@ -63,6 +63,15 @@ const char *awq_b200_last_error(void);
  * Process-wide; for tests. */
 int awq_b200_set_decode_kernel(int mode);
 
+/* Every wait a kernel of this library makes on the device (for a shared-memory stage, for another
+ * CTA's phase counter, for another rank's partial sums or flags) gives up after `cycles` SM clock
+ * cycles, sets the error word of its workspace and lets the kernel drain and return; the next
+ * *_check call reports AWQ_ERR_DEVICE_TIMEOUT.  Default 2^31 (about a second); 0 restores the
+ * default.  Process-wide, read when a kernel is launched (a captured graph keeps the value it was
+ * captured with).  The bounded counterpart of the reference waiting on run.wait() and checking
+ * ERT_CMD_STATE_COMPLETED (python/air/backend/xrt.py:204-218). */
+int awq_b200_set_wait_limit(long long cycles);
+
 /* Split-K partial sums of the stream-K decode kernel are combined with f32 atomic adds by
  * default (fastest; the last bits of a result can differ between runs because the order of the
  * adds is not fixed).  on = 1 sums them in a fixed order instead: bit-reproducible, slower. */
@@ -108,7 +117,7 @@ int awq_b200_gemv_bf16(const uint16_t *x, const int32_t *qweight, const int32_t 
  * (a plugin interface that carries only inputs and outputs, a serving process that bans
  * cudaMalloc after start-up, plain C hosts without an allocator).  It has no counterpart in
  * the reference.  The kernel's scratch is a fixed array inside the library image, about
- * 1 MB on every GPU that loads the library, held until the process exits; nothing is
+ * 2 MB on every GPU that loads the library, held until the process exits; nothing is
  * allocated or freed by this call.  Limits: N <= 32768, group size 128, K % 128 == 0,
  * N % 32 == 0, 1 <= B <= 64; anything else returns an error rather than falling back.
  * The first call on each device looks up the array's device address, so make that first
@@ -117,6 +126,13 @@ int awq_b200_gemv_bf16(const uint16_t *x, const int32_t *qweight, const int32_t 
 int awq_b200_gemv_bf16_static(const uint16_t *x, const int32_t *qweight, const int32_t *qzeros,
                               const uint16_t *scales, const uint16_t *residual, uint16_t *y, int B,
                               int K, int N, int group_size, awq_stream_t stream);
+
+/* Synchronise `stream` and report whether a kernel launched by awq_b200_gemv_bf16_static on the
+ * current device gave up on a bounded wait (AWQ_ERR_DEVICE_TIMEOUT) or clamped an activation.  The
+ * error word lives in the built-in array and the next static call clears it, so ask before that
+ * next call.  Allocates nothing.  No counterpart in the reference beyond its run-state check
+ * (python/air/backend/xrt.py:204-218). */
+int awq_b200_static_check(awq_stream_t stream);
 
 /* General form: x in `x_format` (AWQ_ACT_*), y bf16 (y_is_f32 = 0, optional residual) or f32. */
 int awq_b200_gemv_act(const void *x, int x_format, const int32_t *qweight, const int32_t *qzeros,
@@ -340,6 +356,18 @@ int awq_b200_repack_B_to_A(const uint8_t *A_q, const uint16_t *A_s, const uint8_
 int awq_b200_repack_A_to_B(const int32_t *qweight, const int32_t *qzeros, const uint16_t *scales,
                            uint8_t *A_q, uint16_t *A_s, uint8_t *A_z, int M, int K, int group_size,
                            awq_stream_t stream);
+
+/* Layout C, the per-tile packed buffer the reference hands its NPU kernels, back to layout B:
+ * `packed` holds M / m_tile x K / k_chunk tiles in (row block, k chunk) order, each
+ * [Q: m_tile x k_chunk/2 bytes | S: (k_chunk/gs) x m_tile bf16 | Z: (k_chunk/gs) x m_tile bytes]
+ * (tile_bytes = m_tile k_chunk / 2 + 3 (k_chunk / gs) m_tile; 8576 at the GEMV defaults 8 / 2048 / 128).
+ * Inverts pack_inputs of matrix_vector_multiplication/int4_awq/matvec_int4_packed.py:57-103
+ * (any N_CORES / M_PER_LAUNCH: launches, cores and outer steps enumerate consecutive row blocks) and
+ * of matrix_multiplication/int4_awq/matmul_int4_packed.py:57-86 (M = N, m_tile = N_TILE), and so
+ * what awq_pack_for_npu (llms/llama32_1b_int4/awq_pack.py:112-146) produced.  Follow with
+ * awq_b200_repack_B_to_A to get the layout the kernels read. */
+int awq_b200_repack_C_to_B(const uint8_t *packed, uint8_t *A_q, uint16_t *A_s, uint8_t *A_z, int M,
+                           int K, int group_size, int m_tile, int k_chunk, awq_stream_t stream);
 
 #ifdef __cplusplus
 }

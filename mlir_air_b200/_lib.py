@@ -10,7 +10,8 @@ import os
 from ctypes import c_char_p, c_float, c_int, c_size_t, c_void_p
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libawq_b200.so")
+# AWQ_B200_LIB selects another build of the library (for comparing two builds in one process tree)
+LIB_PATH = os.environ.get("AWQ_B200_LIB") or os.path.join(_HERE, "lib", "libawq_b200.so")
 
 AWQ_OK = 0
 AWQ_ERR_INVALID_ARGUMENT = -1
@@ -37,6 +38,8 @@ SIGNATURES = {
     "awq_b200_set_decode_kernel": (c_int, [c_int]),
     "awq_b200_set_gemm_kernel": (c_int, [c_int]),
     "awq_b200_set_deterministic": (c_int, [c_int]),
+    "awq_b200_set_wait_limit": (c_int, [ctypes.c_longlong]),
+    "awq_b200_static_check": (c_int, [_P]),
     "awq_b200_dequant_bf16": (c_int, [_P, _P, _P, _P, c_int, c_int, c_int, _P]),
     "awq_b200_dequant_1d_bf16": (c_int, [_P, _P, _P, _P, c_int, c_int, _P]),
     "awq_b200_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
@@ -72,6 +75,7 @@ SIGNATURES = {
     "awq_b200_gemm_check": (c_int, [_P]),
     "awq_b200_repack_B_to_A": (c_int, [_P] * 6 + [c_int, c_int, c_int, _P]),
     "awq_b200_repack_A_to_B": (c_int, [_P] * 6 + [c_int, c_int, c_int, _P]),
+    "awq_b200_repack_C_to_B": (c_int, [_P] * 4 + [c_int, c_int, c_int, c_int, c_int, _P]),
 }
 
 _lib = None
@@ -88,6 +92,8 @@ def load():
             "(nvcc, sm_100a).  There is no CPU or PyTorch fallback.")
     lib = ctypes.CDLL(LIB_PATH)
     for name, (res, args) in SIGNATURES.items():
+        if os.environ.get("AWQ_B200_LIB") and not hasattr(lib, name):
+            continue  # an older build selected for comparison may lack the newest entry points
         fn = getattr(lib, name)  # AttributeError if the symbol is not exported
         fn.restype = res
         fn.argtypes = args

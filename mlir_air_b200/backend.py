@@ -74,12 +74,14 @@ def _resident(p, slot, build):
 
 
 def _weight_from_gemv_tiles(p, packed, M, slot=None):
+    """Per-tile packed buffer -> resident layout-A weight, unpacked on the GPU
+    (awq_b200_repack_C_to_B, then awq_b200_repack_B_to_A)."""
     from . import ops
 
     def build():
-        A_q, A_s, A_z = layouts.unpack_gemv_tiles(packed, M, p["K"], p["GS"], p["M_TILE"], p["K_CHUNK"], p["N_CORES"],
-                                                  p.get("M_PER_LAUNCH") or M)
-        return ops.repack_B_to_A(_to_dev(A_q), _to_dev(A_s), _to_dev(A_z), p["GS"])
+        layouts._check_gemv_tiling(M, p["K"], p["GS"], p["M_TILE"], p["K_CHUNK"], p["N_CORES"], p.get("M_PER_LAUNCH") or M)
+        return ops.repack_C_to_A(_to_dev(np.ascontiguousarray(packed, dtype=np.uint8).reshape(-1)), M, p["K"], p["GS"],
+                                 p["M_TILE"], p["K_CHUNK"])
 
     return _resident(p, slot, build)
 
@@ -158,9 +160,12 @@ def _run_rms_qkv_rope(p, args):
 def _run_matmul(p, args):
     from . import ops
     A, packed, out = args
-    W_q, W_s, W_z = layouts.unpack_gemm_tiles(packed, p["K"], p["N"], p["GS"], p["N_TILE"], p["K_CHUNK"])
-    w = ops.repack_B_to_A(_to_dev(W_q), _to_dev(W_s), _to_dev(W_z), p["GS"])
+    if p["N"] % p["N_TILE"] or p["K"] % p["K_CHUNK"] or p["K_CHUNK"] % p["GS"]:
+        raise ValueError("N, K, N_TILE, K_CHUNK and GS do not tile")
+    w = _resident(p, 1, lambda: ops.repack_C_to_A(_to_dev(np.ascontiguousarray(packed, dtype=np.uint8).reshape(-1)), p["N"],
+                                                  p["K"], p["GS"], p["N_TILE"], p["K_CHUNK"]))
     y = ops.gemm(_to_dev(np.asarray(A).reshape(p["M"], p["K"])), w)
+    ops.gemm_check()
     return [y], [2]
 
 
@@ -177,6 +182,69 @@ def _run_ffn_int4(p, args):
     y = ops.gemv(it, wd, ws)
     ws.check()
     return [it, y], [7, 8]
+
+
+def _run_ffn_int4_prefill(p, args):
+    """x [seq, hidden], then (qweight, qzeros, scales) of gate/up-interleaved and of down, then `inter` and `out`:
+    the prefill FFN on AWQ weights as two tensor-core GEMMs, SwiGLU in the first one's epilogue."""
+    from . import ops
+    x, gq, gz, gs_, dq, dz, ds, inter, out = args
+    H, gsz = p["hidden"], p["GS"]
+    wgu = _resident(p, 1, lambda: ops.AwqWeight.from_numpy(gq, gz, gs_, gsz))
+    wd = _resident(p, 4, lambda: ops.AwqWeight.from_numpy(dq, dz, ds, gsz))
+    xd = _to_dev(np.asarray(x).reshape(-1, H))
+    it = ops.gemm(xd, wgu, swiglu=True)
+    y = ops.gemm(it, wd)
+    ops.gemm_check()
+    return [it, y], [7, 8]
+
+
+def _o_gemv_ffn(p, wo_p, attn_out, x_residual, gu_p, gamma, wd_p, slots, one_launch):
+    """The post-attention half of a decode layer: res1 = W_o attn + x; out = W_d swiglu(W_gu rms(res1, gamma)) + res1
+    (o_gemv_ffn_int4_multi.py:9-12).  Returns (res1, swiglu or None, out) as device tensors [1, emb] / [1, hidden]."""
+    import torch
+    from . import ops
+    emb, hid = p["emb_dim"], p["hidden_dim"]
+    tile = dict(GS=p["GS"], M_TILE=p["M_TILE"], K_CHUNK=p["K_CHUNK"], N_CORES=p["N_CORES"], __static__=p.get("__static__", ()),
+                __resident__=p.get("__resident__", {}))
+    wo = _weight_from_gemv_tiles(dict(tile, K=emb), wo_p, emb, slot=slots[0])
+    wgu = _weight_from_gemv_tiles(dict(tile, K=emb), gu_p, 2 * hid, slot=slots[1])  # rows gate/up interleaved
+    wd = _weight_from_gemv_tiles(dict(tile, K=hid), wd_p, emb, slot=slots[2])
+    ws = _workspace(p, max(emb, hid), max(2 * hid, emb))
+    g = _to_dev(np.asarray(gamma).reshape(emb))
+    res1 = ops.gemv(_to_dev(np.asarray(attn_out).reshape(1, emb)), wo, ws, residual=_to_dev(np.asarray(x_residual).reshape(1, emb)))
+    swiglu = None
+    if one_launch:
+        # RMSNorm, gate/up + SwiGLU, down + residual in ONE launch, intermediates staying inside the kernel's scratch
+        plan = _resident(dict(p, __static__=("plan",) if slots[1] in p.get("__static__", ()) else ()), "plan",
+                         lambda: ops.FFNStackPlan([wgu], [wd], [g]))
+        out = ops.ffn_stack_decode(plan, res1, ws, eps=p.get("eps", 1e-5))
+    else:
+        normed = ops.rmsnorm(res1, g, p.get("eps", 1e-5))
+        swiglu = ops.gateup_swiglu(normed, wgu, ws)
+        out = ops.gemv(swiglu, wd, ws, residual=res1)
+    ws.check()
+    return res1, swiglu, out
+
+
+def _run_o_gemv_ffn_int4(p, args):
+    """The 15-argument ABI of o_gemv_ffn_int4_multi.py:13-31 (arguments 2, 4, 5, 8, 9, 10, 13 are dead there and
+    ignored here): res1 lands in row 0 of argument 6, the SwiGLU output in argument 11, the result in argument 14."""
+    import torch
+    wo_p, attn_out, _, x_res, _, _, packed_rms, gu_p, _, _, _, _, wd_p, _, out = args
+    emb = p["emb_dim"]
+    packed_rms = np.asarray(packed_rms).reshape(2, emb)
+    res1, swiglu, y = _o_gemv_ffn(p, wo_p, attn_out, x_res, gu_p, packed_rms[1], wd_p, (0, 7, 12), one_launch=False)
+    rms_out = torch.cat([res1.reshape(1, emb), _to_dev(packed_rms[1:2])], 0)
+    return [rms_out, swiglu, y], [6, 11, 14]
+
+
+def _run_o_gemv_ffn_int4_fused(p, args):
+    """The 8-argument ABI of o_gemv_ffn_int4_fused.py:33-42: wo_packed, attn_out, x_residual, gate/up_packed,
+    ffn_norm_w, wdown_packed, output, res1 copy."""
+    wo_p, attn_out, x_res, gu_p, gamma, wd_p, out, res1_out = args
+    res1, _, y = _o_gemv_ffn(p, wo_p, attn_out, x_res, gu_p, gamma, wd_p, (0, 3, 5), one_launch=True)
+    return [y, res1], [6, 7]
 
 
 def _run_ffn_bf16(p, args):
@@ -237,6 +305,9 @@ _INSTANCES: Dict[str, Callable] = {
     "matmul_int4_packed": _run_matmul,
     "rms_qkv_int4_rope": _run_rms_qkv_rope,
     "ffn_swiglu_int4": _run_ffn_int4,
+    "ffn_swiglu_int4_prefill": _run_ffn_int4_prefill,
+    "o_gemv_ffn_int4": _run_o_gemv_ffn_int4,
+    "o_gemv_ffn_int4_fused": _run_o_gemv_ffn_int4_fused,
 }
 
 
@@ -323,7 +394,10 @@ class B200Runner:
 
     def run_test(self, mlir_module, inputs: Sequence[np.ndarray], expected_outputs: Sequence[np.ndarray] = (),
                  stochastic_expected_outputs: Sequence = (), rtol: float = 1e-3, atol: float = 1e-8,
-                 max_mismatch_percentage: float = 0, min_correlation: Optional[float] = None) -> int:
+                 max_mismatch_percentage: float = 0, min_correlation: Optional[float] = None,
+                 max_rel_l2: Optional[float] = None) -> int:
+        """The reference's acceptance rule (rtol / atol / mismatch budget / correlation floor) and, with
+        `max_rel_l2`, this library's own bound on |actual - expected| / |expected| per float output."""
         if stochastic_expected_outputs:
             raise AwqBackendError("stochastic_expected_outputs is not used by the int4-AWQ examples")
         if not expected_outputs:
@@ -342,11 +416,12 @@ class B200Runner:
         backend.unload()
         self.last_outputs = list(actual[len(inputs):])
         ok = self._check_outputs(self.last_outputs, list(expected_outputs), rtol, atol, max_mismatch_percentage,
-                                 min_correlation)
+                                 min_correlation, max_rel_l2)
         print("PASS!" if ok else "failed.")
         return 0 if ok else -1
 
-    def _check_outputs(self, actual_outputs, expected_outputs, rtol, atol, max_mismatch_percentage, min_correlation):
+    def _check_outputs(self, actual_outputs, expected_outputs, rtol, atol, max_mismatch_percentage, min_correlation,
+                       max_rel_l2=None):
         """Same acceptance rule as xrt_runner.py:423-521: float outputs by np.isclose on f64 with a
         mismatch budget and an optional Pearson-correlation floor; integer outputs exactly.  Also
         prints the rel-L2 error, which is what this library's own tests bound."""
@@ -361,6 +436,9 @@ class B200Runner:
                 allowed = int(e.size * max_mismatch_percentage / 100)
                 rel_l2 = float(np.linalg.norm(a - e) / max(np.linalg.norm(e), 1e-30))
                 print(f"Output {i}: rel-L2 {rel_l2:.3e}, {int(bad.sum())} / {e.size} outside rtol={rtol} atol={atol}")
+                if max_rel_l2 is not None and not rel_l2 <= max_rel_l2:
+                    ok = False
+                    print(f"ERROR: Output {i} rel-L2 {rel_l2:.3e} exceeds {max_rel_l2:g}")
                 if self.report_precision:
                     err = np.abs(a - e)
                     print(f"[precision] Output {i} ({err.size} elements): mean_rel_L1={err.mean() / (np.abs(e).mean() + 1e-30):.3e}"

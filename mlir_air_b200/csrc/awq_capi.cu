@@ -6,6 +6,7 @@
 #include <atomic>
 
 #include "awq_common.cuh"
+#include "awq_ptx.cuh"
 
 namespace awq {
 
@@ -13,6 +14,9 @@ static thread_local char g_error[512] = "";
 static std::atomic<int> g_decode_mode{0};
 static std::atomic<int> g_gemm_mode{0};
 static std::atomic<int> g_deterministic{0};
+static std::atomic<long long> g_wait_limit{WAIT_LIMIT_DEFAULT};
+
+long long wait_limit_cycles() { return g_wait_limit.load(); }
 
 int set_error(int code, const char *fmt, ...) {
     va_list ap;
@@ -48,6 +52,21 @@ static DevInfo query_device() {
 int device_sm_count() { return query_device().sms; }
 bool device_is_sm100() { return query_device().major == 10; }
 
+// The word a kernel leaves in its scratch when it could not finish.
+int status_of_device_flag(int flag) {
+    if (flag == 4)
+        return set_error(AWQ_ERR_UNSUPPORTED,
+                         "an activation exceeded the fp16 range (|x| > 65504) and was clamped; select the bf16 "
+                         "activation path with awq_b200_set_decode_kernel(3) and re-initialise the workspace");
+    if (flag != 0)
+        return set_error(AWQ_ERR_DEVICE_TIMEOUT,
+                         "a device-side wait gave up (code %d: 1 = loader waiting for a free stage, 2 = consumer waiting "
+                         "for data, 3 = loader waiting for the previous phase, 4 = normaliser waiting for data, 5 = waiting "
+                         "for the other ranks' arrival flags, 6 = waiting for the other ranks' partial sums); re-initialise "
+                         "the workspace", flag);
+    return AWQ_OK;
+}
+
 static int check_gemv_args(const char *who, const GemvArgs &a) {
     AWQ_REQUIRE(a.B >= 0 && a.K >= 0 && a.N >= 0 && a.group_size > 0, "%s: negative size or group_size <= 0", who);
     AWQ_REQUIRE(a.B <= 64, "%s: batch %d exceeds 64 (use the prefill GEMM)", who, a.B);
@@ -57,6 +76,9 @@ static int check_gemv_args(const char *who, const GemvArgs &a) {
     AWQ_REQUIRE(a.K > 0, "%s: K must be positive", who);
     AWQ_REQUIRE(a.x && a.qweight && a.qzeros && a.scales && a.y, "%s: null pointer", who);
     AWQ_REQUIRE(aligned16(a.scales), "%s: scales must be 16-byte aligned", who);
+    // every kernel stores y (and loads the residual) in 16-byte pieces
+    AWQ_REQUIRE(aligned16(a.y), "%s: the output must be 16-byte aligned", who);
+    AWQ_REQUIRE(!a.residual || aligned16(a.residual), "%s: the residual must be 16-byte aligned", who);
     return AWQ_OK;
 }
 
@@ -95,6 +117,11 @@ extern "C" int awq_b200_set_deterministic(int on) {
     g_deterministic.store(on ? 1 : 0);
     return AWQ_OK;
 }
+extern "C" int awq_b200_set_wait_limit(long long cycles) {
+    AWQ_REQUIRE(cycles >= 0, "set_wait_limit: negative limit");
+    g_wait_limit.store(cycles == 0 ? WAIT_LIMIT_DEFAULT : cycles);
+    return AWQ_OK;
+}
 extern "C" int awq_b200_set_gemm_kernel(int mode) {
     AWQ_REQUIRE(mode >= 0 && mode <= 2, "set_gemm_kernel: mode must be 0, 1 or 2");
     g_gemm_mode.store(mode);
@@ -119,15 +146,7 @@ extern "C" int awq_b200_workspace_check(const void *workspace, awq_stream_t stre
     if (rc) return rc;
     rc = check_cuda(cudaStreamSynchronize(as_stream(stream)), "workspace_check sync");
     if (rc) return rc;
-    if (flag == 4)
-        return set_error(AWQ_ERR_UNSUPPORTED,
-                         "an activation exceeded the fp16 range (|x| > 65504) and was clamped; select the bf16 "
-                         "activation path with awq_b200_set_decode_kernel(3) and re-initialise the workspace");
-    if (flag != 0)
-        return set_error(AWQ_ERR_DEVICE_TIMEOUT,
-                         "a device-side wait gave up (code %d: 1 = producer waiting for a free stage, "
-                         "2 = consumer waiting for data); re-initialise the workspace", flag);
-    return AWQ_OK;
+    return status_of_device_flag(flag);
 }
 
 extern "C" int awq_b200_gemv_act(const void *x, int x_format, const int32_t *qweight, const int32_t *qzeros,

@@ -14,6 +14,8 @@ int set_error(int code, const char *fmt, ...);
 int check_cuda(cudaError_t e, const char *what);
 inline cudaStream_t as_stream(awq_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+int status_of_device_flag(int flag);  // error word of a kernel's scratch -> status + message
+long long wait_limit_cycles();  // limit of every bounded device-side wait (awq_b200_set_wait_limit)
 int device_sm_count();
 bool device_is_sm100();
 

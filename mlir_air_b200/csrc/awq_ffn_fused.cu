@@ -61,7 +61,7 @@ static_assert(sizeof(FusedLayer) % 128 == 0, "tensor maps must stay 64-byte alig
 constexpr int FF_MAX_LAYERS = 1024;
 // State of one launch in the workspace, zeroed by the launcher: two phase counters, then one
 // f32 sum of squares per (layer boundary, batch row).
-constexpr size_t FF_STATE_OFF = SK_WS_PARTIALS;
+constexpr size_t FF_STATE_OFF = SK_WS_END;
 constexpr size_t FF_STATE_HEADER = 64;
 __host__ __device__ constexpr size_t ff_state_bytes(int n_layers) {
     return FF_STATE_HEADER + (size_t)(n_layers + 1) * 8 * sizeof(float);
@@ -74,12 +74,12 @@ __device__ __forceinline__ int ld_acquire_gpu(const int *p) {
 }
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
-// Wait until *ctr >= target; gives up after about a second.
-__device__ __forceinline__ bool wait_count(const int *ctr, int target) {
+// Wait until *ctr >= target; gives up after `limit` cycles.
+__device__ __forceinline__ bool wait_count(const int *ctr, int target, long long limit) {
     if (ld_acquire_gpu(ctr) >= target) return true;
     const long long t0 = clock64();
     while (ld_acquire_gpu(ctr) < target) {
-        if (clock64() - t0 > (1ll << 31)) return false;
+        if (clock64() - t0 > limit) return false;
         __nanosleep(64);
     }
     return true;
@@ -122,8 +122,7 @@ struct FusedArgs {
     int B, H, I;
     int lookahead;  // units the L2 prefetch runs ahead of the shared-memory ring
     int split;      // share of an SM's units that half 0 takes, in 1/1024
-    float *accum;   // per-strip split-K accumulators (zero between uses)
-    int *counters;  // per sub-strip counters of the k groups added so far (zero between uses)
+    unsigned long long *accum;  // split-K accumulator words (zero between uses): gate/up strips, then down strips
     int *err_flag;
     int *state;     // done_gu, done_d, ..., then sumsq[(n_layers + 1) * 8]
     // Tensor parallelism (tp_n > 1): this rank holds a shard of every layer (gate/up columns, down
@@ -133,6 +132,7 @@ struct FusedArgs {
     int tp_n, tp_rank;
     unsigned long long *ll_recv[2][TP_MAX_RANKS];  // every rank's receive slots, mapped into this GPU's address space
     unsigned int *epoch;                           // launches so far on this rank (base of the tags), in peer memory
+    long long wait_limit;                          // cycles after which a device-side wait gives up
 };
 constexpr int FF_LL_WORDS = 16 * 32;  // words of one sub-strip from one rank
 
@@ -319,7 +319,7 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
         auto acquire_slot = [&](int &slot) -> bool {  // slot of unit number `issued`, once the consumers released it
             slot = issued % SK_STAGES;
             const int round = issued / SK_STAGES;
-            if (round > 0 && !mbar_wait_bounded(empty_bar(slot), (round - 1) & 1)) {
+            if (round > 0 && !mbar_wait_bounded(empty_bar(slot), (round - 1) & 1, a.wait_limit)) {
                 atomicExch(a.err_flag, 1);
                 return false;
             }
@@ -367,7 +367,7 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
             // the phase's activations exist once every sub-strip of the previous phase is finalised
             // (tensor parallel: a down sub-strip is finalised by the warp that added up all ranks' sums)
             const int target = p ? (l + 1) * V0 * SK_CONSUMER_WARPS : B + l * V1 * SK_CONSUMER_WARPS;
-            if (!wait_count(p ? done_gu : done_d, target)) {
+            if (!wait_count(p ? done_gu : done_d, target, a.wait_limit)) {
                 atomicExch(a.err_flag, 3);
                 return;
             }
@@ -405,7 +405,7 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
                 for (int i = 0; i < n_units; ++i) {
                     // every unit's barrier is waited for, also those of down units that need no work
                     // here: a parity wait is only meaningful one completion ahead
-                    if (!mbar_wait_bounded(full_bar(slot), round & 1)) {
+                    if (!mbar_wait_bounded(full_bar(slot), round & 1, a.wait_limit)) {
                         if (lane == 0) atomicExch(a.err_flag, 4);
                         return;
                     }
@@ -469,7 +469,7 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
                                 for (int i = 0; i < 16; ++i) all = all && (unsigned int)(w[i] >> 32) == tag;
                                 all = __all_sync(0xffffffffu, all);
                                 // the lanes must leave together: one lane's clock decides for the warp
-                                const bool late = __shfl_sync(0xffffffffu, clock64() - t0 > (1ll << 31) ? 1 : 0, 0) != 0;
+                                const bool late = __shfl_sync(0xffffffffu, clock64() - t0 > a.wait_limit ? 1 : 0, 0) != 0;
                                 if (!all && late) good = false;
                             } while (!all && good);
                             if (good) {
@@ -518,24 +518,12 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
                 float own[2][8];
                 sk_lane_exchange(res, odd, own);
                 const int n = v * SK_STRIP + colw;
-                if (seg_groups != G) {
-                    // every contributor adds its partial into the strip's f32 accumulator with vector
-                    // reductions at L2 and then the number of k groups it covered to the sub-strip's
-                    // counter; the one that completes the count reads the total and leaves both zero
-                    const size_t lane_off = (size_t)cw * 512 + b * 64 + (g8 >> 1) * 8;
-                    float *acc_ptr = a.accum + (size_t)v * SK_PARTIAL_FLOATS + lane_off;
-                    sk_red_partial(acc_ptr, own, lane);
-                    __threadfence();
-                    __syncwarp();
-                    int old = 0;
-                    if (lane == 0) old = atomicAdd(&a.counters[v * SK_CONSUMER_WARPS + cw], seg_groups);
-                    old = __shfl_sync(0xffffffffu, old, 0);
-                    if (old + seg_groups != G) return;
-                    __threadfence();
-                    sk_take_accum(acc_ptr, own);
-                    __syncwarp();
-                    if (lane == 0) a.counters[v * SK_CONSUMER_WARPS + cw] = 0;  // ready for the next phase
-                }
+                // a strip shared with other halves: value and progress travel in one 64-bit atomic per sum; the warp
+                // whose add completes the count has the total (gate/up and down strips use separate accumulators)
+                if (seg_groups != G &&
+                    !sk_handover(a.accum + ((size_t)((p ? V0 : 0) + v) * SK_CONSUMER_WARPS + cw) * SK_ACC_WORDS, own, seg_groups, G,
+                                 lane, a.wait_limit, a.err_flag))
+                    return;
                 if (failed) return;
                 if (!p) {
                     sk_epilogue<EPI_SWIGLU>(own, nullptr, a.inter, B, N, n, b, 1);
@@ -576,8 +564,8 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
                 }
                 ++seg_groups;
                 if (!failed) {
-                    bool ok = mbar_wait_bounded(full_bar(slot), round & 1);
-                    if (ok && !p) ok = mbar_wait_bounded(xready_bar(slot), (xr_parity >> slot) & 1u);
+                    bool ok = mbar_wait_bounded(full_bar(slot), round & 1, a.wait_limit);
+                    if (ok && !p) ok = mbar_wait_bounded(xready_bar(slot), (xr_parity >> slot) & 1u, a.wait_limit);
                     if (!ok) {
                         failed = true;
                         if (lane == 0) atomicExch(a.err_flag, 2);
@@ -612,8 +600,8 @@ size_t ffn_fused_tp_slot_bytes(int H, int n_ranks) {
 
 bool ffn_fused_supported(int B, int H, int I, int group_size) {
     return group_size == SK_GROUP && B >= 1 && B <= 8 && H > 0 && I > 0 && H % SK_GROUP == 0 && I % SK_GROUP == 0 &&
-           (2 * I + SK_STRIP - 1) / SK_STRIP <= SK_MAX_STRIPS && (H + SK_STRIP - 1) / SK_STRIP <= SK_MAX_STRIPS &&
-           device_is_sm100();
+           (2 * I + SK_STRIP - 1) / SK_STRIP + (H + SK_STRIP - 1) / SK_STRIP <= SK_MAX_STRIPS && H / SK_GROUP <= SK_MAX_GROUPS &&
+           I / SK_GROUP <= SK_MAX_GROUPS && device_is_sm100();
 }
 
 int ffn_fused_plan(void *plan_dev, size_t plan_bytes, int n_layers, const int32_t *const *qw_gateup,
@@ -706,6 +694,7 @@ int launch_ffn_fused(const void *plan_dev, int n_layers, const uint16_t *x, uint
     a.I = I;
     a.lookahead = g_ffn_lookahead;
     a.split = g_ffn_split;
+    a.wait_limit = wait_limit_cycles();
     a.tp_n = 1;
     a.tp_rank = 0;
     a.epoch = nullptr;
@@ -724,8 +713,7 @@ int launch_ffn_fused(const void *plan_dev, int n_layers, const uint16_t *x, uint
         // the last word of the flag block behind this rank's slot 0
         a.epoch = reinterpret_cast<unsigned int *>(reinterpret_cast<uint8_t *>(peers->base[peers->rank]) + peers->flag_offset) + 15;
     }
-    a.accum = reinterpret_cast<float *>(ws + SK_WS_ACCUM);
-    a.counters = reinterpret_cast<int *>(ws + SK_WS_HEADER);
+    a.accum = reinterpret_cast<unsigned long long *>(ws + SK_WS_ACCUM);
     a.err_flag = reinterpret_cast<int *>(ws);
     a.state = reinterpret_cast<int *>(ws + FF_STATE_OFF);
     if ((rc = check_cuda(cudaMemsetAsync(ws + FF_STATE_OFF, 0, ff_state_bytes(n_layers), stream), "fused ffn: state reset")))

@@ -172,7 +172,8 @@ template <int MT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
                const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmZ,
-               uint16_t *__restrict__ C, const uint16_t *__restrict__ R, int epi, int M, int N, int K, int ML, int P) {
+               uint16_t *__restrict__ C, const uint16_t *__restrict__ R, int epi, int M, int N, int K, int ML, int P,
+               long long wait_limit) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -229,7 +230,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     if (kb + TC_PREFETCH < k_blocks) tma_prefetch_l2_2d(&tmW, n0 / 8, (kb + TC_PREFETCH) * TC_BK);
                     const int s = it % TC_STAGES, round = it / TC_STAGES;
-                    if (round > 0 && !mbar_wait_bounded(empty_bar(s), (round - 1) & 1)) {
+                    if (round > 0 && !mbar_wait_bounded(empty_bar(s), (round - 1) & 1, wait_limit)) {
                         atomicExch(&g_gemm_error, 1);
                         ok = false;
                         break;
@@ -252,7 +253,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             for (TileWalk tw(ML, P, m_blocks, n_atoms); tw.valid() && ok; tw.next(), ++tile_it) {
                 const uint32_t idesc = TC_IDESC_BASE | ((uint32_t)(tw.atoms() * 64 >> 3) << 17);
                 const int b = tile_it % NBUF, use = tile_it / NBUF;  // buffer and how often it was used before
-                if (use >= 1 && !mbar_wait_bounded(acc_empty(b), (use - 1) & 1)) {
+                if (use >= 1 && !mbar_wait_bounded(acc_empty(b), (use - 1) & 1, wait_limit)) {
                     atomicExch(&g_gemm_error, 2);
                     break;
                 }
@@ -260,7 +261,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 const uint32_t d_tmem = tmem_base + (uint32_t)b * TC_BN;
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % TC_STAGES, round = it / TC_STAGES;
-                    if (!mbar_wait_bounded(full_bar(s), round & 1) || !mbar_wait_bounded(ready_bar(s), round & 1)) {
+                    if (!mbar_wait_bounded(full_bar(s), round & 1, wait_limit) || !mbar_wait_bounded(ready_bar(s), round & 1, wait_limit)) {
                         atomicExch(&g_gemm_error, 3);
                         ok = false;
                         break;
@@ -296,8 +297,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const bool active = j < words;
             for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                 const int s = it % TC_STAGES, round = it / TC_STAGES;
-                if ((round > 0 && !mbar_wait_bounded(empty_bar(s), (round - 1) & 1)) ||
-                    !mbar_wait_bounded(full_bar(s), round & 1)) {
+                if ((round > 0 && !mbar_wait_bounded(empty_bar(s), (round - 1) & 1, wait_limit)) ||
+                    !mbar_wait_bounded(full_bar(s), round & 1, wait_limit)) {
                     if (lane == 0) atomicExch(&g_gemm_error, 4);
                     ok = false;
                     break;
@@ -340,7 +341,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const int b = tile_it % NBUF, use = tile_it / NBUF;
             const int m0 = tw.mb * (MT * TC_BM), n0 = tw.a * 64;
             const int chunks = tw.atoms() * 2;  // 32-column chunks in this sub-tile
-            if (!mbar_wait_bounded(acc_full(b), use & 1)) {
+            if (!mbar_wait_bounded(acc_full(b), use & 1, wait_limit)) {
                 if (lane == 0) atomicExch(&g_gemm_error, 5);
                 break;
             }
@@ -446,9 +447,11 @@ int launch_gemm_tc(const uint16_t *A, const int32_t *qweight, const int32_t *qze
     if (P < 1) P = 1;
     const int ctas = ML * P;
     if (mt == 2)
-        gemm_tc_kernel<2><<<ctas, TC_THREADS, TC_SMEM_BYTES, stream>>>(tmA, tmW, tmS, tmZ, C, residual, epilogue, M, N, K, ML, P);
+        gemm_tc_kernel<2><<<ctas, TC_THREADS, TC_SMEM_BYTES, stream>>>(tmA, tmW, tmS, tmZ, C, residual, epilogue, M, N, K, ML, P,
+                                                                       wait_limit_cycles());
     else
-        gemm_tc_kernel<1><<<ctas, TC_THREADS, TC_SMEM_BYTES, stream>>>(tmA, tmW, tmS, tmZ, C, residual, epilogue, M, N, K, ML, P);
+        gemm_tc_kernel<1><<<ctas, TC_THREADS, TC_SMEM_BYTES, stream>>>(tmA, tmW, tmS, tmZ, C, residual, epilogue, M, N, K, ML, P,
+                                                                       wait_limit_cycles());
     return check_cuda(cudaGetLastError(), "tensor-core gemm launch");
 }
 

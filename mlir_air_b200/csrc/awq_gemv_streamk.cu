@@ -13,18 +13,19 @@
 //    the shape.
 //  * Each of the eight consumer warps owns 64 columns of the strip for the CTA's whole range,
 //    so no warp ever needs another warp's sums: there is no block-level barrier after set-up.
-//    A lane reads one packed word (8 columns) from four k rows with bank-conflict-free LDS.32
-//    from the 128B-swizzled box, pairs rows k/k+1 with two PRMT, and turns nibbles into bf16
-//    pairs (128 + q) with one LOP3 each: that is directly the A fragment of
-//    mma.sync.m16n8k16 (rows = 16 output columns, k = 16).  The activations are the B
-//    fragment (ldmatrix from swizzled smem).
+//    ldmatrix.trans on the 128B-swizzled box hands lane (g, t) the 16-bit half g of a 16-byte
+//    chunk for k rows 2t and 2t + 1 already paired in one register; one LOP3 per nibble pair turns
+//    that into the A fragment of mma.sync.m16n8k16 (rows = 16 output columns, k = 16).  The
+//    activations are the B fragment (ldmatrix from swizzled smem).
 //  * The zero point and scale never touch the inner loop:
 //        sum_k (q - z) s x = s (sum_k (128 + q) x  -  (128 + z) sum_k x)
 //    per group; sum_k x comes from one extra MMA with an all-ones A fragment.
 //  * At the end of a strip segment a warp that covered the whole strip applies the epilogue
-//    from registers.  Otherwise it stores its f32 partial to the workspace and bumps the
-//    counter of its 64-column sub-strip; the warp that arrives last sums all partials in CTA
-//    order (deterministic) and applies the epilogue.  Nothing waits on another CTA.
+//    from registers.  Otherwise it adds its partial sums to the sub-strip's 64-bit accumulator
+//    words, each add carrying the value (fixed point) and the number of k groups it covers in one
+//    atomic (awq_streamk.cuh: sk_handover); the warp whose add completes the count has the
+//    total and applies the epilogue.  No fence, no counter, nothing waits on another CTA, and
+//    the result does not depend on the order of the adds.
 //
 // Epilogues: bf16 (+ residual), f32 (tensor-parallel partial), SwiGLU over interleaved
 // gate/up column pairs (matvec_int4_swiglu_rms.py:511-516 rounding points).
@@ -42,7 +43,7 @@ namespace awq {
 // Leading bytes of a workspace (error flag, counters, accumulators of the strips a product of N
 // columns uses) that must be zero before a launch.
 size_t gemv_streamk_workspace_clear_bytes(int N) {
-    return SK_WS_ACCUM + (size_t)((N + SK_STRIP - 1) / SK_STRIP) * SK_PARTIAL_FLOATS * 4;
+    return SK_WS_ACCUM + (size_t)((N + SK_STRIP - 1) / SK_STRIP) * SK_STRIP_WORDS * 8;
 }
 
 template <int EPI, bool XH>
@@ -50,8 +51,8 @@ __global__ void __launch_bounds__(SK_THREADS, SK_CTAS_PER_SM)
 gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                     const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmZ,
                     const uint16_t *__restrict__ residual, void *__restrict__ y_, int B, int N, int G,
-                    int V, int out_f16, int fast_reduce, float *__restrict__ accum, float *__restrict__ partials,
-                    int *__restrict__ counters, int *__restrict__ err_flag, const PeerPush push) {
+                    int V, int out_f16, unsigned long long *__restrict__ accum, int *__restrict__ err_flag,
+                    const PeerPush push, long long wait_limit) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t bar_base = smem_base + SK_STAGES * SK_STAGE_BYTES;
@@ -116,7 +117,7 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             }
             int slot = 0, round = 1;
             for (int i = n_first; i < n_units; ++i) {
-                if (!mbar_wait_bounded(empty_bar(slot), (round - 1) & 1)) {
+                if (!mbar_wait_bounded(empty_bar(slot), (round - 1) & 1, wait_limit)) {
                     atomicExch(err_flag, 1);
                     break;
                 }
@@ -140,7 +141,7 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     bool failed = false;
 
     float res[4][4];
-    int cur_v = -1;
+    int cur_v = -1, seg_groups = 0;  // strip being accumulated, k groups of it added so far
 
     // Finish the strip segment this warp has been accumulating (strip cur_v).
     auto flush = [&]() {
@@ -149,77 +150,10 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         sk_lane_exchange(res, odd, own);
         const int b = 2 * t4 + odd;
         const int n = v * SK_STRIP + colw;
-        const long long c_lo = sk_owner((long long)v * G, C, U);
-        const long long c_hi = sk_owner((long long)(v + 1) * G - 1, C, U);
-        if (c_hi == c_lo) {
-            if (!failed) sk_epilogue<EPI>(own, residual, y_, B, N, n, b, out_f16);
-            if (EPI == EPI_F32_PUSH && !failed) sk_push_signal(push, err_flag + 8, V * SK_CONSUMER_WARPS, lane);
+        if (seg_groups != G &&
+            !sk_handover(accum + ((size_t)v * SK_CONSUMER_WARPS + warp) * SK_ACC_WORDS, own, seg_groups, G, lane, wait_limit,
+                         err_flag))
             return;
-        }
-        // [warp][batch row][64 columns] inside a strip's accumulator / a CTA's slot
-        const size_t lane_off = (size_t)warp * 512 + b * 64 + (g8 >> 1) * 8;
-        const int n_slots = (int)(c_hi - c_lo) + 1;
-        if (fast_reduce) {
-            // every contributor adds its partial into the strip's f32 accumulator with vector
-            // reductions at L2; the last one reads the total and leaves the accumulator zero
-            float *acc_ptr = accum + (size_t)v * SK_PARTIAL_FLOATS + lane_off;
-            sk_red_partial(acc_ptr, own, lane);
-            __threadfence();
-            __syncwarp();
-            int old = 0;
-            if (lane == 0) old = atomicAdd(&counters[v * SK_CONSUMER_WARPS + warp], 1);
-            old = __shfl_sync(0xffffffffu, old, 0);
-            if (old != n_slots - 1) return;
-            __threadfence();
-            sk_take_accum(acc_ptr, own);
-        } else {
-            // deterministic: one slot per contributing CTA, summed by the last arriver in CTA order
-            float *mine = partials + (size_t)(c + v) * SK_PARTIAL_FLOATS + lane_off;
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                float4 *dst = reinterpret_cast<float4 *>(mine + 32 * h);
-                dst[0] = make_float4(own[h][0], own[h][1], own[h][2], own[h][3]);
-                dst[1] = make_float4(own[h][4], own[h][5], own[h][6], own[h][7]);
-            }
-            __threadfence();
-            __syncwarp();
-            int old = 0;
-            if (lane == 0) old = atomicAdd(&counters[v * SK_CONSUMER_WARPS + warp], 1);
-            old = __shfl_sync(0xffffffffu, old, 0);
-            if (old != n_slots - 1) return;
-            __threadfence();
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-#pragma unroll
-                for (int i = 0; i < 8; ++i) own[h][i] = 0.f;
-            // four slots' loads in flight at a time (the loop is latency-bound otherwise)
-            const float *src0 = partials + (size_t)(c_lo + v) * SK_PARTIAL_FLOATS + lane_off;
-            for (int s0 = 0; s0 < n_slots; s0 += 4) {
-                float4 p[4][4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int sj = s0 + j < n_slots ? s0 + j : n_slots - 1;
-                    const float4 *src = reinterpret_cast<const float4 *>(src0 + (size_t)sj * SK_PARTIAL_FLOATS);
-                    p[j][0] = __ldcg(src);
-                    p[j][1] = __ldcg(src + 1);
-                    p[j][2] = __ldcg(src + 8);
-                    p[j][3] = __ldcg(src + 9);
-                }
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    if (s0 + j >= n_slots) break;
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        own[h][0] += p[j][2 * h].x; own[h][1] += p[j][2 * h].y;
-                        own[h][2] += p[j][2 * h].z; own[h][3] += p[j][2 * h].w;
-                        own[h][4] += p[j][2 * h + 1].x; own[h][5] += p[j][2 * h + 1].y;
-                        own[h][6] += p[j][2 * h + 1].z; own[h][7] += p[j][2 * h + 1].w;
-                    }
-                }
-            }
-        }
-        __syncwarp();
-        if (lane == 0) counters[v * SK_CONSUMER_WARPS + warp] = 0;  // ready for the next launch
         if (!failed) sk_epilogue<EPI>(own, residual, y_, B, N, n, b, out_f16);
         if (EPI == EPI_F32_PUSH && !failed) sk_push_signal(push, err_flag + 8, V * SK_CONSUMER_WARPS, lane);
     };
@@ -229,12 +163,14 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         if (v != cur_v) {
             if (cur_v >= 0) flush();
             cur_v = v;
+            seg_groups = 0;
 #pragma unroll
             for (int e = 0; e < 4; ++e)
 #pragma unroll
                 for (int q = 0; q < 4; ++q) res[e][q] = 0.f;
         }
-        if (!failed && !mbar_wait_bounded(full_bar(slot), round & 1)) {
+        ++seg_groups;
+        if (!failed && !mbar_wait_bounded(full_bar(slot), round & 1, wait_limit)) {
             failed = true;
             if (lane == 0) atomicExch(err_flag, 2);
         }
@@ -300,25 +236,23 @@ int gemv_push_arrivals_per_rank(int N) {
 }
 
 bool gemv_streamk_supported(const GemvArgs &a) {
-    return a.group_size == SK_GROUP && a.K % SK_GROUP == 0 && a.N % 32 == 0 && a.B >= 1 && a.K > 0 && a.N > 0 &&
+    return a.group_size == SK_GROUP && a.K % SK_GROUP == 0 && a.K / SK_GROUP <= SK_MAX_GROUPS && a.N % 32 == 0 && a.B >= 1 &&
+           a.K > 0 && a.N > 0 &&
            aligned16(a.x) && aligned16(a.qweight) && aligned16(a.qzeros) && aligned16(a.scales) &&
            (a.N + SK_STRIP - 1) / SK_STRIP <= SK_MAX_STRIPS && device_is_sm100();
 }
 
-// Scratch without the activation-conversion buffer: fast reduction needs the accumulators of
-// its strips only; the deterministic one also a slot per (CTA, strip) segment.
+// Scratch without the activation-conversion buffer: the header and the accumulators of the strips.
 size_t gemv_streamk_scratch_bytes(int N, bool deterministic) {
-    const size_t V = (size_t)(N + SK_STRIP - 1) / SK_STRIP;
-    if (!deterministic) return SK_WS_ACCUM + V * SK_PARTIAL_FLOATS * 4;
-    int sms = device_sm_count();
-    if (sms <= 0) sms = 148;
-    return SK_WS_PARTIALS + (V + (size_t)sms * SK_CTAS_PER_SM) * SK_PARTIAL_FLOATS * 4;
+    (void)deterministic;  // the hand-over adds integers: every mode is reproducible
+    return SK_WS_ACCUM + (size_t)((N + SK_STRIP - 1) / SK_STRIP) * SK_STRIP_WORDS * 8;
 }
 
 size_t gemv_streamk_workspace_bytes(int B, int K, int N) {
-    // counters + partial slots + room for B rows of activations converted to fp16
+    // header + accumulators of every strip a product may use + room for B rows of activations converted to fp16
     const size_t rows = B < 1 ? 1 : (B > 64 ? 64 : B);
-    return gemv_streamk_scratch_bytes(N, true) + rows * (size_t)(K > 0 ? K : 0) * 2;
+    (void)N;
+    return SK_WS_END + rows * (size_t)(K > 0 ? K : 0) * 2;
 }
 
 template <int EPI, bool XH>
@@ -353,13 +287,10 @@ static int launch_one(const GemvArgs &a, const uint16_t *x, const uint16_t *resi
     if ((long long)ctas > U) ctas = (int)U;
     uint8_t *ws = reinterpret_cast<uint8_t *>(a.workspace);
     int *err_flag = reinterpret_cast<int *>(ws);
-    int *counters = reinterpret_cast<int *>(ws + SK_WS_HEADER);
-    float *accum = reinterpret_cast<float *>(ws + SK_WS_ACCUM);
-    float *partials = reinterpret_cast<float *>(ws + SK_WS_PARTIALS);
+    unsigned long long *accum = reinterpret_cast<unsigned long long *>(ws + SK_WS_ACCUM);
     return check_cuda(launch_pdl(gemv_streamk_kernel<EPI, XH>, dim3(ctas), dim3(SK_THREADS), SK_SMEM_BYTES, a.stream, tmW,
-                                 tmX, tmS, tmZ, residual, y, B, a.N, G, V, a.out_format == ACT_F16 ? 1 : 0,
-                                 a.deterministic ? 0 : 1, accum, partials, counters, err_flag,
-                                 a.push ? *a.push : PeerPush{}),
+                                 tmX, tmS, tmZ, residual, y, B, a.N, G, V, a.out_format == ACT_F16 ? 1 : 0, accum, err_flag,
+                                 a.push ? *a.push : PeerPush{}, wait_limit_cycles()),
                       "stream-K gemv launch");
 }
 
@@ -405,7 +336,7 @@ static int launch_passes(const GemvArgs &a, const uint16_t *x_all) {
 
 int launch_gemv_streamk(const GemvArgs &a) {
     const bool convert = a.x_format == ACT_BF16 && !a.native_bf16;
-    const size_t xh_off = gemv_streamk_scratch_bytes(a.N, true);
+    const size_t xh_off = SK_WS_END;  // the conversion buffer sits behind the accumulators of every possible strip
     const size_t need = convert ? xh_off + (size_t)a.B * a.K * 2 : gemv_streamk_scratch_bytes(a.N, a.deterministic);
     if (!a.workspace || a.workspace_bytes < need)
         return set_error(AWQ_ERR_WORKSPACE, "gemv: workspace of %zu bytes needed, %zu given", need, a.workspace_bytes);

@@ -9,10 +9,9 @@
 // every thread at 168 registers, so lane 0 of consumer warp 0 issues the TMA copies itself, between
 // its units, whenever a stage has been released (and blocks for a release only when the unit it is
 // about to consume has not been requested yet).
-// Units, stage layout (with T activation tiles), decode, split-K reduction with f32 vector
-// atomics and epilogues are those of the 8-row kernel; strip v, tile t uses accumulator and counter
-// slot v T + t.  fp16 activations only (bf16 inputs are converted by the caller), no deterministic
-// mode (those cases take one 8-row pass per tile instead).
+// Units, stage layout (with T activation tiles), decode, split-K hand-over (one 64-bit atomic per
+// sum carrying value and progress) and epilogues are those of the 8-row kernel; strip v, tile t
+// uses accumulator slot v T + t.  fp16 activations only (bf16 inputs are converted by the caller).
 #include <cudaTypedefs.h>
 #include <cuda_fp16.h>
 
@@ -50,7 +49,8 @@ __global__ void __launch_bounds__(mb_threads<T>(), 1)
 gemv_streamk_mb_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                        const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmZ,
                        const uint16_t *__restrict__ residual, void *__restrict__ y_, int B, int N, int G, int V,
-                       int out_f16, float *__restrict__ accum, int *__restrict__ counters, int *__restrict__ err_flag) {
+                       int out_f16, unsigned long long *__restrict__ accum, int *__restrict__ err_flag,
+                       long long wait_limit) {
     using Cfg = MbCfg<T>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -127,7 +127,7 @@ gemv_streamk_mb_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_con
     auto issue_next = [&](bool must) -> bool {
         const uint32_t parity = (uint32_t)(iss_round - 1) & 1u;
         if (must) {
-            if (!mbar_wait_bounded(empty_bar(iss_slot), parity)) {
+            if (!mbar_wait_bounded(empty_bar(iss_slot), parity, wait_limit)) {
                 atomicExch(err_flag, 1);
                 return false;
             }
@@ -174,22 +174,10 @@ gemv_streamk_mb_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_con
             float own[2][8];
             sk_lane_exchange(res[t], odd, own);
             const int b = 8 * t + 2 * t4 + odd;
-            if (seg_groups != G) {
-                const int slot_id = v * T + t;
-                const size_t lane_off = (size_t)warp * 512 + (2 * t4 + odd) * 64 + (g8 >> 1) * 8;
-                float *acc_ptr = accum + (size_t)slot_id * SK_PARTIAL_FLOATS + lane_off;
-                sk_red_partial(acc_ptr, own, lane);
-                __threadfence();
-                __syncwarp();
-                int old = 0;
-                if (lane == 0) old = atomicAdd(&counters[slot_id * SK_CONSUMER_WARPS + warp], seg_groups);
-                old = __shfl_sync(0xffffffffu, old, 0);
-                if (old + seg_groups != G) continue;
-                __threadfence();
-                sk_take_accum(acc_ptr, own);
-                __syncwarp();
-                if (lane == 0) counters[slot_id * SK_CONSUMER_WARPS + warp] = 0;  // ready for the next launch
-            }
+            if (seg_groups != G &&
+                !sk_handover(accum + ((size_t)(v * T + t) * SK_CONSUMER_WARPS + warp) * SK_ACC_WORDS, own, seg_groups, G, lane,
+                             wait_limit, err_flag))
+                continue;
             if (!failed) sk_epilogue<EPI>(own, residual, y_, B, N, n, b, out_f16);
         }
     };
@@ -213,7 +201,7 @@ gemv_streamk_mb_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_con
             while (iss_n < n_units && issue_next(iss_n <= i)) {
             }
         }
-        if (!failed && !mbar_wait_bounded(full_bar(slot), round & 1)) {
+        if (!failed && !mbar_wait_bounded(full_bar(slot), round & 1, wait_limit)) {
             failed = true;
             if (lane == 0) atomicExch(err_flag, 2);
         }
@@ -328,8 +316,8 @@ static int launch_mb(const GemvArgs &a, const uint16_t *x, const uint16_t *resid
     uint8_t *ws = reinterpret_cast<uint8_t *>(a.workspace);
     return check_cuda(launch_pdl(gemv_streamk_mb_kernel<EPI, T>, dim3(ctas), dim3(mb_threads<T>()), Cfg::SMEM_BYTES, a.stream, tmW,
                                  tmX, tmS, tmZ, residual, y, B, a.N, G, V, a.out_format == ACT_F16 ? 1 : 0,
-                                 reinterpret_cast<float *>(ws + SK_WS_ACCUM), reinterpret_cast<int *>(ws + SK_WS_HEADER),
-                                 reinterpret_cast<int *>(ws)),
+                                 reinterpret_cast<unsigned long long *>(ws + SK_WS_ACCUM), reinterpret_cast<int *>(ws),
+                                 wait_limit_cycles()),
                       "multi-row gemv launch");
 }
 
@@ -348,7 +336,7 @@ bool gemv_streamk_mb_supported(const GemvArgs &a, int B) {
     const int V = (a.N + SK_STRIP - 1) / SK_STRIP;
     const int T = B > 16 ? 4 : 2;
     return B > 8 && B <= 32 && !a.deterministic && a.epilogue != EPI_F32_PUSH && V * T <= SK_MAX_STRIPS &&
-           a.workspace_bytes >= SK_WS_PARTIALS;
+           a.workspace_bytes >= SK_WS_END && a.K / SK_GROUP <= SK_MAX_GROUPS;
 }
 
 // x: fp16 [B, K] (already converted), 9 <= B <= 32.

@@ -312,7 +312,7 @@ __global__ void __launch_bounds__(RN_THREADS)
 tp_reduce_add_rmsnorm_kernel(const uint16_t *__restrict__ h, const PeerPartials parts, unsigned int *flags,
                              unsigned int expected, const uint16_t *__restrict__ gamma, float eps,
                              uint16_t *__restrict__ h_out, uint16_t *__restrict__ normed, int K, int normed_f16,
-                             int *err_flag) {
+                             int *err_flag, long long wait_limit) {
     __shared__ float red[8];
     const int n_ranks = parts.n;
     pdl_launch_dependents();
@@ -321,7 +321,7 @@ tp_reduce_add_rmsnorm_kernel(const uint16_t *__restrict__ h, const PeerPartials 
     if ((int)threadIdx.x < n_ranks) {
         const long long t0 = clock64();
         while (ld_acquire_sys_u32(flags + threadIdx.x) < expected) {
-            if (clock64() - t0 > (1ll << 31)) {
+            if (clock64() - t0 > wait_limit) {
                 ok = 0;
                 break;
             }
@@ -568,13 +568,40 @@ __global__ void silu_mul_bf16_kernel(const uint16_t *__restrict__ gate, const ui
     out[i] = f32_to_bf16_bits(g * (1.0f / (1.0f + expf(-g))) * u);
 }
 
+// Per-tile packed buffer (the reference's NPU layout: matvec_int4_packed.py:57-103,
+// matmul_int4_packed.py:57-86) -> logical layout B.  Tiles are ordered (row block, k chunk); a tile is
+// [Q: m_tile x k_chunk/2 bytes | S: n_gpc x m_tile bf16 | Z: n_gpc x m_tile bytes], n_gpc = k_chunk / gs.
+// One thread per output byte of A_q, then per (group, row) entry of A_s / A_z.
+__global__ void repack_C_to_B_q_kernel(const uint8_t *__restrict__ packed, uint8_t *__restrict__ A_q, int M, int K,
+                                       int m_tile, int k_chunk, int tile_bytes) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int kb = K / 2, cb = k_chunk / 2;
+    if (idx >= (size_t)M * kb) return;
+    const int m = (int)(idx / kb), j = (int)(idx % kb);
+    const size_t tile = (size_t)(m / m_tile) * (K / k_chunk) + j / cb;
+    A_q[idx] = packed[tile * tile_bytes + (size_t)(m % m_tile) * cb + j % cb];
+}
+__global__ void repack_C_to_B_sz_kernel(const uint8_t *__restrict__ packed, uint16_t *__restrict__ A_s,
+                                        uint8_t *__restrict__ A_z, int M, int K, int gs, int m_tile, int k_chunk,
+                                        int tile_bytes) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int G = K / gs, n_gpc = k_chunk / gs;
+    if (idx >= (size_t)G * M) return;
+    const int g = (int)(idx / M), m = (int)(idx % M);
+    const size_t tile = (size_t)(m / m_tile) * (K / k_chunk) + g / n_gpc;
+    const uint8_t *t = packed + tile * tile_bytes;
+    const int q_bytes = m_tile * (k_chunk / 2), e = (g % n_gpc) * m_tile + m % m_tile;
+    A_s[idx] = (uint16_t)t[q_bytes + 2 * e] | ((uint16_t)t[q_bytes + 2 * e + 1] << 8);
+    A_z[idx] = t[q_bytes + 2 * n_gpc * m_tile + e];
+}
+
 static inline unsigned blocks_for(size_t n, int threads) { return (unsigned)((n + threads - 1) / threads); }
 
 int launch_tp_reduce_add_rmsnorm(const uint16_t *h, const PeerPartials &parts, unsigned int *flags, int expected,
                                  const uint16_t *gamma, float eps, uint16_t *h_out, uint16_t *normed, int normed_f16, int B,
                                  int K, int *err_flag, cudaStream_t stream) {
     return check_cuda(launch_pdl(tp_reduce_add_rmsnorm_kernel, dim3(B), dim3(RN_THREADS), 0, stream, h, parts, flags,
-                                 (unsigned int)expected, gamma, eps, h_out, normed, K, normed_f16, err_flag),
+                                 (unsigned int)expected, gamma, eps, h_out, normed, K, normed_f16, err_flag, wait_limit_cycles()),
                       "tp_reduce_add_rmsnorm launch");
 }
 
@@ -731,4 +758,20 @@ extern "C" int awq_b200_repack_A_to_B(const int32_t *qweight, const int32_t *qze
                         "repack scales copy");
     if (rc) return rc;
     return check_cuda(cudaGetLastError(), "repack_A_to_B launch");
+}
+
+extern "C" int awq_b200_repack_C_to_B(const uint8_t *packed, uint8_t *A_q, uint16_t *A_s, uint8_t *A_z, int M, int K,
+                                      int group_size, int m_tile, int k_chunk, awq_stream_t stream) {
+    AWQ_REQUIRE(M > 0 && K > 0 && group_size > 0 && m_tile > 0 && k_chunk > 0, "repack_C_to_B: bad size");
+    AWQ_REQUIRE(M % m_tile == 0 && K % k_chunk == 0 && k_chunk % group_size == 0 && k_chunk % 2 == 0,
+                "repack_C_to_B: M %% m_tile, K %% k_chunk, k_chunk %% group_size (M=%d K=%d m_tile=%d k_chunk=%d gs=%d)", M, K,
+                m_tile, k_chunk, group_size);
+    AWQ_REQUIRE(packed && A_q && A_s && A_z, "repack_C_to_B: null pointer");
+    const int n_gpc = k_chunk / group_size, G = K / group_size;
+    const int tile_bytes = m_tile * (k_chunk / 2) + 3 * n_gpc * m_tile;
+    cudaStream_t st = as_stream(stream);
+    repack_C_to_B_q_kernel<<<blocks_for((size_t)M * (K / 2), 256), 256, 0, st>>>(packed, A_q, M, K, m_tile, k_chunk, tile_bytes);
+    repack_C_to_B_sz_kernel<<<blocks_for((size_t)G * M, 256), 256, 0, st>>>(packed, A_s, A_z, M, K, group_size, m_tile, k_chunk,
+                                                                          tile_bytes);
+    return check_cuda(cudaGetLastError(), "repack_C_to_B launch");
 }

@@ -1,6 +1,7 @@
 // Thin inline-PTX wrappers (sm_100a): mbarrier, TMA tensor loads, ldmatrix, mma.sync.
-// Every wait is bounded: it gives up after WAIT_LIMIT_CYCLES and reports failure, so a
-// kernel can flag the error and leave instead of hanging the GPU.
+// Every wait is bounded: it gives up after `limit` clock cycles (a kernel argument, default
+// WAIT_LIMIT_DEFAULT, set by awq_b200_set_wait_limit) and reports failure, so a kernel can flag
+// the error and leave instead of hanging the GPU.
 #pragma once
 
 #include <cuda.h>
@@ -8,7 +9,7 @@
 
 namespace awq {
 
-constexpr long long WAIT_LIMIT_CYCLES = 1ll << 31;  // about a second at ~2 GHz
+constexpr long long WAIT_LIMIT_DEFAULT = 1ll << 31;  // about a second at ~2 GHz
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -39,14 +40,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // Returns false if the phase did not complete within the cycle limit.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, long long limit) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (true) {
 #pragma unroll 1
         for (int i = 0; i < 64; ++i)
             if (mbar_try_wait(bar, parity)) return true;
-        if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
+        if (clock64() - t0 > limit) return false;
         __nanosleep(64);
     }
 }

@@ -3,9 +3,9 @@
 // Some hosts of this library have no way to hand it a scratch buffer: a plugin slot whose
 // interface carries only the reference's inputs and outputs, a runtime that forbids
 // cudaMalloc once serving has started, or C code that links the .so without any allocator of
-// its own.  For them the scratch of the stream-K decode kernel (strip counters and split-K
-// partials) lives in a fixed array inside the library image instead of a caller-owned
-// workspace.  Every GPU that loads the library holds that array (about 1 MB) until the
+// its own.  For them the scratch of the stream-K decode kernel (the split-K
+// accumulators) lives in a fixed array inside the library image instead of a caller-owned
+// workspace.  Every GPU that loads the library holds that array (about 2 MB) until the
 // process exits.
 #include <mutex>
 
@@ -13,10 +13,10 @@
 
 namespace awq {
 
-// Room for 64 strips of 512 columns (N <= 32768): 16 KB of header + counters, then one 16 KB
-// f32 accumulator per strip.
+// Room for 64 strips of 512 columns (N <= 32768): a 16 KB header, then 32 KB of 64-bit accumulator
+// words per strip.
 constexpr int STATIC_MAX_N = 32768;
-constexpr size_t STATIC_SCRATCH_BYTES = 16384 + (size_t)64 * 16384;
+constexpr size_t STATIC_SCRATCH_BYTES = 16384 + (size_t)64 * 32768;
 
 static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
 
@@ -57,6 +57,8 @@ extern "C" int awq_b200_gemv_bf16_static(const uint16_t *x, const int32_t *qweig
     AWQ_REQUIRE(N <= STATIC_MAX_N, "gemv_static: N = %d exceeds the built-in scratch (at most %d columns); "
                 "use awq_b200_gemv_bf16 with a caller-owned workspace", N, STATIC_MAX_N);
     AWQ_REQUIRE(x && qweight && qzeros && scales && y, "gemv_static: null pointer");
+    AWQ_REQUIRE(aligned16(y) && (!residual || aligned16(residual)),
+                "gemv_static: the output and the residual must be 16-byte aligned");
     void *scratch = nullptr;
     int rc = static_scratch_for_current_device(&scratch);
     if (rc) return rc;
@@ -70,11 +72,25 @@ extern "C" int awq_b200_gemv_bf16_static(const uint16_t *x, const int32_t *qweig
     if (gemv_streamk_scratch_bytes(N, false) > STATIC_SCRATCH_BYTES)
         return set_error(AWQ_ERR_UNSUPPORTED, "gemv_static: %zu bytes of scratch are needed for N = %d, the built-in "
                          "array has %zu", gemv_streamk_scratch_bytes(N, false), N, STATIC_SCRATCH_BYTES);
-    // The array keeps whatever the previous call left.  The error flag, the strip counters and the
-    // strips' accumulators must read zero when the kernel starts, so clear them on the caller's
-    // stream first.
+    // The array keeps whatever the previous call left.  The error flag and the strips' accumulators
+    // must read zero when the kernel starts, so clear them on the caller's stream first.
     rc = check_cuda(cudaMemsetAsync(scratch, 0, gemv_streamk_workspace_clear_bytes(N), as_stream(stream)),
-                    "gemv_static: clearing counters");
+                    "gemv_static: clearing the accumulators");
     if (rc) return rc;
     return launch_gemv_streamk(a);
+}
+
+// The kernel reports a wait that gave up in word 0 of the built-in array, and the next static call
+// clears that word again: ask before making that next call.
+extern "C" int awq_b200_static_check(awq_stream_t stream) {
+    void *scratch = nullptr;
+    int rc = static_scratch_for_current_device(&scratch);
+    if (rc) return rc;
+    int flag = 0;
+    rc = check_cuda(cudaMemcpyAsync(&flag, scratch, sizeof(int), cudaMemcpyDeviceToHost, as_stream(stream)),
+                    "static_check copy");
+    if (rc) return rc;
+    rc = check_cuda(cudaStreamSynchronize(as_stream(stream)), "static_check sync");
+    if (rc) return rc;
+    return status_of_device_flag(flag);
 }

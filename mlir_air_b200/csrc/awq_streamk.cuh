@@ -28,25 +28,102 @@ constexpr int SK_OFF_Z = SK_OFF_S + SK_S_BYTES;
 constexpr int SK_STAGE_BYTES = 36 * 1024;         // + 256 B of norm weights in the fused stack kernel
 constexpr int SK_BAR_BYTES = 2 * SK_STAGES * 8 + 16;
 constexpr int SK_SMEM_BYTES = SK_STAGES * SK_STAGE_BYTES + SK_BAR_BYTES + 1024;
-constexpr int SK_PARTIAL_FLOATS = 8 * SK_STRIP;        // one slot: [warp][batch 8][64 columns]
+constexpr int SK_ACC_WORDS = 16 * 32;                  // one 64-column sub-strip: 16 sums per lane, [sum][lane]
+constexpr int SK_STRIP_WORDS = SK_CONSUMER_WARPS * SK_ACC_WORDS;
 static_assert(SK_TX_BYTES <= SK_STAGE_BYTES, "stage too small");
 static_assert(SK_CTAS_PER_SM * (SK_SMEM_BYTES + 1024) <= 228 * 1024, "shared memory budget");
 
-// Workspace: [0, 256) header (int error flag); a fixed region of sub-strip counters (one per 64
-// columns); the per-strip f32 accumulators of the fast reduction (strip v at a fixed offset, up
-// to SK_MAX_STRIPS); then, for the deterministic reduction only, one partial slot per (CTA,
-// strip) segment.  Counters and accumulators are all zero between launches (the last arriver
-// resets what it used), and their offsets do not depend on the shape, so one workspace serves
-// products of different shapes back to back.
+// Workspace: [0, 256) header (int error flag, counter of the peer push); then, from SK_WS_ACCUM
+// on, the split-K accumulators: one 64-bit word per (strip, warp, batch row, column), strip v at a
+// fixed offset (up to SK_MAX_STRIPS).  All words are zero between launches (the warp that
+// completes a sum takes it out and leaves zero), and the offsets do not depend on the shape, so
+// one workspace serves products of different shapes back to back.
 constexpr size_t SK_WS_HEADER = 256;
 constexpr int SK_MAX_STRIPS = 504;  // N up to 258,048 columns
-constexpr size_t SK_WS_ACCUM = SK_WS_HEADER + (size_t)SK_MAX_STRIPS * SK_CONSUMER_WARPS * 4;  // 16 KB
-constexpr size_t SK_WS_PARTIALS = SK_WS_ACCUM + (size_t)SK_MAX_STRIPS * SK_PARTIAL_FLOATS * 4;
-constexpr int SK_MAX_CTAS = 2048;
+constexpr size_t SK_WS_ACCUM = 16384;
+constexpr size_t SK_WS_END = SK_WS_ACCUM + (size_t)SK_MAX_STRIPS * SK_STRIP_WORDS * 8;
+constexpr int SK_MAX_CTAS = 1023;
 
+// ---- split-K hand-over: value and progress in ONE 64-bit atomic ------------------------------
+// A partial sum travels as a fixed-point integer (2^-20 resolution) in the low 54 bits of a word
+// and the number of k groups it covers in the high 10 bits, so a single atom.add carries both: the
+// word's group count says when the sum is complete, and no fence, counter or ordering between
+// separate memory operations is needed.  Integer addition is associative, so the total does not
+// depend on the order in which the contributions arrive: results are bit-reproducible.
+// Every contribution adds groups * 2^43 so that the value field never goes negative;
+// |partial sum| must stay below 2^43 * 2^-20 = 8.39e6 (it is clamped and flagged otherwise), and a
+// product may have at most 1023 groups.
+constexpr int SK_FX_COUNT_SHIFT = 54;
+constexpr unsigned long long SK_FX_VALUE_MASK = (1ull << SK_FX_COUNT_SHIFT) - 1;
+constexpr long long SK_FX_BIAS = 1ll << 43;
+constexpr float SK_FX_SCALE = 1048576.f;  // 2^20
+constexpr float SK_FX_LIMIT = 8.38e6f;
+constexpr int SK_MAX_GROUPS = 1023;
 
-__device__ __forceinline__ void red_add_v4(float *addr, float a, float b, float c, float d) {
-    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+__device__ __forceinline__ unsigned long long sk_fx_encode(float v, int groups, bool &clamped) {
+    if (!(fabsf(v) <= SK_FX_LIMIT)) {  // also NaN
+        clamped = true;
+        v = v != v ? 0.f : copysignf(SK_FX_LIMIT, v);
+    }
+    const long long fx = __float2ll_rn(v * SK_FX_SCALE) + (long long)groups * SK_FX_BIAS;
+    return ((unsigned long long)groups << SK_FX_COUNT_SHIFT) + (unsigned long long)fx;
+}
+__device__ __forceinline__ float sk_fx_decode(unsigned long long word, int G) {
+    const long long fx = (long long)(word & SK_FX_VALUE_MASK) - (long long)G * SK_FX_BIAS;
+    return (float)fx * (1.f / SK_FX_SCALE);
+}
+__device__ __forceinline__ unsigned long long ld_relaxed_gpu_u64(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Hand this warp's partial sums of a sub-strip (own[h][j], `seg_groups` of the product's G groups)
+// to the sub-strip's accumulator words at `sub`.  Returns true in exactly one contributor per use
+// of the accumulator: the one whose add completed word 0 of lane 0.  It then holds the complete
+// sums in `own` (the other words are normally complete too; where another contributor's adds are
+// still on their way it re-reads them, bounded by `wait_limit` cycles) and has left the words zero.
+__device__ __forceinline__ bool sk_handover(unsigned long long *sub, float (&own)[2][8], int seg_groups, int G, int lane,
+                                            long long wait_limit, int *err_flag) {
+    unsigned long long *w = sub + lane;
+    unsigned long long tot[16];
+    bool clamped = false;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) tot[i] = sk_fx_encode(own[i >> 3][i & 7], seg_groups, clamped);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) tot[i] += atomicAdd(w + 32 * i, tot[i]);
+    if (clamped) atomicExch(err_flag, 7);
+    const int pilot = __shfl_sync(0xffffffffu, (int)(tot[0] >> SK_FX_COUNT_SHIFT), 0);
+    if (pilot != G) return false;
+    bool complete = true;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) complete = complete && (int)(tot[i] >> SK_FX_COUNT_SHIFT) == G;
+    if (!__all_sync(0xffffffffu, complete)) {
+        const long long t0 = clock64();
+        bool all, late;
+        do {
+            complete = true;
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                if ((int)(tot[i] >> SK_FX_COUNT_SHIFT) != G) {
+                    tot[i] = ld_relaxed_gpu_u64(w + 32 * i);
+                    complete = complete && (int)(tot[i] >> SK_FX_COUNT_SHIFT) == G;
+                }
+            all = __all_sync(0xffffffffu, complete);
+            // the lanes must leave together: one lane's clock decides for the warp
+            late = __shfl_sync(0xffffffffu, clock64() - t0 > wait_limit ? 1 : 0, 0) != 0;
+        } while (!all && !late);
+        if (!all) {
+            if (lane == 0) atomicExch(err_flag, 8);
+            return false;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        w[32 * i] = 0ull;  // nobody else touches the word before its next use
+        own[i >> 3][i & 7] = sk_fx_decode(tot[i], G);
+    }
+    return true;
 }
 
 // CTA that owns unit x when U units are split over C CTAs as [c U / C, (c + 1) U / C).
@@ -143,45 +220,6 @@ __device__ __forceinline__ void sk_epilogue(const float (&own)[2][8], const uint
     }
 }
 
-
-// Add a lane's partial (own[h][0..7] = 8 consecutive columns at acc_ptr + 32 h) into the strip's f32
-// accumulator with vector reductions at L2.  Lanes L and L ^ 8 hold neighbouring 32-byte sectors;
-// they swap half a sector first so that each reduction instruction carries whole sectors (the two
-// 16-byte pieces of a sector travel in the same instruction) instead of 32 half sectors.
-__device__ __forceinline__ void sk_red_partial(float *acc_ptr, const float (&own)[2][8], int lane) {
-    const bool upper = (lane & 8) != 0;  // this lane's sector is the second of the pair
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        float recv[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) recv[i] = __shfl_xor_sync(0xffffffffu, upper ? own[h][i] : own[h][4 + i], 8);
-        float *mine = acc_ptr + 32 * h;  // this lane's sector; the partner's is 8 floats away
-        if (!upper) {
-            red_add_v4(mine, own[h][0], own[h][1], own[h][2], own[h][3]);      // first half of the lower sector
-            red_add_v4(mine + 8, recv[0], recv[1], recv[2], recv[3]);          // first half of the upper sector
-        } else {
-            red_add_v4(mine - 4, recv[0], recv[1], recv[2], recv[3]);          // second half of the lower sector
-            red_add_v4(mine + 4, own[h][4], own[h][5], own[h][6], own[h][7]);  // second half of the upper sector
-        }
-    }
-}
-
-// The last contributor takes the strip's total out of the accumulator and leaves zeros: all four
-// loads are issued before the first store (a store to the same address between them would make the
-// second pair wait for a whole round trip more).
-__device__ __forceinline__ void sk_take_accum(float *acc_ptr, float (&own)[2][8]) {
-    float4 *s0 = reinterpret_cast<float4 *>(acc_ptr), *s1 = reinterpret_cast<float4 *>(acc_ptr + 32);
-    const float4 a0 = __ldcg(s0), a1 = __ldcg(s0 + 1), b0 = __ldcg(s1), b1 = __ldcg(s1 + 1);
-    own[0][0] = a0.x; own[0][1] = a0.y; own[0][2] = a0.z; own[0][3] = a0.w;
-    own[0][4] = a1.x; own[0][5] = a1.y; own[0][6] = a1.z; own[0][7] = a1.w;
-    own[1][0] = b0.x; own[1][1] = b0.y; own[1][2] = b0.z; own[1][3] = b0.w;
-    own[1][4] = b1.x; own[1][5] = b1.y; own[1][6] = b1.z; own[1][7] = b1.w;
-    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-    s0[0] = z;
-    s0[1] = z;
-    s1[0] = z;
-    s1[1] = z;
-}
 
 // After a warp has stored a finished sub-strip with EPI_F32_PUSH.  Sub-strips are counted on this
 // GPU first (`local_done`, zero between launches); the warp that finishes the launch's last one makes

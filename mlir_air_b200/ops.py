@@ -433,3 +433,26 @@ def repack_A_to_B(w: AwqWeight):
     _lib.call("awq_b200_repack_A_to_B", _ptr(w.qweight), _ptr(w.qzeros), _ptr(w.scales), _ptr(A_q), _ptr(A_s),
               _ptr(A_z), M, K, w.group_size, _stream())
     return A_q, A_s, A_z
+
+
+def repack_C_to_B(packed, M: int, K: int, group_size=128, m_tile=8, k_chunk=2048):
+    """Per-tile packed buffer (uint8, tiles in (row block, k chunk) order: the reference's NPU layout
+    for the GEMV and, with M = N and m_tile = N_TILE, for the GEMM) -> layout B on the device."""
+    _want(packed, torch.uint8, "packed")
+    G = K // group_size
+    tile = m_tile * (k_chunk // 2) + 3 * (k_chunk // group_size) * m_tile
+    if packed.numel() != (M // m_tile) * (K // k_chunk) * tile:
+        raise _lib.AwqBackendError(f"packed buffer has {packed.numel()} bytes, expected {(M // m_tile) * (K // k_chunk)} "
+                                   f"tiles of {tile}")
+    dev = packed.device
+    A_q = torch.empty((M, K // 2), dtype=torch.uint8, device=dev)
+    A_s = torch.empty((G, M), dtype=torch.bfloat16, device=dev)
+    A_z = torch.empty((G, M), dtype=torch.uint8, device=dev)
+    _lib.call("awq_b200_repack_C_to_B", _ptr(packed), _ptr(A_q), _ptr(A_s), _ptr(A_z), M, K, group_size, m_tile, k_chunk,
+              _stream())
+    return A_q, A_s, A_z
+
+
+def repack_C_to_A(packed, M: int, K: int, group_size=128, m_tile=8, k_chunk=2048) -> AwqWeight:
+    """Per-tile packed buffer -> resident layout-A weight (two device passes, once per weight)."""
+    return repack_B_to_A(*repack_C_to_B(packed, M, K, group_size, m_tile, k_chunk), group_size)

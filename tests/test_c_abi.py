@@ -43,6 +43,19 @@ def test_argument_errors_need_no_gpu():
     assert _err(lib.awq_b200_gemv_bf16(p, p, p, p, None, p, 1, 256, 12, 128, p, 1 << 20, None))[0] == INV  # N % 8
     assert _err(lib.awq_b200_gemv_bf16(p, p, p, p, None, p, 65, 256, 64, 128, p, 1 << 20, None))[0] == INV  # batch > 64
     assert _err(lib.awq_b200_gemv_bf16(None, p, p, p, None, p, 1, 256, 64, 128, p, 1 << 20, None))[0] == INV  # null x
+    # a misaligned output or residual is an argument error, not a device fault: the kernels move both in 16-byte pieces
+    odd = ctypes.c_void_p(256 + 2)
+    rc, msg = _err(lib.awq_b200_gemv_bf16(p, p, p, p, None, odd, 1, 256, 64, 128, p, 1 << 20, None))
+    assert rc == INV and "output" in msg and "16-byte" in msg
+    rc, msg = _err(lib.awq_b200_gemv_bf16(p, p, p, p, odd, p, 1, 256, 64, 128, p, 1 << 20, None))
+    assert rc == INV and "residual" in msg
+    assert _err(lib.awq_b200_gemv_f32(p, p, p, p, ctypes.c_void_p(256 + 8), 1, 256, 64, 128, p, 1 << 20, None))[0] == INV
+    assert _err(lib.awq_b200_gateup_swiglu_bf16(p, p, p, p, odd, 1, 256, 64, 128, p, 1 << 20, None))[0] == INV
+    assert _err(lib.awq_b200_gemv_bf16_static(p, p, p, p, None, odd, 1, 256, 64, 128, None))[0] == INV
+    assert _err(lib.awq_b200_gemv_bf16_static(p, p, p, p, odd, p, 1, 256, 64, 128, None))[0] == INV
+    # the limit of device-side waits
+    assert _err(lib.awq_b200_set_wait_limit(-1))[0] == INV
+    assert lib.awq_b200_set_wait_limit(1 << 20) == 0 and lib.awq_b200_set_wait_limit(0) == 0
     # rope
     rc, msg = _err(lib.awq_b200_rope_halfsplit_bf16(p, 256, p, p, 256, 1, 4, 40, None))
     assert rc == INV and "head_dim" in msg

@@ -111,6 +111,47 @@ def test_stack_llama70b_dims_matches_per_layer_kernels(ops):
     assert rel <= 5e-3
 
 
+def test_stack_llama70b_dims_vs_oracle_golden(ops):
+    """Benchmark configuration 5 dims against the numpy oracle: tests/golden/ffn_stack_70b.npz holds the
+    hidden state after each of two seeded layers (hidden 8192, intermediate 28672, batch 8), computed on
+    the CPU by tests/golden/make_golden_stack70b.py.  The weights are regenerated here from the seeds.
+    Checked per layer from the golden input of that layer and end to end, for the one-launch stack
+    kernel and for the per-layer kernels."""
+    import golden_util
+    from gpu_util import dev_weight, to_dev, to_host
+    g = golden_util.load("ffn_stack_70b")
+    cfg = {k: int(g[k]) for k in golden_util.STACK70B}
+    assert cfg == golden_util.STACK70B, "fixture was generated for another configuration"
+    H, I, L = cfg["hidden"], cfg["intermediate"], cfg["layers"]
+    gold = g["h"]  # [L, 8, H] bf16
+    x = golden_util.stack70b_input(cfg)
+    gus, downs, gammas = [], [], []
+    for l in range(L):
+        gate, up, down, gamma = golden_util.stack70b_layer(l, cfg)
+        gus.append(ops.interleave_gate_up(dev_weight(*gate), dev_weight(*up)))
+        downs.append(dev_weight(*down))
+        gammas.append(to_dev(gamma))
+        del gate, up, down
+    ws = ops.Workspace(max(H, I), max(2 * I, H))
+    errs = {}
+    # per layer, from the golden input of that layer: one-launch kernel on a one-layer plan, and the per-layer entry point
+    for l in range(L):
+        h_in = to_dev(x if l == 0 else gold[l - 1])
+        plan1 = ops.FFNStackPlan([gus[l]], [downs[l]], [gammas[l]])
+        errs[f"fused layer {l}"] = O.rel_l2(to_host(ops.ffn_stack_decode(plan1, h_in, ws)), gold[l])
+        ws.check()
+        errs[f"per-layer layer {l}"] = O.rel_l2(
+            to_host(ops.ffn_decode(h_in, gus[l], downs[l], ws, gamma=gammas[l], residual=h_in)), gold[l])
+        ws.check()
+    # end to end: both layers in one launch, batch 8 and batch 1 (row 0 alone)
+    plan = ops.FFNStackPlan(gus, downs, gammas)
+    errs["fused end to end"] = O.rel_l2(to_host(ops.ffn_stack_decode(plan, to_dev(x), ws)), gold[L - 1])
+    errs["fused end to end, batch 1"] = O.rel_l2(to_host(ops.ffn_stack_decode(plan, to_dev(x[:1]), ws)), gold[L - 1][:1])
+    ws.check()
+    bad = {k: v for k, v in errs.items() if not v <= REL_L2_TOL}
+    assert not bad, errs
+
+
 def test_stack_rejects_what_it_cannot_run(ops):
     import torch
     from gpu_util import dev_weight, synth_awq, to_dev

@@ -43,7 +43,8 @@ def test_static_matches_workspace_entry_point_two_calls_in_a_row():
     ops.set_decode_kernel("streamk_bf16")  # the allocation-free entry multiplies bf16 activations as they are
     stream = torch.cuda.current_stream().cuda_stream
     try:
-        for call, (B, seed) in enumerate([(8, 1), (3, 2)]):
+        # 8 and 3 rows: one pass; 20 rows: three passes of 8 rows over the one shared set of accumulators
+        for call, (B, seed) in enumerate([(8, 1), (3, 2), (20, 3)]):
             x = randn_bf16((B, K), seed=seed)
             r = randn_bf16((B, N), seed=seed + 10)
             xd, rd = to_dev(x), to_dev(r)
@@ -55,7 +56,8 @@ def test_static_matches_workspace_entry_point_two_calls_in_a_row():
             _lib.check(lib.awq_b200_gemv_bf16_static(xd.data_ptr(), w.qweight.data_ptr(), w.qzeros.data_ptr(),
                                                      w.scales.data_ptr(), rd.data_ptr(), y_new.data_ptr(), B, K, N,
                                                      128, stream), "gemv_bf16_static")
-            torch.cuda.synchronize()
+            # a wait that gave up would be reported here (and only here: the next static call clears the word)
+            _lib.check(lib.awq_b200_static_check(stream), "static_check")
             a, e = to_host(y_new), to_host(y_ref)
             assert np.isfinite(a.astype(np.float32)).all(), f"call {call}: output not fully written"
             assert O.rel_l2(a, e) <= REL_L2_TOL, f"call {call}"
