@@ -9,10 +9,17 @@
 // Same units, shared-memory ring, nibble decode and split-K reduction as the single-product
 // stream-K kernel (awq_gemv_streamk.cu); what is new is how the phases chain inside the launch:
 //
-//  * Every CTA walks a static list: its gate/up unit range of layer 0, its down range of layer 0,
-//    its gate/up range of layer 1, ...  The loader keeps the ring full across phase
-//    changes: the weights of the next phase's first units are requested before the phase's
-//    activations exist.
+//  * An SM's units of a phase are one contiguous range of the phase's strip-major unit list, and
+//    the CTA's two halves share it dynamically: half 0 takes units from the front of the range,
+//    half 1 from the back, each claiming its next unit from a shared-memory counter when its ring
+//    has room, until the two meet.  Neither waits for the other and the faster half simply takes
+//    more units, so both reach the end of the phase within about a unit of each other.  (With the
+//    range cut in the middle the two halves of an SM finished a gate/up phase up to 7 us apart: the
+//    hardware does not share issue slots evenly between two sets of warps, and which set it
+//    prefers varies from SM to SM.)  The loader of a half writes a descriptor of the claimed unit
+//    into shared memory next to the stage, and an end-of-phase marker takes one ring turn.
+//  * The loader keeps the ring full across phase changes: the weights of the next phase's first
+//    units are requested before the phase's activations exist.
 //  * A phase's activations exist when every 64-column sub-strip of the previous phase has been
 //    finalised; finalising warps count up `done_gu` / `done_d` in global memory (release), the
 //    loaders wait for the count (acquire, bounded).  All CTAs of the launch are resident
@@ -49,6 +56,9 @@ namespace awq {
 
 int encode_tensor_map_2d(CUtensorMap *map, int dtype, const void *base, uint64_t dim0, uint64_t dim1,
                          uint64_t stride1_bytes, uint32_t box0, uint32_t box1, int swizzle);
+int encode_tensor_map_3d(CUtensorMap *map, int dtype, const void *base, uint64_t dim0, uint64_t dim1, uint64_t dim2,
+                         uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1, uint32_t box2,
+                         int swizzle);
 
 // One layer's tensor maps, device resident (TMA reads the descriptor from global memory).
 struct alignas(128) FusedLayer {
@@ -58,7 +68,7 @@ struct alignas(128) FusedLayer {
 };
 static_assert(sizeof(FusedLayer) % 128 == 0, "tensor maps must stay 64-byte aligned in the array");
 
-constexpr int FF_MAX_LAYERS = 1024;
+constexpr int FF_MAX_LAYERS = 1024;  // 2 claim words per layer in shared memory
 // State of one launch in the workspace, zeroed by the launcher: two phase counters, then one
 // f32 sum of squares per (layer boundary, batch row).
 constexpr size_t FF_STATE_OFF = SK_WS_END;
@@ -87,10 +97,8 @@ __device__ __forceinline__ bool wait_count(const int *ctr, int target, long long
 
 // One CTA per SM, made of two independent halves.  A half is what a CTA of the single-product
 // kernel is: 8 consumer warps and its own 3-stage ring, plus a loader warp (one thread drives
-// TMA) and a normaliser warp.  The SM's units of a phase are one contiguous range, cut between
-// the halves at `split` / 1024 of its length: the hardware does not share issue slots evenly
-// between two sets of warps, and the set it prefers gets the larger part so that both finish
-// together.
+// TMA) and a normaliser warp.  The SM's units of a phase are one contiguous range that the two
+// halves take from both ends.
 constexpr int FF_HALVES = 2;
 constexpr int FF_CONSUMER_WARPS = FF_HALVES * SK_CONSUMER_WARPS;
 constexpr int FF_WARPS = FF_CONSUMER_WARPS + 2 * FF_HALVES;
@@ -99,12 +107,21 @@ constexpr int FF_OFF_GAMMA = SK_OFF_Z + SK_Z_BYTES;  // 128 bf16 norm weights of
 constexpr int FF_GAMMA_BYTES = SK_GROUP * 2;
 constexpr int FF_RING_BYTES = SK_STAGES * SK_STAGE_BYTES;
 constexpr int FF_BARS_PER_HALF = 3 * SK_STAGES;
-constexpr int FF_SMEM_BYTES = FF_HALVES * FF_RING_BYTES + FF_HALVES * FF_BARS_PER_HALF * 8 + 16 + 1024;
+constexpr int FF_BAR_BYTES = FF_HALVES * FF_BARS_PER_HALF * 8;
+constexpr int FF_DESC_BYTES = FF_HALVES * SK_STAGES * 16;  // per stage: layer, phase (| FF_END), strip, group
+constexpr int FF_CLAIM_WORDS = 2 * FF_MAX_LAYERS;          // units of this SM taken so far, one word per phase
+constexpr int FF_END = 2;                                  // descriptor flag: the half has no more units in this phase
+constexpr int FF_SMEM_BYTES = FF_HALVES * FF_RING_BYTES + FF_BAR_BYTES + FF_DESC_BYTES + FF_CLAIM_WORDS * 4 + 16 + 1024;
 static_assert(FF_OFF_GAMMA + FF_GAMMA_BYTES <= SK_STAGE_BYTES, "stage too small");
 static_assert(FF_SMEM_BYTES + 1024 + 128 <= 228 * 1024, "shared memory budget");
 
 __device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap *map, int x, int y) {
     asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap *map, int x, int y, int z, uint64_t policy) {
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.L2::cache_hint [%0, {%1, %2, %3}], %4;" ::"l"(map), "r"(x), "r"(y),
+                 "r"(z), "l"(policy)
+                 : "memory");
 }
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
@@ -121,7 +138,6 @@ struct FusedArgs {
     float eps;
     int B, H, I;
     int lookahead;  // units the L2 prefetch runs ahead of the shared-memory ring
-    int split;      // share of an SM's units that half 0 takes, in 1/1024
     unsigned long long *accum;  // split-K accumulator words (zero between uses): gate/up strips, then down strips
     int *err_flag;
     int *state;     // done_gu, done_d, ..., then sumsq[(n_layers + 1) * 8]
@@ -133,6 +149,7 @@ struct FusedArgs {
     unsigned long long *ll_recv[2][TP_MAX_RANKS];  // every rank's receive slots, mapped into this GPU's address space
     unsigned int *epoch;                           // launches so far on this rank (base of the tags), in peer memory
     long long wait_limit;                          // cycles after which a device-side wait gives up
+    int w3d_gu, w3d_d;  // the weight tensor map of a phase is 3-D: one copy fetches both 256-column boxes of a unit
 };
 constexpr int FF_LL_WORDS = 16 * 32;  // words of one sub-strip from one rank
 
@@ -145,51 +162,16 @@ __device__ __forceinline__ unsigned long long ld_relaxed_sys_u64(const unsigned 
     return v;
 }
 
-// The unit range [u0, u1) of one half in one phase: the SM's range [s U / S, (s + 1) U / S), cut.
-__device__ __forceinline__ void ff_range(long long U, int half, int split, long long &u0, long long &u1) {
+// The unit range [lo, hi) of this SM in a phase of U units.
+__device__ __forceinline__ void ff_sm_range(long long U, int &lo, int &hi) {
     const long long S = gridDim.x, s = blockIdx.x;
-    const long long lo = s * U / S, hi = (s + 1) * U / S;
-    const long long mid = lo + ((hi - lo) * split + 512) / 1024;
-    u0 = half ? mid : lo;
-    u1 = half ? hi : mid;
+    lo = (int)(s * U / S);
+    hi = (int)((s + 1) * U / S);
 }
 
-// One half's walk over its units: for every layer its gate/up range, then its down range.
-struct UnitCursor {
-    int l, p, v, g, left;  // layer, phase (0 gate/up, 1 down), strip, group, units left in the phase
-    int G0, V0, G1, V1, n_layers, half, split;
-    __device__ __forceinline__ UnitCursor(int g0, int v0, int g1, int v1, int layers, int half_, int split_)
-        : G0(g0), V0(v0), G1(g1), V1(v1), n_layers(layers), half(half_), split(split_) {
-        l = 0;
-        p = 0;
-        enter();
-    }
-    __device__ __forceinline__ int groups() const { return p ? G1 : G0; }
-    // position on the first unit of phase (l, p), skipping phases in which this half has no unit
-    __device__ __forceinline__ void enter() {
-        while (l < n_layers) {
-            const int G = groups();
-            long long u0, u1;
-            ff_range((long long)(p ? V1 : V0) * G, half, split, u0, u1);
-            if (u1 > u0) {
-                v = (int)(u0 / G);
-                g = (int)(u0 % G);
-                left = (int)(u1 - u0);
-                return;
-            }
-            if (++p == 2) { p = 0; ++l; }
-        }
-    }
-    __device__ __forceinline__ bool valid() const { return l < n_layers; }
-    __device__ __forceinline__ void next() {
-        if (--left > 0) {
-            if (++g == groups()) { g = 0; ++v; }
-            return;
-        }
-        if (++p == 2) { p = 0; ++l; }
-        enter();
-    }
-};
+// Take one more unit of a phase (n units in this SM's range) if any is left: one shared-memory atomic on
+// the phase's own word, which starts at zero.
+__device__ __forceinline__ bool ff_claim(unsigned int *word, int n) { return atomicAdd(word, 1u) < (unsigned int)n; }
 
 // End of a down sub-strip: lane's 2 x 8 finished sums of batch row b at columns n + 32 h + i.
 // hidden state = bf16(sum + residual), its squares go to the next layer's RMSNorm sums.  `res0`,
@@ -240,8 +222,11 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
     const uint32_t bar_base =
         ((smem_u32(smem_raw) + 1023u) & ~1023u) + FF_HALVES * FF_RING_BYTES + half * FF_BARS_PER_HALF * 8;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };                      // TMA landed
-    auto empty_bar = [&](int s) { return bar_base + 8u * (SK_STAGES + s); };       // consumers done
+    auto empty_bar = [&](int s) { return bar_base + 8u * (SK_STAGES + s); };       // consumers and normaliser done
     auto xready_bar = [&](int s) { return bar_base + 8u * (2 * SK_STAGES + s); };  // activations normalised
+    const uint32_t aux_base = ((smem_u32(smem_raw) + 1023u) & ~1023u) + FF_HALVES * FF_RING_BYTES + FF_BAR_BYTES;
+    auto desc_addr = [&](int s) { return aux_base + (uint32_t)(half * SK_STAGES + s) * 16u; };
+    unsigned int *claim_words = reinterpret_cast<unsigned int *>(smem_raw + (aux_base - smem_u32(smem_raw)) + FF_DESC_BYTES);
 
     const int B = a.B, H = a.H, I = a.I;
     // phase 0: gate/up, K = H, N = 2I; phase 1: down, K = I, N = H
@@ -257,11 +242,12 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
     if (role == 1 && lane == 0) {  // each loader sets up its half's barriers
         for (int s = 0; s < SK_STAGES; ++s) {
             mbar_init(full_bar(s), 1);
-            mbar_init(empty_bar(s), SK_CONSUMER_WARPS);
+            mbar_init(empty_bar(s), SK_CONSUMER_WARPS + 1);
             mbar_init(xready_bar(s), 1);
         }
         mbar_fence_init();
     }
+    for (int i = threadIdx.x; i < 2 * a.n_layers; i += FF_THREADS) claim_words[i] = 0u;
     // sum of squares of the input rows (layer 0's RMSNorm): rows b, b + gridDim.x, ... per CTA
     for (int row_i = blockIdx.x; row_i < B; row_i += gridDim.x) {
         const uint16_t *row = a.x + (size_t)row_i * H;
@@ -291,32 +277,43 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
     }
     __syncthreads();
 
+    // this SM's unit range of a gate/up phase and of a down phase (the same in every layer), and how far into it
+    // (from its own end) a half prefetches: a little past the middle
+    int lo0, hi0, lo1, hi1;
+    ff_sm_range((long long)V0 * G0, lo0, hi0);
+    ff_sm_range((long long)V1 * G1, lo1, hi1);
+    const int lim0 = (hi0 - lo0) / 2 + 2 < hi0 - lo0 ? (hi0 - lo0) / 2 + 2 : hi0 - lo0;
+    const int lim1 = (hi1 - lo1) / 2 + 2 < hi1 - lo1 ? (hi1 - lo1) / 2 + 2 : hi1 - lo1;
+    auto maps = [&](int l, int p, const CUtensorMap *&tmW, const CUtensorMap *&tmS, const CUtensorMap *&tmZ) {
+        const FusedLayer *Ly = a.layers + l;
+        tmW = p ? &Ly->w_d : &Ly->w_gu;
+        tmS = p ? &Ly->s_d : &Ly->s_gu;
+        tmZ = p ? &Ly->z_d : &Ly->z_gu;
+    };
+    // this half's c-th unit of a range [lo, hi): half 0 walks up from lo, half 1 down from hi - 1
+    auto unit_of = [&](int lo, int hi, int c) { return half ? hi - 1 - c : lo + c; };
+    // Request this half's c-th unit of phase (l, p) into L2.  Weights depend on nothing, so HBM keeps streaming
+    // while a phase waits.  Issued by the normaliser warp: the loader thread has no time to spare.
+    auto prefetch_unit = [&](int l, int p, int c) {
+        const int G = p ? G1 : G0;
+        const int u = p ? unit_of(lo1, hi1, c) : unit_of(lo0, hi0, c), v = u / G, g = u - v * G;
+        const CUtensorMap *tmW, *tmS, *tmZ;
+        maps(l, p, tmW, tmS, tmZ);
+        if (p ? a.w3d_d : a.w3d_gu) {
+            tma_prefetch_l2_3d(tmW, 0, g * SK_GROUP, v * (SK_STRIP / SK_BOX_COLS), l2_policy_evict_first());
+        } else {
+#pragma unroll
+            for (int bx = 0; bx < SK_STRIP / SK_BOX_COLS; ++bx)
+                tma_prefetch_l2_2d(tmW, (v * SK_STRIP + bx * SK_BOX_COLS) / 8, g * SK_GROUP);
+        }
+    };
+
     if (role == 1) {
         // ------------------------------ loader (one thread) ------------------------------
         if (lane != 0) return;
         const uint64_t stream_policy = l2_policy_evict_first();
-        UnitCursor cur(G0, V0, G1, V1, a.n_layers, half, a.split), pf = cur;
-        int issued = 0, prefetched = 0;
-        auto maps = [&](int l, int p, const CUtensorMap *&tmW, const CUtensorMap *&tmS, const CUtensorMap *&tmZ) {
-            const FusedLayer *Ly = a.layers + l;
-            tmW = p ? &Ly->w_d : &Ly->w_gu;
-            tmS = p ? &Ly->s_d : &Ly->s_gu;
-            tmZ = p ? &Ly->z_d : &Ly->z_gu;
-        };
-        // keep HBM streaming into L2 `lookahead` units ahead of the ring, across phase and layer
-        // boundaries: weights depend on nothing, so the stream does not stop while a phase waits
-        auto run_prefetch = [&]() {
-            while (pf.valid() && prefetched < issued + a.lookahead) {
-                const CUtensorMap *tmW, *tmS, *tmZ;
-                maps(pf.l, pf.p, tmW, tmS, tmZ);
-#pragma unroll
-                for (int bx = 0; bx < SK_STRIP / SK_BOX_COLS; ++bx)
-                    tma_prefetch_l2_2d(tmW, (pf.v * SK_STRIP + bx * SK_BOX_COLS) / 8, pf.g * SK_GROUP);
-                pf.next();
-                ++prefetched;
-            }
-        };
-        auto acquire_slot = [&](int &slot) -> bool {  // slot of unit number `issued`, once the consumers released it
+        int issued = 0;  // ring turns so far (units and end-of-phase markers)
+        auto acquire_slot = [&](int &slot) -> bool {  // slot of ring turn `issued`, once its previous turn was released
             slot = issued % SK_STAGES;
             const int round = issued / SK_STAGES;
             if (round > 0 && !mbar_wait_bounded(empty_bar(slot), (round - 1) & 1, a.wait_limit)) {
@@ -325,169 +322,203 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
             }
             return true;
         };
-        auto load_weights = [&](int slot, const UnitCursor &u) {
+        auto put_desc = [&](int slot, int l, int p, int v, int g) {
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(desc_addr(slot)), "r"(l), "r"(p), "r"(v), "r"(g) : "memory");
+        };
+        auto load_weights = [&](int slot, int l, int p, int v, int g) {
             const CUtensorMap *tmW, *tmS, *tmZ;
-            maps(u.l, u.p, tmW, tmS, tmZ);
+            maps(l, p, tmW, tmS, tmZ);
             const uint32_t st = smem_base + slot * SK_STAGE_BYTES;
             const uint32_t bar = full_bar(slot);
-            mbar_expect_tx(bar, u.p ? SK_TX_BYTES : SK_TX_BYTES + FF_GAMMA_BYTES);
+            put_desc(slot, l, p, v, g);  // before the arrive below, whose release makes it visible with the data
+            mbar_expect_tx(bar, p ? SK_TX_BYTES : SK_TX_BYTES + FF_GAMMA_BYTES);
+            if (p ? a.w3d_d : a.w3d_gu) {
+                tma_load_3d_hint(st, tmW, 0, g * SK_GROUP, v * (SK_STRIP / SK_BOX_COLS), bar, stream_policy);
+            } else {
 #pragma unroll
-            for (int bx = 0; bx < SK_STRIP / SK_BOX_COLS; ++bx)
-                tma_load_2d_hint(st + bx * SK_WBOX_BYTES, tmW, (u.v * SK_STRIP + bx * SK_BOX_COLS) / 8, u.g * SK_GROUP, bar,
-                                 stream_policy);
-#pragma unroll
-            for (int bx = 0; bx < SK_STRIP / SK_BOX_COLS; ++bx)
-                tma_load_2d(st + SK_OFF_S + bx * SK_BOX_COLS * 2, tmS, u.v * SK_STRIP + bx * SK_BOX_COLS, u.g, bar);
-            tma_load_2d(st + SK_OFF_Z, tmZ, u.v * (SK_STRIP / 8), u.g, bar);
+                for (int bx = 0; bx < SK_STRIP / SK_BOX_COLS; ++bx)
+                    tma_load_2d_hint(st + bx * SK_WBOX_BYTES, tmW, (v * SK_STRIP + bx * SK_BOX_COLS) / 8, g * SK_GROUP, bar,
+                                     stream_policy);
+            }
+            tma_load_2d(st + SK_OFF_S, tmS, v * (SK_STRIP / 2), g, bar);  // the scales as 32-bit pairs: 512 in one box
+            tma_load_2d(st + SK_OFF_Z, tmZ, v * (SK_STRIP / 8), g, bar);
         };
-        auto load_activations = [&](int slot, const UnitCursor &u) {
+        auto load_activations = [&](int slot, int l, int p, int g) {
             const uint32_t st = smem_base + slot * SK_STAGE_BYTES;
             const uint32_t bar = full_bar(slot);
             // down: the SwiGLU output as it is; gate/up: the raw hidden state and the norm weights
             // of the unit's k range, which the normaliser warp turns into activations in place
-            const CUtensorMap *tmX = u.p ? &tmXi : (u.l == 0 ? &tmH0 : &tmH);
-            tma_load_2d(st + SK_OFF_X, tmX, u.g * SK_GROUP, 0, bar);
-            tma_load_2d(st + SK_OFF_X + 1024, tmX, u.g * SK_GROUP + 64, 0, bar);
-            if (!u.p) bulk_load_1d(st + FF_OFF_GAMMA, a.layers[u.l].gamma + (size_t)u.g * SK_GROUP, FF_GAMMA_BYTES, bar);
+            const CUtensorMap *tmX = p ? &tmXi : (l == 0 ? &tmH0 : &tmH);
+            tma_load_3d(st + SK_OFF_X, tmX, 0, 0, g * (SK_GROUP / 64), bar);  // both [8 x 64] boxes of the group
+            if (!p) bulk_load_1d(st + FF_OFF_GAMMA, a.layers[l].gamma + (size_t)g * SK_GROUP, FF_GAMMA_BYTES, bar);
         };
-        while (cur.valid()) {
-            // a phase begins: the weights of its first units do not depend on the previous phase
-            const int l = cur.l, p = cur.p;
-            const int n_units = cur.left;
-            const int n_first = n_units < SK_STAGES ? n_units : SK_STAGES;
-            int slots[SK_STAGES];
-            UnitCursor first = cur;
-            for (int i = 0; i < n_first; ++i) {
-                run_prefetch();
-                if (!acquire_slot(slots[i])) return;
-                load_weights(slots[i], cur);
-                ++issued;
-                cur.next();
-            }
-            // the phase's activations exist once every sub-strip of the previous phase is finalised
-            // (tensor parallel: a down sub-strip is finalised by the warp that added up all ranks' sums)
-            const int target = p ? (l + 1) * V0 * SK_CONSUMER_WARPS : B + l * V1 * SK_CONSUMER_WARPS;
-            if (!wait_count(p ? done_gu : done_d, target, a.wait_limit)) {
-                atomicExch(a.err_flag, 3);
-                return;
-            }
-            fence_proxy_async_all();  // generic-proxy writes of the previous phase before the tensor copies read them
-            for (int i = 0; i < n_first; ++i) {
-                load_activations(slots[i], first);
-                first.next();
-            }
-            for (int i = n_first; i < n_units; ++i) {
-                run_prefetch();
+        for (int l = 0; l < a.n_layers; ++l) {
+            for (int p = 0; p < 2; ++p) {
+                const int G = p ? G1 : G0;
+                const int lo = p ? lo1 : lo0, hi = p ? hi1 : hi0;
+                unsigned int *word = claim_words + 2 * l + p;
+                int mine = 0;  // units this half has taken in this phase
+                bool more = true;
+                // a phase begins: the weights of its first units do not depend on the previous phase
+                int slots[SK_STAGES], gs[SK_STAGES], n_first = 0;
+                while (n_first < SK_STAGES && (more = ff_claim(word, hi - lo))) {
+                    const int u = unit_of(lo, hi, mine), v = u / G, g = u - v * G;
+                    if (!acquire_slot(slots[n_first])) return;
+                    load_weights(slots[n_first], l, p, v, g);
+                    gs[n_first++] = g;
+                    ++issued;
+                    ++mine;
+                }
+                // the phase's activations exist once every sub-strip of the previous phase is finalised
+                // (tensor parallel: a down sub-strip is finalised by the warp that added up all ranks' sums)
+                const int target = p ? (l + 1) * V0 * SK_CONSUMER_WARPS : B + l * V1 * SK_CONSUMER_WARPS;
+                if (!wait_count(p ? done_gu : done_d, target, a.wait_limit)) {
+                    atomicExch(a.err_flag, 3);
+                    return;
+                }
+                fence_proxy_async_all();  // generic-proxy writes of the previous phase before the tensor copies read them
+                for (int i = 0; i < n_first; ++i) load_activations(slots[i], l, p, gs[i]);
+                while (more && (more = ff_claim(word, hi - lo))) {
+                    const int u = unit_of(lo, hi, mine), v = u / G, g = u - v * G;
+                    int slot;
+                    if (!acquire_slot(slot)) return;
+                    load_weights(slot, l, p, v, g);
+                    load_activations(slot, l, p, g);
+                    ++issued;
+                    ++mine;
+                }
+                // the range is used up: one ring turn tells this half's warps that the phase is over for them
                 int slot;
                 if (!acquire_slot(slot)) return;
-                load_weights(slot, cur);
-                load_activations(slot, cur);
+                put_desc(slot, l, p | FF_END, 0, 0);
+                mbar_arrive(full_bar(slot));
                 ++issued;
-                cur.next();
             }
         }
         return;
     }
 
+    auto read_desc = [&](int slot, int &l, int &p, int &v, int &g) {
+        const uint4 d = lds128(desc_addr(slot));
+        l = (int)d.x;
+        p = (int)d.y;
+        v = (int)d.z;
+        g = (int)d.w;
+    };
+
     if (role == 2) {
         // ------------------------------ normaliser warp ------------------------------
-        // RMSNorm of a gate/up unit's 8 x 128 hidden values, in place in the stage: lane (r, q4)
-        // takes 16-byte chunks q4, q4 + 4, q4 + 8, q4 + 12 of batch row r where the tensor copy of
-        // the 128B-swizzled [8 x 64] box pair put them; bf16 rounding, then the fp16 form
+        // Follows the half's ring turn by turn.  RMSNorm of a gate/up unit's 8 x 128 hidden values, in place in
+        // the stage: lane (r, q4) takes 16-byte chunks q4, q4 + 4, q4 + 8, q4 + 12 of batch row r where the
+        // tensor copy of the 128B-swizzled [8 x 64] box pair put them; bf16 rounding, then the fp16 form
         const int r = lane >> 2, q4 = lane & 3;
-        int slot = 0, round = 0;
-        for (int l = 0; l < a.n_layers; ++l) {
-            for (int p = 0; p < 2; ++p) {
-                long long u0, u1;
-                ff_range((long long)(p ? V1 : V0) * (p ? G1 : G0), half, a.split, u0, u1);
-                const int n_units = (int)(u1 - u0);
-                float rstd = 0.f;
-                for (int i = 0; i < n_units; ++i) {
-                    // every unit's barrier is waited for, also those of down units that need no work
-                    // here: a parity wait is only meaningful one completion ahead
-                    if (!mbar_wait_bounded(full_bar(slot), round & 1, a.wait_limit)) {
-                        if (lane == 0) atomicExch(a.err_flag, 4);
-                        return;
-                    }
-                    if (!p) {
-                        if (i == 0 && r < B) {  // complete: the loader passed the phase barrier before it requested h
-                            const float total = __ldcg(sumsq + (size_t)l * 8 + r);
-                            rstd = (float)(1.0 / sqrt((double)(total / (float)H) + (double)a.eps));
-                        }
-                        const uint32_t st = smem_base + slot * SK_STAGE_BYTES;
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const int ch = q4 + 4 * j;
-                            const uint32_t addr = st + SK_OFF_X + (ch >> 3) * 1024 + r * 128 + (((ch & 7) ^ r) << 4);
-                            const uint4 hv = lds128(addr), gv = lds128(st + FF_OFF_GAMMA + ch * 16);
-                            const uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w}, gw[4] = {gv.x, gv.y, gv.z, gv.w};
-                            uint32_t o[4];
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const float lo = bf16_bits_to_f32(f32_to_bf16_bits((bf16x2_lo(hw[e]) * rstd) * bf16x2_lo(gw[e])));
-                                const float hi = bf16_bits_to_f32(f32_to_bf16_bits((bf16x2_hi(hw[e]) * rstd) * bf16x2_hi(gw[e])));
-                                o[e] = (uint32_t)bf16_value_to_f16_bits(lo) | ((uint32_t)bf16_value_to_f16_bits(hi) << 16);
-                            }
-                            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]),
-                                         "r"(o[3])
-                                         : "memory");
-                        }
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(xready_bar(slot));
-                    }
-                    if (++slot == SK_STAGES) { slot = 0; ++round; }
-                }
-                if (tp && p) {
-                    // ---- this layer's exchange: sub-strips gw, gw + W, ... of the hidden state are ended here ----
-                    const unsigned int tag = exch0 + (unsigned int)l + 1u;
-                    const int sl = (int)((exch0 + (unsigned int)l) & 1u);
-                    const int n_sub = V1 * SK_CONSUMER_WARPS;
-                    const uint16_t *hres = l == 0 ? a.x : a.out;
-                    const int W = 2 * (int)gridDim.x, gw = 2 * (int)blockIdx.x + half;
-                    for (int sub = gw; sub < n_sub; sub += W) {
-                        const SkLane sg(sub % SK_CONSUMER_WARPS, lane);
-                        const int sb = 2 * sg.t4 + sg.odd, n = (sub / SK_CONSUMER_WARPS) * SK_STRIP + sg.colw;
-                        uint4 rres[2];
-                        ff_load_residual(rres, hres, B, H, n, sb);
-                        float own[2][8];
-#pragma unroll
-                        for (int h = 0; h < 2; ++h)
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) own[h][i] = 0.f;
-                        bool good = true;
-                        const long long t0 = clock64();
-                        for (int rk = 0; rk < a.tp_n && good; ++rk) {
-                            const unsigned long long *src =
-                                a.ll_recv[sl][a.tp_rank] + ((size_t)rk * n_sub + sub) * FF_LL_WORDS + lane;
-                            unsigned long long w[16];
-                            bool all;
-                            do {
-#pragma unroll
-                                for (int i = 0; i < 16; ++i) w[i] = ld_relaxed_sys_u64(src + i * 32);
-                                all = true;
-#pragma unroll
-                                for (int i = 0; i < 16; ++i) all = all && (unsigned int)(w[i] >> 32) == tag;
-                                all = __all_sync(0xffffffffu, all);
-                                // the lanes must leave together: one lane's clock decides for the warp
-                                const bool late = __shfl_sync(0xffffffffu, clock64() - t0 > a.wait_limit ? 1 : 0, 0) != 0;
-                                if (!all && late) good = false;
-                            } while (!all && good);
-                            if (good) {
-#pragma unroll
-                                for (int i = 0; i < 16; ++i) own[i >> 3][i & 7] += __uint_as_float((unsigned int)w[i]);
-                            }
-                        }
-                        if (!good) {
-                            if (lane == 0) atomicExch(a.err_flag, 6);
-                            return;
-                        }
-                        ff_down_epilogue(own, rres, a.out, sumsq + (size_t)(l + 1) * 8, B, H, n, sb, lane);
-                        __threadfence();
-                        __syncwarp();
-                        if (lane == 0) atomicAdd(done_d, 1);
-                    }
+        int rstd_layer = -1;
+        float rstd = 0.f;
+        for (int turn = 0;; ++turn) {
+            const int slot = turn % SK_STAGES;
+            if (!mbar_wait_bounded(full_bar(slot), (turn / SK_STAGES) & 1, a.wait_limit)) {
+                if (lane == 0) atomicExch(a.err_flag, 4);
+                return;
+            }
+            int l, p, v, g;
+            read_desc(slot, l, p, v, g);
+            if (lane == 0 && a.lookahead > 0) {
+                // keep L2 `lookahead` units ahead of what this half is loading: its own direction inside the
+                // phase, and at the end of a phase its first units of the next one
+                if (p & FF_END) {
+                    const int nl = (p & 1) ? l + 1 : l, np = (p & 1) ^ 1;
+                    if (nl < a.n_layers)
+                        for (int c = 0; c < a.lookahead && c < (np ? lim1 : lim0); ++c) prefetch_unit(nl, np, c);
+                } else {
+                    const int u = v * (p ? G1 : G0) + g;
+                    const int c = (p ? (half ? hi1 - 1 - u : u - lo1) : (half ? hi0 - 1 - u : u - lo0)) + SK_STAGES - 1 + a.lookahead;
+                    if (c < (p ? lim1 : lim0)) prefetch_unit(l, p, c);
                 }
             }
+            if (p == 0) {
+                if (rstd_layer != l) {  // complete: the loader passed the phase barrier before it requested h
+                    rstd_layer = l;
+                    if (r < B) {
+                        const float total = __ldcg(sumsq + (size_t)l * 8 + r);
+                        rstd = (float)(1.0 / sqrt((double)(total / (float)H) + (double)a.eps));
+                    }
+                }
+                const uint32_t st = smem_base + slot * SK_STAGE_BYTES;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int ch = q4 + 4 * j;
+                    const uint32_t addr = st + SK_OFF_X + (ch >> 3) * 1024 + r * 128 + (((ch & 7) ^ r) << 4);
+                    const uint4 hv = lds128(addr), gv = lds128(st + FF_OFF_GAMMA + ch * 16);
+                    const uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w}, gw[4] = {gv.x, gv.y, gv.z, gv.w};
+                    uint32_t o[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float lo = bf16_bits_to_f32(f32_to_bf16_bits((bf16x2_lo(hw[e]) * rstd) * bf16x2_lo(gw[e])));
+                        const float hi = bf16_bits_to_f32(f32_to_bf16_bits((bf16x2_hi(hw[e]) * rstd) * bf16x2_hi(gw[e])));
+                        o[e] = (uint32_t)bf16_value_to_f16_bits(lo) | ((uint32_t)bf16_value_to_f16_bits(hi) << 16);
+                    }
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]),
+                                 "r"(o[3])
+                                 : "memory");
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(xready_bar(slot));
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty_bar(slot));  // the descriptor has been read: the turn may be reused
+            if (!(p & FF_END)) continue;
+            p &= 1;
+            if (tp && p) {
+                // ---- this layer's exchange: sub-strips gw, gw + W, ... of the hidden state are ended here ----
+                const unsigned int tag = exch0 + (unsigned int)l + 1u;
+                const int sl = (int)((exch0 + (unsigned int)l) & 1u);
+                const int n_sub = V1 * SK_CONSUMER_WARPS;
+                const uint16_t *hres = l == 0 ? a.x : a.out;
+                const int W = 2 * (int)gridDim.x, gw = 2 * (int)blockIdx.x + half;
+                for (int sub = gw; sub < n_sub; sub += W) {
+                    const SkLane sg(sub % SK_CONSUMER_WARPS, lane);
+                    const int sb = 2 * sg.t4 + sg.odd, n = (sub / SK_CONSUMER_WARPS) * SK_STRIP + sg.colw;
+                    uint4 rres[2];
+                    ff_load_residual(rres, hres, B, H, n, sb);
+                    float own[2][8];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) own[h][i] = 0.f;
+                    bool good = true;
+                    const long long t0 = clock64();
+                    for (int rk = 0; rk < a.tp_n && good; ++rk) {
+                        const unsigned long long *src =
+                            a.ll_recv[sl][a.tp_rank] + ((size_t)rk * n_sub + sub) * FF_LL_WORDS + lane;
+                        unsigned long long w[16];
+                        bool all;
+                        do {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) w[i] = ld_relaxed_sys_u64(src + i * 32);
+                            all = true;
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) all = all && (unsigned int)(w[i] >> 32) == tag;
+                            all = __all_sync(0xffffffffu, all);
+                            // the lanes must leave together: one lane's clock decides for the warp
+                            const bool late = __shfl_sync(0xffffffffu, clock64() - t0 > a.wait_limit ? 1 : 0, 0) != 0;
+                            if (!all && late) good = false;
+                        } while (!all && good);
+                        if (good) {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) own[i >> 3][i & 7] += __uint_as_float((unsigned int)w[i]);
+                        }
+                    }
+                    if (!good) {
+                        if (lane == 0) atomicExch(a.err_flag, 6);
+                        return;
+                    }
+                    ff_down_epilogue(own, rres, a.out, sumsq + (size_t)(l + 1) * 8, B, H, n, sb, lane);
+                    __threadfence();
+                    __syncwarp();
+                    if (lane == 0) atomicAdd(done_d, 1);
+                }
+            }
+            if (p && l == a.n_layers - 1) break;
         }
         if (tp && blockIdx.x == 0 && half == 0 && lane == 0) *a.epoch = exch0 / (unsigned int)a.n_layers + 1u;
         return;
@@ -496,98 +527,104 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
     // ------------------------------ consumers ------------------------------
     const int cw = warp % SK_CONSUMER_WARPS;  // this warp's 64 columns of every strip
     const SkLane geo(cw, lane);
-    const int g8 = geo.g8, t4 = geo.t4, odd = geo.odd, colw = geo.colw;
+    const int t4 = geo.t4, odd = geo.odd, colw = geo.colw;
     const int b = 2 * t4 + odd;  // batch row of this lane after the lane exchange
     bool failed = false;
-    int slot = 0, round = 0;
     uint32_t xr_parity = 0;  // bit s: parity of the next completion of xready_bar(s) (only gate/up units use it)
+    float res[4][4];
+    int cur_l = 0, cur_p = 0, cur_v = -1, seg_groups = 0;  // strip being accumulated, k groups of it added so far
 
-    for (int l = 0; l < a.n_layers; ++l) {
-        for (int p = 0; p < 2; ++p) {
-            const int G = p ? G1 : G0, N = p ? H : 2 * I;
-            long long u0, u1;
-            ff_range((long long)(p ? V1 : V0) * G, half, a.split, u0, u1);
-            const int n_units = (int)(u1 - u0);
-            const uint16_t *residual = l == 0 ? a.x : a.out;
-            float res[4][4];
-            int cur_v = -1, seg_groups = 0;  // strip being accumulated, k groups of it added so far
-
-            // Finish the strip segment this warp has been accumulating (strip cur_v).
-            auto flush = [&]() {
-                const int v = cur_v;
-                float own[2][8];
-                sk_lane_exchange(res, odd, own);
-                const int n = v * SK_STRIP + colw;
-                // a strip shared with other halves: value and progress travel in one 64-bit atomic per sum; the warp
-                // whose add completes the count has the total (gate/up and down strips use separate accumulators)
-                if (seg_groups != G &&
-                    !sk_handover(a.accum + ((size_t)((p ? V0 : 0) + v) * SK_CONSUMER_WARPS + cw) * SK_ACC_WORDS, own, seg_groups, G,
-                                 lane, a.wait_limit, a.err_flag))
-                    return;
-                if (failed) return;
-                if (!p) {
-                    sk_epilogue<EPI_SWIGLU>(own, nullptr, a.inter, B, N, n, b, 1);
-                } else if (tp) {
-                    // this rank's sums of the sub-strip go to every rank, value and tag in one 8-byte word; the
-                    // warp that collects the sub-strip on each rank ends it
-                    const unsigned long long tag = (unsigned long long)(exch0 + (unsigned int)l + 1u) << 32;
-                    const int sl = (int)((exch0 + (unsigned int)l) & 1u);
-                    const size_t w0 = ((size_t)a.tp_rank * (V1 * SK_CONSUMER_WARPS) + v * SK_CONSUMER_WARPS + cw) * FF_LL_WORDS + lane;
-                    for (int rk = 0; rk < a.tp_n; ++rk) {
-                        unsigned long long *dst = a.ll_recv[sl][(a.tp_rank + rk) % a.tp_n] + w0;  // own rank first, then round the ring
+    // Hand over what this warp accumulated for strip cur_v of phase (cur_l, cur_p).
+    auto flush = [&]() {
+        const int l = cur_l, p = cur_p, v = cur_v;
+        const int G = p ? G1 : G0, N = p ? H : 2 * I;
+        float own[2][8];
+        sk_lane_exchange(res, odd, own);
+        const int n = v * SK_STRIP + colw;
+        // a strip shared with other halves: value and progress travel in one 64-bit atomic per sum; the warp
+        // whose add completes the count has the total (gate/up and down strips use separate accumulators)
+        if (seg_groups != G &&
+            !sk_handover(a.accum + ((size_t)((p ? V0 : 0) + v) * SK_CONSUMER_WARPS + cw) * SK_ACC_WORDS, own, seg_groups, G, lane,
+                         a.wait_limit, a.err_flag))
+            return;
+        if (failed) return;
+        if (!p) {
+            sk_epilogue<EPI_SWIGLU>(own, nullptr, a.inter, B, N, n, b, 1);
+        } else if (tp) {
+            // this rank's sums of the sub-strip go to every rank, value and tag in one 8-byte word; the
+            // warp that collects the sub-strip on each rank ends it
+            const unsigned long long tag = (unsigned long long)(exch0 + (unsigned int)l + 1u) << 32;
+            const int sl = (int)((exch0 + (unsigned int)l) & 1u);
+            const size_t w0 = ((size_t)a.tp_rank * (V1 * SK_CONSUMER_WARPS) + v * SK_CONSUMER_WARPS + cw) * FF_LL_WORDS + lane;
+            for (int rk = 0; rk < a.tp_n; ++rk) {
+                unsigned long long *dst = a.ll_recv[sl][(a.tp_rank + rk) % a.tp_n] + w0;  // own rank first, then round the ring
 #pragma unroll
-                        for (int i = 0; i < 16; ++i)
-                            st_relaxed_sys_u64(dst + i * 32, tag | (unsigned long long)__float_as_uint(own[i >> 3][i & 7]));
-                    }
-                    return;
-                } else {
-                    // hidden state: bf16(sum + residual), and its squares for the next layer's RMSNorm
-                    uint4 rres[2];
-                    ff_load_residual(rres, residual, B, N, n, b);
-                    ff_down_epilogue(own, rres, a.out, sumsq + (size_t)(l + 1) * 8, B, N, n, b, lane);
-                }
-                __threadfence();
-                __syncwarp();
-                if (lane == 0) atomicAdd(p ? done_d : done_gu, 1);
-            };
-
-            int v = n_units > 0 ? (int)(u0 / G) : 0, g = n_units > 0 ? (int)(u0 % G) : 0;
-            for (int i = 0; i < n_units; ++i) {
-                if (v != cur_v) {
-                    if (cur_v >= 0) flush();
-                    cur_v = v;
-                    seg_groups = 0;
-#pragma unroll
-                    for (int e = 0; e < 4; ++e)
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) res[e][q] = 0.f;
-                }
-                ++seg_groups;
-                if (!failed) {
-                    bool ok = mbar_wait_bounded(full_bar(slot), round & 1, a.wait_limit);
-                    if (ok && !p) ok = mbar_wait_bounded(xready_bar(slot), (xr_parity >> slot) & 1u, a.wait_limit);
-                    if (!ok) {
-                        failed = true;
-                        if (lane == 0) atomicExch(a.err_flag, 2);
-                    }
-                }
-                if (!p) xr_parity ^= 1u << slot;
-                if (!failed) sk_consume_unit<true>(smem_base + slot * SK_STAGE_BYTES, geo, res, empty_bar(slot), lane);
-                if (++g == G) { g = 0; ++v; }
-                if (++slot == SK_STAGES) { slot = 0; ++round; }
+                for (int i = 0; i < 16; ++i)
+                    st_relaxed_sys_u64(dst + i * 32, tag | (unsigned long long)__float_as_uint(own[i >> 3][i & 7]));
             }
-            if (cur_v >= 0) flush();
+            return;
+        } else {
+            // hidden state: bf16(sum + residual), and its squares for the next layer's RMSNorm
+            uint4 rres[2];
+            ff_load_residual(rres, l == 0 ? a.x : a.out, B, N, n, b);
+            ff_down_epilogue(own, rres, a.out, sumsq + (size_t)(l + 1) * 8, B, N, n, b, lane);
         }
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) atomicAdd(p ? done_d : done_gu, 1);
+    };
+
+    for (int turn = 0;; ++turn) {
+        const int slot = turn % SK_STAGES;
+        int l = 0, p = 0, v = 0, g = 0;
+        if (!failed && !mbar_wait_bounded(full_bar(slot), (turn / SK_STAGES) & 1, a.wait_limit)) {
+            failed = true;
+            if (lane == 0) atomicExch(a.err_flag, 2);
+        }
+        if (failed) break;  // nothing more can be trusted: leave (the other warps' waits run out too)
+        read_desc(slot, l, p, v, g);
+        if (p & FF_END) {
+            // the half's last unit of this phase has been consumed
+            if (cur_v >= 0) flush();
+            cur_v = -1;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty_bar(slot));
+            if ((p & 1) && l == a.n_layers - 1) break;
+            continue;
+        }
+        if (cur_v >= 0 && v != cur_v) {  // units of one phase come strip by strip
+            flush();
+            cur_v = -1;
+        }
+        if (cur_v < 0) {
+            cur_l = l;
+            cur_p = p;
+            cur_v = v;
+            seg_groups = 0;
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) res[e][q] = 0.f;
+        }
+        ++seg_groups;
+        if (!p) {
+            if (!mbar_wait_bounded(xready_bar(slot), (xr_parity >> slot) & 1u, a.wait_limit)) {
+                failed = true;
+                if (lane == 0) atomicExch(a.err_flag, 2);
+                break;
+            }
+            xr_parity ^= 1u << slot;
+        }
+        sk_consume_unit<true>(smem_base + slot * SK_STAGE_BYTES, geo, res, empty_bar(slot), lane);
     }
 }
 
 // ---------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------
-static int g_ffn_lookahead = 2;
-static int g_ffn_split = 512;
+static int g_ffn_lookahead = 0;  // measured: with the halves sharing an SM's units dynamically the L2 look-ahead no longer pays
 void ffn_fused_set_lookahead(int units) { g_ffn_lookahead = units < 0 ? 0 : (units > 64 ? 64 : units); }
-void ffn_fused_set_split(int per_1024) { g_ffn_split = per_1024 < 0 ? 0 : (per_1024 > 1024 ? 1024 : per_1024); }
+void ffn_fused_set_split(int per_1024) { (void)per_1024; }  // the halves of a CTA share its units dynamically
 
 size_t ffn_fused_plan_bytes(int n_layers) { return (size_t)(n_layers > 0 ? n_layers : 0) * sizeof(FusedLayer); }
 
@@ -626,20 +663,25 @@ int ffn_fused_plan(void *plan_dev, size_t plan_bytes, int n_layers, const int32_
                     "ffn_stack_plan: pointers of layer %d must be 16-byte aligned", l);
         FusedLayer &L = host[(size_t)l];
         int rc;
-        if ((rc = encode_tensor_map_2d(&L.w_gu, CU_TENSOR_MAP_DATA_TYPE_INT32, qw_gateup[l], nb0, H, (uint64_t)nb0 * 4, 32,
-                                       SK_GROUP, CU_TENSOR_MAP_SWIZZLE_128B)))
-            return rc;
-        if ((rc = encode_tensor_map_2d(&L.s_gu, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, s_gateup[l], N0, G0, (uint64_t)N0 * 2,
-                                       SK_BOX_COLS, 1, CU_TENSOR_MAP_SWIZZLE_NONE)))
+        // weights: where the columns are whole 256-column boxes, a 3-D view (32 words, k rows, boxes) lets one copy
+        // fetch both boxes of a unit; scales as 32-bit pairs, so that a strip's 512 fit one box of 256 elements
+        auto weight_map = [&](CUtensorMap *m, const int32_t *qw, int nb, int K) {
+            if (nb % 32 == 0)
+                return encode_tensor_map_3d(m, CU_TENSOR_MAP_DATA_TYPE_INT32, qw, 32, K, nb / 32, (uint64_t)nb * 4, 128, 32,
+                                            SK_GROUP, SK_STRIP / SK_BOX_COLS, CU_TENSOR_MAP_SWIZZLE_128B);
+            return encode_tensor_map_2d(m, CU_TENSOR_MAP_DATA_TYPE_INT32, qw, nb, K, (uint64_t)nb * 4, 32, SK_GROUP,
+                                        CU_TENSOR_MAP_SWIZZLE_128B);
+        };
+        if ((rc = weight_map(&L.w_gu, qw_gateup[l], nb0, H))) return rc;
+        if ((rc = encode_tensor_map_2d(&L.s_gu, CU_TENSOR_MAP_DATA_TYPE_UINT32, s_gateup[l], N0 / 2, G0, (uint64_t)N0 * 2,
+                                       SK_STRIP / 2, 1, CU_TENSOR_MAP_SWIZZLE_NONE)))
             return rc;
         if ((rc = encode_tensor_map_2d(&L.z_gu, CU_TENSOR_MAP_DATA_TYPE_INT32, qz_gateup[l], nb0, G0, (uint64_t)nb0 * 4,
                                        SK_STRIP / 8, 1, CU_TENSOR_MAP_SWIZZLE_NONE)))
             return rc;
-        if ((rc = encode_tensor_map_2d(&L.w_d, CU_TENSOR_MAP_DATA_TYPE_INT32, qw_down[l], nb1, I, (uint64_t)nb1 * 4, 32,
-                                       SK_GROUP, CU_TENSOR_MAP_SWIZZLE_128B)))
-            return rc;
-        if ((rc = encode_tensor_map_2d(&L.s_d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, s_down[l], N1, G1, (uint64_t)N1 * 2,
-                                       SK_BOX_COLS, 1, CU_TENSOR_MAP_SWIZZLE_NONE)))
+        if ((rc = weight_map(&L.w_d, qw_down[l], nb1, I))) return rc;
+        if ((rc = encode_tensor_map_2d(&L.s_d, CU_TENSOR_MAP_DATA_TYPE_UINT32, s_down[l], N1 / 2, G1, (uint64_t)N1 * 2,
+                                       SK_STRIP / 2, 1, CU_TENSOR_MAP_SWIZZLE_NONE)))
             return rc;
         if ((rc = encode_tensor_map_2d(&L.z_d, CU_TENSOR_MAP_DATA_TYPE_INT32, qz_down[l], nb1, G1, (uint64_t)nb1 * 4,
                                        SK_STRIP / 8, 1, CU_TENSOR_MAP_SWIZZLE_NONE)))
@@ -664,15 +706,14 @@ int launch_ffn_fused(const void *plan_dev, int n_layers, const uint16_t *x, uint
 
     CUtensorMap tmXi, tmH0, tmH;
     int rc;
-    if ((rc = encode_tensor_map_2d(&tmXi, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, inter, I, B, (uint64_t)I * 2, 64, 8,
-                                   CU_TENSOR_MAP_SWIZZLE_128B)))
-        return rc;
-    if ((rc = encode_tensor_map_2d(&tmH0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x, H, B, (uint64_t)H * 2, 64, 8,
-                                   CU_TENSOR_MAP_SWIZZLE_128B)))
-        return rc;
-    if ((rc = encode_tensor_map_2d(&tmH, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, out, H, B, (uint64_t)H * 2, 64, 8,
-                                   CU_TENSOR_MAP_SWIZZLE_128B)))
-        return rc;
+    // activations [B, K] as (64 k, rows, K / 64 blocks): one copy fetches both [8 x 64] boxes of a group
+    auto act_map = [&](CUtensorMap *m, int dtype, const void *base, int K) {
+        return encode_tensor_map_3d(m, dtype, base, 64, (uint64_t)B, (uint64_t)K / 64, (uint64_t)K * 2, 128, 64, 8, 2,
+                                    CU_TENSOR_MAP_SWIZZLE_128B);
+    };
+    if ((rc = act_map(&tmXi, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, inter, I))) return rc;
+    if ((rc = act_map(&tmH0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x, H))) return rc;
+    if ((rc = act_map(&tmH, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, out, H))) return rc;
     const int G0 = H / SK_GROUP, V0 = (2 * I + SK_STRIP - 1) / SK_STRIP;
     const int G1 = I / SK_GROUP, V1 = (H + SK_STRIP - 1) / SK_STRIP;
     const long long U0 = (long long)V0 * G0, U1 = (long long)V1 * G1;
@@ -693,8 +734,9 @@ int launch_ffn_fused(const void *plan_dev, int n_layers, const uint16_t *x, uint
     a.H = H;
     a.I = I;
     a.lookahead = g_ffn_lookahead;
-    a.split = g_ffn_split;
     a.wait_limit = wait_limit_cycles();
+    a.w3d_gu = (2 * I / 8) % 32 == 0 ? 1 : 0;
+    a.w3d_d = (H / 8) % 32 == 0 ? 1 : 0;
     a.tp_n = 1;
     a.tp_rank = 0;
     a.epoch = nullptr;

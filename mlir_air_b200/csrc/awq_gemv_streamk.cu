@@ -211,22 +211,31 @@ static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
     return fn;
 }
 
-int encode_tensor_map_2d(CUtensorMap *map, int dtype, const void *base, uint64_t dim0, uint64_t dim1,
-                         uint64_t stride1_bytes, uint32_t box0, uint32_t box1, int swizzle) {
+// Tiled tensor map of rank 2 or 3 (dim2 == 0: rank 2).  dim0 is contiguous; stride1 / stride2 are the byte strides
+// of dim1 / dim2 (multiples of 16, in any order of size).
+int encode_tensor_map_3d(CUtensorMap *map, int dtype, const void *base, uint64_t dim0, uint64_t dim1, uint64_t dim2,
+                         uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1, uint32_t box2,
+                         int swizzle) {
     PFN_cuTensorMapEncodeTiled_v12000 fn = get_encode_fn();
     if (!fn) return set_error(AWQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-    cuuint64_t dims[2] = {dim0, dim1};
-    cuuint64_t strides[1] = {stride1_bytes};
-    cuuint32_t box[2] = {box0, box1};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, (CUtensorMapDataType)dtype, 2, const_cast<void *>(base), dims, strides, box, estr,
+    const int rank = dim2 ? 3 : 2;
+    cuuint64_t dims[3] = {dim0, dim1, dim2};
+    cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+    cuuint32_t box[3] = {box0, box1, box2};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, (CUtensorMapDataType)dtype, rank, const_cast<void *>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, (CUtensorMapSwizzle)swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
-        return set_error(AWQ_ERR_CUDA, "cuTensorMapEncodeTiled failed (CUresult %d; dims %llu x %llu, stride %llu)",
-                         (int)r, (unsigned long long)dim0, (unsigned long long)dim1,
-                         (unsigned long long)stride1_bytes);
+        return set_error(AWQ_ERR_CUDA, "cuTensorMapEncodeTiled failed (CUresult %d; dims %llu x %llu x %llu, strides %llu, %llu)",
+                         (int)r, (unsigned long long)dim0, (unsigned long long)dim1, (unsigned long long)dim2,
+                         (unsigned long long)stride1_bytes, (unsigned long long)stride2_bytes);
     return AWQ_OK;
+}
+
+int encode_tensor_map_2d(CUtensorMap *map, int dtype, const void *base, uint64_t dim0, uint64_t dim1,
+                         uint64_t stride1_bytes, uint32_t box0, uint32_t box1, int swizzle) {
+    return encode_tensor_map_3d(map, dtype, base, dim0, dim1, 0, stride1_bytes, 0, box0, box1, 1, swizzle);
 }
 
 // A rank signals once per EPI_F32_PUSH launch, when its last sub-strip is stored.

@@ -38,14 +38,15 @@ def test_static_weights_stay_resident_per_bo_key():
     spec = mv.build_module(64, 512, 128, 8, 256, 4, 32)
     kc = KernelCache(profiler=Profiler(True))
     kc.compile_and_cache("o_gemv", spec, {"instance_name": "matvec_int4_packed"})
+    from mlir_air_b200 import ops
     calls = {"n": 0}
-    real = backend.layouts.unpack_gemv_tiles
+    real = ops.repack_C_to_A  # the per-tile buffer is unpacked on the GPU (awq_b200_repack_C_to_B + _B_to_A)
 
     def counting(*a, **k):
         calls["n"] += 1
         return real(*a, **k)
 
-    backend.layouts.unpack_gemv_tiles = counting
+    ops.repack_C_to_A = counting
     try:
         out = np.zeros(64, bfloat16)
         for layer in range(2):
@@ -62,5 +63,5 @@ def test_static_weights_stay_resident_per_bo_key():
         kc.load_and_run("o_gemv", {}, g["packed"], g["B"], out, output_indices=[2])
         assert calls["n"] == 4
     finally:
-        backend.layouts.unpack_gemv_tiles = real
+        ops.repack_C_to_A = real
     assert "o_gemv: 8 calls" in kc.profiler.report()
