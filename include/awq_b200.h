@@ -51,8 +51,11 @@ int awq_b200_version(void);
 const char *awq_b200_last_error(void);
 
 /* 16-bit activation formats of the *_act entry points.  Public inputs and outputs are bf16; fp16
- * is the format activations take between the kernels of one FFN (exact for bf16-rounded values
- * inside the fp16 range), because the GEMV kernel multiplies fp16 activations fastest. */
+ * is the format activations take between the kernels of one FFN, because the GEMV kernel
+ * multiplies fp16 activations fastest.  A bf16 value converts to fp16 without loss when
+ * 2^-14 <= |x| <= 65504; smaller values land in fp16 subnormals (they keep 2^-24 absolute
+ * resolution and reach zero below 2^-25), larger ones become infinities, which surface as an
+ * AWQ_ERR_UNSUPPORTED from the next *_check call (use awq_b200_set_decode_kernel(3) then). */
 #define AWQ_ACT_BF16 0
 #define AWQ_ACT_F16 1
 
@@ -72,9 +75,10 @@ int awq_b200_set_decode_kernel(int mode);
  * ERT_CMD_STATE_COMPLETED (python/air/backend/xrt.py:204-218). */
 int awq_b200_set_wait_limit(long long cycles);
 
-/* Split-K partial sums of the stream-K decode kernel are combined with f32 atomic adds by
- * default (fastest; the last bits of a result can differ between runs because the order of the
- * adds is not fixed).  on = 1 sums them in a fixed order instead: bit-reproducible, slower. */
+/* Kept for compatibility: split-K partial sums are handed over as fixed-point integers (2^-20
+ * resolution, |partial sum| < 8.38e6, beyond which the next *_check call reports
+ * AWQ_ERR_UNSUPPORTED), and integer addition does not depend on the order of the adds, so results
+ * are bit-reproducible whatever this is set to. */
 int awq_b200_set_deterministic(int on);
 
 /* ---- AWQ dequant --------------------------------------------------------------
@@ -252,16 +256,15 @@ int awq_b200_tp_reduce_add_rmsnorm_act(const uint16_t *h, const void *const *pee
  * decode: `inter` is 16-bit [B, I] scratch; `workspace` holds at least
  * awq_b200_ffn_stack_workspace_bytes(n_layers) bytes prepared by awq_b200_workspace_init.
  * x may alias out.  All CTAs of the launch wait for one another on counters in the workspace,
- * so the stream must be the only user of that workspace, and the launch takes two CTAs per
- * SM: run nothing else on the device that could keep them from becoming resident together.
- * Split-K sums use f32 atomics (run-to-run differences in the last bits, like the default
- * decode kernel).  Needs group 128, H % 128 == 0, I % 128 == 0; AWQ_ERR_UNSUPPORTED otherwise.
+ * so the stream must be the only user of that workspace, and the launch takes one CTA per SM
+ * with all of its shared memory (a cooperative launch: it fails at once, instead of timing out,
+ * where the CTAs cannot all be resident because something else holds SMs).
+ * Split-K sums are added as integers: results are bit-reproducible.  Needs group 128, H % 128 == 0, I % 128 == 0; AWQ_ERR_UNSUPPORTED otherwise.
  * Device-side waits are bounded; awq_b200_workspace_check reports a timeout. */
 /* Tuning of the stack kernel; a negative value leaves a setting as it is.
- * lookahead_units: 36 KB units per half-CTA that are prefetched into L2 ahead of the
- *   shared-memory ring (default 2, 0 = off, at most 64; 2 units on 148 SMs are 21 MB of L2).
- * split_per_1024: the kernel runs one CTA per SM made of two independent halves; the SM's units
- *   of a phase are cut between them at split / 1024 (default 512 = even). */
+ * lookahead_units: 36 KB units per half-CTA requested into L2 ahead of the shared-memory ring
+ *   (default 0 = off, at most 64).
+ * split_per_1024: ignored (the two halves of a CTA share the SM's units dynamically). */
 int awq_b200_set_ffn_stack_tuning(int lookahead_units, int split_per_1024);
 size_t awq_b200_ffn_stack_plan_bytes(int n_layers);
 size_t awq_b200_ffn_stack_workspace_bytes(int n_layers);

@@ -56,14 +56,18 @@ bool device_is_sm100() { return query_device().major == 10; }
 int status_of_device_flag(int flag) {
     if (flag == 4)
         return set_error(AWQ_ERR_UNSUPPORTED,
-                         "an activation exceeded the fp16 range (|x| > 65504) and was clamped; select the bf16 "
+                         "an activation exceeded the fp16 range (|x| > 65504) and became an infinity; select the bf16 "
                          "activation path with awq_b200_set_decode_kernel(3) and re-initialise the workspace");
+    if (flag == 7)
+        return set_error(AWQ_ERR_UNSUPPORTED,
+                         "a split-K partial sum was NaN, infinite or beyond the range of the fixed-point hand-over "
+                         "(|sum| < 8.38e6): the output is not valid; re-initialise the workspace");
     if (flag != 0)
         return set_error(AWQ_ERR_DEVICE_TIMEOUT,
                          "a device-side wait gave up (code %d: 1 = loader waiting for a free stage, 2 = consumer waiting "
                          "for data, 3 = loader waiting for the previous phase, 4 = normaliser waiting for data, 5 = waiting "
-                         "for the other ranks' arrival flags, 6 = waiting for the other ranks' partial sums); re-initialise "
-                         "the workspace", flag);
+                         "for the other ranks' arrival flags, 6 = waiting for the other ranks' partial sums, 8 = waiting for "
+                         "another contributor's split-K sums); re-initialise the workspace", flag);
     return AWQ_OK;
 }
 
@@ -234,20 +238,22 @@ extern "C" int awq_b200_ffn_decode_bf16(const uint16_t *x, const uint16_t *gamma
                                         void *workspace, size_t workspace_bytes, awq_stream_t stream) {
     AWQ_REQUIRE(inter, "ffn_decode: inter buffer is required");
     AWQ_REQUIRE(!gamma || normed, "ffn_decode: normed buffer is required with gamma");
-    // The intermediates travel between the three kernels as fp16 (exact for bf16-rounded values
-    // inside the fp16 range): that is the activation format the GEMV kernel multiplies fastest.
+    // The intermediates travel between the three kernels as fp16 (exact for bf16-rounded values with
+    // 2^-14 <= |x| <= 65504): that is the activation format the GEMV kernel multiplies fastest.
+    // (With awq_b200_set_decode_kernel(3) they stay bf16, for activations beyond the fp16 range.)
     int rc;
+    const int fmt = g_decode_mode.load() == 3 ? ACT_BF16 : ACT_F16;
     const void *xin = x;
     int xfmt = ACT_BF16;
     if (gamma) {
-        if ((rc = awq_b200_rmsnorm_act(x, gamma, eps, normed, ACT_F16, B, H, stream))) return rc;
+        if ((rc = awq_b200_rmsnorm_act(x, gamma, eps, normed, fmt, B, H, stream))) return rc;
         xin = normed;
-        xfmt = ACT_F16;
+        xfmt = fmt;
     }
-    if ((rc = awq_b200_gateup_swiglu_act(xin, xfmt, qw_gateup, qz_gateup, s_gateup, inter, ACT_F16, B, H, I, group_size,
+    if ((rc = awq_b200_gateup_swiglu_act(xin, xfmt, qw_gateup, qz_gateup, s_gateup, inter, fmt, B, H, I, group_size,
                                          workspace, workspace_bytes, stream)))
         return rc;
-    return awq_b200_gemv_act(inter, ACT_F16, qw_down, qz_down, s_down, residual, out, 0, B, I, H, group_size, workspace,
+    return awq_b200_gemv_act(inter, fmt, qw_down, qz_down, s_down, residual, out, 0, B, I, H, group_size, workspace,
                              workspace_bytes, stream);
 }
 

@@ -1,13 +1,15 @@
 // AWQ int4 -> bf16 dequant (layout A -> dense [K, N]) and the 1-D form of the dequant example.
 //
 // HBM-bound: 0.52 B read + 2 B written per weight.  One thread owns one packed word column
-// (8 output columns) for ROWS_PER_THREAD consecutive k of one group: the group's zero word and
-// eight scales are loaded once, each k costs one coalesced 4-byte load and one 16-byte store.
+// (8 output columns) for DQ_ROWS consecutive k.  All of its weight words are requested before
+// the first one is used (a 2048 x 2048 weight is a few microseconds of traffic, so what counts is
+// how many bytes are in flight, not how few instructions run); the group's zero word and eight
+// scales are loaded once per group, each k costs one coalesced 4-byte load and one 16-byte store.
 #include "awq_common.cuh"
 
 namespace awq {
 
-constexpr int DQ_ROWS_PER_THREAD = 16;
+constexpr int DQ_ROWS = 8;
 constexpr int DQ_THREADS = 128;
 
 // w = bf16_rne(float(q - z) * float(s)); the f32 product is exact, so this is the single
@@ -19,17 +21,22 @@ dequant_kernel(const uint32_t *__restrict__ qweight, const uint32_t *__restrict_
     const int nb = N >> 3;
     const int j = blockIdx.x * DQ_THREADS + threadIdx.x;  // packed word column
     if (j >= nb) return;
-    const int k_begin = blockIdx.y * DQ_ROWS_PER_THREAD;
-    const int k_end = min(K, k_begin + DQ_ROWS_PER_THREAD);
+    const int k_begin = blockIdx.y * DQ_ROWS;
+    uint32_t qw[DQ_ROWS];
+#pragma unroll
+    for (int r = 0; r < DQ_ROWS; ++r) qw[r] = k_begin + r < K ? __ldg(qweight + (size_t)(k_begin + r) * nb + j) : 0u;
     int cur_group = -1;
     float s[8];
     int z[8];
-    for (int k = k_begin; k < k_end; ++k) {
+#pragma unroll
+    for (int r = 0; r < DQ_ROWS; ++r) {
+        const int k = k_begin + r;
+        if (k >= K) break;
         const int g = k / group_size;
-        if (g != cur_group) {
+        if (g != cur_group) {  // at most once per thread when DQ_ROWS divides the group size
             cur_group = g;
-            const uint32_t zw = qzeros[(size_t)g * nb + j];
-            const uint4 sv = *reinterpret_cast<const uint4 *>(scales + (size_t)g * N + 8 * j);
+            const uint32_t zw = __ldg(qzeros + (size_t)g * nb + j);
+            const uint4 sv = __ldg(reinterpret_cast<const uint4 *>(scales + (size_t)g * N + 8 * j));
             const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
@@ -37,12 +44,11 @@ dequant_kernel(const uint32_t *__restrict__ qweight, const uint32_t *__restrict_
                 s[c] = (c & 1) ? bf16x2_hi(sw[c >> 1]) : bf16x2_lo(sw[c >> 1]);
             }
         }
-        const uint32_t qw = __ldg(qweight + (size_t)k * nb + j);
         uint32_t o[4];
 #pragma unroll
         for (int c = 0; c < 8; c += 2) {
-            const float w0 = (float)((int)awq_nibble(qw, c) - z[c]) * s[c];
-            const float w1 = (float)((int)awq_nibble(qw, c + 1) - z[c + 1]) * s[c + 1];
+            const float w0 = (float)((int)awq_nibble(qw[r], c) - z[c]) * s[c];
+            const float w1 = (float)((int)awq_nibble(qw[r], c + 1) - z[c + 1]) * s[c + 1];
             o[c >> 1] = pack_bf16x2(w0, w1);
         }
         *reinterpret_cast<uint4 *>(out + (size_t)k * N + 8 * j) = make_uint4(o[0], o[1], o[2], o[3]);
@@ -79,7 +85,7 @@ extern "C" int awq_b200_dequant_bf16(const int32_t *qweight, const int32_t *qzer
     if (K == 0 || N == 0) return AWQ_OK;
     AWQ_REQUIRE(qweight && qzeros && scales && out, "dequant: null pointer");
     AWQ_REQUIRE(aligned16(scales) && aligned16(out), "dequant: scales/out must be 16-byte aligned");
-    dim3 grid((N / 8 + DQ_THREADS - 1) / DQ_THREADS, (K + DQ_ROWS_PER_THREAD - 1) / DQ_ROWS_PER_THREAD);
+    dim3 grid((N / 8 + DQ_THREADS - 1) / DQ_THREADS, (K + DQ_ROWS - 1) / DQ_ROWS);
     AWQ_REQUIRE(grid.y <= 65535u, "dequant: K (%d) too large", K);
     dequant_kernel<<<grid, DQ_THREADS, 0, as_stream(stream)>>>(
         reinterpret_cast<const uint32_t *>(qweight), reinterpret_cast<const uint32_t *>(qzeros), scales,

@@ -760,8 +760,19 @@ int launch_ffn_fused(const void *plan_dev, int n_layers, const uint16_t *x, uint
     a.state = reinterpret_cast<int *>(ws + FF_STATE_OFF);
     if ((rc = check_cuda(cudaMemsetAsync(ws + FF_STATE_OFF, 0, ff_state_bytes(n_layers), stream), "fused ffn: state reset")))
         return rc;
-    ffn_fused_kernel<<<ctas, FF_THREADS, FF_SMEM_BYTES, stream>>>(tmXi, tmH0, tmH, a);
-    return check_cuda(cudaGetLastError(), "fused ffn launch");
+    // Cooperative: the CTAs wait for one another, so they must all be resident.  With this attribute a launch
+    // that cannot place them all (another kernel holding SMs) fails at once instead of running into its waits.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ctas);
+    cfg.blockDim = dim3(FF_THREADS);
+    cfg.dynamicSmemBytes = FF_SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return check_cuda(cudaLaunchKernelEx(&cfg, ffn_fused_kernel, tmXi, tmH0, tmH, a), "fused ffn launch");
 }
 
 }  // namespace awq

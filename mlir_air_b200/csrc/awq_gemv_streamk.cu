@@ -183,7 +183,7 @@ gemv_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     if (cur_v >= 0) flush();
 }
 
-// x bf16 -> fp16 (values beyond the fp16 range are clamped and reported through the error flag)
+// x bf16 -> fp16 (a value beyond the fp16 range becomes an infinity and is reported through the error flag)
 __global__ void cvt_bf16_to_f16_kernel(const uint16_t *__restrict__ x, uint16_t *__restrict__ xh, size_t n,
                                        int *__restrict__ err_flag) {
     pdl_launch_dependents();

@@ -81,7 +81,7 @@ gemv_generic_kernel(const uint16_t *__restrict__ x, const uint32_t *__restrict__
                 const float other = __shfl_xor_sync(0xffffffffu, sum, 1);
                 if (bb < B && n < N && !(col & 1)) {
                     uint16_t o = swiglu_bits(sum, other);
-                    if (out_f16) o = __half_as_ushort(__float2half_rn(fminf(fmaxf(bf16_bits_to_f32(o), -65504.f), 65504.f)));
+                    if (out_f16) o = __half_as_ushort(__float2half_rn(bf16_bits_to_f32(o)));
                     reinterpret_cast<uint16_t *>(y_)[(size_t)bb * (N >> 1) + (n >> 1)] = o;
                 }
             } else if (bb < B && n < N) {
@@ -286,8 +286,8 @@ rmsnorm_kernel(const uint16_t *__restrict__ h, const float *__restrict__ partial
                 uint16_t lo = f32_to_bf16_bits((v[c][2 * e] * rstd) * bf16x2_lo(gw[e]));
                 uint16_t hi = f32_to_bf16_bits((v[c][2 * e + 1] * rstd) * bf16x2_hi(gw[e]));
                 if (normed_f16) {
-                    lo = __half_as_ushort(__float2half_rn(fminf(fmaxf(bf16_bits_to_f32(lo), -65504.f), 65504.f)));
-                    hi = __half_as_ushort(__float2half_rn(fminf(fmaxf(bf16_bits_to_f32(hi), -65504.f), 65504.f)));
+                    lo = __half_as_ushort(__float2half_rn(bf16_bits_to_f32(lo)));
+                    hi = __half_as_ushort(__float2half_rn(bf16_bits_to_f32(hi)));
                 }
                 o[e] = (uint32_t)lo | ((uint32_t)hi << 16);
             }
@@ -379,8 +379,8 @@ tp_reduce_add_rmsnorm_kernel(const uint16_t *__restrict__ h, const PeerPartials 
                     uint16_t lo = f32_to_bf16_bits((v[c][2 * e] * rstd) * bf16x2_lo(gw[e]));
                     uint16_t hi = f32_to_bf16_bits((v[c][2 * e + 1] * rstd) * bf16x2_hi(gw[e]));
                     if (normed_f16) {
-                        lo = __half_as_ushort(__float2half_rn(fminf(fmaxf(bf16_bits_to_f32(lo), -65504.f), 65504.f)));
-                        hi = __half_as_ushort(__float2half_rn(fminf(fmaxf(bf16_bits_to_f32(hi), -65504.f), 65504.f)));
+                        lo = __half_as_ushort(__float2half_rn(bf16_bits_to_f32(lo)));
+                        hi = __half_as_ushort(__float2half_rn(bf16_bits_to_f32(hi)));
                     }
                     o[e] = (uint32_t)lo | ((uint32_t)hi << 16);
                 }
@@ -559,6 +559,90 @@ linear_bf16_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__ 
     }
 }
 
+// The same product on the tensor cores, for more than a few rows (the GEMMs of the bf16 prefill FFN,
+// ffn_swiglu/prefill/ffn_kernels.cc:55-83): y[M, N] = x[M, K] @ W[N, K]^T, both operands K-major, so
+// x tiles are the A fragments and W tiles the B fragments of mma.sync.m16n8k16 as they lie.  64 x 64
+// output tile per CTA, four warps of 32 x 32, K in steps of 32 through a two-stage cp.async ring; rows
+// are padded to 80 bytes so that ldmatrix reads are free of bank conflicts.  A sibling path: it is
+// not tuned beyond that.
+constexpr int LT_BM = 64, LT_BN = 64, LT_BK = 32, LT_LD = LT_BK + 8;
+
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void *src, bool valid) {
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+
+__global__ void __launch_bounds__(128)
+linear_bf16_tc_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__ W, uint16_t *__restrict__ y, int M,
+                      int K, int N) {
+    __shared__ __align__(16) uint16_t As[2][LT_BM][LT_LD];
+    __shared__ __align__(16) uint16_t Bs[2][LT_BN][LT_LD];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int wm = warp >> 1, wn = warp & 1;
+    const int m0 = blockIdx.y * LT_BM, n0 = blockIdx.x * LT_BN;
+    const int n_kt = (K + LT_BK - 1) / LT_BK;
+
+    auto issue = [&](int kt, int buf) {
+        // 64 rows x four 16-byte chunks per matrix: two chunks of each per thread; rows and k beyond the
+        // matrices are filled with zeros
+#pragma unroll
+        for (int c = threadIdx.x; c < LT_BM * 4; c += 128) {
+            const int r = c >> 2, k = kt * LT_BK + (c & 3) * 8;
+            const bool va = m0 + r < M && k < K, vb = n0 + r < N && k < K;
+            cp_async16_zfill(smem_u32(&As[buf][r][(c & 3) * 8]), va ? x + (size_t)(m0 + r) * K + k : x, va);
+            cp_async16_zfill(smem_u32(&Bs[buf][r][(c & 3) * 8]), vb ? W + (size_t)(n0 + r) * K + k : W, vb);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    float acc[2][4][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
+
+    issue(0, 0);
+    for (int kt = 0; kt < n_kt; ++kt) {
+        const int buf = kt & 1;
+        if (kt + 1 < n_kt) {
+            issue(kt + 1, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < LT_BK; ks += 16) {
+            uint32_t af[2][4], bfr[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+                ldmatrix_x4(af[i], smem_u32(&As[buf][wm * 32 + i * 16 + (lane & 15)][ks + (lane >> 4) * 8]));
+#pragma unroll
+            for (int j = 0; j < 2; ++j)  // two n-tiles of 8 per ldmatrix: {b0, b1} of tile 2j, then of tile 2j + 1
+                ldmatrix_x4(bfr[j], smem_u32(&Bs[buf][wn * 32 + j * 16 + (lane & 7) + ((lane >> 4) << 3)][ks + ((lane >> 3) & 1) * 8]));
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    mma_bf16_16816(acc[i][j], af[i][0], af[i][1], af[i][2], af[i][3], bfr[j >> 1][(j & 1) * 2], bfr[j >> 1][(j & 1) * 2 + 1]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int m = m0 + wm * 32 + i * 16 + (lane >> 2) + 8 * h, n = n0 + wn * 32 + j * 8 + 2 * (lane & 3);
+                if (m >= M) continue;
+                if (n < N) y[(size_t)m * N + n] = f32_to_bf16_bits(acc[i][j][2 * h]);
+                if (n + 1 < N) y[(size_t)m * N + n + 1] = f32_to_bf16_bits(acc[i][j][2 * h + 1]);
+            }
+}
+
 // out = bf16(g * sigmoid(g) * u) in f32: the golden form of ffn_swiglu/decode/ffn_decode.py:309-311.
 __global__ void silu_mul_bf16_kernel(const uint16_t *__restrict__ gate, const uint16_t *__restrict__ up,
                                      uint16_t *__restrict__ out, size_t n) {
@@ -695,8 +779,13 @@ extern "C" int awq_b200_linear_bf16(const uint16_t *x, const uint16_t *W, uint16
     if (M == 0 || N == 0) return AWQ_OK;
     AWQ_REQUIRE(x && W && y, "linear_bf16: null pointer");
     AWQ_REQUIRE(aligned16(x) && aligned16(W), "linear_bf16: x and W must be 16-byte aligned");
+    if (M >= 16) {  // a GEMM: tensor cores
+        dim3 tgrid((N + LT_BN - 1) / LT_BN, (M + LT_BM - 1) / LT_BM);
+        AWQ_REQUIRE(tgrid.y <= 65535u, "linear_bf16: M (%d) too large", M);
+        linear_bf16_tc_kernel<<<tgrid, 128, 0, as_stream(stream)>>>(x, W, y, M, K, N);
+        return check_cuda(cudaGetLastError(), "linear_bf16 launch");
+    }
     dim3 grid((N + 7) / 8, (M + LB_ROWS - 1) / LB_ROWS);
-    AWQ_REQUIRE(grid.y <= 65535u, "linear_bf16: M (%d) too large", M);
     linear_bf16_kernel<<<grid, 256, 0, as_stream(stream)>>>(x, W, y, M, K, N);
     return check_cuda(cudaGetLastError(), "linear_bf16 launch");
 }

@@ -170,11 +170,10 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
     }
 }
 
-// bf16-rounded value -> fp16 bits, clamped to the finite fp16 range.
-__device__ __forceinline__ uint16_t bf16_value_to_f16_bits(float v) {
-    v = fminf(fmaxf(v, -65504.f), 65504.f);
-    return __half_as_ushort(__float2half_rn(v));
-}
+// bf16-rounded value -> fp16 bits.  Nothing is clamped: a value beyond the fp16 range becomes an infinity and a
+// NaN stays a NaN, so an overflow inside a chain of kernels shows in the output (and trips the range check of
+// the split-K hand-over) instead of turning into a plausible finite number.
+__device__ __forceinline__ uint16_t bf16_value_to_f16_bits(float v) { return __half_as_ushort(__float2half_rn(v)); }
 
 // One lane's share of a finished strip after the lane exchange: batch row b, and for each
 // 32-column half h of the warp's 64 columns, 8 consecutive columns starting at n + 32 h.

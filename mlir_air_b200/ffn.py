@@ -129,7 +129,7 @@ class DecodeFFNStack:
         self.ws = Workspace(maxK, maxN, device=device)
         max_il = max(l.down.K for l in self.layers)
         bf = dict(dtype=torch.bfloat16, device=device)
-        self._h = [torch.empty((max_batch, hidden), **bf) for _ in range(2)]
+        self._h = [torch.zeros((max_batch, hidden), **bf) for _ in range(2)]  # zeros: a capture's warm-up run reads them
         # intermediates between the kernels of a layer are fp16 (the GEMV kernel's fastest input)
         self._normed = torch.empty((max_batch, hidden), dtype=torch.float16, device=device)
         self._inter = torch.empty((max_batch, max_il), dtype=torch.float16, device=device)

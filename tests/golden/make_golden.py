@@ -65,7 +65,9 @@ def main():
     ap.add_argument("--out", default=os.path.dirname(os.path.abspath(__file__)))
     ap.add_argument("--big", action="store_true",
                     help="also replay the reference's 2048x2048 GEMV test shape (about 15 s)")
+    ap.add_argument("--only", default="", help="comma-separated fixture names to (re)write; default: all")
     args = ap.parse_args()
+    only = set(filter(None, args.only.split(",")))
     sys.dont_write_bytecode = True
     sys.meta_path.insert(0, _AirStub())
     pe = os.path.join(args.reference, "programming_examples")
@@ -81,8 +83,13 @@ def main():
         sys.path.insert(0, os.path.join(pe, extra))
     qkv = _import_from(os.path.join(pe, "llms", "llama32_1b_int4", "multi_launch_builder"), "rms_qkv_int4_rope_multi")
     lw = _import_from(os.path.join(pe, "llms", "llama32_1b"), "llama32_1b_weights")
+    ap_ = _import_from(os.path.join(pe, "llms", "llama32_1b_int4"), "awq_pack")
+    ofm = _import_from(os.path.join(pe, "llms", "llama32_1b_int4", "multi_launch_builder"), "o_gemv_ffn_int4_multi")
+    off = _import_from(os.path.join(pe, "llms", "llama32_1b_int4", "multi_launch_builder"), "o_gemv_ffn_int4_fused")
 
     def save(name, **arrs):
+        if only and name not in only:
+            return
         out = {}
         for k, v in arrs.items():
             v = np.asarray(v)
@@ -108,6 +115,32 @@ def main():
     qweight, qzeros, scales, nibs, z_nibs = rp._gen_synthetic_awq(192, 48, 64, seed=7)
     save("awq_repacker_gs64", qweight=qweight, qzeros=qzeros, scales=scales, nibs=nibs,
          z_nibs=z_nibs, w_dense=rp.dequant_to_bf16(qweight, qzeros, scales, 64))
+
+    # --- awq_pack.py: the dequant, the NPU packer and the min/max quantiser on seeded inputs ---
+    qweight, qzeros, scales, _, _ = rp._gen_synthetic_awq(256, 64, 128, seed=11)
+    Wb = (np.random.default_rng(12).standard_normal((256, 48)) * 0.05).astype(bfloat16)  # [K, N] prefill orientation
+    Wq, Ws, Wz = ap_.fake_quantize_awq_int4(np.ascontiguousarray(Wb.T), gs=64)
+    save("awq_pack_256x64", qweight=qweight, qzeros=qzeros, scales=scales.astype(bfloat16),
+         dense=ap_.awq_dequant_layer(qweight, qzeros, scales.astype(bfloat16), gs=128),
+         packed=ap_.awq_pack_for_npu(qweight, qzeros, scales.astype(bfloat16), gs=128, n_tile=16, k_chunk=128, M_seq=64),
+         W=Wb, W_q=Wq, W_s=Ws, W_z=Wz,
+         W_packed=ap_.pack_weight_for_int4_gemm(Wb, 64, gs=64, n_tile=16, k_chunk=128))
+
+    # --- o_gemv_ffn_int4_{multi,fused}.py: the post-attention block goldens at a small shape ---
+    emb, hid, gs_ = 256, 512, 128
+    np.random.seed(42)
+    wo = ofm._gen_int4_weights(emb, emb, gs_, 100)
+    gu = ofm._gen_int4_weights(2 * hid, emb, gs_, 150)
+    wd = ofm._gen_int4_weights(emb, hid, gs_, 200)
+    attn = np.random.randn(emb).astype(bfloat16)
+    xres = np.random.randn(emb).astype(bfloat16)
+    fnw = (np.random.randn(emb) * 0.1 + 1.0).astype(bfloat16)
+    res1 = mva.cpu_reference(wo[0], wo[1], wo[2], attn, xres)
+    swi = off.lgu_cpu_reference(gu[0], gu[1], gu[2], res1, fnw)
+    save("o_gemv_ffn_int4_256x512", wo_q=wo[0], wo_s=wo[1], wo_z=wo[2], gu_q=gu[0], gu_s=gu[1], gu_z=gu[2], wd_q=wd[0],
+         wd_s=wd[1], wd_z=wd[2], attn_out=attn, x_residual=xres, ffn_norm_w=fnw,
+         multi_out=ofm.o_gemv_ffn_int4_reference(wo[3], attn, xres, fnw, gu[3][0::2], gu[3][1::2], wd[3]),
+         res1=res1, swiglu=swi, fused_out=off.ld_cpu_reference(wd[0], wd[1], wd[2], swi, res1))
 
     # --- rms_qkv_int4_rope_multi.py: RMSNorm -> Q/K/V int4 GEMVs -> half-split RoPE on Q and K, its
     #     __main__ data recipe (:640-687) at a small shape, positions 0..3 of the reference's LUT ---

@@ -19,6 +19,8 @@ SCRIPTS = [
     "matrix_multiplication.int4_awq.matmul_int4_packed",
     "silu_and_mul.silu_and_mul",
     "llms.llama32_1b_int4.multi_launch_builder.rms_qkv_int4_rope_multi",
+    "llms.llama32_1b_int4.multi_launch_builder.o_gemv_ffn_int4_multi",
+    "llms.llama32_1b_int4.multi_launch_builder.o_gemv_ffn_int4_fused",
 ]
 
 
@@ -59,3 +61,53 @@ def test_bad_tilings_are_rejected():
         matvec.build_module(2050, 8192)
     with pytest.raises(ValueError):
         mv.build_module(64, 512, 128, 8, 256, 4, 48)    # M_PER_LAUNCH does not divide M
+
+
+def test_int4_ffn_flags_name_registered_instances(capsys):
+    from mlir_air_b200.backend import _INSTANCES
+    from mlir_air_b200.programming_examples.ffn_swiglu.decode import ffn_decode
+    from mlir_air_b200.programming_examples.ffn_swiglu.prefill import ffn_prefill
+    for mod, flags in ((ffn_prefill, ["--int4", "--hidden", "256", "--intermediate", "512", "--seq-len", "32", "-p"]),
+                       (ffn_decode, ["--int4", "--hidden", "256", "--intermediate", "512", "-p"]),
+                       (ffn_decode, ["--int4", "--hidden", "256", "--intermediate", "512", "--tp", "2", "-p"])):
+        with pytest.raises(SystemExit) as e:
+            mod.main(flags)
+        assert e.value.code == 0
+        m = re.search(r"b200\.kernel @(\w+)\(", capsys.readouterr().out)
+        assert m and m.group(1) in _INSTANCES
+    with pytest.raises(SystemExit) as e:  # --tp is a property of the int4 path
+        ffn_decode.main(["--tp", "2"])
+    assert e.value.code != 0
+
+
+def test_post_attention_block_builders_reject_bad_tilings():
+    from mlir_air_b200.programming_examples.llms.llama32_1b_int4.multi_launch_builder import o_gemv_ffn_int4_fused as f
+    from mlir_air_b200.programming_examples.llms.llama32_1b_int4.multi_launch_builder import o_gemv_ffn_int4_multi as m
+    assert m._packed_dims(2048, 2048, 128, 8, 2048, 8, 2048) == (256, 8576)  # tiles, bytes per tile
+    with pytest.raises(ValueError):
+        m.build_o_gemv_ffn_int4_module(emb_dim=2048 + 8)
+    with pytest.raises(ValueError):
+        f.build_module(K=2048, M_LA=1024, M_LGU=16384, K_LD=8192)  # res1 must double as the down projection's residual
+    assert f.build_o_gemv_ffn_int4_fused_module(512, 1024, k_chunk=512).params["hidden_dim"] == 1024
+
+
+def test_post_attention_block_goldens_match_the_reference_fixture():
+    """lgu_cpu_reference, ld_cpu_reference and o_gemv_ffn_int4_reference as restated in the mirrors against what
+    mlir-air's own functions returned on the same inputs (tests/golden/o_gemv_ffn_int4_256x512.npz)."""
+    import numpy as np
+    from golden_util import bits, load
+    from mlir_air_b200.programming_examples import _common as C
+    from mlir_air_b200.programming_examples.llms.llama32_1b_int4.multi_launch_builder import o_gemv_ffn_int4_fused as f
+    from mlir_air_b200.programming_examples.llms.llama32_1b_int4.multi_launch_builder import o_gemv_ffn_int4_multi as m
+    from ml_dtypes import bfloat16
+    g = load("o_gemv_ffn_int4_256x512")
+    sw = f.lgu_cpu_reference(g["gu_q"], g["gu_s"], g["gu_z"], g["res1"], g["ffn_norm_w"])
+    assert np.array_equal(bits(sw), bits(g["swiglu"]))
+    assert np.array_equal(bits(f.ld_cpu_reference(g["wd_q"], g["wd_s"], g["wd_z"], g["swiglu"], g["res1"])), bits(g["fused_out"]))
+    deq = lambda k: C.dequant_B(g[k + "_q"], g[k + "_s"], g[k + "_z"]).astype(bfloat16)  # noqa: E731
+    gu = deq("gu")
+    out = m.o_gemv_ffn_int4_reference(deq("wo"), g["attn_out"], g["x_residual"], g["ffn_norm_w"], gu[0::2], gu[1::2], deq("wd"))
+    assert np.array_equal(bits(out), bits(g["multi_out"]))
+    # the seeded generator is the reference's
+    q, s_, z, d = m._gen_int4_weights(256, 256, 128, 100)
+    assert np.array_equal(q, g["wo_q"]) and np.array_equal(bits(s_), bits(g["wo_s"])) and np.array_equal(z, g["wo_z"])
