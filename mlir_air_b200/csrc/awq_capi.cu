@@ -98,7 +98,10 @@ static int run_gemv(const char *who, GemvArgs a) {
                          "%s: stream-K kernel needs group 128, K %% 128 == 0, N %% 32 == 0, 16-byte aligned "
                          "pointers and an sm_100 device (K=%d N=%d gs=%d)", who, a.K, a.N, a.group_size);
     if (mode != 1 && fast_ok) {
-        a.native_bf16 = (mode == 3);
+        // bf16 activations: converting them to fp16 first (a small kernel in front) buys a cheaper nibble decode, which
+        // pays once a launch streams tens of megabytes; below that the extra launch costs more than it saves
+        const bool small = (double)a.K * a.N * 0.52 < 48e6 && a.B <= 8;
+        a.native_bf16 = mode == 3 || (mode == 0 && a.x_format == ACT_BF16 && small);
         a.deterministic = g_deterministic.load() != 0;
         return launch_gemv_streamk(a);
     }

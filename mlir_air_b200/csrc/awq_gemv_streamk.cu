@@ -261,7 +261,7 @@ size_t gemv_streamk_workspace_bytes(int B, int K, int N) {
     // header + accumulators of every strip a product may use + room for B rows of activations converted to fp16
     const size_t rows = B < 1 ? 1 : (B > 64 ? 64 : B);
     (void)N;
-    return SK_WS_END + rows * (size_t)(K > 0 ? K : 0) * 2;
+    return SK_WS_XH + rows * (size_t)(K > 0 ? K : 0) * 2;
 }
 
 template <int EPI, bool XH>
@@ -345,7 +345,7 @@ static int launch_passes(const GemvArgs &a, const uint16_t *x_all) {
 
 int launch_gemv_streamk(const GemvArgs &a) {
     const bool convert = a.x_format == ACT_BF16 && !a.native_bf16;
-    const size_t xh_off = SK_WS_END;  // the conversion buffer sits behind the accumulators of every possible strip
+    const size_t xh_off = SK_WS_XH;  // the conversion buffer sits behind the accumulators of every possible strip and the stack kernel's state
     const size_t need = convert ? xh_off + (size_t)a.B * a.K * 2 : gemv_streamk_scratch_bytes(a.N, a.deterministic);
     if (!a.workspace || a.workspace_bytes < need)
         return set_error(AWQ_ERR_WORKSPACE, "gemv: workspace of %zu bytes needed, %zu given", need, a.workspace_bytes);

@@ -42,6 +42,10 @@ constexpr size_t SK_WS_HEADER = 256;
 constexpr int SK_MAX_STRIPS = 504;  // N up to 258,048 columns
 constexpr size_t SK_WS_ACCUM = 16384;
 constexpr size_t SK_WS_END = SK_WS_ACCUM + (size_t)SK_MAX_STRIPS * SK_STRIP_WORDS * 8;
+// behind the accumulators: the state of the one-launch stack kernel (awq_ffn_fused.cu), then room to convert
+// activations to fp16
+constexpr size_t SK_WS_FUSED_STATE = 5u << 20;
+constexpr size_t SK_WS_XH = SK_WS_END + SK_WS_FUSED_STATE;
 constexpr int SK_MAX_CTAS = 1023;
 
 // ---- split-K hand-over: value and progress in ONE 64-bit atomic ------------------------------
