@@ -15,8 +15,8 @@ LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libawq_b200.so")
 SOURCES = ["awq_capi.cu", "awq_dequant.cu", "awq_generic.cu", "awq_gemv_streamk.cu", "awq_gemv_streamk_mb.cu", "awq_gemm_tc.cu",
            "awq_static_scratch.cu", "awq_ffn_fused.cu"]
-NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "--use_fast_math=false", "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall"]
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
+              "-Xcompiler", "-Wall"]
 
 
 def _nvcc():
@@ -48,8 +48,7 @@ def build(force=False, verbose=False):
     procs = []
     for src in sources():
         obj = os.path.join(LIB_DIR, os.path.basename(src)[:-3] + ".o")
-        cmd = [_nvcc(), *[f for f in NVCC_FLAGS if f != "--use_fast_math=false"], "-I", os.path.join(ROOT, "include"),
-               "-I", CSRC, "-c", src, "-o", obj]
+        cmd = [_nvcc(), *NVCC_FLAGS, "-I", os.path.join(ROOT, "include"), "-I", CSRC, "-c", src, "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")
