@@ -320,8 +320,23 @@ int awq_b200_gemm_fused_bf16(const uint16_t *A, const int32_t *qweight, const in
                              const uint16_t *scales, const uint16_t *residual, uint16_t *C, int swiglu,
                              int M, int K, int N, int group_size, awq_stream_t stream);
 
-/* Synchronise `stream` and report whether the tensor-core GEMM gave up on a bounded device-side
- * wait since the last check (AWQ_ERR_DEVICE_TIMEOUT); the counterpart of xrt.py:204-218. */
+/* The same three products for a decode batch of 9 <= M <= 64 token rows (the batched-decode golden of
+ * matmul_int4_packed.py:97-105 with M = batch; the reference's decode kernels take one row at a time,
+ * mv_int4_bf16.cc:403-436).  Bound by streaming the weights like the GEMV, so the work is cut into
+ * (256-column tile, 128-row k-block) units dealt evenly to the SMs; the f32 sums of each SM's share of a
+ * tile go through `workspace` (awq_b200_gemm_decode_workspace_bytes(M, N) bytes; no initialisation
+ * needed; calls sharing it must not overlap) and a second small launch adds them in a fixed order and
+ * applies the epilogue, so results do not depend on the order of arrival.  Two kernel launches per call.
+ * group_size 128, K % 128 == 0, N % 32 == 0 (AWQ_ERR_UNSUPPORTED otherwise). */
+size_t awq_b200_gemm_decode_workspace_bytes(int M, int N);
+int awq_b200_gemm_decode_bf16(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros,
+                              const uint16_t *scales, const uint16_t *residual, uint16_t *C, int swiglu,
+                              int M, int K, int N, int group_size, void *workspace,
+                              size_t workspace_bytes, awq_stream_t stream);
+
+/* Synchronise `stream` and report whether a tensor-core GEMM (prefill or batched decode) gave up on a
+ * bounded device-side wait since the last check (AWQ_ERR_DEVICE_TIMEOUT); the counterpart of
+ * xrt.py:204-218. */
 int awq_b200_gemm_check(awq_stream_t stream);
 
 /* Choose the prefill kernel: 0 = automatic, 1 = generic CUDA-core kernel,

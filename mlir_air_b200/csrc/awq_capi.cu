@@ -361,4 +361,28 @@ extern "C" int awq_b200_gemm_fused_bf16(const uint16_t *A, const int32_t *qweigh
                           swiglu ? GEMM_EPI_SWIGLU : (residual ? GEMM_EPI_RESIDUAL : GEMM_EPI_BF16), residual);
 }
 
-extern "C" int awq_b200_gemm_check(awq_stream_t stream) { return gemm_tc_check(as_stream(stream)); }
+extern "C" int awq_b200_gemm_check(awq_stream_t stream) {
+    const int rc = gemm_tc_check(as_stream(stream));
+    const int rc2 = gemm_decode_check(as_stream(stream));
+    return rc ? rc : rc2;
+}
+
+extern "C" size_t awq_b200_gemm_decode_workspace_bytes(int M, int N) { return gemm_decode_workspace_bytes(M, N); }
+
+extern "C" int awq_b200_gemm_decode_bf16(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros,
+                                         const uint16_t *scales, const uint16_t *residual, uint16_t *C, int swiglu, int M,
+                                         int K, int N, int group_size, void *workspace, size_t workspace_bytes,
+                                         awq_stream_t stream) {
+    AWQ_REQUIRE(M >= 0 && K > 0 && N > 0 && group_size > 0, "gemm_decode: bad size");
+    AWQ_REQUIRE(!(swiglu && residual), "gemm_decode: SwiGLU and residual do not combine");
+    if (M == 0) return AWQ_OK;
+    AWQ_REQUIRE(A && qweight && qzeros && scales && C, "gemm_decode: null pointer");
+    AWQ_REQUIRE(aligned16(A) && aligned16(scales) && aligned16(qweight) && aligned16(qzeros) && aligned16(C) &&
+                    aligned16(residual) && aligned16(workspace), "gemm_decode: pointers must be 16-byte aligned");
+    if (!gemm_decode_supported(M, K, N, group_size))
+        return set_error(AWQ_ERR_UNSUPPORTED, "gemm_decode: needs M <= 64, group 128, K %% 128 == 0, N %% 32 == 0 "
+                         "(M=%d K=%d N=%d gs=%d)", M, K, N, group_size);
+    return launch_gemm_decode(A, qweight, qzeros, scales, C, M, K, N, as_stream(stream),
+                              swiglu ? GEMM_EPI_SWIGLU : (residual ? GEMM_EPI_RESIDUAL : GEMM_EPI_BF16), residual, workspace,
+                              workspace_bytes);
+}

@@ -150,6 +150,13 @@ int launch_gemm_tc(const uint16_t *A, const int32_t *qweight, const int32_t *qze
                    cudaStream_t stream, int epilogue = GEMM_EPI_BF16, const uint16_t *residual = nullptr);
 
 int gemm_tc_check(cudaStream_t stream);
+// Batched-decode GEMM (M <= 128 token rows): stream-K over (column tile, k-block) units, split-K partials through `workspace`.
+bool gemm_decode_supported(int M, int K, int N, int group_size);
+size_t gemm_decode_workspace_bytes(int M, int N);
+int launch_gemm_decode(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros, const uint16_t *scales, uint16_t *C, int M,
+                       int K, int N, cudaStream_t stream, int epilogue, const uint16_t *residual, void *workspace,
+                       size_t workspace_bytes);
+int gemm_decode_check(cudaStream_t stream);
 int gemv_push_arrivals_per_rank(int N);  // arrivals a rank signals per EPI_F32_PUSH launch of N columns
 int launch_tp_reduce_add_rmsnorm(const uint16_t *h, const PeerPartials &parts, unsigned int *flags, int expected,
                                  const uint16_t *gamma, float eps, uint16_t *h_out, uint16_t *normed, int normed_f16, int B,

@@ -1,0 +1,573 @@
+// Batched-decode GEMM  C[M, N] = A[M, K] @ W  for AWQ int4 weights, 9 <= M <= 128 token rows
+// (the batched-decode golden of matrix_multiplication/int4_awq/matmul_int4_packed.py:97-105 with M = batch),
+// with the decode block's epilogues: bf16, bf16 + residual, SwiGLU over interleaved gate/up column pairs.
+//
+// With this few rows the product is bound by streaming the weights (0.52 B each, used once), like the GEMV,
+// but there are too many rows for mma.sync to keep up, so the multiplies go to tcgen05.  A dequantised bf16
+// tile in shared memory, as in the prefill kernel (awq_gemm_tc.cu), costs 4 bytes of shared-memory traffic per
+// weight (2 written, 2 read by the MMA): more shared-memory cycles per SM than the weights' share of HBM time.
+// So here the dequantised weights never touch shared memory:
+//
+//  * The operands are swapped: the weights are the MMA's M side (128 weight columns per instruction), the
+//    token rows its N side (16 to 64, the batch rounded up), and the M-side operand is read from TENSOR MEMORY.
+//    The dequant warps fetch the packed words with ldmatrix.trans (a register then holds the nibbles of four
+//    columns at k and k + 1), turn each nibble pair into (q - z) s as a bf16 pair with one LOP3 and two
+//    bf16x2 operations, and write the pairs into tensor memory with tcgen05.st.16x256b: a weight column per
+//    TMEM lane, 64 TMEM columns per 128 k.  Which lane holds which column is a fixed permutation inside each
+//    group of 32 columns (the one the nibble order gives for free); the epilogue undoes it.
+//  * An instruction costs in proportion to the batch, and the accumulator has a weight column per TMEM lane
+//    and a token row per TMEM column.
+//  * Work unit = (256-column tile, 128 k = one quantisation group).  The units, tile-major, are cut into one
+//    contiguous range per SM (stream-K), so every SM streams the same number of bytes whatever the shape: a
+//    range covers the end of one tile, some whole tiles and the start of another.
+//  * Four TMA copies per unit (token rows, 16 KB of packed words, scales, zeros) into a ring of 6 to 8 stages.
+//  * The main kernel does no epilogue arithmetic.  Every segment (a CTA's units of one tile) writes its sums
+//    (f32, plain coalesced stores) into the slot of the workspace that belongs to its position among the
+//    tile's contributors, and a second, small kernel (gemm_decode_fixup_kernel, every SM, one thread per four
+//    columns of a row) adds the slots of each tile in their fixed order and applies the epilogue.  No atomics,
+//    no counters, nothing to zero, and the result does not depend on the order of arrival.  (Measured first:
+//    the contributor that completes a tile finishing it inside the main kernel.  Four warps pulling five
+//    contributors' sums with the few loads their registers allow kept the whole GPU waiting 20 to 50 us at
+//    the end of a down projection, and the SwiGLU of a whole tile took the epilogue warp 26 us of issue
+//    slots that the dequant warps, the bottleneck, share.)
+//
+//   warp 0      producer (one elected lane): TMA loads into the input ring
+//   warp 1      MMA issuer (one elected lane): 16 tcgen05.mma (M 128, N = padded batch, K 16, A from tensor memory)
+//               per unit; tcgen05.commit frees the input stage and the weight buffer, and at the end of a
+//               segment hands the accumulator over
+//   warps 4-19  dequant: warp w owns TMEM lanes 32 (w % 4) .. + 31 of one 128-column half and 64 of the 128 k
+//   warps 20-23 drain: tcgen05.ld (each warp its 32 TMEM lanes of both halves) and stores into the slot; two
+//               accumulators alternate, so a segment drains while the next one runs
+//
+// Tensor memory (512 columns): two or three weight buffers of 128 columns, two accumulators of 2 x batch columns.
+// Every wait is bounded; on expiry the kernel records an error and all roles drain, so the tensor memory is
+// always released.
+#include <cudaTypedefs.h>
+#include <cuda_bf16.h>
+
+#include <mutex>
+
+#include "awq_common.cuh"
+#include "awq_ptx.cuh"
+#include "awq_streamk.cuh"
+
+namespace awq {
+
+int encode_tensor_map_2d(CUtensorMap *map, int dtype, const void *base, uint64_t dim0, uint64_t dim1,
+                         uint64_t stride1_bytes, uint32_t box0, uint32_t box1, int swizzle);
+int encode_tensor_map_3d(CUtensorMap *map, int dtype, const void *base, uint64_t dim0, uint64_t dim1, uint64_t dim2,
+                         uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1, uint32_t box2,
+                         int swizzle);
+
+constexpr int DG_BN = 256, DG_BK = 64, DG_GROUP = 128;
+constexpr int DG_ABUF_COLS = 2 * (DG_GROUP / 2);        // a weight buffer in tensor memory: two 128-column halves x 128 k
+                                                        // as bf16 pairs = 128 TMEM columns
+constexpr int DG_W_BYTES = DG_GROUP * (DG_BN / 8) * 4;  // 16 KB of packed words: a unit (128 k, one quantisation group)
+constexpr int DG_S_BYTES = DG_BN * 2;
+constexpr int DG_Z_BYTES = DG_BN / 8 * 4;
+constexpr int DG_SZ_BYTES = 1024;                       // scales, then zeros
+constexpr int DG_DEQUANT_WARPS = 16;
+constexpr int DG_DEQUANT_WARP0 = 4, DG_EPI_WARP0 = DG_DEQUANT_WARP0 + DG_DEQUANT_WARPS;
+constexpr int DG_THREADS = (DG_EPI_WARP0 + 4) * 32;  // 768
+constexpr uint32_t DG_TMEM_COLS = 512;
+constexpr int DG_MAX_ROWS = 64;
+constexpr int DG_MAX_TILES = 4096;
+
+// NB = token rows the MMA sees (its N): the batch rounded up to 16, 32 or 64.
+template <int NB>
+struct DgCfg {
+    static constexpr int A_BYTES = 2 * NB * DG_BK * 2;  // two tiles of token rows x 64 k, 128-byte rows
+    static constexpr int STAGE_BYTES = A_BYTES + DG_W_BYTES + DG_SZ_BYTES;
+    static constexpr int RING_BUDGET = 220 * 1024;
+    static constexpr int STAGES = RING_BUDGET / STAGE_BYTES < 8 ? RING_BUDGET / STAGE_BYTES : 8;
+    static constexpr int ABUF = (int)(DG_TMEM_COLS - 4 * NB) / DG_ABUF_COLS;  // weight buffers: 3 up to 32 rows, 2 with 64
+    static constexpr int ACC_COL0 = ABUF * DG_ABUF_COLS;                      // accumulators start behind them
+    static constexpr int NUM_BARS = 2 * STAGES + 2 * ABUF + 4;
+    static constexpr int OFF_BARS = STAGES * STAGE_BYTES;
+    static constexpr int SMEM_BYTES = OFF_BARS + NUM_BARS * 8 + 16 + 1024;
+    // f32 accumulate, bf16 x bf16, A (weights, tensor memory) and B (token rows) K-major, M 128, N NB
+    static constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NB >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    static_assert(ABUF >= 2 && ACC_COL0 + 4 * NB <= (int)DG_TMEM_COLS, "tensor memory budget");
+    static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+    static_assert(STAGE_BYTES % 1024 == 0, "swizzled tiles need 1024-byte alignment");
+    static_assert(STAGES >= 3, "input ring too shallow");
+};
+
+__device__ int g_gemm_dec_error;  // 0 = ok; set when a bounded wait gave up
+
+// ---- tcgen05 wrappers (as in awq_gemm_tc.cu) ----------------------------------------------------
+__device__ __forceinline__ void dg_tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void dg_tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void dg_tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void dg_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void dg_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void dg_umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// the same with the M-side operand in tensor memory (a lane per row, a 32-bit column per two k)
+__device__ __forceinline__ void dg_umma_bf16_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 16 lanes x 8 columns: lane l of the warp gives columns 2 (l % 4), + 1 of TMEM lane l / 4 (r0, r1) and of lane l / 4 + 8 (r2, r3)
+__device__ __forceinline__ void dg_tmem_st_16x256b(uint32_t taddr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
+    asm volatile("tcgen05.st.sync.aligned.16x256b.x1.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(r0), "r"(r1), "r"(r2), "r"(r3) : "memory");
+}
+__device__ __forceinline__ void dg_tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void dg_umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void dg_tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+// One lane of a converged warp.  The code around it stays warp-uniform, so that the compiler keeps descriptors and
+// addresses in uniform registers, which is where the TMA and MMA instructions take them from: issued from inside an
+// `if (lane == 0)` region instead, every operand is first moved over from a vector register, and one tcgen05.mma or
+// cp.async.bulk.tensor then costs the issuing thread 100 to 200 cycles.
+__device__ __forceinline__ bool dg_elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+__device__ __forceinline__ void dg_tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// K-major tile of 128-byte rows, 128B swizzle, 8-row atoms 1024 B apart.
+__device__ __forceinline__ uint64_t dg_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+__device__ __forceinline__ uint32_t dg_bf16x2_sub(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t dg_bf16x2_mul(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+// The walk over a CTA's units, the same for every warp role: unit u = tile * KB + kb (KB units of 128 k per tile),
+// range [u0, u1).
+struct UnitWalk {
+    int KB, u, u1;
+    __device__ __forceinline__ UnitWalk(int tiles, int kb_count) : KB(kb_count) {
+        const long long U = (long long)tiles * kb_count, C = gridDim.x, c = blockIdx.x;
+        u = (int)(c * U / C);
+        u1 = (int)((c + 1) * U / C);
+    }
+    __device__ __forceinline__ bool valid() const { return u < u1; }
+    __device__ __forceinline__ int tile() const { return u / KB; }
+    __device__ __forceinline__ int kb() const { return u - tile() * KB; }
+    // units of the current tile that this CTA still has, from u on
+    __device__ __forceinline__ int left_in_tile() const {
+        const int end = (tile() + 1) * KB;
+        return (end < u1 ? end : u1) - u;
+    }
+};
+
+// The first CTA whose range (UnitWalk) reaches into tile t.
+__device__ __forceinline__ int dg_first_cta(int t, int KB, int tiles) {
+    const long long U = (long long)tiles * KB, C = gridDim.x;
+    return (int)((((long long)t * KB + 1) * C + U - 1) / U) - 1;
+}
+// Partial sums of a tile in the workspace: slot [contributor][token row m][column of the tile], so that the 32 lanes
+// of a warp (columns) touch one 128-byte line.
+template <int NB>
+__device__ __forceinline__ float *dg_slot_word(float *slots, int slots_per_tile, int tile, int contributor, int m, int col) {
+    return slots + (((size_t)tile * slots_per_tile + contributor) * NB + m) * DG_BN + col;
+}
+
+// Which column of its group of 32 a TMEM lane holds: the dequant warps place the four columns of a 16-bit half word
+// (nibbles e = 0..3: columns 2e + half of word `word`) in lanes g, g + 8, g + 16, g + 24 with g = 2 word + half.
+__device__ __forceinline__ int dg_lane_column(int lane) {
+    const int g = lane & 7, e = lane >> 3;
+    return 8 * (g >> 1) + 2 * e + (g & 1);
+}
+
+template <int NB>
+__global__ void __launch_bounds__(DG_THREADS, 1)
+gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
+                   const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmZ,
+                   int M, int N, int K, int tiles, float *__restrict__ slots, int slots_per_tile, long long wait_limit) {
+    using Cfg = DgCfg<NB>;
+    constexpr int STAGES = Cfg::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar_base = smem_base + Cfg::OFF_BARS;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_gen + Cfg::OFF_BARS + Cfg::NUM_BARS * 8);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };                     // TMA landed in input stage s
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };         // MMA and dequant done with input stage s
+    auto ready_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };     // weight buffer b dequantised
+    auto bfree_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + Cfg::ABUF + b); };       // MMA done with weight buffer b
+    auto acc_full = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 * Cfg::ABUF + b); };    // segment complete
+    auto acc_empty = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 * Cfg::ABUF + 2 + b); };  // accumulator drained
+    auto stage_addr = [&](int s) { return smem_base + (uint32_t)s * Cfg::STAGE_BYTES; };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr uint32_t TX_BYTES = Cfg::A_BYTES + DG_W_BYTES + DG_S_BYTES + DG_Z_BYTES;
+    const int KB = K / DG_GROUP;  // units per tile
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1 + DG_DEQUANT_WARPS);  // the MMA's commit and the dequant warps (they read W, S, Z)
+        }
+        for (int b = 0; b < Cfg::ABUF; ++b) {
+            mbar_init(ready_bar(b), DG_DEQUANT_WARPS);
+            mbar_init(bfree_bar(b), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full(b), 1);
+            mbar_init(acc_empty(b), 4);
+        }
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        dg_tmem_alloc(smem_u32(tmem_slot), DG_TMEM_COLS);
+        dg_tmem_relinquish();
+    }
+    dg_fence_before();
+    __syncthreads();
+    dg_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------ producer ------------------------------
+        // the whole warp walks the units; one elected lane issues the unit's four copies
+        if (dg_elect_one()) {
+            tma_prefetch_desc(&tmA);
+            tma_prefetch_desc(&tmW);
+            tma_prefetch_desc(&tmS);
+            tma_prefetch_desc(&tmZ);
+        }
+        const uint64_t stream_policy = l2_policy_evict_first();
+        int it = 0;
+        for (UnitWalk w(tiles, KB); w.valid(); ++w.u, ++it) {
+            const int s = it % STAGES, round = it / STAGES;
+            if (round > 0 && !mbar_wait_bounded(empty_bar(s), (round - 1) & 1, wait_limit)) {
+                if (lane == 0) atomicExch(&g_gemm_dec_error, 1);
+                break;
+            }
+            const int n0 = w.tile() * DG_BN, g = w.kb();
+            const uint32_t st = stage_addr(s), bar = full_bar(s);
+            if (dg_elect_one()) {
+                mbar_expect_tx(bar, TX_BYTES);
+                tma_load_3d(st, &tmA, 0, 0, 2 * g, bar);
+                tma_load_2d_hint(st + Cfg::A_BYTES, &tmW, n0 / 8, g * DG_GROUP, bar, stream_policy);
+                tma_load_2d(st + Cfg::A_BYTES + DG_W_BYTES, &tmS, n0, g, bar);
+                tma_load_2d(st + Cfg::A_BYTES + DG_W_BYTES + DG_S_BYTES, &tmZ, n0 / 8, g, bar);
+            }
+            __syncwarp();
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        // the whole warp walks the units and waits; one elected lane issues
+        int it = 0, seg_it = 0;
+        bool ok = true;
+        UnitWalk w(tiles, KB);
+        while (w.valid() && ok) {
+            const int n_seg = w.left_in_tile();  // this segment: n_seg units of one tile
+            const int b = seg_it & 1, use = seg_it >> 1;
+            if (use >= 1 && !mbar_wait_bounded(acc_empty(b), (use - 1) & 1, wait_limit)) {
+                if (lane == 0) atomicExch(&g_gemm_dec_error, 2);
+                break;
+            }
+            dg_fence_after();
+            const uint32_t d_tmem = tmem_base + Cfg::ACC_COL0 + (uint32_t)b * (2 * NB);
+            for (int i = 0; i < n_seg; ++i, ++it, ++w.u) {
+                const int s = it % STAGES, round = it / STAGES;
+                const int ab = it % Cfg::ABUF, around = it / Cfg::ABUF;
+                if (!mbar_wait_bounded(full_bar(s), round & 1, wait_limit) ||
+                    !mbar_wait_bounded(ready_bar(ab), around & 1, wait_limit)) {
+                    if (lane == 0) atomicExch(&g_gemm_dec_error, 3);
+                    ok = false;
+                    break;
+                }
+                dg_fence_after();
+                const uint32_t a_tmem = tmem_base + (uint32_t)ab * DG_ABUF_COLS;
+                // token rows: K-major 128-byte rows, two tiles of 64 k, 32 bytes further in the row per step
+                const uint64_t x_desc = dg_desc_sw128(stage_addr(s));
+                const uint32_t acc0 = i ? 1u : 0u;
+                if (dg_elect_one()) {
+#pragma unroll
+                    for (int k16 = 0; k16 < DG_GROUP / 16; ++k16) {
+#pragma unroll
+                        for (int h = 0; h < 2; ++h)  // the tile's two halves of 128 weight columns
+                            dg_umma_bf16_ta(d_tmem + h * NB, a_tmem + h * (DG_GROUP / 2) + 8 * k16,
+                                            x_desc + (uint64_t)((k16 >> 2) * ((Cfg::A_BYTES / 2) >> 4) + 2 * (k16 & 3)), Cfg::IDESC,
+                                            k16 ? 1u : acc0);
+                    }
+                    dg_umma_commit(empty_bar(s));
+                    dg_umma_commit(bfree_bar(ab));
+                }
+                __syncwarp();
+            }
+            if (ok && dg_elect_one()) dg_umma_commit(acc_full(b));
+            __syncwarp();
+            ++seg_it;
+        }
+    } else if (warp >= DG_DEQUANT_WARP0 && warp < DG_EPI_WARP0) {
+        // ------------------------------ dequant ------------------------------
+        const int dw = warp - DG_DEQUANT_WARP0;
+        const int q = warp & 3;        // TMEM lanes 32 q .. 32 q + 31 (a warp may only touch its own quarter)
+        const int h = (dw >> 2) & 1;   // which 128-column half of the tile
+        const int kh = dw >> 3;        // which 64 of the unit's 128 k
+        const int g = lane >> 2;       // ldmatrix.trans: lane (g, t = lane % 4) gets 16-bit column g of the chunk, rows 2t and 2t + 1
+        const int chunk = 4 * h + q;   // the warp's 32 columns are one 16-byte chunk (4 packed words) of a 128-byte row
+        // Row addresses of the four 8 x 8 matrices of one ldmatrix.x4: matrix m = 2 sp + x serves k16 step sp of the call
+        // and holds rows k = 16 step + 4 j + 2 x + {0, 1} (j = 0..3), so that lane (g, t) receives the k pair 2t + x:
+        // TMEM columns 2t and 2t + 1 of the step are what tcgen05.st.16x256b takes from this lane.
+        const int mi = lane >> 3, rr = lane & 7;
+        const int k_lane = 64 * kh + 16 * (mi >> 1) + 4 * (rr >> 1) + 2 * (mi & 1) + (rr & 1);  // + 32 for the second call
+        const uint32_t w_off = (uint32_t)k_lane * 128 + (uint32_t)((chunk ^ (k_lane & 7)) << 4);  // 128B swizzle; k + 32 keeps k & 7
+        int it = 0;
+        for (UnitWalk w(tiles, KB); w.valid(); ++w.u, ++it) {
+            const int s = it % STAGES, round = it / STAGES;
+            const int ab = it % Cfg::ABUF, around = it / Cfg::ABUF;
+            if (!mbar_wait_bounded(full_bar(s), round & 1, wait_limit)) {
+                if (lane == 0) atomicExch(&g_gemm_dec_error, 4);
+                break;
+            }
+            const uint32_t st = stage_addr(s) + Cfg::A_BYTES;  // packed words, then scales, then zeros
+            // this lane's four columns (nibbles e of its half word): 128 + z and the scale, each twice (k, k + 1)
+            const uint32_t zw = lds32(st + DG_W_BYTES + DG_S_BYTES + (4 * chunk + (g >> 1)) * 4) >> (16 * (g & 1));
+            uint32_t zz[4], ss[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                zz[e] = (((zw >> (4 * e)) & 0xFu) * 0x00010001u) | 0x43004300u;
+                uint32_t sc;
+                asm volatile("ld.shared.u16 %0, [%1];" : "=r"(sc) : "r"(st + DG_W_BYTES + (32 * chunk + 8 * (g >> 1) + 2 * e + (g & 1)) * 2));
+                ss[e] = sc * 0x00010001u;
+            }
+            uint32_t r[2][4];
+            ldmatrix_x4_trans(r[0], st + w_off);
+            ldmatrix_x4_trans(r[1], st + w_off + 32 * 128);
+            if (around > 0 && !mbar_wait_bounded(bfree_bar(ab), (around - 1) & 1, wait_limit)) {
+                if (lane == 0) atomicExch(&g_gemm_dec_error, 4);
+                break;
+            }
+            dg_fence_after();
+            const uint32_t a_tmem = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(ab * DG_ABUF_COLS + h * (DG_GROUP / 2) + 32 * kh);
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+#pragma unroll
+                for (int sp = 0; sp < 2; ++sp) {  // k16 step 2c + sp of this warp's 64 k
+                    const uint32_t lo = r[c][2 * sp], hi = r[c][2 * sp + 1];  // k pairs 2t and 2t + 1
+                    uint32_t v[8];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        v[2 * e] = dg_bf16x2_mul(dg_bf16x2_sub(nib2_to_bf16x2_biased(lo >> (4 * e)), zz[e]), ss[e]);
+                        v[2 * e + 1] = dg_bf16x2_mul(dg_bf16x2_sub(nib2_to_bf16x2_biased(hi >> (4 * e)), zz[e]), ss[e]);
+                    }
+                    // lanes g and g + 8 hold nibbles 0 and 1, lanes g + 16 and g + 24 nibbles 2 and 3
+                    dg_tmem_st_16x256b(a_tmem + 8 * (2 * c + sp), v[0], v[1], v[2], v[3]);
+                    dg_tmem_st_16x256b(a_tmem + (16u << 16) + 8 * (2 * c + sp), v[4], v[5], v[6], v[7]);
+                }
+            dg_tmem_st_wait();
+            dg_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(ready_bar(ab));
+                mbar_arrive(empty_bar(s));  // this warp has read the stage's words, scales and zeros
+            }
+        }
+    } else if (warp >= DG_EPI_WARP0) {
+        // ------------------------------ drain ------------------------------
+        const int q = warp & 3;  // this warp's 32 TMEM lanes: columns 32 q + lane of each 128-column half
+        int seg_it = 0;
+        UnitWalk w(tiles, KB);
+        while (w.valid()) {
+            const int tile = w.tile(), n_seg = w.left_in_tile();
+            w.u += n_seg;
+            const int b = seg_it & 1, use = seg_it >> 1;
+            ++seg_it;
+            const int n0 = tile * DG_BN;
+            if (!mbar_wait_bounded(acc_full(b), use & 1, wait_limit)) {
+                if (lane == 0) atomicExch(&g_gemm_dec_error, 5);
+                break;
+            }
+            dg_fence_after();
+            const uint32_t t_acc = tmem_base + ((uint32_t)(32 * q) << 16) + Cfg::ACC_COL0 + (uint32_t)b * (2 * NB);
+            // N is a multiple of 32: a warp's 32 columns are all inside the matrix or all outside
+            const bool in0 = n0 + 32 * q < N, in1 = n0 + 128 + 32 * q < N;
+            // the segment's sums go into this CTA's slot among the tile's contributors
+            const int me = (int)blockIdx.x - dg_first_cta(tile, KB, tiles);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                if (!(h ? in1 : in0)) continue;
+                const int col = 128 * h + 32 * q + dg_lane_column(lane);
+#pragma unroll 1
+                for (int m0 = 0; m0 < M; m0 += 16) {
+                    uint32_t r[16];
+                    dg_tmem_ld_32x32b_x16(t_acc + (uint32_t)(h * NB + m0), r);
+                    dg_tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        if (m0 + i < M) __stcg(dg_slot_word<NB>(slots, slots_per_tile, tile, me, m0 + i, col), __uint_as_float(r[i]));
+                }
+            }
+            dg_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty(b));
+        }
+    }
+
+    dg_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        dg_fence_after();
+        dg_tmem_dealloc(tmem_base, DG_TMEM_COLS);
+    }
+}
+
+// Second pass: one thread per four columns of a token row adds the slots of the tile's contributors in their order and
+// applies the epilogue.  `main_ctas` is the main kernel's grid size (the ranges of its CTAs decide who contributed to
+// which tile).
+template <int NB>
+__global__ void __launch_bounds__(256)
+gemm_decode_fixup_kernel(uint16_t *__restrict__ C, const uint16_t *__restrict__ R, int epi, int M, int N, int KB, int tiles,
+                         int main_ctas, const float *__restrict__ slots, int slots_per_tile) {
+    const int per_tile = M * (DG_BN / 4);
+    const long long total = (long long)tiles * per_tile;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+        const int tile = (int)(idx / per_tile), rest = (int)(idx - (long long)tile * per_tile);
+        const int m = rest / (DG_BN / 4), col = 4 * (rest - m * (DG_BN / 4)), n = tile * DG_BN + col;
+        if (n >= N) continue;
+        const long long U = (long long)tiles * KB;
+        const int first = (int)((((long long)tile * KB + 1) * main_ctas + U - 1) / U) - 1;
+        const int last = (int)((((long long)(tile + 1) * KB) * main_ctas + U - 1) / U) - 1;
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int c = 0; c <= last - first; ++c) {
+            const float4 v = __ldcg(reinterpret_cast<const float4 *>(slots + (((size_t)tile * slots_per_tile + c) * NB + m) * DG_BN + col));
+            sum.x += v.x, sum.y += v.y, sum.z += v.z, sum.w += v.w;
+        }
+        if (epi == GEMM_EPI_SWIGLU) {
+            const uint32_t o = (uint32_t)swiglu_bits(sum.x, sum.y) | ((uint32_t)swiglu_bits(sum.z, sum.w) << 16);
+            *reinterpret_cast<uint32_t *>(C + (size_t)m * (N >> 1) + (n >> 1)) = o;
+        } else {
+            if (epi == GEMM_EPI_RESIDUAL) {
+                const uint2 rv = *reinterpret_cast<const uint2 *>(R + (size_t)m * N + n);
+                sum.x += bf16x2_lo(rv.x), sum.y += bf16x2_hi(rv.x), sum.z += bf16x2_lo(rv.y), sum.w += bf16x2_hi(rv.y);
+            }
+            *reinterpret_cast<uint2 *>(C + (size_t)m * N + n) = make_uint2(pack_bf16x2(sum.x, sum.y), pack_bf16x2(sum.z, sum.w));
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+bool gemm_decode_supported(int M, int K, int N, int group_size) {
+    return group_size == DG_GROUP && K % DG_GROUP == 0 && N % 32 == 0 && M >= 1 && M <= DG_MAX_ROWS && K > 0 &&
+           N > 0 && (N + DG_BN - 1) / DG_BN <= DG_MAX_TILES && device_is_sm100();
+}
+
+static int dg_rows(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : 64); }
+
+static int dg_sm_count() {
+    const int sms = device_sm_count();
+    return sms > 0 ? sms : 148;
+}
+// Slots a tile needs: the most CTAs whose ranges can reach into one tile.
+static int dg_slots_per_tile(int tiles) { return dg_sm_count() / tiles + 2; }
+
+// The slots of every tile.
+size_t gemm_decode_workspace_bytes(int M, int N) {
+    if (M < 1 || N < 1) return 0;
+    const size_t tiles = (size_t)(N + DG_BN - 1) / DG_BN;
+    return tiles * dg_slots_per_tile((int)tiles) * DG_BN * dg_rows(M) * 4;
+}
+
+template <int NB>
+static int launch_dg(const CUtensorMap &tmA, const CUtensorMap &tmW, const CUtensorMap &tmS, const CUtensorMap &tmZ, uint16_t *C,
+                     const uint16_t *residual, int epilogue, int M, int N, int K, int tiles, void *workspace, cudaStream_t stream) {
+    using Cfg = DgCfg<NB>;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(gemm_decode_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    });
+    if (attr_err != cudaSuccess) return check_cuda(attr_err, "decode gemm: shared memory attribute");
+    const int sms = dg_sm_count();
+    const long long U = (long long)tiles * (K / DG_GROUP);
+    const int ctas = (long long)sms < U ? sms : (int)U;
+    float *slots = reinterpret_cast<float *>(workspace);
+    const int spt = dg_slots_per_tile(tiles);
+    gemm_decode_kernel<NB><<<ctas, DG_THREADS, Cfg::SMEM_BYTES, stream>>>(
+        tmA, tmW, tmS, tmZ, M, N, K, tiles, slots, spt, wait_limit_cycles());
+    int rc = check_cuda(cudaGetLastError(), "decode gemm launch");
+    if (rc) return rc;
+    const long long quads = (long long)tiles * M * (DG_BN / 4);
+    const int blocks = (int)((quads + 255) / 256 < 8LL * sms ? (quads + 255) / 256 : 8LL * sms);
+    gemm_decode_fixup_kernel<NB><<<blocks, 256, 0, stream>>>(C, residual, epilogue, M, N, K / DG_GROUP, tiles, ctas, slots, spt);
+    return check_cuda(cudaGetLastError(), "decode gemm fix-up launch");
+}
+
+int launch_gemm_decode(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros, const uint16_t *scales, uint16_t *C, int M,
+                       int K, int N, cudaStream_t stream, int epilogue, const uint16_t *residual, void *workspace,
+                       size_t workspace_bytes) {
+    const size_t need = gemm_decode_workspace_bytes(M, N);
+    if (!workspace || workspace_bytes < need)
+        return set_error(AWQ_ERR_WORKSPACE, "gemm_decode: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+    const int G = K / DG_GROUP, nb = N / 8, rows = dg_rows(M);
+    const int tiles = (N + DG_BN - 1) / DG_BN;
+    CUtensorMap tmA, tmW, tmS, tmZ;
+    int rc;
+    // token rows as (64 k, rows, K / 64): one copy brings the two 64-k tiles of a unit
+    if ((rc = encode_tensor_map_3d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, A, DG_BK, M, K / DG_BK, (uint64_t)K * 2, DG_BK * 2, DG_BK,
+                                   rows, 2, CU_TENSOR_MAP_SWIZZLE_128B)))
+        return rc;
+    if ((rc = encode_tensor_map_2d(&tmW, CU_TENSOR_MAP_DATA_TYPE_INT32, qweight, nb, K, (uint64_t)nb * 4, DG_BN / 8, DG_GROUP,
+                                   CU_TENSOR_MAP_SWIZZLE_128B)))
+        return rc;
+    if ((rc = encode_tensor_map_2d(&tmS, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, scales, N, G, (uint64_t)N * 2, DG_BN, 1,
+                                   CU_TENSOR_MAP_SWIZZLE_NONE)))
+        return rc;
+    if ((rc = encode_tensor_map_2d(&tmZ, CU_TENSOR_MAP_DATA_TYPE_INT32, qzeros, nb, G, (uint64_t)nb * 4, DG_BN / 8, 1,
+                                   CU_TENSOR_MAP_SWIZZLE_NONE)))
+        return rc;
+#define DG_LAUNCH(NBV) launch_dg<NBV>(tmA, tmW, tmS, tmZ, C, residual, epilogue, M, N, K, tiles, workspace, stream)
+    return rows == 16 ? DG_LAUNCH(16) : (rows == 32 ? DG_LAUNCH(32) : DG_LAUNCH(64));
+#undef DG_LAUNCH
+}
+
+int gemm_decode_check(cudaStream_t stream) {
+    int flag = 0;
+    int rc = check_cuda(cudaStreamSynchronize(stream), "gemm_decode_check sync");
+    if (rc) return rc;
+    rc = check_cuda(cudaMemcpyFromSymbol(&flag, g_gemm_dec_error, sizeof(int)), "gemm_decode_check read");
+    if (rc) return rc;
+    if (flag != 0) {
+        int zero = 0;
+        cudaMemcpyToSymbol(g_gemm_dec_error, &zero, sizeof(int));
+        return set_error(AWQ_ERR_DEVICE_TIMEOUT,
+                         "decode gemm: a device-side wait gave up (role %d: 1 producer, 2/3 MMA issuer, 4 dequant, 5 epilogue); "
+                         "re-initialise the workspace", flag);
+    }
+    return AWQ_OK;
+}
+
+}  // namespace awq

@@ -128,6 +128,9 @@ class DecodeFFNStack:
         maxN = max([hidden] + [l.gateup.N for l in self.layers])
         self.ws = Workspace(maxK, maxN, device=device)
         max_il = max(l.down.K for l in self.layers)
+        # split-K sums of the batched-decode GEMM (batches of 9 to 64 rows on one GPU)
+        self.gemm_ws = ops.GemmDecodeWorkspace(maxN, device=device, batch=min(max_batch, 64)) \
+            if self.tp == 1 and max_batch >= self.GEMM_BATCH else None
         bf = dict(dtype=torch.bfloat16, device=device)
         self._h = [torch.zeros((max_batch, hidden), **bf) for _ in range(2)]  # zeros: a capture's warm-up run reads them
         # intermediates between the kernels of a layer are fp16 (the GEMV kernel's fastest input)
@@ -191,13 +194,12 @@ class DecodeFFNStack:
     def uses_fused(self, batch: int) -> bool:
         return self.plan is not None and batch <= 8
 
-    # From this batch on one GPU, a layer is two tensor-core GEMMs (weights dequantised once per pass
-    # into shared memory, SwiGLU / residual in the epilogue) instead of one GEMV pass per 8 rows:
-    # measured per 70B layer, a GEMM pass costs as much as 4.9 GEMV passes.
-    GEMM_BATCH = 40
+    # From this batch on one GPU, a layer is two batched-decode tensor-core GEMMs (weights streamed once
+    # per layer whatever the batch, SwiGLU / residual in the epilogue) instead of one GEMV pass per 8 rows.
+    GEMM_BATCH = 9
 
     def uses_gemm(self, batch: int) -> bool:
-        if self.tp != 1 or batch < self.GEMM_BATCH:
+        if self.tp != 1 or batch < self.GEMM_BATCH or batch > 64 or self.gemm_ws is None:
             return False
         return all(l.gamma is not None and l.gateup.group_size == 128 and l.down.group_size == 128 and
                    l.gateup.K % 128 == 0 and l.down.K % 128 == 0 and l.gateup.N % 32 == 0 and l.down.N % 32 == 0
@@ -208,7 +210,7 @@ class DecodeFFNStack:
         if self.uses_fused(batch):
             return 1
         if self.uses_gemm(batch):
-            return 3 * len(self.layers)
+            return 5 * len(self.layers)  # norm, and two launches (product, sum of the SMs' shares + epilogue) per GEMM
         passes = (batch + 7) // 8  # the decode kernels take 8 rows per launch
         n = len(self.layers)
         if self.tp == 1:
@@ -236,8 +238,8 @@ class DecodeFFNStack:
                 il = l.down.K
                 it = inter.view(-1)[:B * il].view(B, il).view(torch.bfloat16)
                 ops.rmsnorm(h, l.gamma, self.eps, out=nb)
-                ops.gemm(nb, l.gateup, out=it, swiglu=True)
-                ops.gemm(it, l.down, out=other, residual=h)
+                ops.gemm_decode(nb, l.gateup, self.gemm_ws, out=it, swiglu=True)
+                ops.gemm_decode(it, l.down, self.gemm_ws, out=other, residual=h)
                 h, other = other, h
             return h
         if self.tp == 1:
@@ -317,3 +319,5 @@ class DecodeFFNStack:
 
     def check(self):
         self.ws.check()
+        if self.gemm_ws is not None:
+            ops.gemm_check()

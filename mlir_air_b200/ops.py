@@ -106,7 +106,8 @@ def set_decode_kernel(mode: str):
 
 
 def set_deterministic(on: bool):
-    """Sum split-K partials in a fixed order (bit-reproducible, slower) instead of f32 atomics."""
+    """Kept for callers of earlier versions; a no-op: split-K partials are summed as integers, so every result is
+    bit-reproducible already."""
     _lib.call("awq_b200_set_deterministic", 1 if on else 0)
 
 
@@ -362,6 +363,36 @@ def gemm(A, w: AwqWeight, out=None, residual=None, swiglu=False):
         out = torch.empty((A.shape[0], w.N), dtype=torch.bfloat16, device=A.device)
     _lib.call("awq_b200_gemm_bf16", _ptr(A), _ptr(w.qweight), _ptr(w.qzeros), _ptr(w.scales), _ptr(out), A.shape[0],
               w.K, w.N, w.group_size, _stream())
+    return out
+
+
+class GemmDecodeWorkspace:
+    """Caller-owned scratch of `gemm_decode` (the f32 sums of each SM's share of a tile) for up to `batch` rows and `N`
+    columns.  One per stream: calls that share it must not overlap on the GPU."""
+
+    def __init__(self, N: int, device="cuda", batch: int = 64):
+        self.batch, self.N = int(batch), int(N)
+        self.nbytes = int(_lib.load().awq_b200_gemm_decode_workspace_bytes(self.batch, self.N))
+        self.buf = torch.empty(self.nbytes, dtype=torch.uint8, device=device)
+
+    def fits(self, M, N):
+        return int(_lib.load().awq_b200_gemm_decode_workspace_bytes(int(M), int(N))) <= self.nbytes
+
+
+def gemm_decode(A, w: AwqWeight, ws: GemmDecodeWorkspace, out=None, residual=None, swiglu=False):
+    """C [M, N] = A [M, K] @ W for a decode batch of M <= 64 rows (weights streamed once, all SMs busy whatever the
+    shape); `residual` / `swiglu` as in `gemm`."""
+    _want(A, torch.bfloat16, "A")
+    if A.dim() != 2 or A.shape[1] != w.K:
+        raise _lib.AwqBackendError(f"A must be [M, {w.K}], got {tuple(A.shape)}")
+    n_out = w.N // 2 if swiglu else w.N
+    if out is None:
+        out = torch.empty((A.shape[0], n_out), dtype=torch.bfloat16, device=A.device)
+    _want(out, torch.bfloat16, "out")
+    if residual is not None:
+        _want(residual, torch.bfloat16, "residual")
+    _lib.call("awq_b200_gemm_decode_bf16", _ptr(A), _ptr(w.qweight), _ptr(w.qzeros), _ptr(w.scales), _ptr(residual), _ptr(out),
+              1 if swiglu else 0, A.shape[0], w.K, w.N, w.group_size, _ptr(ws.buf), ws.nbytes, _stream())
     return out
 
 

@@ -196,8 +196,8 @@ def test_gemm_epilogues_vs_oracle(ops, M, K, N):
 
 
 def test_stack_large_batch_takes_the_gemm_path(ops):
-    """Batch 40 and 64 on one GPU: two tensor-core GEMMs per layer; same results as one GEMV pass per
-    8 rows (the path batch 16 takes) and as the oracle."""
+    """Batches 9 to 64 on one GPU: two batched-decode tensor-core GEMMs per layer; same results as one pass of the
+    stack kernel per 8 rows and as the oracle; run twice to show that a step leaves the split-K workspace clean."""
     import torch
     from gpu_util import randn_bf16, to_dev, to_host
     from mlir_air_b200 import ffn
@@ -205,14 +205,15 @@ def test_stack_large_batch_takes_the_gemm_path(ops):
     layers_np = _layers_np(H, I, L, seed=77)
     plan, gus, downs, gammas = _plan(ops, layers_np)
     stack = ffn.DecodeFFNStack([ffn.FFNLayer(g, d, gm) for g, d, gm in zip(gus, downs, gammas)], H, max_batch=64)
-    assert stack.uses_gemm(40) and stack.uses_gemm(64) and not stack.uses_gemm(32)
-    assert stack.launches_per_step(64) == 3 * L
-    for B in (40, 64):
+    assert stack.uses_gemm(9) and stack.uses_gemm(64) and not stack.uses_gemm(8)
+    assert stack.launches_per_step(64) == 5 * L
+    for B in (9, 32, 40, 64):
         x = randn_bf16((B, H), seed=B)
         y = to_host(stack.step(to_dev(x)))
         ops.gemm_check()
         assert O.rel_l2(y, _oracle_stack(x, layers_np)) <= REL_L2_TOL
-        # the GEMV path on the same rows, 16 at a time
+        assert np.array_equal(y.view(np.uint16), to_host(stack.step(to_dev(x))).view(np.uint16))
+        # the stack kernel on the same rows, 8 at a time
         parts = [to_host(stack.step(to_dev(x[i:i + 8]))) for i in range(0, B, 8)]
         # the GEMM multiplies bf16-rounded weights, the GEMV keeps (q - z) s in f32: both inside the bar
         assert O.rel_l2(y, np.concatenate(parts, 0)) <= REL_L2_TOL
@@ -220,3 +221,48 @@ def test_stack_large_batch_takes_the_gemm_path(ops):
         g1 = to_host(stack.replay(B).clone())
         assert O.rel_l2(g1, _oracle_stack(x, layers_np)) <= REL_L2_TOL
     stack.check()
+
+
+# (M, K, N): one k-block pair and one tile; a ragged last tile; more units than SMs with tiles shared by several SMs and
+# SMs covering several tiles; K deeper than the input ring many times over
+@pytest.mark.parametrize("M,K,N", [(9, 128, 256), (16, 256, 32), (33, 1024, 1312), (64, 2048, 5632), (64, 8192, 512),
+                                   (17, 512, 800), (48, 1024, 2048), (12, 5632, 2048)])
+def test_gemm_decode_vs_oracle(ops, M, K, N):
+    """Batched-decode GEMM (stream-K over column tiles and k-blocks, split-K sums as integers) against the oracle, all
+    three epilogues; a second call on the same workspace gives the same bits."""
+    from gpu_util import dev_weight, randn_bf16, synth_awq, to_dev, to_host
+    bits = lambda a: a.view(np.uint16)  # noqa: E731
+    A = randn_bf16((M, K), seed=M + 1)
+    w = synth_awq(K, N, 128, seed=N + 2)
+    R = randn_bf16((M, N), seed=3)
+    ws = ops.GemmDecodeWorkspace(N, batch=M)
+    dw = dev_weight(*w)
+    y = to_host(ops.gemm_decode(to_dev(A), dw, ws))
+    ops.gemm_check()
+    ref_bf16w = (A.astype(np.float32) @ O.dequant_to_bf16(*w, 128).astype(np.float32)).astype(bfloat16)
+    assert O.rel_l2(y, ref_bf16w) <= 3e-3  # same products, summation order only
+    assert O.rel_l2(y, O.gemv_A_ref(A, *w, 128)) <= REL_L2_TOL
+    yr = to_host(ops.gemm_decode(to_dev(A), dw, ws, residual=to_dev(R)))
+    ops.gemm_check()
+    assert O.rel_l2(yr, O.gemv_A_ref(A, *w, 128, residual=R)) <= REL_L2_TOL
+    assert np.array_equal(bits(yr), bits(to_host(ops.gemm_decode(to_dev(A), dw, ws, residual=to_dev(R)))))
+    if N % 64 == 0:
+        gate, up = synth_awq(K, N // 2, 128, seed=4), synth_awq(K, N // 2, 128, seed=5)
+        wgu = ops.interleave_gate_up(dev_weight(*gate), dev_weight(*up))
+        t = to_host(ops.gemm_decode(to_dev(A), wgu, ws, swiglu=True))
+        ops.gemm_check()
+        assert t.shape == (M, N // 2)
+        assert O.rel_l2(t, O.gateup_swiglu_A_ref(A, gate, up, 128)) <= REL_L2_TOL
+
+
+def test_gemm_decode_rejects_what_it_cannot_run(ops):
+    import torch
+    from gpu_util import dev_weight, randn_bf16, synth_awq, to_dev
+    from mlir_air_b200._lib import AwqBackendError
+    w = dev_weight(*synth_awq(256, 256, 128, seed=1))
+    ws = ops.GemmDecodeWorkspace(256, batch=16)
+    with pytest.raises(AwqBackendError):  # more rows than the kernel takes
+        ops.gemm_decode(to_dev(randn_bf16((65, 256), seed=1)), w, ws)
+    with pytest.raises(AwqBackendError):  # workspace too small for these rows (sized for 16, called with 17)
+        ops.gemm_decode(to_dev(randn_bf16((17, 256), seed=1)), w, ws)
+    assert ops.gemm_decode(torch.zeros((0, 256), dtype=torch.bfloat16, device="cuda"), w, ws).shape == (0, 256)

@@ -95,7 +95,7 @@ def test_stack_launch_accounting():
     class _L:  # just enough of a layer for the accounting helper
         pass
     s = ffn.DecodeFFNStack.__new__(ffn.DecodeFFNStack)
-    s.layers, s.tp, s.plan = [None] * 80, 1, None
+    s.layers, s.tp, s.plan, s.gemm_ws = [None] * 80, 1, None, None  # no split-K workspace: batches above 8 take GEMV passes
     assert s.launches_per_step(8) == 240 and s.launches_per_step(16) == 80 * 5
     s.uses_gemm = lambda batch: False
     s.plan = object()  # with a fused plan: one launch for up to 8 rows, per-layer kernels beyond
