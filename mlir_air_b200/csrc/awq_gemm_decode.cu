@@ -140,15 +140,6 @@ __device__ __forceinline__ void dg_tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (
         : "r"(taddr)
         : "memory");
 }
-// One lane of a converged warp.  The code around it stays warp-uniform, so that the compiler keeps descriptors and
-// addresses in uniform registers, which is where the TMA and MMA instructions take them from: issued from inside an
-// `if (lane == 0)` region instead, every operand is first moved over from a vector register, and one tcgen05.mma or
-// cp.async.bulk.tensor then costs the issuing thread 100 to 200 cycles.
-__device__ __forceinline__ bool dg_elect_one() {
-    uint32_t pred;
-    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
-    return pred != 0;
-}
 __device__ __forceinline__ void dg_tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // K-major tile of 128-byte rows, 128B swizzle, 8-row atoms 1024 B apart.
 __device__ __forceinline__ uint64_t dg_desc_sw128(uint32_t smem_addr) {
@@ -259,7 +250,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     if (warp == 0) {
         // ------------------------------ producer ------------------------------
         // the whole warp walks the units; one elected lane issues the unit's four copies
-        if (dg_elect_one()) {
+        if (elect_one()) {
             tma_prefetch_desc(&tmA);
             tma_prefetch_desc(&tmW);
             tma_prefetch_desc(&tmS);
@@ -269,13 +260,13 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         int it = 0;
         for (UnitWalk w(tiles, KB); w.valid(); ++w.u, ++it) {
             const int s = it % STAGES, round = it / STAGES;
-            if (round > 0 && !mbar_wait_bounded(empty_bar(s), (round - 1) & 1, wait_limit)) {
+            if (round > 0 && !mbar_wait_bounded_warp(empty_bar(s), (round - 1) & 1, wait_limit)) {
                 if (lane == 0) atomicExch(&g_gemm_dec_error, 1);
                 break;
             }
             const int n0 = w.tile() * DG_BN, g = w.kb();
             const uint32_t st = stage_addr(s), bar = full_bar(s);
-            if (dg_elect_one()) {
+            if (elect_one()) {
                 mbar_expect_tx(bar, TX_BYTES);
                 tma_load_3d(st, &tmA, 0, 0, 2 * g, bar);
                 tma_load_2d_hint(st + Cfg::A_BYTES, &tmW, n0 / 8, g * DG_GROUP, bar, stream_policy);
@@ -293,7 +284,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         while (w.valid() && ok) {
             const int n_seg = w.left_in_tile();  // this segment: n_seg units of one tile
             const int b = seg_it & 1, use = seg_it >> 1;
-            if (use >= 1 && !mbar_wait_bounded(acc_empty(b), (use - 1) & 1, wait_limit)) {
+            if (use >= 1 && !mbar_wait_bounded_warp(acc_empty(b), (use - 1) & 1, wait_limit)) {
                 if (lane == 0) atomicExch(&g_gemm_dec_error, 2);
                 break;
             }
@@ -302,8 +293,8 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             for (int i = 0; i < n_seg; ++i, ++it, ++w.u) {
                 const int s = it % STAGES, round = it / STAGES;
                 const int ab = it % Cfg::ABUF, around = it / Cfg::ABUF;
-                if (!mbar_wait_bounded(full_bar(s), round & 1, wait_limit) ||
-                    !mbar_wait_bounded(ready_bar(ab), around & 1, wait_limit)) {
+                if (!mbar_wait_bounded_warp(full_bar(s), round & 1, wait_limit) ||
+                    !mbar_wait_bounded_warp(ready_bar(ab), around & 1, wait_limit)) {
                     if (lane == 0) atomicExch(&g_gemm_dec_error, 3);
                     ok = false;
                     break;
@@ -313,7 +304,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 // token rows: K-major 128-byte rows, two tiles of 64 k, 32 bytes further in the row per step
                 const uint64_t x_desc = dg_desc_sw128(stage_addr(s));
                 const uint32_t acc0 = i ? 1u : 0u;
-                if (dg_elect_one()) {
+                if (elect_one()) {
 #pragma unroll
                     for (int k16 = 0; k16 < DG_GROUP / 16; ++k16) {
 #pragma unroll
@@ -327,7 +318,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 }
                 __syncwarp();
             }
-            if (ok && dg_elect_one()) dg_umma_commit(acc_full(b));
+            if (ok && elect_one()) dg_umma_commit(acc_full(b));
             __syncwarp();
             ++seg_it;
         }

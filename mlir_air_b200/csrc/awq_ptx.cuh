@@ -52,6 +52,24 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     }
 }
 
+// One lane of a converged warp.  The code around it stays warp-uniform, so that the compiler keeps descriptors and
+// addresses in uniform registers, which is where the TMA and MMA instructions take them from: issued from inside an
+// `if (lane == 0)` region instead, every operand is first moved over from a vector register, and one tcgen05.mma or
+// cp.async.bulk.tensor then costs the issuing thread 100 to 200 cycles.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+
+// The same wait for a converged warp whose code must stay warp-uniform: lane 0 polls (one lane's worth of issue
+// slots, like a single waiting thread), every lane gets the answer.
+__device__ __forceinline__ bool mbar_wait_bounded_warp(uint32_t bar, uint32_t parity, long long limit) {
+    int ok = 0;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait_bounded(bar, parity, limit) ? 1 : 0;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
     uint64_t p;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));

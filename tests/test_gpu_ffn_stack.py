@@ -89,22 +89,25 @@ def test_stack_llama70b_dims_matches_per_layer_kernels(ops):
     plain = ffn.DecodeFFNStack(layers, H, max_batch=16, fused=False)
     assert fused.uses_fused(8) and not fused.uses_fused(16) and not plain.uses_fused(8)
     assert fused.launches_per_step(8) == 1
+    gen = torch.Generator(device="cuda").manual_seed(1234)
     for B in (8, 1):
-        x = (torch.randn((B, H), device="cuda") * 0.5).to(torch.bfloat16)
+        x = (torch.randn((B, H), device="cuda", generator=gen) * 0.5).to(torch.bfloat16)
         a = fused.step(x).float()
         b = plain.step(x).float()
         fused.check()
         plain.check()
         assert torch.isfinite(a).all()
+        # two valid paths (fp16 against bf16 intermediates, different summation orders), each inside the bar against
+        # the oracle: between them the same bar
         rel = float((a - b).norm() / b.norm())
-        assert rel <= 5e-3, (B, rel)
+        assert rel <= REL_L2_TOL, (B, rel)
         fused.load_input(x)
         g1 = fused.replay(B).float().clone()
         fused.load_input(x)
         g2 = fused.replay(B).float().clone()
         fused.check()
-        assert float((g1 - b).norm() / b.norm()) <= 5e-3
-        assert float((g2 - b).norm() / b.norm()) <= 5e-3
+        assert float((g1 - b).norm() / b.norm()) <= REL_L2_TOL
+        assert float((g2 - b).norm() / b.norm()) <= REL_L2_TOL
     # a batch the fused kernel does not take goes through the per-layer kernels
     x = (torch.randn((16, H), device="cuda") * 0.5).to(torch.bfloat16)
     rel = float((fused.step(x).float() - plain.step(x).float()).norm() / plain.step(x).float().norm())
