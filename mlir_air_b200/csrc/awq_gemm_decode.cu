@@ -82,7 +82,7 @@ struct DgCfg {
     static constexpr int STAGES = RING_BUDGET / STAGE_BYTES < 8 ? RING_BUDGET / STAGE_BYTES : 8;
     static constexpr int ABUF = (int)(DG_TMEM_COLS - 4 * NB) / DG_ABUF_COLS;  // weight buffers: 3 up to 32 rows, 2 with 64
     static constexpr int ACC_COL0 = ABUF * DG_ABUF_COLS;                      // accumulators start behind them
-    static constexpr int NUM_BARS = 2 * STAGES + 2 * ABUF + 4;
+    static constexpr int NUM_BARS = 3 * STAGES + 2 * ABUF + 4;
     static constexpr int OFF_BARS = STAGES * STAGE_BYTES;
     static constexpr int SMEM_BYTES = OFF_BARS + NUM_BARS * 8 + 16 + 1024;
     // f32 accumulate, bf16 x bf16, A (weights, tensor memory) and B (token rows) K-major, M 128, N NB
@@ -211,7 +211,8 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t bar_base = smem_base + Cfg::OFF_BARS;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_gen + Cfg::OFF_BARS + Cfg::NUM_BARS * 8);
-    auto full_bar = [&](int s) { return bar_base + 8u * s; };                     // TMA landed in input stage s
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };                     // packed words, scales, zeros landed in stage s
+    auto xfull_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 2 * Cfg::ABUF + 4 + s); };  // its token rows landed
     auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };         // MMA and dequant done with input stage s
     auto ready_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };     // weight buffer b dequantised
     auto bfree_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + Cfg::ABUF + b); };       // MMA done with weight buffer b
@@ -220,12 +221,13 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     auto stage_addr = [&](int s) { return smem_base + (uint32_t)s * Cfg::STAGE_BYTES; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    constexpr uint32_t TX_BYTES = Cfg::A_BYTES + DG_W_BYTES + DG_S_BYTES + DG_Z_BYTES;
+    constexpr uint32_t W_TX_BYTES = DG_W_BYTES + DG_S_BYTES + DG_Z_BYTES;
     const int KB = K / DG_GROUP;  // units per tile
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full_bar(s), 1);
+            mbar_init(xfull_bar(s), 1);
             mbar_init(empty_bar(s), 1 + DG_DEQUANT_WARPS);  // the MMA's commit and the dequant warps (they read W, S, Z)
         }
         for (int b = 0; b < Cfg::ABUF; ++b) {
@@ -246,6 +248,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     __syncthreads();
     dg_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
 
     if (warp == 0) {
         // ------------------------------ producer ------------------------------
@@ -257,23 +260,39 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             tma_prefetch_desc(&tmZ);
         }
         const uint64_t stream_policy = l2_policy_evict_first();
+        auto load_weights = [&](int s, int n0, int g) {
+            const uint32_t st = stage_addr(s) + Cfg::A_BYTES, bar = full_bar(s);
+            if (elect_one()) {
+                mbar_expect_tx(bar, W_TX_BYTES);
+                tma_load_2d_hint(st, &tmW, n0 / 8, g * DG_GROUP, bar, stream_policy);
+                tma_load_2d(st + DG_W_BYTES, &tmS, n0, g, bar);
+                tma_load_2d(st + DG_W_BYTES + DG_S_BYTES, &tmZ, n0 / 8, g, bar);
+            }
+            __syncwarp();
+        };
+        auto load_rows = [&](int s, int g) {
+            if (elect_one()) {
+                mbar_expect_tx(xfull_bar(s), Cfg::A_BYTES);
+                tma_load_3d(stage_addr(s), &tmA, 0, 0, 2 * g, xfull_bar(s));
+            }
+            __syncwarp();
+        };
+        // The weights do not depend on the previous kernel in the stream: fill the ring with them, and only then wait for
+        // that kernel, whose output the token rows are.
+        UnitWalk w(tiles, KB);
         int it = 0;
-        for (UnitWalk w(tiles, KB); w.valid(); ++w.u, ++it) {
+        for (UnitWalk f = w; f.valid() && it < STAGES; ++f.u, ++it) load_weights(it, f.tile() * DG_BN, f.kb());
+        pdl_wait();
+        it = 0;
+        for (UnitWalk f = w; f.valid() && it < STAGES; ++f.u, ++it) load_rows(it, f.kb());
+        for (w.u += it; w.valid(); ++w.u, ++it) {
             const int s = it % STAGES, round = it / STAGES;
-            if (round > 0 && !mbar_wait_bounded_warp(empty_bar(s), (round - 1) & 1, wait_limit)) {
+            if (!mbar_wait_bounded_warp(empty_bar(s), (round - 1) & 1, wait_limit)) {
                 if (lane == 0) atomicExch(&g_gemm_dec_error, 1);
                 break;
             }
-            const int n0 = w.tile() * DG_BN, g = w.kb();
-            const uint32_t st = stage_addr(s), bar = full_bar(s);
-            if (elect_one()) {
-                mbar_expect_tx(bar, TX_BYTES);
-                tma_load_3d(st, &tmA, 0, 0, 2 * g, bar);
-                tma_load_2d_hint(st + Cfg::A_BYTES, &tmW, n0 / 8, g * DG_GROUP, bar, stream_policy);
-                tma_load_2d(st + Cfg::A_BYTES + DG_W_BYTES, &tmS, n0, g, bar);
-                tma_load_2d(st + Cfg::A_BYTES + DG_W_BYTES + DG_S_BYTES, &tmZ, n0 / 8, g, bar);
-            }
-            __syncwarp();
+            load_weights(s, w.tile() * DG_BN, w.kb());
+            load_rows(s, w.kb());
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
@@ -293,7 +312,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             for (int i = 0; i < n_seg; ++i, ++it, ++w.u) {
                 const int s = it % STAGES, round = it / STAGES;
                 const int ab = it % Cfg::ABUF, around = it / Cfg::ABUF;
-                if (!mbar_wait_bounded_warp(full_bar(s), round & 1, wait_limit) ||
+                if (!mbar_wait_bounded_warp(xfull_bar(s), round & 1, wait_limit) ||
                     !mbar_wait_bounded_warp(ready_bar(ab), around & 1, wait_limit)) {
                     if (lane == 0) atomicExch(&g_gemm_dec_error, 3);
                     ok = false;
@@ -390,6 +409,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     } else if (warp >= DG_EPI_WARP0) {
         // ------------------------------ drain ------------------------------
         const int q = warp & 3;  // this warp's 32 TMEM lanes: columns 32 q + lane of each 128-column half
+        pdl_wait();  // the previous kernel in the stream may still be reading the slots
         int seg_it = 0;
         UnitWalk w(tiles, KB);
         while (w.valid()) {
@@ -437,36 +457,36 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 }
 
 // Second pass: one thread per four columns of a token row adds the slots of the tile's contributors in their order and
-// applies the epilogue.  `main_ctas` is the main kernel's grid size (the ranges of its CTAs decide who contributed to
-// which tile).
+// applies the epilogue.  A block takes four token rows of one tile.  `main_ctas` is the main kernel's grid size (the
+// ranges of its CTAs decide who contributed to which tile).
 template <int NB>
 __global__ void __launch_bounds__(256)
 gemm_decode_fixup_kernel(uint16_t *__restrict__ C, const uint16_t *__restrict__ R, int epi, int M, int N, int KB, int tiles,
                          int main_ctas, const float *__restrict__ slots, int slots_per_tile) {
-    const int per_tile = M * (DG_BN / 4);
-    const long long total = (long long)tiles * per_tile;
-    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
-        const int tile = (int)(idx / per_tile), rest = (int)(idx - (long long)tile * per_tile);
-        const int m = rest / (DG_BN / 4), col = 4 * (rest - m * (DG_BN / 4)), n = tile * DG_BN + col;
-        if (n >= N) continue;
-        const long long U = (long long)tiles * KB;
-        const int first = (int)((((long long)tile * KB + 1) * main_ctas + U - 1) / U) - 1;
-        const int last = (int)((((long long)(tile + 1) * KB) * main_ctas + U - 1) / U) - 1;
-        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int c = 0; c <= last - first; ++c) {
-            const float4 v = __ldcg(reinterpret_cast<const float4 *>(slots + (((size_t)tile * slots_per_tile + c) * NB + m) * DG_BN + col));
-            sum.x += v.x, sum.y += v.y, sum.z += v.z, sum.w += v.w;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row_chunks = (M + 3) >> 2;
+    const int tile = blockIdx.x / row_chunks, m = 4 * (blockIdx.x - tile * row_chunks) + (threadIdx.x >> 6);
+    const int col = 4 * (threadIdx.x & 63), n = tile * DG_BN + col;
+    if (m >= M || n >= N) return;
+    const long long U = (long long)tiles * KB;
+    const int first = (int)((((long long)tile * KB + 1) * main_ctas + U - 1) / U) - 1;
+    const int last = (int)((((long long)(tile + 1) * KB) * main_ctas + U - 1) / U) - 1;
+    const float *src = slots + (((size_t)tile * slots_per_tile) * NB + m) * DG_BN + col;
+    float4 sum = __ldcg(reinterpret_cast<const float4 *>(src));
+    for (int c = 1; c <= last - first; ++c) {
+        const float4 v = __ldcg(reinterpret_cast<const float4 *>(src + (size_t)c * NB * DG_BN));
+        sum.x += v.x, sum.y += v.y, sum.z += v.z, sum.w += v.w;
+    }
+    if (epi == GEMM_EPI_SWIGLU) {
+        const uint32_t o = (uint32_t)swiglu_bits(sum.x, sum.y) | ((uint32_t)swiglu_bits(sum.z, sum.w) << 16);
+        *reinterpret_cast<uint32_t *>(C + (size_t)m * (N >> 1) + (n >> 1)) = o;
+    } else {
+        if (epi == GEMM_EPI_RESIDUAL) {
+            const uint2 rv = *reinterpret_cast<const uint2 *>(R + (size_t)m * N + n);
+            sum.x += bf16x2_lo(rv.x), sum.y += bf16x2_hi(rv.x), sum.z += bf16x2_lo(rv.y), sum.w += bf16x2_hi(rv.y);
         }
-        if (epi == GEMM_EPI_SWIGLU) {
-            const uint32_t o = (uint32_t)swiglu_bits(sum.x, sum.y) | ((uint32_t)swiglu_bits(sum.z, sum.w) << 16);
-            *reinterpret_cast<uint32_t *>(C + (size_t)m * (N >> 1) + (n >> 1)) = o;
-        } else {
-            if (epi == GEMM_EPI_RESIDUAL) {
-                const uint2 rv = *reinterpret_cast<const uint2 *>(R + (size_t)m * N + n);
-                sum.x += bf16x2_lo(rv.x), sum.y += bf16x2_hi(rv.x), sum.z += bf16x2_lo(rv.y), sum.w += bf16x2_hi(rv.y);
-            }
-            *reinterpret_cast<uint2 *>(C + (size_t)m * N + n) = make_uint2(pack_bf16x2(sum.x, sum.y), pack_bf16x2(sum.z, sum.w));
-        }
+        *reinterpret_cast<uint2 *>(C + (size_t)m * N + n) = make_uint2(pack_bf16x2(sum.x, sum.y), pack_bf16x2(sum.z, sum.w));
     }
 }
 
@@ -507,14 +527,14 @@ static int launch_dg(const CUtensorMap &tmA, const CUtensorMap &tmW, const CUten
     const int ctas = (long long)sms < U ? sms : (int)U;
     float *slots = reinterpret_cast<float *>(workspace);
     const int spt = dg_slots_per_tile(tiles);
-    gemm_decode_kernel<NB><<<ctas, DG_THREADS, Cfg::SMEM_BYTES, stream>>>(
-        tmA, tmW, tmS, tmZ, M, N, K, tiles, slots, spt, wait_limit_cycles());
-    int rc = check_cuda(cudaGetLastError(), "decode gemm launch");
+    int rc = check_cuda(launch_pdl(gemm_decode_kernel<NB>, dim3(ctas), dim3(DG_THREADS), Cfg::SMEM_BYTES, stream, tmA, tmW, tmS, tmZ, M, N, K,
+                                   tiles, slots, spt, wait_limit_cycles()),
+                        "decode gemm launch");
     if (rc) return rc;
-    const long long quads = (long long)tiles * M * (DG_BN / 4);
-    const int blocks = (int)((quads + 255) / 256 < 8LL * sms ? (quads + 255) / 256 : 8LL * sms);
-    gemm_decode_fixup_kernel<NB><<<blocks, 256, 0, stream>>>(C, residual, epilogue, M, N, K / DG_GROUP, tiles, ctas, slots, spt);
-    return check_cuda(cudaGetLastError(), "decode gemm fix-up launch");
+    const int blocks = tiles * ((M + 3) / 4);
+    return check_cuda(launch_pdl(gemm_decode_fixup_kernel<NB>, dim3(blocks), dim3(256), 0, stream, C, residual, epilogue, M, N, K / DG_GROUP,
+                                 tiles, ctas, (const float *)slots, spt),
+                      "decode gemm fix-up launch");
 }
 
 int launch_gemm_decode(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros, const uint16_t *scales, uint16_t *C, int M,

@@ -195,8 +195,9 @@ class DecodeFFNStack:
         return self.plan is not None and batch <= 8
 
     # From this batch on one GPU, a layer is two batched-decode tensor-core GEMMs (weights streamed once
-    # per layer whatever the batch, SwiGLU / residual in the epilogue) instead of one GEMV pass per 8 rows.
-    GEMM_BATCH = 9
+    # per layer whatever the batch, SwiGLU / residual in the epilogue) instead of one GEMV pass per 8 rows
+    # (up to 16 rows the two-tile GEMV pass measured the same).
+    GEMM_BATCH = 17
 
     def uses_gemm(self, batch: int) -> bool:
         if self.tp != 1 or batch < self.GEMM_BATCH or batch > 64 or self.gemm_ws is None:
