@@ -264,7 +264,9 @@ int awq_b200_tp_reduce_add_rmsnorm_act(const uint16_t *h, const void *const *pee
 /* Tuning of the stack kernel; a negative value leaves a setting as it is.
  * lookahead_units: 36 KB units per half-CTA requested into L2 ahead of the shared-memory ring
  *   (default 0 = off, at most 64).
- * split_per_1024: ignored (the two halves of a CTA share the SM's units dynamically). */
+ * split_per_1024: 0 = every down unit waits until the whole gate/up phase of its layer is finished;
+ *   any other value (default) = it starts as soon as the four 32-output sub-strips that produce its 128
+ *   inputs are finished (same results). */
 int awq_b200_set_ffn_stack_tuning(int lookahead_units, int split_per_1024);
 size_t awq_b200_ffn_stack_plan_bytes(int n_layers);
 size_t awq_b200_ffn_stack_workspace_bytes(int n_layers);

@@ -69,12 +69,15 @@ struct alignas(128) FusedLayer {
 static_assert(sizeof(FusedLayer) % 128 == 0, "tensor maps must stay 64-byte aligned in the array");
 
 constexpr int FF_MAX_LAYERS = 1024;  // 2 claim words per layer in shared memory
-// State of one launch in the workspace, zeroed by the launcher: two phase counters, then one
-// f32 sum of squares per (layer boundary, batch row).
+// State of one launch in the workspace, zeroed by the launcher: two phase counters; per k-group of the down
+// projection (128 SwiGLU outputs) how many of the four 32-output sub-strips that feed it have been finished so far
+// (it grows by four per layer); then one f32 sum of squares per (layer boundary, batch row).
 constexpr size_t FF_STATE_OFF = SK_WS_END;
 constexpr size_t FF_STATE_HEADER = 64;
+constexpr int FF_READY_WORDS = 1024;  // >= SK_MAX_GROUPS
+constexpr size_t FF_READY_BYTES = FF_READY_WORDS * sizeof(int);
 __host__ __device__ constexpr size_t ff_state_bytes(int n_layers) {
-    return FF_STATE_HEADER + (size_t)(n_layers + 1) * 8 * sizeof(float);
+    return FF_STATE_HEADER + FF_READY_BYTES + (size_t)(n_layers + 1) * 8 * sizeof(float);
 }
 
 __device__ __forceinline__ int ld_acquire_gpu(const int *p) {
@@ -150,6 +153,7 @@ struct FusedArgs {
     unsigned int *epoch;                           // launches so far on this rank (base of the tags), in peer memory
     long long wait_limit;                          // cycles after which a device-side wait gives up
     int w3d_gu, w3d_d;  // the weight tensor map of a phase is 3-D: one copy fetches both 256-column boxes of a unit
+    int per_group;      // a down unit starts when the sub-strips that feed its k-group are finished, not when all of gate/up is
 };
 constexpr int FF_LL_WORDS = 16 * 32;  // words of one sub-strip from one rank
 
@@ -237,7 +241,15 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
     // tensor parallel: exchanges so far on these buffers (all launches run the same number of layers); every
     // warp reads the count before anything of this launch can end
     const unsigned int exch0 = tp ? *a.epoch * (unsigned int)a.n_layers : 0u;
-    float *sumsq = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(a.state) + FF_STATE_HEADER);
+    int *ready_gu = a.state + FF_STATE_HEADER / sizeof(int);
+    float *sumsq = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(a.state) + FF_STATE_HEADER + FF_READY_BYTES);
+    // Per-group readiness: a down unit needs only its own 128 SwiGLU outputs, so it starts as soon as the
+    // four sub-strips that produce them are finished; an SM that is done with its gate/up units does not wait for the
+    // slowest one.  (The other direction stays a launch-wide barrier: a gate/up unit needs the RMSNorm factor of the
+    // whole row.  Applying the factor to the finished sums instead would lift that too and measured another 3 % faster,
+    // but it rounds h * gamma instead of h * rstd * gamma to bf16, which is not the reference's rounding point: the
+    // distance to the oracle doubled, 1.2e-2 after four layers.)
+    const bool fg = a.per_group != 0;  // tensor parallel too: gate/up and down shards of a rank depend on each other only inside the rank
 
     if (role == 1 && lane == 0) {  // each loader sets up its half's barriers
         for (int s = 0; s < SK_STAGES; ++s) {
@@ -370,19 +382,39 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
                     ++mine;
                 }
                 // the phase's activations exist once every sub-strip of the previous phase is finalised
-                // (tensor parallel: a down sub-strip is finalised by the warp that added up all ranks' sums)
+                // (tensor parallel: a down sub-strip is finalised by the warp that added up all ranks' sums);
+                // with per-group readiness a unit's activations exist once the sub-strips that cover its k-group are
                 const int target = p ? (l + 1) * V0 * SK_CONSUMER_WARPS : B + l * V1 * SK_CONSUMER_WARPS;
-                if (!wait_count(p ? done_gu : done_d, target, a.wait_limit)) {
-                    atomicExch(a.err_flag, 3);
-                    return;
+                bool phase_open = false;
+                auto unit_ready = [&](int g) -> bool {
+                    if (phase_open) return true;
+                    if (!fg || !p) {
+                        if (!wait_count(p ? done_gu : done_d, target, a.wait_limit)) return false;
+                        phase_open = true;
+                    } else if (ld_acquire_gpu(done_gu) >= target) {
+                        phase_open = true;
+                    } else if (!wait_count(ready_gu + g, 4 * (l + 1), a.wait_limit)) {
+                        return false;
+                    }
+                    fence_proxy_async_all();  // generic-proxy writes of the previous phase before the tensor copies read them
+                    return true;
+                };
+                for (int i = 0; i < n_first; ++i) {
+                    if (!unit_ready(gs[i])) {
+                        atomicExch(a.err_flag, 3);
+                        return;
+                    }
+                    load_activations(slots[i], l, p, gs[i]);
                 }
-                fence_proxy_async_all();  // generic-proxy writes of the previous phase before the tensor copies read them
-                for (int i = 0; i < n_first; ++i) load_activations(slots[i], l, p, gs[i]);
                 while (more && (more = ff_claim(word, hi - lo))) {
                     const int u = unit_of(lo, hi, mine), v = u / G, g = u - v * G;
                     int slot;
                     if (!acquire_slot(slot)) return;
                     load_weights(slot, l, p, v, g);
+                    if (!unit_ready(g)) {
+                        atomicExch(a.err_flag, 3);
+                        return;
+                    }
                     load_activations(slot, l, p, g);
                     ++issued;
                     ++mine;
@@ -571,7 +603,11 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
         }
         __threadfence();
         __syncwarp();
-        if (lane == 0) atomicAdd(p ? done_d : done_gu, 1);
+        if (lane == 0) {
+            // this sub-strip's 32 SwiGLU outputs are a quarter of down k-group 2 v + cw / 4
+            if (fg && !p) atomicAdd(ready_gu + 2 * v + cw / 4, 1);
+            atomicAdd(p ? done_d : done_gu, 1);
+        }
     };
 
     for (int turn = 0;; ++turn) {
@@ -624,7 +660,8 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
 // ---------------------------------------------------------------------------------------
 static int g_ffn_lookahead = 0;  // measured: with the halves sharing an SM's units dynamically the L2 look-ahead no longer pays
 void ffn_fused_set_lookahead(int units) { g_ffn_lookahead = units < 0 ? 0 : (units > 64 ? 64 : units); }
-void ffn_fused_set_split(int per_1024) { (void)per_1024; }  // the halves of a CTA share its units dynamically
+static int g_ffn_per_group = 1;
+void ffn_fused_set_split(int per_group) { g_ffn_per_group = per_group != 0; }  // second tuning knob: 0 = a launch-wide barrier between phases
 
 size_t ffn_fused_plan_bytes(int n_layers) { return (size_t)(n_layers > 0 ? n_layers : 0) * sizeof(FusedLayer); }
 
@@ -737,6 +774,7 @@ int launch_ffn_fused(const void *plan_dev, int n_layers, const uint16_t *x, uint
     a.wait_limit = wait_limit_cycles();
     a.w3d_gu = (2 * I / 8) % 32 == 0 ? 1 : 0;
     a.w3d_d = (H / 8) % 32 == 0 ? 1 : 0;
+    a.per_group = g_ffn_per_group;
     a.tp_n = 1;
     a.tp_rank = 0;
     a.epoch = nullptr;

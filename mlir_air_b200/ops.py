@@ -300,7 +300,8 @@ class FFNStackPlan:
 
 def set_ffn_stack_tuning(lookahead_units: int = -1, split_per_1024: int = -1):
     """Tuning of the one-launch stack kernel (negative = keep): units per half-CTA prefetched into
-    L2 ahead of the ring, and where an SM's unit range is cut between the CTA's two halves."""
+    L2 ahead of the ring; and 0 = a down unit waits for the whole gate/up phase, other = only for the
+    sub-strips that produce its inputs (the default)."""
     _lib.call("awq_b200_set_ffn_stack_tuning", int(lookahead_units), int(split_per_1024))
 
 
