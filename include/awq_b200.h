@@ -336,6 +336,13 @@ int awq_b200_gemm_decode_bf16(const uint16_t *A, const int32_t *qweight, const i
                               int M, int K, int N, int group_size, void *workspace,
                               size_t workspace_bytes, awq_stream_t stream);
 
+/* The same product with the f32 sums as output, C f32 [M, N]: a tensor-parallel rank's partial of the down
+ * projection, to be added up across the ranks (no counterpart in the reference, which has no multi-GPU
+ * form of this path). */
+int awq_b200_gemm_decode_f32(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros,
+                             const uint16_t *scales, float *C, int M, int K, int N, int group_size,
+                             void *workspace, size_t workspace_bytes, awq_stream_t stream);
+
 /* Synchronise `stream` and report whether a tensor-core GEMM (prefill or batched decode) gave up on a
  * bounded device-side wait since the last check (AWQ_ERR_DEVICE_TIMEOUT); the counterpart of
  * xrt.py:204-218. */

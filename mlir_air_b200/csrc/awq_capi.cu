@@ -369,6 +369,21 @@ extern "C" int awq_b200_gemm_check(awq_stream_t stream) {
 
 extern "C" size_t awq_b200_gemm_decode_workspace_bytes(int M, int N) { return gemm_decode_workspace_bytes(M, N); }
 
+extern "C" int awq_b200_gemm_decode_f32(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros, const uint16_t *scales,
+                                        float *C, int M, int K, int N, int group_size, void *workspace, size_t workspace_bytes,
+                                        awq_stream_t stream) {
+    AWQ_REQUIRE(M >= 0 && K > 0 && N > 0 && group_size > 0, "gemm_decode_f32: bad size");
+    if (M == 0) return AWQ_OK;
+    AWQ_REQUIRE(A && qweight && qzeros && scales && C, "gemm_decode_f32: null pointer");
+    AWQ_REQUIRE(aligned16(A) && aligned16(scales) && aligned16(qweight) && aligned16(qzeros) && aligned16(C) && aligned16(workspace),
+                "gemm_decode_f32: pointers must be 16-byte aligned");
+    if (!gemm_decode_supported(M, K, N, group_size))
+        return set_error(AWQ_ERR_UNSUPPORTED, "gemm_decode_f32: needs M <= 64, group 128, K %% 128 == 0, N %% 32 == 0 "
+                         "(M=%d K=%d N=%d gs=%d)", M, K, N, group_size);
+    return launch_gemm_decode(A, qweight, qzeros, scales, reinterpret_cast<uint16_t *>(C), M, K, N, as_stream(stream), GEMM_EPI_F32,
+                              nullptr, workspace, workspace_bytes);
+}
+
 extern "C" int awq_b200_gemm_decode_bf16(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros,
                                          const uint16_t *scales, const uint16_t *residual, uint16_t *C, int swiglu, int M,
                                          int K, int N, int group_size, void *workspace, size_t workspace_bytes,

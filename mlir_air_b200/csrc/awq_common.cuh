@@ -144,7 +144,7 @@ int launch_gemm_generic(const uint16_t *A, const int32_t *qweight, const int32_t
 bool gemm_tc_supported(int M, int K, int N, int group_size);
 // Epilogues of the tensor-core GEMM: C bf16 [M, N] = bf16(sum (+ residual)), or SwiGLU over interleaved
 // gate/up column pairs into C bf16 [M, N / 2].
-enum GemmEpilogue : int { GEMM_EPI_BF16 = 0, GEMM_EPI_RESIDUAL = 1, GEMM_EPI_SWIGLU = 2 };
+enum GemmEpilogue : int { GEMM_EPI_BF16 = 0, GEMM_EPI_RESIDUAL = 1, GEMM_EPI_SWIGLU = 2, GEMM_EPI_F32 = 3 };  // F32: the f32 sums as they are (batched-decode GEMM only)
 int launch_gemm_tc(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros,
                    const uint16_t *scales, uint16_t *C, int M, int K, int N, int group_size,
                    cudaStream_t stream, int epilogue = GEMM_EPI_BF16, const uint16_t *residual = nullptr);

@@ -478,7 +478,9 @@ gemm_decode_fixup_kernel(uint16_t *__restrict__ C, const uint16_t *__restrict__ 
         const float4 v = __ldcg(reinterpret_cast<const float4 *>(src + (size_t)c * NB * DG_BN));
         sum.x += v.x, sum.y += v.y, sum.z += v.z, sum.w += v.w;
     }
-    if (epi == GEMM_EPI_SWIGLU) {
+    if (epi == GEMM_EPI_F32) {  // a tensor-parallel rank's partial sums, to be added up across the ranks
+        *reinterpret_cast<float4 *>(reinterpret_cast<float *>(C) + (size_t)m * N + n) = sum;
+    } else if (epi == GEMM_EPI_SWIGLU) {
         const uint32_t o = (uint32_t)swiglu_bits(sum.x, sum.y) | ((uint32_t)swiglu_bits(sum.z, sum.w) << 16);
         *reinterpret_cast<uint32_t *>(C + (size_t)m * (N >> 1) + (n >> 1)) = o;
     } else {

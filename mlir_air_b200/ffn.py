@@ -130,7 +130,7 @@ class DecodeFFNStack:
         max_il = max(l.down.K for l in self.layers)
         # split-K sums of the batched-decode GEMM (batches of 9 to 64 rows on one GPU)
         self.gemm_ws = ops.GemmDecodeWorkspace(maxN, device=device, batch=min(max_batch, 64)) \
-            if self.tp == 1 and max_batch >= self.GEMM_BATCH else None
+            if max_batch >= self.GEMM_BATCH else None
         bf = dict(dtype=torch.bfloat16, device=device)
         self._h = [torch.zeros((max_batch, hidden), **bf) for _ in range(2)]  # zeros: a capture's warm-up run reads them
         # intermediates between the kernels of a layer are fp16 (the GEMV kernel's fastest input)
@@ -200,7 +200,7 @@ class DecodeFFNStack:
     GEMM_BATCH = 17
 
     def uses_gemm(self, batch: int) -> bool:
-        if self.tp != 1 or batch < self.GEMM_BATCH or batch > 64 or self.gemm_ws is None:
+        if batch < self.GEMM_BATCH or batch > 64 or self.gemm_ws is None:
             return False
         return all(l.gamma is not None and l.gateup.group_size == 128 and l.down.group_size == 128 and
                    l.gateup.K % 128 == 0 and l.down.K % 128 == 0 and l.gateup.N % 32 == 0 and l.down.N % 32 == 0
@@ -211,7 +211,9 @@ class DecodeFFNStack:
         if self.uses_fused(batch):
             return 1
         if self.uses_gemm(batch):
-            return 5 * len(self.layers)  # norm, and two launches (product, sum of the SMs' shares + epilogue) per GEMM
+            # norm, and two launches (product, sum of the SMs' shares + epilogue) per GEMM; tensor parallel: the norm is
+            # fused with the residual add behind the allreduce, plus the first layer's norm
+            return 5 * len(self.layers) + (1 if self.tp > 1 else 0)
         passes = (batch + 7) // 8  # the decode kernels take 8 rows per launch
         n = len(self.layers)
         if self.tp == 1:
@@ -233,6 +235,21 @@ class DecodeFFNStack:
                     torch.distributed.all_reduce(self._align, group=self.group)
                 return ops.ffn_stack_decode_tp(self.plan, h, self.ws, self.plan_peers, eps=self.eps, inter=inter, out=other)
             return ops.ffn_stack_decode(self.plan, h, self.ws, eps=self.eps, inter=inter, out=other)
+        if self.uses_gemm(B) and self.tp > 1:
+            # tensor parallel: gate/up shard -> SwiGLU, down shard -> f32 partial, allreduce, residual add fused with
+            # the next layer's norm
+            nb = self._normed[:B].view(torch.bfloat16)
+            ops.rmsnorm(h, self.layers[0].gamma, self.eps, out=nb)
+            for idx, l in enumerate(self.layers):
+                il = l.down.K
+                it = inter.view(-1)[:B * il].view(B, il).view(torch.bfloat16)
+                ops.gemm_decode(nb, l.gateup, self.gemm_ws, out=it, swiglu=True)
+                ops.gemm_decode(it, l.down, self.gemm_ws, out=partial, f32_out=True)
+                torch.distributed.all_reduce(partial, group=self.group)
+                nxt = self.layers[idx + 1].gamma if idx + 1 < len(self.layers) else None
+                ops.add_rmsnorm(h, partial, nxt, self.eps, h_out=other, normed=nb if nxt is not None else None)
+                h, other = other, h
+            return h
         if self.uses_gemm(B):
             nb = self._normed[:B].view(torch.bfloat16)  # the GEMM's A operand is bf16
             for l in self.layers:

@@ -380,12 +380,21 @@ class GemmDecodeWorkspace:
         return int(_lib.load().awq_b200_gemm_decode_workspace_bytes(int(M), int(N))) <= self.nbytes
 
 
-def gemm_decode(A, w: AwqWeight, ws: GemmDecodeWorkspace, out=None, residual=None, swiglu=False):
+def gemm_decode(A, w: AwqWeight, ws: GemmDecodeWorkspace, out=None, residual=None, swiglu=False, f32_out=False):
     """C [M, N] = A [M, K] @ W for a decode batch of M <= 64 rows (weights streamed once, all SMs busy whatever the
-    shape); `residual` / `swiglu` as in `gemm`."""
+    shape); `residual` / `swiglu` as in `gemm`; `f32_out`: the f32 sums themselves (a tensor-parallel partial)."""
     _want(A, torch.bfloat16, "A")
     if A.dim() != 2 or A.shape[1] != w.K:
         raise _lib.AwqBackendError(f"A must be [M, {w.K}], got {tuple(A.shape)}")
+    if f32_out:
+        if residual is not None or swiglu:
+            raise _lib.AwqBackendError("gemm_decode: f32_out takes neither residual nor swiglu")
+        if out is None:
+            out = torch.empty((A.shape[0], w.N), dtype=torch.float32, device=A.device)
+        _want(out, torch.float32, "out")
+        _lib.call("awq_b200_gemm_decode_f32", _ptr(A), _ptr(w.qweight), _ptr(w.qzeros), _ptr(w.scales), _ptr(out), A.shape[0],
+                  w.K, w.N, w.group_size, _ptr(ws.buf), ws.nbytes, _stream())
+        return out
     n_out = w.N // 2 if swiglu else w.N
     if out is None:
         out = torch.empty((A.shape[0], n_out), dtype=torch.bfloat16, device=A.device)

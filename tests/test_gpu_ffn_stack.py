@@ -245,6 +245,10 @@ def test_gemm_decode_vs_oracle(ops, M, K, N):
     ref_bf16w = (A.astype(np.float32) @ O.dequant_to_bf16(*w, 128).astype(np.float32)).astype(bfloat16)
     assert O.rel_l2(y, ref_bf16w) <= 3e-3  # same products, summation order only
     assert O.rel_l2(y, O.gemv_A_ref(A, *w, 128)) <= REL_L2_TOL
+    # the f32 sums themselves (what a tensor-parallel rank hands to the allreduce): rounded, they are the bf16 output
+    import torch
+    yf = ops.gemm_decode(to_dev(A), dw, ws, f32_out=True)
+    assert yf.dtype == torch.float32 and np.array_equal(bits(to_host(yf.to(torch.bfloat16))), bits(y))
     yr = to_host(ops.gemm_decode(to_dev(A), dw, ws, residual=to_dev(R)))
     ops.gemm_check()
     assert O.rel_l2(yr, O.gemv_A_ref(A, *w, 128, residual=R)) <= REL_L2_TOL

@@ -99,3 +99,76 @@ def test_tp_push_matches_nccl_and_oracle(world, B, H, I, L):
         assert d["oracle"] <= 1e-2 and d["again"] <= 1e-2 and d["graph1"] <= 1e-2 and d["graph2"] <= 1e-2, res
         assert d["vs_nccl"] <= 5e-3, res
         assert max(d["one"], d["one2"], d["one3"], d["one4"]) <= 1e-2 and d["one_vs_nccl"] <= 5e-3, res
+
+
+def _worker_gemm(rank, world, port, H, I, L, B, out):
+    import torch.distributed as dist
+    from gpu_util import synth_awq, to_dev, to_host
+    from mlir_air_b200 import ffn, ops
+    from mlir_air_b200.ops import AwqWeight
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        group = dist.group.WORLD
+        i0, i1 = ffn.tp_shard_bounds(I, world)[rank]
+        layers, full = [], []
+        for l in range(L):
+            gate = synth_awq(H, I, 128, seed=10 * l)
+            up = synth_awq(H, I, 128, seed=10 * l + 1)
+            down = synth_awq(I, H, 128, seed=10 * l + 2, scale_lo=0.0005, scale_hi=0.004)
+            gamma = (np.random.default_rng(10 * l + 3).standard_normal(H) * 0.1 + 1.0).astype(bfloat16)
+            full.append((gate, up, down, gamma))
+            gu = ops.interleave_gate_up(AwqWeight.from_numpy(*gate, 128), AwqWeight.from_numpy(*up, 128))
+            layers.append(ffn.FFNLayer(ffn.shard_gateup(gu, i0, i1), ffn.shard_down(AwqWeight.from_numpy(*down, 128), i0, i1),
+                                       to_dev(gamma)))
+        x = np.random.default_rng(7).standard_normal((B, H)).astype(bfloat16)
+        st = ffn.DecodeFFNStack(layers, H, max_batch=64, group=group)
+        assert st.uses_gemm(B) and st.launches_per_step(B) == 5 * L + 1
+        y = to_host(st.step(to_dev(x)))
+        y2 = to_host(st.step(to_dev(x)))
+        st.load_input(to_dev(x))
+        g1 = to_host(st.replay(B).clone())
+        st.check()
+        old = ffn.DecodeFFNStack(layers, H, max_batch=64, group=group)
+        old.gemm_ws = None  # the per-layer GEMV passes with the allreduce in between
+        assert not old.uses_gemm(B)
+        y_old = to_host(old.step(to_dev(x)))
+        old.check()
+        h = x
+        for gate, up, down, gamma in full:
+            h = O.ffn_layer_A_ref(h, gamma, gate, up, down, 128)
+        out[rank] = dict(oracle=O.rel_l2(y, h), again=bool(np.array_equal(y.view(np.uint16), y2.view(np.uint16))),
+                         graph=O.rel_l2(g1, h), vs_gemv=O.rel_l2(y, y_old))
+        torch.cuda.synchronize()
+        dist.barrier()
+    except Exception:  # noqa: BLE001 -- show it before the hard exit below
+        import traceback
+        traceback.print_exc()
+    finally:
+        os._exit(0 if rank in out else 1)
+
+
+@pytest.mark.parametrize("world,B,H,I,L", [(2, 32, 1024, 2816, 3), (2, 17, 2048, 5632, 2)])
+def test_tp_batched_decode_gemm_matches_oracle(world, B, H, I, L):
+    """Batches of 17 to 64 rows on tensor-parallel ranks: gate/up shard and down shard through the batched-decode GEMM, the
+    down partial as f32 (awq_b200_gemm_decode_f32), one allreduce per layer, residual add fused with the next norm."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        out = mgr.dict()
+        port = 29600 + (os.getpid() + H + B) % 300
+        procs = [ctx.Process(target=_worker_gemm, args=(r, world, port, H, I, L, B, out)) for r in range(world)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(300)
+        for p in procs:
+            if p.is_alive():
+                p.kill()
+        assert all(p.exitcode == 0 for p in procs), dict(out)
+        res = dict(out)
+    assert len(res) == world, res
+    for r, d in res.items():
+        assert d["oracle"] <= 1e-2 and d["graph"] <= 1e-2 and d["vs_gemv"] <= 1e-2 and d["again"], res
