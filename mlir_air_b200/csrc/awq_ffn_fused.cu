@@ -71,11 +71,12 @@ static_assert(sizeof(FusedLayer) % 128 == 0, "tensor maps must stay 64-byte alig
 constexpr int FF_MAX_LAYERS = 1024;  // 2 claim words per layer in shared memory
 // State of one launch in the workspace, zeroed by the launcher: two phase counters; per k-group of the down
 // projection (128 SwiGLU outputs) how many of the four 32-output sub-strips that feed it have been finished so far
-// (it grows by four per layer); then one f32 sum of squares per (layer boundary, batch row).
+// (it grows by four per layer), and per k-group of the gate/up projection (128 hidden values) how many of its two
+// 64-column sub-strips (two per layer); then one f32 sum of squares per (layer boundary, batch row).
 constexpr size_t FF_STATE_OFF = SK_WS_END;
 constexpr size_t FF_STATE_HEADER = 64;
-constexpr int FF_READY_WORDS = 1024;  // >= SK_MAX_GROUPS
-constexpr size_t FF_READY_BYTES = FF_READY_WORDS * sizeof(int);
+constexpr int FF_READY_WORDS = 1024;  // >= SK_MAX_GROUPS, per direction
+constexpr size_t FF_READY_BYTES = 2 * FF_READY_WORDS * sizeof(int);
 __host__ __device__ constexpr size_t ff_state_bytes(int n_layers) {
     return FF_STATE_HEADER + FF_READY_BYTES + (size_t)(n_layers + 1) * 8 * sizeof(float);
 }
@@ -241,14 +242,16 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
     // tensor parallel: exchanges so far on these buffers (all launches run the same number of layers); every
     // warp reads the count before anything of this launch can end
     const unsigned int exch0 = tp ? *a.epoch * (unsigned int)a.n_layers : 0u;
-    int *ready_gu = a.state + FF_STATE_HEADER / sizeof(int);
+    int *ready_gu = a.state + FF_STATE_HEADER / sizeof(int), *ready_d = ready_gu + FF_READY_WORDS;
     float *sumsq = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(a.state) + FF_STATE_HEADER + FF_READY_BYTES);
     // Per-group readiness: a down unit needs only its own 128 SwiGLU outputs, so it starts as soon as the
     // four sub-strips that produce them are finished; an SM that is done with its gate/up units does not wait for the
-    // slowest one.  (The other direction stays a launch-wide barrier: a gate/up unit needs the RMSNorm factor of the
-    // whole row.  Applying the factor to the finished sums instead would lift that too and measured another 3 % faster,
-    // but it rounds h * gamma instead of h * rstd * gamma to bf16, which is not the reference's rounding point: the
-    // distance to the oracle doubled, 1.2e-2 after four layers.)
+    // slowest one.  In the other direction a gate/up unit's 128 raw hidden values are requested as soon as the two
+    // down sub-strips that produce them are finished, but the normaliser warp turns them into activations only when the
+    // whole down phase is over: the RMSNorm factor belongs to the whole row.  (Applying the factor to the finished sums
+    // instead would lift that too and measured another 3 % faster, but it rounds h * gamma instead of h * rstd * gamma
+    // to bf16, which is not the reference's rounding point: the distance to the oracle doubled, 1.2e-2 after four
+    // layers.)
     const bool fg = a.per_group != 0;  // tensor parallel too: gate/up and down shards of a rank depend on each other only inside the rank
 
     if (role == 1 && lane == 0) {  // each loader sets up its half's barriers
@@ -388,14 +391,16 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
                 bool phase_open = false;
                 auto unit_ready = [&](int g) -> bool {
                     if (phase_open) return true;
-                    if (!fg || !p) {
+                    if (!fg || (!p && tp)) {  // tensor parallel: the hidden state comes out of the exchange, which counts only the phase
                         if (!wait_count(p ? done_gu : done_d, target, a.wait_limit)) return false;
                         phase_open = true;
-                    } else if (ld_acquire_gpu(done_gu) >= target) {
+                    } else if (ld_acquire_gpu(p ? done_gu : done_d) >= target) {
                         phase_open = true;
-                    } else if (!wait_count(ready_gu + g, 4 * (l + 1), a.wait_limit)) {
-                        return false;
-                    }
+                    } else if (p) {
+                        if (!wait_count(ready_gu + g, 4 * (l + 1), a.wait_limit)) return false;
+                    } else if (l > 0) {
+                        if (!wait_count(ready_d + g, 2 * l, a.wait_limit)) return false;
+                    }  // layer 0 reads the caller's input
                     fence_proxy_async_all();  // generic-proxy writes of the previous phase before the tensor copies read them
                     return true;
                 };
@@ -468,7 +473,17 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
                 }
             }
             if (p == 0) {
-                if (rstd_layer != l) {  // complete: the loader passed the phase barrier before it requested h
+                if (rstd_layer != l) {
+                    // the row sums are complete when the whole down phase before this layer is (with per-group readiness
+                    // the loader may have requested h before that)
+                    if (fg && !tp) {
+                        int ok = 0;
+                        if (lane == 0) ok = wait_count(done_d, B + l * V1 * SK_CONSUMER_WARPS, a.wait_limit) ? 1 : 0;
+                        if (!__shfl_sync(0xffffffffu, ok, 0)) {
+                            if (lane == 0) atomicExch(a.err_flag, 3);
+                            return;
+                        }
+                    }
                     rstd_layer = l;
                     if (r < B) {
                         const float total = __ldcg(sumsq + (size_t)l * 8 + r);
@@ -604,8 +619,9 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tmXi, const __grid_constant
         __threadfence();
         __syncwarp();
         if (lane == 0) {
-            // this sub-strip's 32 SwiGLU outputs are a quarter of down k-group 2 v + cw / 4
-            if (fg && !p) atomicAdd(ready_gu + 2 * v + cw / 4, 1);
+            // this sub-strip's 32 SwiGLU outputs are a quarter of down k-group 2 v + cw / 4; its 64 hidden values are half
+            // of gate/up k-group 4 v + cw / 2
+            if (fg) atomicAdd(p ? ready_d + 4 * v + cw / 2 : ready_gu + 2 * v + cw / 4, 1);
             atomicAdd(p ? done_d : done_gu, 1);
         }
     };
