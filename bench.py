@@ -537,7 +537,8 @@ def run_ours(a):
         except Exception:
             pk = 1590.0
         prefill = {"workload": "int4 GEMM [2048 x 4096] x AWQ [4096 x 14336]", "us": us, "tflops": tf,
-                   "frac_of_measured_bf16_peak": tf / pk, "frac_of_2250": tf / 2250.0, "kernel": "gemm_tc_kernel (tcgen05)"}
+                   "frac_of_measured_bf16_peak": tf / pk, "frac_of_2250": tf / 2250.0,
+                   "kernel": "gemm_tm_kernel (tcgen05, dequantised weights in tensor memory)"}
         del wp, Ap, Cp
 
     # ---- the other way to use N GPUs (extra key, not the headline): every rank holds the whole stack

@@ -296,6 +296,10 @@ int awq_b200_ffn_stack_decode_bf16(const void *plan, int n_layers, const uint16_
  * kernels of the ranks wait for one another (bounded; awq_b200_workspace_check reports a timeout).
  * No counterpart in the reference, whose only inter-GPU mechanism is its symmetric heap
  * (runtime_lib/airgpu/symmetric_heap.cpp:172-312). */
+/* The messages of the exchange are numbered by the launches that finished on a rank (a word behind the
+ * rank's first slot) times the layer count: a set of receive slots belongs to one plan, and after a launch
+ * that failed on any rank (AWQ_ERR_DEVICE_TIMEOUT from awq_b200_workspace_check, an argument error on one
+ * rank only) all ranks must zero their slots and flag blocks together before the next launch. */
 size_t awq_b200_ffn_stack_tp_slot_bytes(int H, int n_ranks);
 int awq_b200_ffn_stack_decode_tp_bf16(const void *plan, int n_layers, const uint16_t *x,
                                       uint16_t *out, uint16_t *inter, float eps, int B, int H,
@@ -348,8 +352,9 @@ int awq_b200_gemm_decode_f32(const uint16_t *A, const int32_t *qweight, const in
  * xrt.py:204-218. */
 int awq_b200_gemm_check(awq_stream_t stream);
 
-/* Choose the prefill kernel: 0 = automatic, 1 = generic CUDA-core kernel,
- * 2 = tcgen05 tensor-core kernel (AWQ_ERR_UNSUPPORTED where it cannot run). */
+/* Choose the prefill kernel: 0 = automatic, 1 = generic CUDA-core kernel, 2 = tcgen05 kernel with the
+ * dequantised weights as a shared-memory tile, 3 = tcgen05 kernel with the dequantised weights in tensor
+ * memory (2 and 3: AWQ_ERR_UNSUPPORTED where they cannot run; automatic takes 3 from 1024 rows on). */
 int awq_b200_set_gemm_kernel(int mode);
 
 /* ---- bf16 sibling path (un-quantised weights) ----------------------------------------------

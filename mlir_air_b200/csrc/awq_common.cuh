@@ -150,6 +150,11 @@ int launch_gemm_tc(const uint16_t *A, const int32_t *qweight, const int32_t *qze
                    cudaStream_t stream, int epilogue = GEMM_EPI_BF16, const uint16_t *residual = nullptr);
 
 int gemm_tc_check(cudaStream_t stream);
+// The same GEMM with the dequantised weights in tensor memory (operands swapped: weights are the MMA's M side).
+bool gemm_tm_supported(int M, int K, int N, int group_size);
+int launch_gemm_tm(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros, const uint16_t *scales, uint16_t *C, int M, int K,
+                   int N, cudaStream_t stream, int epilogue = GEMM_EPI_BF16, const uint16_t *residual = nullptr);
+int gemm_tm_check(cudaStream_t stream);
 // Batched-decode GEMM (M <= 128 token rows): stream-K over (column tile, k-block) units, split-K partials through `workspace`.
 bool gemm_decode_supported(int M, int K, int N, int group_size);
 size_t gemm_decode_workspace_bytes(int M, int N);

@@ -101,6 +101,12 @@ def random_layer(hidden: int, intermediate: int, seed: int, device="cuda", group
     return FFNLayer(rnd(hidden, 2 * il), rnd(il, hidden), gamma)
 
 
+def _lib_call_workspace_init(ws: Workspace):
+    from . import _lib
+    _lib.call("awq_b200_workspace_init", ws.buf.data_ptr(), ws.nbytes, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.current_stream().synchronize()
+
+
 class DecodeFFNStack:
     """A stack of decode FFN layers with resident weights.
 
@@ -334,6 +340,15 @@ class DecodeFFNStack:
         self._pin_out[:B].copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         return self._pin_out[:B].view(torch.int16).numpy().view(bfloat16).copy()
+
+    def resync(self):
+        """Collective, tensor parallel only: after a failed step on any rank, bring the ranks' exchange buffers back to
+        the same state (every rank must call it; nothing of this stack may be in flight)."""
+        for peers in (self.plan_peers, self.peers):
+            if peers is not None:
+                peers.reset()
+        with torch.cuda.device(self.device):
+            _lib_call_workspace_init(self.ws)
 
     def check(self):
         self.ws.check()

@@ -112,7 +112,7 @@ def set_deterministic(on: bool):
 
 
 def set_gemm_kernel(mode: str):
-    _lib.call("awq_b200_set_gemm_kernel", {"auto": 0, "generic": 1, "tc": 2}[mode])
+    _lib.call("awq_b200_set_gemm_kernel", {"auto": 0, "generic": 1, "tc": 2, "tm": 3}[mode])
 
 
 def dequant(w: AwqWeight, out: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -82,6 +82,18 @@ class PeerBuffers:
         self._recv_arrays = [arr(*[p + s * self.stride for p in self.ptrs]) for s in range(n_slots)]
         self._flag_arrays = [arr(*[p + s * self.stride + self.recv_bytes for p in self.ptrs]) for s in range(n_slots)]
 
+    def reset(self):
+        """Collective: zero this rank's slots, flags and launch count, on every rank, with nothing in flight.  To be
+        called by all ranks after any of them saw a launch fail (a device-side wait that gave up, an argument error on
+        one rank only): the in-kernel exchange numbers its messages by the launches that finished on a rank, and ranks
+        that disagree about that number would wait for each other's messages in vain.  A peer buffer also belongs to
+        one plan (one layer count): the message numbers of a launch are launches x layers + layer."""
+        torch.cuda.synchronize(self.buf.device)
+        dist.barrier(group=self.group)
+        self.buf.zero_()
+        torch.cuda.synchronize(self.buf.device)
+        dist.barrier(group=self.group)
+
     def base_array(self):
         """ctypes array of every rank's buffer base (argument peer_base)."""
         return self._recv_arrays[0]

@@ -404,6 +404,35 @@ def test_gemm_tensor_core_kernel(ops, M, K, N):
     assert O.rel_l2(c, ref_f32w) <= REL_L2_TOL
 
 
+@pytest.mark.parametrize("M,K,N", [(192, 128, 256), (1, 128, 32), (130, 384, 288), (300, 1024, 1056), (512, 2048, 768), (2048, 512, 256),
+                                   (65, 256, 4096)])
+def test_gemm_tensor_memory_kernel(ops, M, K, N):
+    """The tcgen05 kernel that keeps the dequantised weights in tensor memory (operands swapped, 192-row tiles): ragged
+    row and column tiles, several tiles per CTA, all three epilogues, against both goldens."""
+    ops.set_gemm_kernel("tm")
+    try:
+        qw, qz, s = synth_awq(K, N, 128, seed=3 * M + N)
+        A = randn_bf16((M, K), seed=7)
+        w = dev_weight(qw, qz, s)
+        c = to_host(ops.gemm(to_dev(A), w))
+        ops.gemm_check()
+        ref_f32w = (A.astype(np.float32) @ O.dequant_f32(qw, qz, s, 128)).astype(bfloat16)
+        ref_bf16w = (A.astype(np.float32) @ O.dequant_to_bf16(qw, qz, s, 128).astype(np.float32)).astype(bfloat16)
+        assert O.rel_l2(c, ref_bf16w) <= 3e-3   # same products, f32 summation order only
+        assert O.rel_l2(c, ref_f32w) <= REL_L2_TOL
+        R = randn_bf16((M, N), seed=9)
+        cr = to_host(ops.gemm(to_dev(A), w, residual=to_dev(R)))
+        assert O.rel_l2(cr, O.gemv_A_ref(A, qw, qz, s, 128, residual=R)) <= REL_L2_TOL
+        if N % 64 == 0:
+            gate, up = synth_awq(K, N // 2, 128, seed=4), synth_awq(K, N // 2, 128, seed=5)
+            wgu = ops.interleave_gate_up(dev_weight(*gate), dev_weight(*up))
+            t = to_host(ops.gemm(to_dev(A), wgu, swiglu=True))
+            assert O.rel_l2(t, O.gateup_swiglu_A_ref(A, gate, up, 128)) <= REL_L2_TOL
+        ops.gemm_check()
+    finally:
+        ops.set_gemm_kernel("auto")
+
+
 def test_gemm_cfg4_full_size(ops):
     """Benchmark configuration 4: [2048, 4096] x [4096, 14336]."""
     M, K, N = 2048, 4096, 14336

@@ -59,13 +59,17 @@ def _worker(rank, world, port, H, I, L, B, out):
         one.load_input(to_dev(x))
         y_one4 = to_host(one.replay(B).clone())
         one.check()
+        one.resync()  # what all ranks do after a failed launch on any of them: slots, flags and launch count back to zero
+        y_one5 = to_host(one.step(to_dev(x)))
+        one.check()
         h = x
         for gate, up, down, gamma in full:
             h = O.ffn_layer_A_ref(h, gamma, gate, up, down, 128)
         out[rank] = dict(how=push.peers.how, oracle=O.rel_l2(y_push, h), again=O.rel_l2(y_push2, h),
                          vs_nccl=O.rel_l2(y_push, y_nccl), graph1=O.rel_l2(g1, h), graph2=O.rel_l2(g2, h),
                          nccl_oracle=O.rel_l2(y_nccl, h), one=O.rel_l2(y_one, h), one2=O.rel_l2(y_one2, h),
-                         one3=O.rel_l2(y_one3, h), one4=O.rel_l2(y_one4, h), one_vs_nccl=O.rel_l2(y_one, y_nccl))
+                         one3=O.rel_l2(y_one3, h), one4=O.rel_l2(y_one4, h), one5=O.rel_l2(y_one5, h),
+                         one_vs_nccl=O.rel_l2(y_one, y_nccl))
         torch.cuda.synchronize()
         dist.barrier()
     except Exception:  # noqa: BLE001 -- show it before the hard exit below
@@ -98,7 +102,7 @@ def test_tp_push_matches_nccl_and_oracle(world, B, H, I, L):
     for r, d in res.items():
         assert d["oracle"] <= 1e-2 and d["again"] <= 1e-2 and d["graph1"] <= 1e-2 and d["graph2"] <= 1e-2, res
         assert d["vs_nccl"] <= 5e-3, res
-        assert max(d["one"], d["one2"], d["one3"], d["one4"]) <= 1e-2 and d["one_vs_nccl"] <= 5e-3, res
+        assert max(d["one"], d["one2"], d["one3"], d["one4"], d["one5"]) <= 1e-2 and d["one_vs_nccl"] <= 5e-3, res
 
 
 def _worker_gemm(rank, world, port, H, I, L, B, out):
