@@ -35,7 +35,8 @@
 //   warp 1      MMA issuer (one elected lane): 16 tcgen05.mma (M 128, N = padded batch, K 16, A from tensor memory)
 //               per unit; tcgen05.commit frees the input stage and the weight buffer, and at the end of a
 //               segment hands the accumulator over
-//   warps 4-19  dequant: warp w owns TMEM lanes 32 (w % 4) .. + 31 of one 128-column half and 64 of the 128 k
+//   warps 4-19  dequant: two groups of eight take alternate units; in a group warp w owns TMEM lanes 32 (w % 4) .. + 31
+//               of one 128-column half
 //   warps 20-23 drain: tcgen05.ld (each warp its 32 TMEM lanes of both halves) and stores into the slot; two
 //               accumulators alternate, so a segment drains while the next one runs
 //
@@ -156,10 +157,10 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full_bar(s), 1);
             mbar_init(xfull_bar(s), 1);
-            mbar_init(empty_bar(s), 1 + DG_DEQUANT_WARPS);  // the MMA's commit and the dequant warps (they read W, S, Z)
+            mbar_init(empty_bar(s), 1 + DG_DEQUANT_WARPS / 2);  // the MMA's commit and the eight dequant warps of the unit's group
         }
         for (int b = 0; b < Cfg::ABUF; ++b) {
-            mbar_init(ready_bar(b), DG_DEQUANT_WARPS);
+            mbar_init(ready_bar(b), DG_DEQUANT_WARPS / 2);
             mbar_init(bfree_bar(b), 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -271,20 +272,24 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         }
     } else if (warp >= DG_DEQUANT_WARP0 && warp < DG_EPI_WARP0) {
         // ------------------------------ dequant ------------------------------
+        // Two groups of eight warps take alternate units, so that one group computes while the other waits for its loads
+        // and its tensor-memory stores; inside a group warp w owns TMEM lanes 32 (w % 4) .. + 31 of one 128-column half,
+        // all 128 k.
         const int dw = warp - DG_DEQUANT_WARP0;
+        const int grp = dw >> 3;
         const int q = warp & 3;        // TMEM lanes 32 q .. 32 q + 31 (a warp may only touch its own quarter)
         const int h = (dw >> 2) & 1;   // which 128-column half of the tile
-        const int kh = dw >> 3;        // which 64 of the unit's 128 k
         const int g = lane >> 2;       // ldmatrix.trans: lane (g, t = lane % 4) gets 16-bit column g of the chunk, rows 2t and 2t + 1
         const int chunk = 4 * h + q;   // the warp's 32 columns are one 16-byte chunk (4 packed words) of a 128-byte row
-        // Row addresses of the four 8 x 8 matrices of one ldmatrix.x4: matrix m = 2 sp + x serves k16 step sp of the call
-        // and holds rows k = 16 step + 4 j + 2 x + {0, 1} (j = 0..3), so that lane (g, t) receives the k pair 2t + x:
+        // Row addresses of the four 8 x 8 matrices of one ldmatrix.x4: matrix m = 2 sp + x serves k16 step sp of the call's
+        // 32 k and holds rows k = 16 sp + 4 j + 2 x + {0, 1} (j = 0..3), so that lane (g, t) receives the k pair 2t + x:
         // TMEM columns 2t and 2t + 1 of the step are what tcgen05.st.16x256b takes from this lane.
         const int mi = lane >> 3, rr = lane & 7;
-        const int k_lane = 64 * kh + 16 * (mi >> 1) + 4 * (rr >> 1) + 2 * (mi & 1) + (rr & 1);  // + 32 for the second call
-        const uint32_t w_off = (uint32_t)k_lane * 128 + (uint32_t)((chunk ^ (k_lane & 7)) << 4);  // 128B swizzle; k + 32 keeps k & 7
-        int it = 0;
-        for (UnitWalk w(tiles, KB); w.valid(); ++w.u, ++it) {
+        const int k_lane = 16 * (mi >> 1) + 4 * (rr >> 1) + 2 * (mi & 1) + (rr & 1);  // + 32 c for call c
+        const uint32_t w_off = (uint32_t)k_lane * 128 + (uint32_t)((chunk ^ (k_lane & 7)) << 4);  // 128B swizzle; k + 32 c keeps k & 7
+        UnitWalk w(tiles, KB);
+        const int n_units = w.u1 - w.u;
+        for (int it = grp; it < n_units; it += 2) {
             const int s = it % STAGES, round = it / STAGES;
             const int ab = it % Cfg::ABUF, around = it / Cfg::ABUF;
             if (!mbar_wait_bounded(full_bar(s), round & 1, wait_limit)) {
@@ -292,29 +297,30 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 break;
             }
             const uint32_t st = stage_addr(s) + Cfg::A_BYTES;  // packed words, then scales, then zeros
-            // this lane's four columns (nibbles e of its half word): 128 + z and the scale, each twice (k, k + 1)
+            // this lane's four columns (nibbles e of its half word: columns 2e + (g & 1) of the word): 128 + z and the scale,
+            // each twice (k, k + 1)
             const uint32_t zw = lds32(st + DG_W_BYTES + DG_S_BYTES + (4 * chunk + (g >> 1)) * 4) >> (16 * (g & 1));
+            const uint4 sv = lds128(st + DG_W_BYTES + (32 * chunk + 8 * (g >> 1)) * 2);
+            const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
             uint32_t zz[4], ss[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                zz[e] = (((zw >> (4 * e)) & 0xFu) * 0x00010001u) | 0x43004300u;
-                uint32_t sc;
-                asm volatile("ld.shared.u16 %0, [%1];" : "=r"(sc) : "r"(st + DG_W_BYTES + (32 * chunk + 8 * (g >> 1) + 2 * e + (g & 1)) * 2));
-                ss[e] = sc * 0x00010001u;
+                zz[e] = ((zw >> (4 * e)) & 0xFu) * 0x00010001u + 0x43004300u;
+                asm("prmt.b32 %0, %1, %1, %2;" : "=r"(ss[e]) : "r"(sw[e]), "r"((g & 1) ? 0x3232u : 0x1010u));
             }
-            uint32_t r[2][4];
-            ldmatrix_x4_trans(r[0], st + w_off);
-            ldmatrix_x4_trans(r[1], st + w_off + 32 * 128);
+            uint32_t r[4][4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) ldmatrix_x4_trans(r[c], st + w_off + c * 32 * 128);
             if (around > 0 && !mbar_wait_bounded(bfree_bar(ab), (around - 1) & 1, wait_limit)) {
                 if (lane == 0) atomicExch(&g_gemm_dec_error, 4);
                 break;
             }
             dg_fence_after();
-            const uint32_t a_tmem = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(ab * DG_ABUF_COLS + h * (DG_GROUP / 2) + 32 * kh);
+            const uint32_t a_tmem = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(ab * DG_ABUF_COLS + h * (DG_GROUP / 2));
 #pragma unroll
-            for (int c = 0; c < 2; ++c)
+            for (int c = 0; c < 4; ++c)
 #pragma unroll
-                for (int sp = 0; sp < 2; ++sp) {  // k16 step 2c + sp of this warp's 64 k
+                for (int sp = 0; sp < 2; ++sp) {  // k16 step 2c + sp of the unit
                     const uint32_t lo = r[c][2 * sp], hi = r[c][2 * sp + 1];  // k pairs 2t and 2t + 1
                     uint32_t v[8];
 #pragma unroll
