@@ -441,11 +441,12 @@ static int dg_sm_count() {
 // Slots a tile needs: the most CTAs whose ranges can reach into one tile.
 static int dg_slots_per_tile(int tiles) { return dg_sm_count() / tiles + 2; }
 
-// The slots of every tile.
+// The slots of every tile.  tiles x slots_per_tile <= SMs + 2 tiles: that bound is what is asked for, so that a workspace
+// sized for some N also serves every smaller N (tiles x (SMs / tiles + 2) itself does not grow monotonically with N).
 size_t gemm_decode_workspace_bytes(int M, int N) {
     if (M < 1 || N < 1) return 0;
     const size_t tiles = (size_t)(N + DG_BN - 1) / DG_BN;
-    return tiles * dg_slots_per_tile((int)tiles) * DG_BN * dg_rows(M) * 4;
+    return ((size_t)dg_sm_count() + 2 * tiles) * DG_BN * dg_rows(M) * 4;
 }
 
 template <int NB>

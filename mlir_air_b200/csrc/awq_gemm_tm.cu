@@ -267,13 +267,15 @@ gemm_tm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const int rows = M - m_base < tile_rows ? M - m_base : tile_rows;
             if (n0 + 128 * h + 32 * q < N) {  // N is a multiple of 32: the warp's columns are all in or all out
                 const int n = n0 + 128 * h + 32 * q + dg_lane_column(lane);
+                // 32 token rows per tensor-memory load (the accumulator has 192 columns whatever the tile's rows, so a load
+                // may run past the rows that were multiplied; what it brings from there is not stored)
 #pragma unroll 1
-                for (int mc = 0; mc < rows; mc += 16) {
-                    uint32_t r[16];
-                    dg_tmem_ld_32x32b_x16(t_acc + (uint32_t)mc, r);
+                for (int mc = 0; mc < rows; mc += 32) {
+                    uint32_t r[32];
+                    dg_tmem_ld_32x32b_x32(t_acc + (uint32_t)mc, r);
                     dg_tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
+                    for (int i = 0; i < 32; ++i) {
                         const int m = m_base + mc + i;
                         if (mc + i >= rows) break;  // warp-uniform
                         const float v = __uint_as_float(r[i]);

@@ -136,7 +136,7 @@ class DecodeFFNStack:
         max_il = max(l.down.K for l in self.layers)
         # split-K sums of the batched-decode GEMM (batches of 9 to 64 rows on one GPU)
         self.gemm_ws = ops.GemmDecodeWorkspace(maxN, device=device, batch=min(max_batch, 64)) \
-            if max_batch >= self.GEMM_BATCH else None
+            if max_batch >= self.GEMM_BATCH else None  # (its size grows with N: the widest product decides)
         bf = dict(dtype=torch.bfloat16, device=device)
         self._h = [torch.zeros((max_batch, hidden), **bf) for _ in range(2)]  # zeros: a capture's warm-up run reads them
         # intermediates between the kernels of a layer are fp16 (the GEMV kernel's fastest input)

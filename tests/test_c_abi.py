@@ -90,3 +90,15 @@ def test_argument_errors_need_no_gpu():
     # knobs
     assert _err(lib.awq_b200_set_decode_kernel(7))[0] == INV
     assert lib.awq_b200_set_decode_kernel(0) == 0 and lib.awq_b200_set_ffn_stack_tuning(-1, -1) == 0
+
+
+def test_gemm_decode_workspace_serves_every_narrower_product():
+    """A workspace sized for N columns must also serve every product with fewer columns (a tensor-parallel rank runs its
+    gate/up shard and the full-width down projection through one workspace): the size may not shrink when N grows."""
+    lib = _lib.load()
+    for rows in (16, 32, 64):
+        prev = 0
+        for n in range(32, 65536 + 1, 32):
+            b = int(lib.awq_b200_gemm_decode_workspace_bytes(rows, n))
+            assert b >= prev, (rows, n, b, prev)
+            prev = b
