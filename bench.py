@@ -318,7 +318,8 @@ def time_other_configs(a, torch, ops, ffn, peak):
         torch.cuda.synchronize()
         us = e0.elapsed_time(e1) * 1e3 / (20 * nl)
         g3[str(B)] = dict(_hbm_entry(us, per + 4 * B * H * 2, peak), tokens_per_s=B / (us * 1e-6),
-                          path="one launch of the stack kernel for all layers" if st.uses_fused(B) else "per-layer kernels")
+                          path="one launch of the stack kernel for all layers" if st.uses_fused(B) else
+                          ("per layer: RMSNorm + two batched-decode GEMMs" if st.uses_gemm(B) else "per-layer kernels"))
     st.check()
     out["ffn_cfg3"] = {"workload": f"decode SwiGLU FFN hidden 4096 / intermediate 11008 with RMSNorm and residual, {nl} distinct "
                                    "layers back to back, time per layer", "layers": nl, "batch": g3}

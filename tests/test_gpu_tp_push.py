@@ -156,7 +156,7 @@ def _worker_gemm(rank, world, port, H, I, L, B, out):
 # (the third case: 11 groups of the intermediate dimension on 2 ranks, shards of 6 and 5 groups; the fourth: 4 ranks)
 @pytest.mark.parametrize("world,B,H,I,L", [(2, 32, 1024, 2816, 3), (2, 17, 2048, 5632, 2), (2, 64, 1024, 1408, 2), (4, 40, 1024, 2816, 2)])
 def test_tp_batched_decode_gemm_matches_oracle(world, B, H, I, L):
-    """Batches of 17 to 64 rows on tensor-parallel ranks: gate/up shard and down shard through the batched-decode GEMM, the
+    """Batches of 9 to 64 rows on tensor-parallel ranks: gate/up shard and down shard through the batched-decode GEMM, the
     down partial as f32 (awq_b200_gemm_decode_f32), one allreduce per layer, residual add fused with the next norm."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
