@@ -55,7 +55,7 @@ def parse():
 # (kernel, hidden, intermediate per rank, batch).  The stack kernel's figure is per layer (a 2-layer
 # capture, halved) and is scaled by the layer count; shapes that were not captured report null.
 NCU_TRAFFIC = {
-    ("ffn_fused_kernel", 8192, 28672, 8): {"bytes_per_layer": 370828544, "source": "profiles/ffn_fused_70b_stack.md"},
+    ("ffn_fused_kernel", 8192, 28672, 8): {"bytes_per_layer": 370109184, "source": "profiles/ffn_fused_70b_stack.md"},
     ("gemv_streamk_kernel<EPI_SWIGLU>", 8192, 28672, 8): {"bytes": 252018688, "source": "profiles/gemv_streamk_70b_ffn_layer.md"},
 }
 
