@@ -293,7 +293,7 @@ def time_other_configs(a, torch, ops, ffn, peak):
         g2[str(B)] = _hbm_entry(us, K * N * BYTES_PER_WEIGHT + B * K * 2 + B * N * 2, peak)
     wsp.check()
     out["gemv_cfg2"] = {"workload": "decode GEMV [B x 4096] x AWQ [4096 x 11008], one awq_b200_gemv_bf16 call per weight "
-                                    "(bf16 activations converted to fp16 by a small kernel in front of each GEMV)",
+                                    "(one kernel launch each: at this size the bf16 activations are multiplied as they are)",
                         "copies": copies, "batch": g2}
     del ws_
     # ---- configuration 3: decode SwiGLU FFN 4096 / 11008 ----
