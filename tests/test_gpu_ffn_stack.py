@@ -226,6 +226,25 @@ def test_stack_large_batch_takes_the_gemm_path(ops):
     stack.check()
 
 
+@pytest.mark.parametrize("B", [32, 64])
+def test_stack_batched_decode_gemm_vs_oracle_hidden_2048(ops, B):
+    """The GEMM path of the stack at hidden 2048 / intermediate 5632, 32 and 64 token rows, two layers, against the oracle:
+    eager and as a replayed CUDA graph."""
+    from gpu_util import randn_bf16, to_dev, to_host
+    from mlir_air_b200 import ffn
+    H, I, L = 2048, 5632, 2
+    layers_np = _layers_np(H, I, L, seed=91)
+    plan, gus, downs, gammas = _plan(ops, layers_np)
+    stack = ffn.DecodeFFNStack([ffn.FFNLayer(g, d, gm) for g, d, gm in zip(gus, downs, gammas)], H, max_batch=64)
+    assert stack.uses_gemm(B)
+    x = randn_bf16((B, H), seed=B + 1)
+    ref = _oracle_stack(x, layers_np)
+    assert O.rel_l2(to_host(stack.step(to_dev(x))), ref) <= REL_L2_TOL
+    stack.load_input(to_dev(x))
+    assert O.rel_l2(to_host(stack.replay(B).clone()), ref) <= REL_L2_TOL
+    stack.check()
+
+
 # (M, K, N): one k-block pair and one tile; a ragged last tile; more units than SMs with tiles shared by several SMs and
 # SMs covering several tiles; K deeper than the input ring many times over
 @pytest.mark.parametrize("M,K,N", [(9, 128, 256), (16, 256, 32), (33, 1024, 1312), (64, 2048, 5632), (64, 8192, 512),
