@@ -58,6 +58,8 @@ const char *awq_b200_last_error(void);
  * AWQ_ERR_UNSUPPORTED from the next *_check call (use awq_b200_set_decode_kernel(3) then). */
 #define AWQ_ACT_BF16 0
 #define AWQ_ACT_F16 1
+/* f32 sums as the output of awq_b200_gemm_decode_act (beside the two 16-bit formats). */
+#define AWQ_OUT_F32 2
 
 /* Choose the decode kernel: 0 = automatic (TMA + tensor-core stream-K kernel when the
  * shape allows it, else the generic kernel), 1 = force generic, 2 = force stream-K
@@ -346,6 +348,17 @@ int awq_b200_gemm_decode_bf16(const uint16_t *A, const int32_t *qweight, const i
 int awq_b200_gemm_decode_f32(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros,
                              const uint16_t *scales, float *C, int M, int K, int N, int group_size,
                              void *workspace, size_t workspace_bytes, awq_stream_t stream);
+
+/* General form of the two above.  A in `a_format` (AWQ_ACT_*): with fp16 token rows the weights are
+ * dequantised to fp16 as well ((q - z) exact, one rounding of the product with the scale to 11
+ * significant bits, where the bf16 form keeps 8), which is what a decode stack of several layers wants
+ * between its kernels.  C in `c_format`: AWQ_ACT_BF16 (any epilogue), AWQ_ACT_F16 (plain or SwiGLU; the
+ * SwiGLU value is rounded to bf16 as the reference does, then stored as fp16) or AWQ_OUT_F32 (plain sums,
+ * C f32 [M, N]).  Scales below 2^-14 lose precision as fp16 (see AWQ_ACT_*). */
+int awq_b200_gemm_decode_act(const void *A, int a_format, const int32_t *qweight, const int32_t *qzeros,
+                             const uint16_t *scales, const uint16_t *residual, void *C, int c_format,
+                             int swiglu, int M, int K, int N, int group_size, void *workspace,
+                             size_t workspace_bytes, awq_stream_t stream);
 
 /* Synchronise `stream` and report whether a tensor-core GEMM (prefill or batched decode) gave up on a
  * bounded device-side wait since the last check (AWQ_ERR_DEVICE_TIMEOUT); the counterpart of

@@ -160,7 +160,7 @@ bool gemm_decode_supported(int M, int K, int N, int group_size);
 size_t gemm_decode_workspace_bytes(int M, int N);
 int launch_gemm_decode(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros, const uint16_t *scales, uint16_t *C, int M,
                        int K, int N, cudaStream_t stream, int epilogue, const uint16_t *residual, void *workspace,
-                       size_t workspace_bytes);
+                       size_t workspace_bytes, int a_f16 = 0, int c_f16 = 0);  // fp16 token rows / fp16 output (not with a residual)
 int gemm_decode_check(cudaStream_t stream);
 int gemv_push_arrivals_per_rank(int N);  // arrivals a rank signals per EPI_F32_PUSH launch of N columns
 int launch_tp_reduce_add_rmsnorm(const uint16_t *h, const PeerPartials &parts, unsigned int *flags, int expected,

@@ -87,8 +87,10 @@ struct DgCfg {
     static constexpr int NUM_BARS = 3 * STAGES + 2 * ABUF + 4;
     static constexpr int OFF_BARS = STAGES * STAGE_BYTES;
     static constexpr int SMEM_BYTES = OFF_BARS + NUM_BARS * 8 + 16 + 1024;
-    // f32 accumulate, bf16 x bf16, A (weights, tensor memory) and B (token rows) K-major, M 128, N NB
-    static constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NB >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    // f32 accumulate, A (weights, tensor memory) and B (token rows) K-major, M 128, N NB; both operands bf16 (format 1) or both
+    // fp16 (format 0)
+    static constexpr uint32_t IDESC_F16 = (1u << 4) | ((uint32_t)(NB >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    static constexpr uint32_t IDESC_BF16 = IDESC_F16 | (1u << 7) | (1u << 10);
     static_assert(ABUF >= 2 && ACC_COL0 + 4 * NB <= (int)DG_TMEM_COLS, "tensor memory budget");
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
     static_assert(STAGE_BYTES % 1024 == 0, "swizzled tiles need 1024-byte alignment");
@@ -128,7 +130,9 @@ __device__ __forceinline__ float *dg_slot_word(float *slots, int slots_per_tile,
     return slots + (((size_t)tile * slots_per_tile + contributor) * NB + m) * DG_BN + col;
 }
 
-template <int NB>
+// XH: the token rows are fp16 and so are the dequantised weights (11 significant bits instead of 8: what the decode stack
+// uses between its kernels, like the GEMV kernels); otherwise both are bf16.
+template <int NB, bool XH>
 __global__ void __launch_bounds__(DG_THREADS, 1)
 gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
                    const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmZ,
@@ -258,7 +262,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 #pragma unroll
                         for (int h = 0; h < 2; ++h)  // the tile's two halves of 128 weight columns
                             dg_umma_bf16_ta(d_tmem + h * NB, a_tmem + h * (DG_GROUP / 2) + 8 * k16,
-                                            x_desc + (uint64_t)((k16 >> 2) * ((Cfg::A_BYTES / 2) >> 4) + 2 * (k16 & 3)), Cfg::IDESC,
+                                            x_desc + (uint64_t)((k16 >> 2) * ((Cfg::A_BYTES / 2) >> 4) + 2 * (k16 & 3)), XH ? Cfg::IDESC_F16 : Cfg::IDESC_BF16,
                                             k16 ? 1u : acc0);
                     }
                     dg_umma_commit(empty_bar(s));
@@ -305,8 +309,12 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             uint32_t zz[4], ss[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                zz[e] = ((zw >> (4 * e)) & 0xFu) * 0x00010001u + 0x43004300u;
+                zz[e] = ((zw >> (4 * e)) & 0xFu) * 0x00010001u + (XH ? 0x64006400u : 0x43004300u);  // 1024 + z / 128 + z
                 asm("prmt.b32 %0, %1, %1, %2;" : "=r"(ss[e]) : "r"(sw[e]), "r"((g & 1) ? 0x3232u : 0x1010u));
+                if (XH) {  // the scale as fp16 (exact for scales of 2^-14 and more)
+                    const uint32_t hbits = bf16_value_to_f16_bits(__uint_as_float(ss[e] << 16));
+                    ss[e] = hbits * 0x00010001u;
+                }
             }
             uint32_t r[4][4];
 #pragma unroll
@@ -325,8 +333,13 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     uint32_t v[8];
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        v[2 * e] = dg_bf16x2_mul(dg_bf16x2_sub(nib2_to_bf16x2_biased(lo >> (4 * e)), zz[e]), ss[e]);
-                        v[2 * e + 1] = dg_bf16x2_mul(dg_bf16x2_sub(nib2_to_bf16x2_biased(hi >> (4 * e)), zz[e]), ss[e]);
+                        if (XH) {  // (1024 + q) - (1024 + z) and the product, each exact or rounded once, in fp16
+                            v[2 * e] = dg_f16x2_mul(dg_f16x2_sub(lop3_and_or(lo >> (4 * e), 0x000F000Fu, 0x64006400u), zz[e]), ss[e]);
+                            v[2 * e + 1] = dg_f16x2_mul(dg_f16x2_sub(lop3_and_or(hi >> (4 * e), 0x000F000Fu, 0x64006400u), zz[e]), ss[e]);
+                        } else {
+                            v[2 * e] = dg_bf16x2_mul(dg_bf16x2_sub(nib2_to_bf16x2_biased(lo >> (4 * e)), zz[e]), ss[e]);
+                            v[2 * e + 1] = dg_bf16x2_mul(dg_bf16x2_sub(nib2_to_bf16x2_biased(hi >> (4 * e)), zz[e]), ss[e]);
+                        }
                     }
                     // lanes g and g + 8 hold nibbles 0 and 1, lanes g + 16 and g + 24 nibbles 2 and 3
                     dg_tmem_st_16x256b(a_tmem + 8 * (2 * c + sp), v[0], v[1], v[2], v[3]);
@@ -395,7 +408,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 // ranges of its CTAs decide who contributed to which tile).
 template <int NB>
 __global__ void __launch_bounds__(256)
-gemm_decode_fixup_kernel(uint16_t *__restrict__ C, const uint16_t *__restrict__ R, int epi, int M, int N, int KB, int tiles,
+gemm_decode_fixup_kernel(uint16_t *__restrict__ C, const uint16_t *__restrict__ R, int epi, int c_f16, int M, int N, int KB, int tiles,
                          int main_ctas, const float *__restrict__ slots, int slots_per_tile) {
     pdl_launch_dependents();
     pdl_wait();
@@ -415,14 +428,24 @@ gemm_decode_fixup_kernel(uint16_t *__restrict__ C, const uint16_t *__restrict__ 
     if (epi == GEMM_EPI_F32) {  // a tensor-parallel rank's partial sums, to be added up across the ranks
         *reinterpret_cast<float4 *>(reinterpret_cast<float *>(C) + (size_t)m * N + n) = sum;
     } else if (epi == GEMM_EPI_SWIGLU) {
-        const uint32_t o = (uint32_t)swiglu_bits(sum.x, sum.y) | ((uint32_t)swiglu_bits(sum.z, sum.w) << 16);
-        *reinterpret_cast<uint32_t *>(C + (size_t)m * (N >> 1) + (n >> 1)) = o;
+        uint32_t o0 = swiglu_bits(sum.x, sum.y), o1 = swiglu_bits(sum.z, sum.w);
+        if (c_f16) {  // the bf16 value, in the fp16 form the next product reads
+            o0 = bf16_value_to_f16_bits(bf16_bits_to_f32((uint16_t)o0));
+            o1 = bf16_value_to_f16_bits(bf16_bits_to_f32((uint16_t)o1));
+        }
+        *reinterpret_cast<uint32_t *>(C + (size_t)m * (N >> 1) + (n >> 1)) = o0 | (o1 << 16);
     } else {
         if (epi == GEMM_EPI_RESIDUAL) {
             const uint2 rv = *reinterpret_cast<const uint2 *>(R + (size_t)m * N + n);
             sum.x += bf16x2_lo(rv.x), sum.y += bf16x2_hi(rv.x), sum.z += bf16x2_lo(rv.y), sum.w += bf16x2_hi(rv.y);
         }
-        *reinterpret_cast<uint2 *>(C + (size_t)m * N + n) = make_uint2(pack_bf16x2(sum.x, sum.y), pack_bf16x2(sum.z, sum.w));
+        if (c_f16) {
+            const uint32_t o0 = (uint32_t)bf16_value_to_f16_bits(sum.x) | ((uint32_t)bf16_value_to_f16_bits(sum.y) << 16);
+            const uint32_t o1 = (uint32_t)bf16_value_to_f16_bits(sum.z) | ((uint32_t)bf16_value_to_f16_bits(sum.w) << 16);
+            *reinterpret_cast<uint2 *>(C + (size_t)m * N + n) = make_uint2(o0, o1);
+        } else {
+            *reinterpret_cast<uint2 *>(C + (size_t)m * N + n) = make_uint2(pack_bf16x2(sum.x, sum.y), pack_bf16x2(sum.z, sum.w));
+        }
     }
 }
 
@@ -449,14 +472,15 @@ size_t gemm_decode_workspace_bytes(int M, int N) {
     return ((size_t)dg_sm_count() + 2 * tiles) * DG_BN * dg_rows(M) * 4;
 }
 
-template <int NB>
+template <int NB, bool XH>
 static int launch_dg(const CUtensorMap &tmA, const CUtensorMap &tmW, const CUtensorMap &tmS, const CUtensorMap &tmZ, uint16_t *C,
-                     const uint16_t *residual, int epilogue, int M, int N, int K, int tiles, void *workspace, cudaStream_t stream) {
+                     const uint16_t *residual, int epilogue, int c_f16, int M, int N, int K, int tiles, void *workspace,
+                     cudaStream_t stream) {
     using Cfg = DgCfg<NB>;
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(gemm_decode_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+        attr_err = cudaFuncSetAttribute(gemm_decode_kernel<NB, XH>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     });
     if (attr_err != cudaSuccess) return check_cuda(attr_err, "decode gemm: shared memory attribute");
     const int sms = dg_sm_count();
@@ -464,19 +488,19 @@ static int launch_dg(const CUtensorMap &tmA, const CUtensorMap &tmW, const CUten
     const int ctas = (long long)sms < U ? sms : (int)U;
     float *slots = reinterpret_cast<float *>(workspace);
     const int spt = dg_slots_per_tile(tiles);
-    int rc = check_cuda(launch_pdl(gemm_decode_kernel<NB>, dim3(ctas), dim3(DG_THREADS), Cfg::SMEM_BYTES, stream, tmA, tmW, tmS, tmZ, M, N, K,
+    int rc = check_cuda(launch_pdl(gemm_decode_kernel<NB, XH>, dim3(ctas), dim3(DG_THREADS), Cfg::SMEM_BYTES, stream, tmA, tmW, tmS, tmZ, M, N, K,
                                    tiles, slots, spt, wait_limit_cycles()),
                         "decode gemm launch");
     if (rc) return rc;
     const int blocks = tiles * ((M + 3) / 4);
-    return check_cuda(launch_pdl(gemm_decode_fixup_kernel<NB>, dim3(blocks), dim3(256), 0, stream, C, residual, epilogue, M, N, K / DG_GROUP,
+    return check_cuda(launch_pdl(gemm_decode_fixup_kernel<NB>, dim3(blocks), dim3(256), 0, stream, C, residual, epilogue, c_f16, M, N, K / DG_GROUP,
                                  tiles, ctas, (const float *)slots, spt),
                       "decode gemm fix-up launch");
 }
 
 int launch_gemm_decode(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros, const uint16_t *scales, uint16_t *C, int M,
                        int K, int N, cudaStream_t stream, int epilogue, const uint16_t *residual, void *workspace,
-                       size_t workspace_bytes) {
+                       size_t workspace_bytes, int a_f16, int c_f16) {
     const size_t need = gemm_decode_workspace_bytes(M, N);
     if (!workspace || workspace_bytes < need)
         return set_error(AWQ_ERR_WORKSPACE, "gemm_decode: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
@@ -485,7 +509,7 @@ int launch_gemm_decode(const uint16_t *A, const int32_t *qweight, const int32_t 
     CUtensorMap tmA, tmW, tmS, tmZ;
     int rc;
     // token rows as (64 k, rows, K / 64): one copy brings the two 64-k tiles of a unit
-    if ((rc = encode_tensor_map_3d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, A, DG_BK, M, K / DG_BK, (uint64_t)K * 2, DG_BK * 2, DG_BK,
+    if ((rc = encode_tensor_map_3d(&tmA, a_f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, A, DG_BK, M, K / DG_BK, (uint64_t)K * 2, DG_BK * 2, DG_BK,
                                    rows, 2, CU_TENSOR_MAP_SWIZZLE_128B)))
         return rc;
     if ((rc = encode_tensor_map_2d(&tmW, CU_TENSOR_MAP_DATA_TYPE_INT32, qweight, nb, K, (uint64_t)nb * 4, DG_BN / 8, DG_GROUP,
@@ -497,8 +521,9 @@ int launch_gemm_decode(const uint16_t *A, const int32_t *qweight, const int32_t 
     if ((rc = encode_tensor_map_2d(&tmZ, CU_TENSOR_MAP_DATA_TYPE_INT32, qzeros, nb, G, (uint64_t)nb * 4, DG_BN / 8, 1,
                                    CU_TENSOR_MAP_SWIZZLE_NONE)))
         return rc;
-#define DG_LAUNCH(NBV) launch_dg<NBV>(tmA, tmW, tmS, tmZ, C, residual, epilogue, M, N, K, tiles, workspace, stream)
-    return rows == 16 ? DG_LAUNCH(16) : (rows == 32 ? DG_LAUNCH(32) : DG_LAUNCH(64));
+#define DG_LAUNCH(NBV, XHV) launch_dg<NBV, XHV>(tmA, tmW, tmS, tmZ, C, residual, epilogue, c_f16, M, N, K, tiles, workspace, stream)
+    if (a_f16) return rows == 16 ? DG_LAUNCH(16, true) : (rows == 32 ? DG_LAUNCH(32, true) : DG_LAUNCH(64, true));
+    return rows == 16 ? DG_LAUNCH(16, false) : (rows == 32 ? DG_LAUNCH(32, false) : DG_LAUNCH(64, false));
 #undef DG_LAUNCH
 }
 

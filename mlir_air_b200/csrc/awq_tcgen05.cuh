@@ -83,6 +83,16 @@ __device__ __forceinline__ uint32_t dg_bf16x2_mul(uint32_t a, uint32_t b) {
     asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
     return r;
 }
+__device__ __forceinline__ uint32_t dg_f16x2_sub(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t dg_f16x2_mul(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
 // Which column of its group of 32 a TMEM lane holds: the dequant warps place the four columns of a 16-bit half word
 // (nibbles e = 0..3: columns 2e + half of word `word`) in lanes g, g + 8, g + 16, g + 24 with g = 2 word + half.
 __device__ __forceinline__ int dg_lane_column(int lane) {

@@ -244,25 +244,25 @@ class DecodeFFNStack:
         if self.uses_gemm(B) and self.tp > 1:
             # tensor parallel: gate/up shard -> SwiGLU, down shard -> f32 partial, allreduce, residual add fused with
             # the next layer's norm
-            nb = self._normed[:B].view(torch.bfloat16)
-            ops.rmsnorm(h, self.layers[0].gamma, self.eps, out=nb)
+            # activations between the kernels are fp16, as in the GEMV path: the products then run on fp16 operands
+            ops.rmsnorm(h, self.layers[0].gamma, self.eps, out=normed, out_f16=True)
             for idx, l in enumerate(self.layers):
                 il = l.down.K
-                it = inter.view(-1)[:B * il].view(B, il).view(torch.bfloat16)
-                ops.gemm_decode(nb, l.gateup, self.gemm_ws, out=it, swiglu=True)
+                it = inter.view(-1)[:B * il].view(B, il)
+                ops.gemm_decode(normed, l.gateup, self.gemm_ws, out=it, swiglu=True, out_f16=True)
                 ops.gemm_decode(it, l.down, self.gemm_ws, out=partial, f32_out=True)
                 torch.distributed.all_reduce(partial, group=self.group)
                 nxt = self.layers[idx + 1].gamma if idx + 1 < len(self.layers) else None
-                ops.add_rmsnorm(h, partial, nxt, self.eps, h_out=other, normed=nb if nxt is not None else None)
+                ops.add_rmsnorm(h, partial, nxt, self.eps, h_out=other, normed=normed if nxt is not None else None,
+                                normed_f16=True)
                 h, other = other, h
             return h
         if self.uses_gemm(B):
-            nb = self._normed[:B].view(torch.bfloat16)  # the GEMM's A operand is bf16
             for l in self.layers:
                 il = l.down.K
-                it = inter.view(-1)[:B * il].view(B, il).view(torch.bfloat16)
-                ops.rmsnorm(h, l.gamma, self.eps, out=nb)
-                ops.gemm_decode(nb, l.gateup, self.gemm_ws, out=it, swiglu=True)
+                it = inter.view(-1)[:B * il].view(B, il)
+                ops.rmsnorm(h, l.gamma, self.eps, out=normed, out_f16=True)
+                ops.gemm_decode(normed, l.gateup, self.gemm_ws, out=it, swiglu=True, out_f16=True)
                 ops.gemm_decode(it, l.down, self.gemm_ws, out=other, residual=h)
                 h, other = other, h
             return h

@@ -93,7 +93,7 @@ class Workspace:
             _lib.call("awq_b200_workspace_check", self.buf.data_ptr(), _stream())
 
 
-ACT_BF16, ACT_F16 = 0, 1
+ACT_BF16, ACT_F16, OUT_F32 = 0, 1, 2
 
 
 def _act_dtype(f16: bool):
@@ -380,28 +380,28 @@ class GemmDecodeWorkspace:
         return int(_lib.load().awq_b200_gemm_decode_workspace_bytes(int(M), int(N))) <= self.nbytes
 
 
-def gemm_decode(A, w: AwqWeight, ws: GemmDecodeWorkspace, out=None, residual=None, swiglu=False, f32_out=False):
+def gemm_decode(A, w: AwqWeight, ws: GemmDecodeWorkspace, out=None, residual=None, swiglu=False, f32_out=False, out_f16=False):
     """C [M, N] = A [M, K] @ W for a decode batch of M <= 64 rows (weights streamed once, all SMs busy whatever the
-    shape); `residual` / `swiglu` as in `gemm`; `f32_out`: the f32 sums themselves (a tensor-parallel partial)."""
-    _want(A, torch.bfloat16, "A")
+    shape); `residual` / `swiglu` as in `gemm`; `f32_out`: the f32 sums themselves (a tensor-parallel partial).
+    A may be bf16 or fp16 (the weights are then dequantised to fp16 too: 11 significant bits instead of 8);
+    `out_f16` stores a plain or SwiGLU result as fp16 for a following fp16 product."""
+    if A.dtype not in (torch.bfloat16, torch.float16):
+        raise _lib.AwqBackendError(f"A must be bf16 or fp16, got {A.dtype}")
+    _want(A, A.dtype, "A")
     if A.dim() != 2 or A.shape[1] != w.K:
         raise _lib.AwqBackendError(f"A must be [M, {w.K}], got {tuple(A.shape)}")
-    if f32_out:
-        if residual is not None or swiglu:
-            raise _lib.AwqBackendError("gemm_decode: f32_out takes neither residual nor swiglu")
-        if out is None:
-            out = torch.empty((A.shape[0], w.N), dtype=torch.float32, device=A.device)
-        _want(out, torch.float32, "out")
-        _lib.call("awq_b200_gemm_decode_f32", _ptr(A), _ptr(w.qweight), _ptr(w.qzeros), _ptr(w.scales), _ptr(out), A.shape[0],
-                  w.K, w.N, w.group_size, _ptr(ws.buf), ws.nbytes, _stream())
-        return out
-    n_out = w.N // 2 if swiglu else w.N
+    if f32_out and (residual is not None or swiglu or out_f16):
+        raise _lib.AwqBackendError("gemm_decode: f32_out takes neither residual, swiglu nor out_f16")
+    if out_f16 and residual is not None:
+        raise _lib.AwqBackendError("gemm_decode: the residual add goes with a bf16 output")
+    dt = torch.float32 if f32_out else _act_dtype(out_f16)
     if out is None:
-        out = torch.empty((A.shape[0], n_out), dtype=torch.bfloat16, device=A.device)
-    _want(out, torch.bfloat16, "out")
+        out = torch.empty((A.shape[0], w.N // 2 if swiglu else w.N), dtype=dt, device=A.device)
+    _want(out, dt, "out")
     if residual is not None:
         _want(residual, torch.bfloat16, "residual")
-    _lib.call("awq_b200_gemm_decode_bf16", _ptr(A), _ptr(w.qweight), _ptr(w.qzeros), _ptr(w.scales), _ptr(residual), _ptr(out),
+    _lib.call("awq_b200_gemm_decode_act", _ptr(A), ACT_F16 if A.dtype == torch.float16 else ACT_BF16, _ptr(w.qweight),
+              _ptr(w.qzeros), _ptr(w.scales), _ptr(residual), _ptr(out), OUT_F32 if f32_out else (ACT_F16 if out_f16 else ACT_BF16),
               1 if swiglu else 0, A.shape[0], w.K, w.N, w.group_size, _ptr(ws.buf), ws.nbytes, _stream())
     return out
 

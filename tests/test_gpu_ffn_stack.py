@@ -281,6 +281,45 @@ def test_gemm_decode_vs_oracle(ops, M, K, N):
         assert O.rel_l2(t, O.gateup_swiglu_A_ref(A, gate, up, 128)) <= REL_L2_TOL
 
 
+@pytest.mark.parametrize("M,K,N", [(9, 128, 256), (33, 1024, 1312), (64, 2048, 5632), (17, 8192, 512)])
+def test_gemm_decode_fp16_operands_vs_oracle(ops, M, K, N):
+    """The same product on fp16 token rows and weights dequantised to fp16 (what the decode stack runs between its
+    kernels): every epilogue against the oracle, nearer to it than the bf16 form, fp16 and bf16 outputs of one
+    value agreeing, and repeatable bits."""
+    import torch
+    from gpu_util import dev_weight, randn_bf16, synth_awq, to_dev, to_host
+    bits = lambda a: a.view(np.uint16)  # noqa: E731
+    A = randn_bf16((M, K), seed=M + 7)
+    w = synth_awq(K, N, 128, seed=N + 8)
+    R = randn_bf16((M, N), seed=9)
+    ws = ops.GemmDecodeWorkspace(N, batch=M)
+    dw = dev_weight(*w)
+    Ah = to_dev(A).to(torch.float16)  # exact: |values| of a unit normal sit well inside fp16's normal range
+    yf = ops.gemm_decode(Ah, dw, ws, f32_out=True)
+    ops.gemm_check()
+    exact = A.astype(np.float32) @ O.dequant_f32(*w, 128)
+    err_h = O.rel_l2(yf.cpu().numpy(), exact)
+    err_b = O.rel_l2(ops.gemm_decode(to_dev(A), dw, ws, f32_out=True).cpu().numpy(), exact)
+    assert err_h <= 5e-4 and err_h < 0.5 * err_b, (err_h, err_b)  # 11 against 8 significant bits of every weight
+    y = to_host(ops.gemm_decode(Ah, dw, ws))
+    assert np.array_equal(bits(y), bits(to_host(yf.to(torch.bfloat16))))
+    assert O.rel_l2(y, O.gemv_A_ref(A, *w, 128)) <= 3e-3
+    y16 = ops.gemm_decode(Ah, dw, ws, out_f16=True)
+    assert y16.dtype == torch.float16 and torch.equal(y16, yf.to(torch.float16))
+    yr = to_host(ops.gemm_decode(Ah, dw, ws, residual=to_dev(R)))
+    ops.gemm_check()
+    assert O.rel_l2(yr, O.gemv_A_ref(A, *w, 128, residual=R)) <= 3e-3
+    assert np.array_equal(bits(yr), bits(to_host(ops.gemm_decode(Ah, dw, ws, residual=to_dev(R)))))
+    if N % 64 == 0:
+        gate, up = synth_awq(K, N // 2, 128, seed=4), synth_awq(K, N // 2, 128, seed=5)
+        wgu = ops.interleave_gate_up(dev_weight(*gate), dev_weight(*up))
+        t = ops.gemm_decode(Ah, wgu, ws, swiglu=True)
+        t16 = ops.gemm_decode(Ah, wgu, ws, swiglu=True, out_f16=True)
+        ops.gemm_check()
+        assert t16.dtype == torch.float16 and torch.equal(t16, t.to(torch.float16))  # the bf16 value, stored as fp16
+        assert O.rel_l2(to_host(t), O.gateup_swiglu_A_ref(A, gate, up, 128)) <= 3e-3
+
+
 def test_gemm_decode_rejects_what_it_cannot_run(ops):
     import torch
     from gpu_util import dev_weight, randn_bf16, synth_awq, to_dev
@@ -292,3 +331,10 @@ def test_gemm_decode_rejects_what_it_cannot_run(ops):
     with pytest.raises(AwqBackendError):  # workspace too small for these rows (sized for 16, called with 17)
         ops.gemm_decode(to_dev(randn_bf16((17, 256), seed=1)), w, ws)
     assert ops.gemm_decode(torch.zeros((0, 256), dtype=torch.bfloat16, device="cuda"), w, ws).shape == (0, 256)
+    x = to_dev(randn_bf16((16, 256), seed=1))
+    with pytest.raises(AwqBackendError):  # the residual joins a bf16 output only
+        ops.gemm_decode(x, w, ws, residual=x, out_f16=True)
+    with pytest.raises(AwqBackendError):  # f32 sums carry no epilogue
+        ops.gemm_decode(x, w, ws, f32_out=True, swiglu=True)
+    with pytest.raises(AwqBackendError):
+        ops.gemm_decode(x.float(), w, ws)
