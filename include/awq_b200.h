@@ -360,6 +360,18 @@ int awq_b200_gemm_decode_act(const void *A, int a_format, const int32_t *qweight
                              int swiglu, int M, int K, int N, int group_size, void *workspace,
                              size_t workspace_bytes, awq_stream_t stream);
 
+/* The same product for M <= 32 token rows with the packed nibbles themselves as the tensor core's operand
+ * (a nibble q in a byte is the e4m3 number q * 2^-9) and the token rows split into two e4m3 pieces per
+ * element (exact for a bf16 value within 2^-14 of its row's largest magnitude); zero point and scale are
+ * applied to the per-group sums in f32, as the reference's golden does, so no weight is rounded.  Three
+ * launches: the split of the token rows, the product, the addition of the partial sums.  Arguments as
+ * awq_b200_gemm_decode_act; the workspace also holds the split rows, hence K in its size. */
+size_t awq_b200_gemm_decode_f8_workspace_bytes(int M, int K, int N);
+int awq_b200_gemm_decode_f8(const void *A, int a_format, const int32_t *qweight, const int32_t *qzeros,
+                            const uint16_t *scales, const uint16_t *residual, void *C, int c_format,
+                            int swiglu, int M, int K, int N, int group_size, void *workspace,
+                            size_t workspace_bytes, awq_stream_t stream);
+
 /* Synchronise `stream` and report whether a tensor-core GEMM (prefill or batched decode) gave up on a
  * bounded device-side wait since the last check (AWQ_ERR_DEVICE_TIMEOUT); the counterpart of
  * xrt.py:204-218. */

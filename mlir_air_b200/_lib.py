@@ -76,6 +76,8 @@ SIGNATURES = {
     "awq_b200_gemm_decode_workspace_bytes": (c_size_t, [c_int, c_int]),
     "awq_b200_gemm_decode_f32": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P, c_size_t, _P]),
     "awq_b200_gemm_decode_act": (c_int, [_P, c_int, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_size_t, _P]),
+    "awq_b200_gemm_decode_f8_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "awq_b200_gemm_decode_f8": (c_int, [_P, c_int, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_size_t, _P]),
     "awq_b200_gemm_decode_bf16": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, c_size_t, _P]),
     "awq_b200_repack_B_to_A": (c_int, [_P] * 6 + [c_int, c_int, c_int, _P]),
     "awq_b200_repack_A_to_B": (c_int, [_P] * 6 + [c_int, c_int, c_int, _P]),

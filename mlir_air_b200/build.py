@@ -13,7 +13,7 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libawq_b200.so")
-SOURCES = ["awq_capi.cu", "awq_dequant.cu", "awq_generic.cu", "awq_gemv_streamk.cu", "awq_gemv_streamk_mb.cu", "awq_gemm_tc.cu", "awq_gemm_decode.cu", "awq_gemm_tm.cu",
+SOURCES = ["awq_capi.cu", "awq_dequant.cu", "awq_generic.cu", "awq_gemv_streamk.cu", "awq_gemv_streamk_mb.cu", "awq_gemm_tc.cu", "awq_gemm_decode.cu", "awq_gemm_decode_f8.cu", "awq_gemm_tm.cu",
            "awq_static_scratch.cu", "awq_ffn_fused.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "-Xcompiler", "-Wall"]

@@ -369,7 +369,8 @@ extern "C" int awq_b200_gemm_check(awq_stream_t stream) {
     const int rc = gemm_tc_check(as_stream(stream));
     const int rc2 = gemm_decode_check(as_stream(stream));
     const int rc3 = gemm_tm_check(as_stream(stream));
-    return rc ? rc : (rc2 ? rc2 : rc3);
+    const int rc4 = gemm_decode_f8_check(as_stream(stream));
+    return rc ? rc : (rc2 ? rc2 : (rc3 ? rc3 : rc4));
 }
 
 extern "C" size_t awq_b200_gemm_decode_workspace_bytes(int M, int N) { return gemm_decode_workspace_bytes(M, N); }
@@ -411,6 +412,32 @@ extern "C" int awq_b200_gemm_decode_act(const void *A, int a_format, const int32
     return launch_gemm_decode(reinterpret_cast<const uint16_t *>(A), qweight, qzeros, scales, reinterpret_cast<uint16_t *>(C), M, K, N,
                               as_stream(stream), epi, residual, workspace, workspace_bytes, a_format == AWQ_ACT_F16,
                               c_format == AWQ_ACT_F16);
+}
+
+extern "C" size_t awq_b200_gemm_decode_f8_workspace_bytes(int M, int K, int N) { return gemm_decode_f8_workspace_bytes(M, K, N); }
+
+extern "C" int awq_b200_gemm_decode_f8(const void *A, int a_format, const int32_t *qweight, const int32_t *qzeros,
+                                       const uint16_t *scales, const uint16_t *residual, void *C, int c_format, int swiglu, int M,
+                                       int K, int N, int group_size, void *workspace, size_t workspace_bytes,
+                                       awq_stream_t stream) {
+    AWQ_REQUIRE(M >= 0 && K > 0 && N > 0 && group_size > 0, "gemm_decode_f8: bad size");
+    AWQ_REQUIRE(a_format == AWQ_ACT_BF16 || a_format == AWQ_ACT_F16, "gemm_decode_f8: a_format must be AWQ_ACT_BF16 or AWQ_ACT_F16");
+    AWQ_REQUIRE(c_format == AWQ_ACT_BF16 || c_format == AWQ_ACT_F16 || c_format == AWQ_OUT_F32,
+                "gemm_decode_f8: c_format must be AWQ_ACT_BF16, AWQ_ACT_F16 or AWQ_OUT_F32");
+    AWQ_REQUIRE(!(swiglu && residual), "gemm_decode_f8: SwiGLU and residual do not combine");
+    AWQ_REQUIRE(!(c_format != AWQ_ACT_BF16 && residual), "gemm_decode_f8: the residual add goes with a bf16 output");
+    AWQ_REQUIRE(!(c_format == AWQ_OUT_F32 && swiglu), "gemm_decode_f8: the f32 output carries plain sums, not SwiGLU");
+    if (M == 0) return AWQ_OK;
+    AWQ_REQUIRE(A && qweight && qzeros && scales && C, "gemm_decode_f8: null pointer");
+    AWQ_REQUIRE(aligned16(A) && aligned16(scales) && aligned16(qweight) && aligned16(qzeros) && aligned16(C) &&
+                    aligned16(residual) && aligned16(workspace), "gemm_decode_f8: pointers must be 16-byte aligned");
+    if (!gemm_decode_f8_supported(M, K, N, group_size))
+        return set_error(AWQ_ERR_UNSUPPORTED, "gemm_decode_f8: needs M <= 32, group 128, K %% 128 == 0, N %% 32 == 0 "
+                         "(M=%d K=%d N=%d gs=%d)", M, K, N, group_size);
+    const int epi = c_format == AWQ_OUT_F32 ? GEMM_EPI_F32 : (swiglu ? GEMM_EPI_SWIGLU : (residual ? GEMM_EPI_RESIDUAL : GEMM_EPI_BF16));
+    return launch_gemm_decode_f8(reinterpret_cast<const uint16_t *>(A), a_format == AWQ_ACT_F16, qweight, qzeros, scales,
+                                 reinterpret_cast<uint16_t *>(C), M, K, N, as_stream(stream), epi, residual, c_format == AWQ_ACT_F16,
+                                 workspace, workspace_bytes);
 }
 
 extern "C" int awq_b200_gemm_decode_bf16(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros,

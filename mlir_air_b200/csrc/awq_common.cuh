@@ -162,6 +162,14 @@ int launch_gemm_decode(const uint16_t *A, const int32_t *qweight, const int32_t 
                        int K, int N, cudaStream_t stream, int epilogue, const uint16_t *residual, void *workspace,
                        size_t workspace_bytes, int a_f16 = 0, int c_f16 = 0);  // fp16 token rows / fp16 output (not with a residual)
 int gemm_decode_check(cudaStream_t stream);
+// The same product for up to 32 token rows with the nibbles and the split token rows as fp8 operands (awq_gemm_decode_f8.cu);
+// its workspace holds the split rows as well, hence K.
+bool gemm_decode_f8_supported(int M, int K, int N, int group_size);
+size_t gemm_decode_f8_workspace_bytes(int M, int K, int N);
+int launch_gemm_decode_f8(const uint16_t *A, int a_f16, const int32_t *qweight, const int32_t *qzeros, const uint16_t *scales,
+                          uint16_t *C, int M, int K, int N, cudaStream_t stream, int epilogue, const uint16_t *residual, int c_f16,
+                          void *workspace, size_t workspace_bytes);
+int gemm_decode_f8_check(cudaStream_t stream);
 int gemv_push_arrivals_per_rank(int N);  // arrivals a rank signals per EPI_F32_PUSH launch of N columns
 int launch_tp_reduce_add_rmsnorm(const uint16_t *h, const PeerPartials &parts, unsigned int *flags, int expected,
                                  const uint16_t *gamma, float eps, uint16_t *h_out, uint16_t *normed, int normed_f16, int B,

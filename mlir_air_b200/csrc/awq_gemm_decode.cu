@@ -49,31 +49,21 @@
 #include <mutex>
 
 #include "awq_common.cuh"
+#include "awq_gemm_decode.cuh"
 #include "awq_ptx.cuh"
 #include "awq_streamk.cuh"
 #include "awq_tcgen05.cuh"
 
 namespace awq {
 
-int encode_tensor_map_2d(CUtensorMap *map, int dtype, const void *base, uint64_t dim0, uint64_t dim1,
-                         uint64_t stride1_bytes, uint32_t box0, uint32_t box1, int swizzle);
-int encode_tensor_map_3d(CUtensorMap *map, int dtype, const void *base, uint64_t dim0, uint64_t dim1, uint64_t dim2,
-                         uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1, uint32_t box2,
-                         int swizzle);
-
-constexpr int DG_BN = 256, DG_BK = 64, DG_GROUP = 128;
 constexpr int DG_ABUF_COLS = 2 * (DG_GROUP / 2);        // a weight buffer in tensor memory: two 128-column halves x 128 k
                                                         // as bf16 pairs = 128 TMEM columns
-constexpr int DG_W_BYTES = DG_GROUP * (DG_BN / 8) * 4;  // 16 KB of packed words: a unit (128 k, one quantisation group)
-constexpr int DG_S_BYTES = DG_BN * 2;
-constexpr int DG_Z_BYTES = DG_BN / 8 * 4;
 constexpr int DG_SZ_BYTES = 1024;                       // scales, then zeros
 constexpr int DG_DEQUANT_WARPS = 16;
 constexpr int DG_DEQUANT_WARP0 = 4, DG_EPI_WARP0 = DG_DEQUANT_WARP0 + DG_DEQUANT_WARPS;
 constexpr int DG_THREADS = (DG_EPI_WARP0 + 4) * 32;  // 768
 constexpr uint32_t DG_TMEM_COLS = 512;
 constexpr int DG_MAX_ROWS = 64;
-constexpr int DG_MAX_TILES = 4096;
 
 // NB = token rows the MMA sees (its N): the batch rounded up to 16, 32 or 64.
 template <int NB>
@@ -98,37 +88,6 @@ struct DgCfg {
 };
 
 __device__ int g_gemm_dec_error;  // 0 = ok; set when a bounded wait gave up
-
-// The walk over a CTA's units, the same for every warp role: unit u = tile * KB + kb (KB units of 128 k per tile),
-// range [u0, u1).
-struct UnitWalk {
-    int KB, u, u1;
-    __device__ __forceinline__ UnitWalk(int tiles, int kb_count) : KB(kb_count) {
-        const long long U = (long long)tiles * kb_count, C = gridDim.x, c = blockIdx.x;
-        u = (int)(c * U / C);
-        u1 = (int)((c + 1) * U / C);
-    }
-    __device__ __forceinline__ bool valid() const { return u < u1; }
-    __device__ __forceinline__ int tile() const { return u / KB; }
-    __device__ __forceinline__ int kb() const { return u - tile() * KB; }
-    // units of the current tile that this CTA still has, from u on
-    __device__ __forceinline__ int left_in_tile() const {
-        const int end = (tile() + 1) * KB;
-        return (end < u1 ? end : u1) - u;
-    }
-};
-
-// The first CTA whose range (UnitWalk) reaches into tile t.
-__device__ __forceinline__ int dg_first_cta(int t, int KB, int tiles) {
-    const long long U = (long long)tiles * KB, C = gridDim.x;
-    return (int)((((long long)t * KB + 1) * C + U - 1) / U) - 1;
-}
-// Partial sums of a tile in the workspace: slot [contributor][token row m][column of the tile], so that the 32 lanes
-// of a warp (columns) touch one 128-byte line.
-template <int NB>
-__device__ __forceinline__ float *dg_slot_word(float *slots, int slots_per_tile, int tile, int contributor, int m, int col) {
-    return slots + (((size_t)tile * slots_per_tile + contributor) * NB + m) * DG_BN + col;
-}
 
 // XH: the token rows are fp16 and so are the dequantised weights (11 significant bits instead of 8: what the decode stack
 // uses between its kernels, like the GEMV kernels); otherwise both are bf16.
@@ -408,8 +367,9 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 // ranges of its CTAs decide who contributed to which tile).
 template <int NB>
 __global__ void __launch_bounds__(256)
-gemm_decode_fixup_kernel(uint16_t *__restrict__ C, const uint16_t *__restrict__ R, int epi, int c_f16, int M, int N, int KB, int tiles,
-                         int main_ctas, const float *__restrict__ slots, int slots_per_tile) {
+gemm_decode_fixup_kernel(uint16_t *__restrict__ C, const uint16_t *__restrict__ R, int epi, int c_f16, float sum_scale,
+                         const float *__restrict__ row_scale, int M, int N, int KB, int tiles, int main_ctas,
+                         const float *__restrict__ slots, int slots_per_tile) {
     pdl_launch_dependents();
     pdl_wait();
     const int row_chunks = (M + 3) >> 2;
@@ -424,6 +384,10 @@ gemm_decode_fixup_kernel(uint16_t *__restrict__ C, const uint16_t *__restrict__ 
     for (int c = 1; c <= last - first; ++c) {
         const float4 v = __ldcg(reinterpret_cast<const float4 *>(src + (size_t)c * NB * DG_BN));
         sum.x += v.x, sum.y += v.y, sum.z += v.z, sum.w += v.w;
+    }
+    if (row_scale) {  // powers of two that the main kernel's operands left out: exact
+        const float f = sum_scale * row_scale[m];
+        sum.x *= f, sum.y *= f, sum.z *= f, sum.w *= f;
     }
     if (epi == GEMM_EPI_F32) {  // a tensor-parallel rank's partial sums, to be added up across the ranks
         *reinterpret_cast<float4 *>(reinterpret_cast<float *>(C) + (size_t)m * N + n) = sum;
@@ -455,14 +419,14 @@ bool gemm_decode_supported(int M, int K, int N, int group_size) {
            N > 0 && (N + DG_BN - 1) / DG_BN <= DG_MAX_TILES && device_is_sm100();
 }
 
-static int dg_rows(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : 64); }
+int dg_rows(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : 64); }
 
-static int dg_sm_count() {
+int dg_sm_count() {
     const int sms = device_sm_count();
     return sms > 0 ? sms : 148;
 }
 // Slots a tile needs: the most CTAs whose ranges can reach into one tile.
-static int dg_slots_per_tile(int tiles) { return dg_sm_count() / tiles + 2; }
+int dg_slots_per_tile(int tiles) { return dg_sm_count() / tiles + 2; }
 
 // The slots of every tile.  tiles x slots_per_tile <= SMs + 2 tiles: that bound is what is asked for, so that a workspace
 // sized for some N also serves every smaller N (tiles x (SMs / tiles + 2) itself does not grow monotonically with N).
@@ -492,10 +456,18 @@ static int launch_dg(const CUtensorMap &tmA, const CUtensorMap &tmW, const CUten
                                    tiles, slots, spt, wait_limit_cycles()),
                         "decode gemm launch");
     if (rc) return rc;
+    return launch_gemm_decode_fixup(NB, C, residual, epilogue, c_f16, 1.f, nullptr, M, N, K / DG_GROUP, tiles, ctas, slots, spt, stream);
+}
+
+int launch_gemm_decode_fixup(int rows, uint16_t *C, const uint16_t *residual, int epilogue, int c_f16, float sum_scale,
+                             const float *row_scale, int M, int N, int KB, int tiles, int main_ctas, const float *slots,
+                             int slots_per_tile, cudaStream_t stream) {
     const int blocks = tiles * ((M + 3) / 4);
-    return check_cuda(launch_pdl(gemm_decode_fixup_kernel<NB>, dim3(blocks), dim3(256), 0, stream, C, residual, epilogue, c_f16, M, N, K / DG_GROUP,
-                                 tiles, ctas, (const float *)slots, spt),
-                      "decode gemm fix-up launch");
+#define DG_FIXUP(NBV)                                                                                                          \
+    launch_pdl(gemm_decode_fixup_kernel<NBV>, dim3(blocks), dim3(256), 0, stream, C, residual, epilogue, c_f16, sum_scale, row_scale, \
+               M, N, KB, tiles, main_ctas, slots, slots_per_tile)
+    return check_cuda(rows == 16 ? DG_FIXUP(16) : (rows == 32 ? DG_FIXUP(32) : DG_FIXUP(64)), "decode gemm fix-up launch");
+#undef DG_FIXUP
 }
 
 int launch_gemm_decode(const uint16_t *A, const int32_t *qweight, const int32_t *qzeros, const uint16_t *scales, uint16_t *C, int M,

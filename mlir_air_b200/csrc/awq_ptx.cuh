@@ -70,6 +70,17 @@ __device__ __forceinline__ bool mbar_wait_bounded_warp(uint32_t bar, uint32_t pa
     return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
+// Up to three waits at once for a converged warp: lane i < n polls barrier i, every lane gets the conjunction.  A wait on
+// an mbarrier costs 150 to 250 cycles even when the phase is already complete, so a role that needs several barriers
+// per step pays for one round trip instead of one per barrier.
+__device__ __forceinline__ bool mbar_wait_multi_warp(int n, uint32_t bar0, uint32_t par0, uint32_t bar1, uint32_t par1, uint32_t bar2,
+                                                     uint32_t par2, long long limit) {
+    const int l = threadIdx.x & 31;
+    bool ok = true;
+    if (l < n) ok = mbar_wait_bounded(l == 0 ? bar0 : (l == 1 ? bar1 : bar2), l == 0 ? par0 : (l == 1 ? par1 : par2), limit);
+    return __all_sync(0xffffffffu, ok);
+}
+
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
     uint64_t p;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));

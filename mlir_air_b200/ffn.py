@@ -135,8 +135,9 @@ class DecodeFFNStack:
         self.ws = Workspace(maxK, maxN, device=device)
         max_il = max(l.down.K for l in self.layers)
         # split-K sums of the batched-decode GEMM (batches of 9 to 64 rows)
-        self.gemm_ws = ops.GemmDecodeWorkspace(maxN, device=device, batch=min(max_batch, 64)) \
-            if max_batch >= self.GEMM_BATCH else None  # (its size grows with N: the widest product decides)
+        # (its size grows with N: the widest product decides; K: room for the split token rows of the fp8-operand kernel)
+        self.gemm_ws = ops.GemmDecodeWorkspace(maxN, device=device, batch=min(max_batch, 64), K=maxK) \
+            if max_batch >= self.GEMM_BATCH else None
         bf = dict(dtype=torch.bfloat16, device=device)
         self._h = [torch.zeros((max_batch, hidden), **bf) for _ in range(2)]  # zeros: a capture's warm-up run reads them
         # intermediates between the kernels of a layer are fp16 (the GEMV kernel's fastest input)
@@ -204,6 +205,13 @@ class DecodeFFNStack:
     # per layer whatever the batch, SwiGLU / residual in the epilogue) instead of one GEMV pass per 8 rows
     # (9-16 rows: the same time as the two-tile GEMV pass at the 70B dimensions, 9 % less at the 7B ones).
     GEMM_BATCH = 9
+    # Up to here the GEMM is the kernel that feeds the tensor core the packed nibbles and split token rows as fp8 (scale and
+    # zero point in f32): 10 % faster than the 16-bit-operand kernel at 16 rows, 3 % at 32, and no weight is rounded.
+    GEMM_F8_BATCH = 32
+
+    def uses_gemm_f8(self, batch: int) -> bool:
+        return self.uses_gemm(batch) and batch <= self.GEMM_F8_BATCH and all(
+            self.gemm_ws.fits_f8(batch, w.K, w.N) for l in self.layers for w in (l.gateup, l.down))
 
     def uses_gemm(self, batch: int) -> bool:
         if batch < self.GEMM_BATCH or batch > 64 or self.gemm_ws is None:
@@ -217,9 +225,10 @@ class DecodeFFNStack:
         if self.uses_fused(batch):
             return 1
         if self.uses_gemm(batch):
-            # norm, and two launches (product, sum of the SMs' shares + epilogue) per GEMM; tensor parallel: the norm is
-            # fused with the residual add behind the allreduce, plus the first layer's norm
-            return 5 * len(self.layers) + (1 if self.tp > 1 else 0)
+            # norm, and two launches (product, sum of the SMs' shares + epilogue) per GEMM, three with the split of the token
+            # rows in front of the fp8-operand kernel; tensor parallel: the norm is fused with the residual add behind the
+            # allreduce, plus the first layer's norm
+            return (7 if self.uses_gemm_f8(batch) else 5) * len(self.layers) + (1 if self.tp > 1 else 0)
         passes = (batch + 7) // 8  # the decode kernels take 8 rows per launch
         n = len(self.layers)
         if self.tp == 1:
@@ -245,12 +254,13 @@ class DecodeFFNStack:
             # tensor parallel: gate/up shard -> SwiGLU, down shard -> f32 partial, allreduce, residual add fused with
             # the next layer's norm
             # activations between the kernels are fp16, as in the GEMV path: the products then run on fp16 operands
+            f8 = self.uses_gemm_f8(B)
             ops.rmsnorm(h, self.layers[0].gamma, self.eps, out=normed, out_f16=True)
             for idx, l in enumerate(self.layers):
                 il = l.down.K
                 it = inter.view(-1)[:B * il].view(B, il)
-                ops.gemm_decode(normed, l.gateup, self.gemm_ws, out=it, swiglu=True, out_f16=True)
-                ops.gemm_decode(it, l.down, self.gemm_ws, out=partial, f32_out=True)
+                ops.gemm_decode(normed, l.gateup, self.gemm_ws, out=it, swiglu=True, out_f16=True, f8=f8)
+                ops.gemm_decode(it, l.down, self.gemm_ws, out=partial, f32_out=True, f8=f8)
                 torch.distributed.all_reduce(partial, group=self.group)
                 nxt = self.layers[idx + 1].gamma if idx + 1 < len(self.layers) else None
                 ops.add_rmsnorm(h, partial, nxt, self.eps, h_out=other, normed=normed if nxt is not None else None,
@@ -258,12 +268,13 @@ class DecodeFFNStack:
                 h, other = other, h
             return h
         if self.uses_gemm(B):
+            f8 = self.uses_gemm_f8(B)
             for l in self.layers:
                 il = l.down.K
                 it = inter.view(-1)[:B * il].view(B, il)
                 ops.rmsnorm(h, l.gamma, self.eps, out=normed, out_f16=True)
-                ops.gemm_decode(normed, l.gateup, self.gemm_ws, out=it, swiglu=True, out_f16=True)
-                ops.gemm_decode(it, l.down, self.gemm_ws, out=other, residual=h)
+                ops.gemm_decode(normed, l.gateup, self.gemm_ws, out=it, swiglu=True, out_f16=True, f8=f8)
+                ops.gemm_decode(it, l.down, self.gemm_ws, out=other, residual=h, f8=f8)
                 h, other = other, h
             return h
         if self.tp == 1:

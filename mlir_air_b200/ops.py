@@ -371,20 +371,29 @@ class GemmDecodeWorkspace:
     """Caller-owned scratch of `gemm_decode` (the f32 sums of each SM's share of a tile) for up to `batch` rows and `N`
     columns.  One per stream: calls that share it must not overlap on the GPU."""
 
-    def __init__(self, N: int, device="cuda", batch: int = 64):
-        self.batch, self.N = int(batch), int(N)
-        self.nbytes = int(_lib.load().awq_b200_gemm_decode_workspace_bytes(self.batch, self.N))
+    def __init__(self, N: int, device="cuda", batch: int = 64, K: int = 0):
+        """`K` > 0 also makes room for the split token rows of `gemm_decode(..., f8=True)` (up to 32 rows of K elements)."""
+        self.batch, self.N, self.K = int(batch), int(N), int(K)
+        lib = _lib.load()
+        self.nbytes = int(lib.awq_b200_gemm_decode_workspace_bytes(self.batch, self.N))
+        if self.K > 0:
+            self.nbytes = max(self.nbytes, int(lib.awq_b200_gemm_decode_f8_workspace_bytes(min(self.batch, 32), self.K, self.N)))
         self.buf = torch.empty(self.nbytes, dtype=torch.uint8, device=device)
 
     def fits(self, M, N):
         return int(_lib.load().awq_b200_gemm_decode_workspace_bytes(int(M), int(N))) <= self.nbytes
 
+    def fits_f8(self, M, K, N):
+        return int(M) <= 32 and 0 < int(_lib.load().awq_b200_gemm_decode_f8_workspace_bytes(int(M), int(K), int(N))) <= self.nbytes
 
-def gemm_decode(A, w: AwqWeight, ws: GemmDecodeWorkspace, out=None, residual=None, swiglu=False, f32_out=False, out_f16=False):
+
+def gemm_decode(A, w: AwqWeight, ws: GemmDecodeWorkspace, out=None, residual=None, swiglu=False, f32_out=False, out_f16=False,
+                f8=False):
     """C [M, N] = A [M, K] @ W for a decode batch of M <= 64 rows (weights streamed once, all SMs busy whatever the
     shape); `residual` / `swiglu` as in `gemm`; `f32_out`: the f32 sums themselves (a tensor-parallel partial).
     A may be bf16 or fp16 (the weights are then dequantised to fp16 too: 11 significant bits instead of 8);
-    `out_f16` stores a plain or SwiGLU result as fp16 for a following fp16 product."""
+    `out_f16` stores a plain or SwiGLU result as fp16 for a following fp16 product.  `f8` (up to 32 rows): the kernel that
+    feeds the tensor core the packed nibbles and split token rows as fp8 and applies zero point and scale in f32."""
     if A.dtype not in (torch.bfloat16, torch.float16):
         raise _lib.AwqBackendError(f"A must be bf16 or fp16, got {A.dtype}")
     _want(A, A.dtype, "A")
@@ -400,7 +409,7 @@ def gemm_decode(A, w: AwqWeight, ws: GemmDecodeWorkspace, out=None, residual=Non
     _want(out, dt, "out")
     if residual is not None:
         _want(residual, torch.bfloat16, "residual")
-    _lib.call("awq_b200_gemm_decode_act", _ptr(A), ACT_F16 if A.dtype == torch.float16 else ACT_BF16, _ptr(w.qweight),
+    _lib.call("awq_b200_gemm_decode_f8" if f8 else "awq_b200_gemm_decode_act", _ptr(A), ACT_F16 if A.dtype == torch.float16 else ACT_BF16, _ptr(w.qweight),
               _ptr(w.qzeros), _ptr(w.scales), _ptr(residual), _ptr(out), OUT_F32 if f32_out else (ACT_F16 if out_f16 else ACT_BF16),
               1 if swiglu else 0, A.shape[0], w.K, w.N, w.group_size, _ptr(ws.buf), ws.nbytes, _stream())
     return out

@@ -209,7 +209,9 @@ def test_stack_large_batch_takes_the_gemm_path(ops):
     plan, gus, downs, gammas = _plan(ops, layers_np)
     stack = ffn.DecodeFFNStack([ffn.FFNLayer(g, d, gm) for g, d, gm in zip(gus, downs, gammas)], H, max_batch=64)
     assert stack.uses_gemm(9) and stack.uses_gemm(64) and not stack.uses_gemm(8)
-    assert stack.launches_per_step(64) == 5 * L
+    # up to 32 rows the kernel with fp8 operands (a third launch per product splits the token rows), the 16-bit one beyond
+    assert stack.uses_gemm_f8(9) and stack.uses_gemm_f8(32) and not stack.uses_gemm_f8(33)
+    assert stack.launches_per_step(64) == 5 * L and stack.launches_per_step(32) == 7 * L
     for B in (9, 17, 32, 40, 64):
         x = randn_bf16((B, H), seed=B)
         y = to_host(stack.step(to_dev(x)))
@@ -218,7 +220,7 @@ def test_stack_large_batch_takes_the_gemm_path(ops):
         assert np.array_equal(y.view(np.uint16), to_host(stack.step(to_dev(x))).view(np.uint16))
         # the stack kernel on the same rows, 8 at a time
         parts = [to_host(stack.step(to_dev(x[i:i + 8]))) for i in range(0, B, 8)]
-        # the GEMM multiplies bf16-rounded weights, the GEMV keeps (q - z) s in f32: both inside the bar
+        # (the 16-bit GEMM rounds the weights to fp16, the fp8-operand GEMM and the GEMV keep (q - z) s in f32)
         assert O.rel_l2(y, np.concatenate(parts, 0)) <= REL_L2_TOL
         stack.load_input(to_dev(x))
         g1 = to_host(stack.replay(B).clone())
@@ -320,6 +322,53 @@ def test_gemm_decode_fp16_operands_vs_oracle(ops, M, K, N):
         assert O.rel_l2(to_host(t), O.gateup_swiglu_A_ref(A, gate, up, 128)) <= 3e-3
 
 
+# (M, K, N) as above, up to 32 rows; the last: a row whose elements span 20 binades and a row of zeros
+@pytest.mark.parametrize("M,K,N", [(9, 128, 256), (16, 256, 32), (32, 1024, 1312), (17, 512, 800), (32, 8192, 512),
+                                   (12, 5632, 2048), (24, 2048, 5632)])
+def test_gemm_decode_fp8_operands_vs_oracle(ops, M, K, N):
+    """The product with the packed nibbles and the split token rows as the tensor core's fp8 operands, zero point and scale
+    applied in f32: every epilogue against the oracle (no weight is rounded, so it sits nearer to the exact product than
+    the 16-bit kernels), bf16 and fp16 inputs, outputs of one value agreeing, repeatable bits."""
+    import torch
+    from gpu_util import dev_weight, randn_bf16, synth_awq, to_dev, to_host
+    bits = lambda a: a.view(np.uint16)  # noqa: E731
+    A = randn_bf16((M, K), seed=M + 11)
+    A[0] = (A[0].astype(np.float32) * np.exp2(np.random.default_rng(5).integers(-18, 3, K))).astype(bfloat16)  # a wide row
+    A[M - 1] = 0  # and an empty one
+    w = synth_awq(K, N, 128, seed=N + 12)
+    R = randn_bf16((M, N), seed=13)
+    ws = ops.GemmDecodeWorkspace(N, batch=M, K=K)
+    assert ws.fits_f8(M, K, N) and not ws.fits_f8(33, K, N)
+    dw = dev_weight(*w)
+    yf = ops.gemm_decode(to_dev(A), dw, ws, f32_out=True, f8=True)
+    ops.gemm_check()
+    exact = A.astype(np.float32) @ O.dequant_f32(*w, 128)
+    assert O.rel_l2(yf.cpu().numpy(), exact) <= 1e-4
+    assert float(np.abs(yf.cpu().numpy()[M - 1]).max()) == 0.0
+    for m in (0, 1):  # the wide row on its own, and an ordinary one
+        assert O.rel_l2(yf.cpu().numpy()[m], exact[m]) <= 1e-4
+    y = to_host(ops.gemm_decode(to_dev(A), dw, ws, f8=True))
+    assert np.array_equal(bits(y), bits(to_host(yf.to(torch.bfloat16))))
+    assert O.rel_l2(y, O.gemv_A_ref(A, *w, 128)) <= 3e-3
+    Ah = to_dev(A).to(torch.float16)  # fp16 token rows: the bf16 values that fp16 holds exactly, others rounded by the cast
+    yh = ops.gemm_decode(Ah, dw, ws, f32_out=True, f8=True)
+    assert O.rel_l2(yh.cpu().numpy(), Ah.float().cpu().numpy() @ O.dequant_f32(*w, 128)) <= 1e-4
+    y16 = ops.gemm_decode(to_dev(A), dw, ws, out_f16=True, f8=True)
+    assert y16.dtype == torch.float16 and torch.equal(y16, yf.to(torch.float16))
+    yr = to_host(ops.gemm_decode(to_dev(A), dw, ws, residual=to_dev(R), f8=True))
+    ops.gemm_check()
+    assert O.rel_l2(yr, O.gemv_A_ref(A, *w, 128, residual=R)) <= 3e-3
+    assert np.array_equal(bits(yr), bits(to_host(ops.gemm_decode(to_dev(A), dw, ws, residual=to_dev(R), f8=True))))
+    if N % 64 == 0:
+        gate, up = synth_awq(K, N // 2, 128, seed=4), synth_awq(K, N // 2, 128, seed=5)
+        wgu = ops.interleave_gate_up(dev_weight(*gate), dev_weight(*up))
+        t = ops.gemm_decode(to_dev(A), wgu, ws, swiglu=True, f8=True)
+        t16 = ops.gemm_decode(to_dev(A), wgu, ws, swiglu=True, out_f16=True, f8=True)
+        ops.gemm_check()
+        assert t16.dtype == torch.float16 and torch.equal(t16, t.to(torch.float16))
+        assert O.rel_l2(to_host(t), O.gateup_swiglu_A_ref(A, gate, up, 128)) <= 3e-3
+
+
 def test_gemm_decode_rejects_what_it_cannot_run(ops):
     import torch
     from gpu_util import dev_weight, randn_bf16, synth_awq, to_dev
@@ -338,3 +387,8 @@ def test_gemm_decode_rejects_what_it_cannot_run(ops):
         ops.gemm_decode(x, w, ws, f32_out=True, swiglu=True)
     with pytest.raises(AwqBackendError):
         ops.gemm_decode(x.float(), w, ws)
+    with pytest.raises(AwqBackendError):  # the fp8-operand kernel needs room for the split token rows
+        ops.gemm_decode(x, w, ws, f8=True)
+    ws8 = ops.GemmDecodeWorkspace(256, batch=64, K=256)
+    with pytest.raises(AwqBackendError):  # and takes 32 rows at most
+        ops.gemm_decode(to_dev(randn_bf16((33, 256), seed=1)), w, ws8, f8=True)
