@@ -319,7 +319,8 @@ def time_other_configs(a, torch, ops, ffn, peak):
         us = e0.elapsed_time(e1) * 1e3 / (20 * nl)
         g3[str(B)] = dict(_hbm_entry(us, per + 4 * B * H * 2, peak), tokens_per_s=B / (us * 1e-6),
                           path="one launch of the stack kernel for all layers" if st.uses_fused(B) else
-                          ("per layer: RMSNorm + two batched-decode GEMMs" if st.uses_gemm(B) else "per-layer kernels"))
+                          ("per layer: RMSNorm + two batched-decode GEMMs (" + ("fp8" if st.uses_gemm_f8(B) else "fp16") + " operands)"
+                           if st.uses_gemm(B) else "per-layer kernels"))
     st.check()
     out["ffn_cfg3"] = {"workload": f"decode SwiGLU FFN hidden 4096 / intermediate 11008 with RMSNorm and residual, {nl} distinct "
                                    "layers back to back, time per layer", "layers": nl, "batch": g3}
@@ -359,7 +360,7 @@ def parity_check(a, torch, ops, ffn, group, rank, world):
     y_eager = st.step(dev16(x))
     st.load_input(dev16(x))
     y_graph = st.replay(B).clone()
-    # the path the batch sweep times for 32 and 64 rows (RMSNorm + two batched-decode GEMMs per layer, fp16 operands), same
+    # the path the batch sweep times for 32 and 64 rows (RMSNorm + two batched-decode GEMMs per layer; fp8 operands at 32 rows), same
     # layers: end to end, and every layer on its own from the oracle's input of that layer; both are judged
     x32 = np.random.default_rng(898).standard_normal((32, H)).astype(bfloat16)
     y32 = st.step(dev16(x32))
@@ -390,7 +391,8 @@ def parity_check(a, torch, ops, ffn, group, rank, world):
                else "per-layer kernels", "oracle": "oracle.awq_oracle.ffn_layer_A_ref, unsharded",
                "batch_32": {"rel_l2": max(max(e32_layers), e32), "rel_l2_per_layer": e32_layers, "rel_l2_end_to_end": e32,
                             "judged": "the chain of all layers, and every layer from the oracle's input of that layer",
-                            "path": "per layer: RMSNorm + two batched-decode GEMMs" if st.uses_gemm(32) else "per-layer kernels"}}
+                            "path": ("per layer: RMSNorm + two batched-decode GEMMs (" + ("fp8" if st.uses_gemm_f8(32) else "fp16") + " operands)")
+                            if st.uses_gemm(32) else "per-layer kernels"}}
     del st, layers
     return res
 

@@ -204,8 +204,8 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             for (int i = 0; i < n_seg; ++i, ++it, ++w.u) {
                 const int s = it % STAGES, round = it / STAGES;
                 const int ab = it % Cfg::ABUF, around = it / Cfg::ABUF;
-                if (!mbar_wait_bounded_warp(xfull_bar(s), round & 1, wait_limit) ||
-                    !mbar_wait_bounded_warp(ready_bar(ab), around & 1, wait_limit)) {
+                // token rows landed and weight buffer written: two lanes wait side by side
+                if (!mbar_wait_multi_warp(2, xfull_bar(s), round & 1, ready_bar(ab), around & 1, 0, 0, wait_limit)) {
                     if (lane == 0) atomicExch(&g_gemm_dec_error, 3);
                     ok = false;
                     break;

@@ -29,8 +29,9 @@
 //
 //   warp 0       producer (TMA: packed words, scales, zeros; split token rows and their group sums)
 //   warp 1       MMA issuer: 8 tcgen05.mma (M 128, N 2 x rows, K 32) per unit into one of two accumulator sets
-//   warps 2-9    regroup the nibbles into tensor memory (a warp: 32 weight columns x 128 k)
-//   warps 10-17  promote (a warp: 32 weight columns x all token rows): tcgen05.ld of the unit's sums, three FMAs per
+//   warps 2-9    regroup the nibbles into tensor memory (a warp: 32 weight columns x 128 k); up to 16 rows a second group
+//                of eight follows and the two take alternate units
+//   the next 8   promote (a warp: 32 weight columns x all token rows): tcgen05.ld of the unit's sums, three FMAs per
 //                (column, row); their arrival also frees the unit's input stage
 // Tensor memory: four weight buffers of 64 columns, two accumulator sets of 4 x rows columns.  Every wait is bounded.
 #include <cudaTypedefs.h>
@@ -46,8 +47,10 @@
 
 namespace awq {
 
-constexpr int F8_REGROUP_WARPS = 8, F8_REGROUP_WARP0 = 2;
-constexpr int F8_PROMOTE_WARP0 = F8_REGROUP_WARP0 + F8_REGROUP_WARPS;
+constexpr int F8_REGROUP_WARPS = 8, F8_REGROUP_WARP0 = 2;  // eight regroup warps per group
+#ifndef F8_REGROUP_GROUPS_16
+#define F8_REGROUP_GROUPS_16 1
+#endif
 constexpr int F8_ABUF_COLS = 64;  // a weight buffer: two 128-column halves x 128 k bytes = 2 x 32 TMEM columns
 constexpr int F8_ABUF = 4;
 constexpr int F8_MAX_ROWS = 32;
@@ -66,7 +69,12 @@ struct F8Cfg {
     // a promote warp: 32 weight columns x all token rows.  (Measured: a second set of eight warps for rows 16-31 made the
     // kernel 9 % slower, 120 against 110 us per 70B layer: the waiting warps' polls cost more than the shorter chain wins.)
     static constexpr int PROMOTE_WARPS = 8;
-    static constexpr int THREADS = (F8_PROMOTE_WARP0 + PROMOTE_WARPS) * 32;  // 576
+    // Up to 16 rows the regroup warps' chain per unit (wait, ldmatrix, bit operations, tensor-memory stores, wait, arrive)
+    // is what limits the kernel: two groups of eight then take alternate units.  With 32 rows the promote warps limit it
+    // and need the registers.
+    static constexpr int REGROUP_GROUPS = F8_REGROUP_GROUPS_16 > 1 && NB == 16 ? 2 : 1;
+    static constexpr int PROMOTE_WARP0 = F8_REGROUP_WARP0 + REGROUP_GROUPS * F8_REGROUP_WARPS;
+    static constexpr int THREADS = (PROMOTE_WARP0 + PROMOTE_WARPS) * 32;  // 576 / 832
     static constexpr int NUM_BARS = 3 * STAGES + 2 * F8_ABUF + 4;
     static constexpr int OFF_BARS = STAGES * STAGE_BYTES;
     static constexpr int SMEM_BYTES = OFF_BARS + NUM_BARS * 8 + 16 + 1024;
@@ -86,6 +94,15 @@ __device__ __forceinline__ void f8_umma_ta(uint32_t d_tmem, uint32_t a_tmem, uin
         "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, p;\n\t}"
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+// (d0, d1) += a * (b0, b1): one packed FMA for two token rows
+__device__ __forceinline__ void f8_fma2(float &d0, float &d1, float a, float b0, float b1) {
+    asm("{\n\t.reg .b64 ra, rb, rc;\n\t"
+        "mov.b64 ra, {%2, %2};\n\tmov.b64 rb, {%3, %4};\n\tmov.b64 rc, {%0, %1};\n\t"
+        "fma.rn.f32x2 rc, ra, rb, rc;\n\t"
+        "mov.b64 {%0, %1}, rc;\n\t}"
+        : "+f"(d0), "+f"(d1)
+        : "f"(a), "f"(b0), "f"(b1));
 }
 __device__ __forceinline__ uint32_t f8_prmt(uint32_t a, uint32_t b, uint32_t sel) {
     uint32_t r;
@@ -298,19 +315,21 @@ gemm_decode_f8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
             }
             __syncwarp();
         }
-    } else if (warp >= F8_REGROUP_WARP0 && warp < F8_PROMOTE_WARP0) {
+    } else if (warp >= F8_REGROUP_WARP0 && warp < Cfg::PROMOTE_WARP0) {
         // ------------------------------ regroup ------------------------------
         // warp w: TMEM lanes 32 (w % 4) .. + 31 of one 128-column half, all 128 k
         const int rw = warp - F8_REGROUP_WARP0;
+        const int grp = rw >> 3;  // the group takes units grp, grp + groups, ...
         const int q = warp & 3;   // TMEM lanes 32 q .. 32 q + 31 (a warp may only touch its own quarter)
-        const int h = rw >> 2;    // which 128-column half of the tile
+        const int h = (rw >> 2) & 1;  // which 128-column half of the tile
         const int chunk = 4 * h + q;  // the warp's 32 columns are one 16-byte chunk (4 packed words) of a 128-byte row
         // ldmatrix.x4.trans: matrix i = rows k = 8 i .. 8 i + 7 of the call's 32 k (conflict-free under the 128-byte
         // swizzle); lane (g = lane / 4, t = lane % 4) then holds half word g of k = 8 i + 2 t, + 1 in register i.
         const int mi = lane >> 3, rr = lane & 7;
         const uint32_t w_off = (uint32_t)(8 * mi + rr) * 128 + (uint32_t)((chunk ^ rr) << 4);  // + 32 * 128 per call
-        int it = 0;
-        for (UnitWalk w(tiles, KB); w.valid(); ++w.u, ++it) {
+        UnitWalk w(tiles, KB);
+        const int n_units = w.u1 - w.u;
+        for (int it = grp; it < n_units; it += Cfg::REGROUP_GROUPS) {
             const int s = it % STAGES, round = it / STAGES;
             const int ab = it % F8_ABUF, around = it / F8_ABUF;
             // the unit's words landed, and the MMA is done with the weight buffer they go to
@@ -340,10 +359,10 @@ gemm_decode_f8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
             __syncwarp();
             if (lane == 0) mbar_arrive(ready_bar(ab));
         }
-    } else if (warp >= F8_PROMOTE_WARP0) {
+    } else if (warp >= Cfg::PROMOTE_WARP0) {
         // ------------------------------ promote ------------------------------
         // thread = one weight column: TMEM lane 32 q + lane of half h
-        const int pw = warp - F8_PROMOTE_WARP0;
+        const int pw = warp - Cfg::PROMOTE_WARP0;
         const int q = warp & 3, h = pw >> 2;
         const int col = 128 * h + 32 * q + dg_lane_column(lane);  // column inside the tile
         const int z_shift = 4 * (((col & 1) << 2) | ((col & 7) >> 1));  // nibble of column c of a packed word: PERM[c]
@@ -371,30 +390,34 @@ gemm_decode_f8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
                 const float z = (float)((lds32(sz + DG_S_BYTES + 4 * (col >> 3)) >> z_shift) & 0xFu);
                 const float c_hi = 512.f * sc, c_lo = 32.f * sc, c_z = -sc * z;  // a nibble reads as q 2^-9, lo as 16 (x - hi)
                 const uint32_t t_acc = tmem_base + ((uint32_t)(32 * q) << 16) + Cfg::ACC_COL0 + (uint32_t)(b * Cfg::ACC_COLS + h * (2 * NB));
+                // 16 token rows at a time (all 32 at once spill); the accumulator set goes back to the MMA as soon as its last
+                // sums are in registers, before the arithmetic on them
 #pragma unroll
                 for (int m0 = 0; m0 < NB; m0 += 16) {
                     uint32_t p_hi[16], p_lo[16];
                     dg_tmem_ld_32x32b_x16(t_acc + (uint32_t)m0, p_hi);
                     dg_tmem_ld_32x32b_x16(t_acc + (uint32_t)(NB + m0), p_lo);
                     dg_tmem_ld_wait();
+                    if (m0 + 16 == NB) {
+                        dg_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(acc_empty(b));
+                    }
 #pragma unroll
                     for (int j = 0; j < 16; j += 4) {
                         const uint4 sxv = lds128(sz + Cfg::SX_OFF + 4 * (m0 + j));
                         const float sx4[4] = {__uint_as_float(sxv.x), __uint_as_float(sxv.y), __uint_as_float(sxv.z), __uint_as_float(sxv.w)};
 #pragma unroll
-                        for (int jj = 0; jj < 4; ++jj) {
-                            float a = fmaf(c_z, sx4[jj], acc[m0 + j + jj]);
-                            a = fmaf(c_lo, __uint_as_float(p_lo[j + jj]), a);
-                            acc[m0 + j + jj] = fmaf(c_hi, __uint_as_float(p_hi[j + jj]), a);
+                        for (int jj = 0; jj < 4; jj += 2) {
+                            float &a0 = acc[m0 + j + jj], &a1 = acc[m0 + j + jj + 1];
+                            f8_fma2(a0, a1, c_z, sx4[jj], sx4[jj + 1]);
+                            f8_fma2(a0, a1, c_lo, __uint_as_float(p_lo[j + jj]), __uint_as_float(p_lo[j + jj + 1]));
+                            f8_fma2(a0, a1, c_hi, __uint_as_float(p_hi[j + jj]), __uint_as_float(p_hi[j + jj + 1]));
                         }
                     }
                 }
-                dg_fence_before();
                 __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(acc_empty(b));
-                    mbar_arrive(empty_bar(s));  // scales, zeros and group sums of the stage have been read
-                }
+                if (lane == 0) mbar_arrive(empty_bar(s));  // scales, zeros and group sums of the stage have been read
             }
             if (!ok) break;
             // the segment's sums go into this CTA's slot among the tile's contributors (N is a multiple of 32: a warp's 32
