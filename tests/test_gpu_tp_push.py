@@ -128,7 +128,9 @@ def _worker_gemm(rank, world, port, H, I, L, B, out):
                                        to_dev(gamma)))
         x = np.random.default_rng(7).standard_normal((B, H)).astype(bfloat16)
         st = ffn.DecodeFFNStack(layers, H, max_batch=64, group=group)
-        assert st.uses_gemm(B) and st.launches_per_step(B) == 5 * L + 1
+        # up to 32 rows the fp8-operand GEMM (a third launch per product splits the token rows), the 16-bit one beyond
+        assert st.uses_gemm(B) and st.uses_gemm_f8(B) == (B <= 32)
+        assert st.launches_per_step(B) == (7 if B <= 32 else 5) * L + 1
         y = to_host(st.step(to_dev(x)))
         y2 = to_host(st.step(to_dev(x)))
         st.load_input(to_dev(x))
