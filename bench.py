@@ -588,7 +588,7 @@ def run_ours(a):
                     "global_batch": world * B, "parallelism": f"{world} replicas of the whole stack, no exchange"}
         del rstack, full
 
-    # ---- the batch sweep of configuration 5 (1 / 8 / 32 / 64 tokens) on a shorter stack unless --sweep ----
+    # ---- the batch sweep of configuration 5 (1 / 8 / 32 / 64 tokens, and 16) on a shorter stack unless --sweep ----
     batches = None
     if not a.no_configs or a.sweep:
         nl = a.layers if a.sweep else min(a.layers, 16)
@@ -597,7 +597,7 @@ def run_ours(a):
         keep_stack = stack
         stack = sub
         batches = {"layers": nl, "note": "ms per step of a stack of `layers` layers; bytes = this rank's weights + activations"}
-        for b in (1, 8, 32, 64):
+        for b in (1, 8, 16, 32, 64):
             ms = time_steps(b, max(3, a.steps // 2), 3)
             by = sub.weight_bytes + nl * 4 * b * a.hidden * 2
             batches[str(b)] = {"ms_per_step": ms, "us_per_layer": ms * 1e3 / nl, "tokens_per_s": b / (ms * 1e-3),
