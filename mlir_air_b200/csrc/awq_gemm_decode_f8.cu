@@ -29,9 +29,8 @@
 //
 //   warp 0       producer (TMA: packed words, scales, zeros; split token rows and their group sums)
 //   warp 1       MMA issuer: 8 tcgen05.mma (M 128, N 2 x rows, K 32) per unit into one of two accumulator sets
-//   warps 2-9    regroup the nibbles into tensor memory (a warp: 32 weight columns x 128 k); up to 16 rows a second group
-//                of eight follows and the two take alternate units
-//   the next 8   promote (a warp: 32 weight columns x all token rows): tcgen05.ld of the unit's sums, three FMAs per
+//   warps 2-9    regroup the nibbles into tensor memory (a warp: 32 weight columns x 128 k)
+//   warps 10-17  promote (a warp: 32 weight columns x all token rows): tcgen05.ld of the unit's sums, three FMAs per
 //                (column, row); their arrival also frees the unit's input stage
 // Tensor memory: four weight buffers of 64 columns, two accumulator sets of 4 x rows columns.  Every wait is bounded.
 #include <cudaTypedefs.h>
@@ -47,10 +46,7 @@
 
 namespace awq {
 
-constexpr int F8_REGROUP_WARPS = 8, F8_REGROUP_WARP0 = 2;  // eight regroup warps per group
-#ifndef F8_REGROUP_GROUPS_16
-#define F8_REGROUP_GROUPS_16 1
-#endif
+constexpr int F8_REGROUP_WARPS = 8, F8_REGROUP_WARP0 = 2;
 constexpr int F8_ABUF_COLS = 64;  // a weight buffer: two 128-column halves x 128 k bytes = 2 x 32 TMEM columns
 constexpr int F8_ABUF = 4;
 constexpr int F8_MAX_ROWS = 32;
@@ -70,11 +66,10 @@ struct F8Cfg {
     // kernel 9 % slower, 120 against 110 us per 70B layer: the waiting warps' polls cost more than the shorter chain wins.)
     static constexpr int PROMOTE_WARPS = 8;
     // Up to 16 rows the regroup warps' chain per unit (wait, ldmatrix, bit operations, tensor-memory stores, wait, arrive)
-    // is what limits the kernel: two groups of eight then take alternate units.  With 32 rows the promote warps limit it
-    // and need the registers.
-    static constexpr int REGROUP_GROUPS = F8_REGROUP_GROUPS_16 > 1 && NB == 16 ? 2 : 1;
-    static constexpr int PROMOTE_WARP0 = F8_REGROUP_WARP0 + REGROUP_GROUPS * F8_REGROUP_WARPS;
-    static constexpr int THREADS = (PROMOTE_WARP0 + PROMOTE_WARPS) * 32;  // 576 / 832
+    // is the longest.  (Measured there: a second group of eight regroup warps, the two taking alternate units, 103
+    // against 94 us per 70B layer; the one group taking two units per round of waits 110 against 90.)
+    static constexpr int PROMOTE_WARP0 = F8_REGROUP_WARP0 + F8_REGROUP_WARPS;
+    static constexpr int THREADS = (PROMOTE_WARP0 + PROMOTE_WARPS) * 32;  // 576
     static constexpr int NUM_BARS = 3 * STAGES + 2 * F8_ABUF + 4;
     static constexpr int OFF_BARS = STAGES * STAGE_BYTES;
     static constexpr int SMEM_BYTES = OFF_BARS + NUM_BARS * 8 + 16 + 1024;
@@ -157,6 +152,7 @@ act_split_kernel(const uint16_t *__restrict__ x, int M, int K, int rows, uint8_t
         // largest magnitude into [128, 256); an all-zero (or non-finite) row is left as it is
         int e = 0;
         if (mx > 0.f && mx < 3.0e38f) frexpf(mx, &e);  // mx = f 2^e, 0.5 <= f < 1
+        e = e < -100 ? -100 : e;  // (a row of nothing but denormals: keep the power of two finite)
         scale = (mx > 0.f && mx < 3.0e38f) ? exp2f((float)(8 - e)) : 1.f;
         if (threadIdx.x == 0 && blockIdx.y == 0) inv[m] = 1.f / scale;
     } else if (threadIdx.x == 0 && blockIdx.y == 0) {
@@ -319,7 +315,6 @@ gemm_decode_f8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
         // ------------------------------ regroup ------------------------------
         // warp w: TMEM lanes 32 (w % 4) .. + 31 of one 128-column half, all 128 k
         const int rw = warp - F8_REGROUP_WARP0;
-        const int grp = rw >> 3;  // the group takes units grp, grp + groups, ...
         const int q = warp & 3;   // TMEM lanes 32 q .. 32 q + 31 (a warp may only touch its own quarter)
         const int h = (rw >> 2) & 1;  // which 128-column half of the tile
         const int chunk = 4 * h + q;  // the warp's 32 columns are one 16-byte chunk (4 packed words) of a 128-byte row
@@ -329,7 +324,7 @@ gemm_decode_f8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
         const uint32_t w_off = (uint32_t)(8 * mi + rr) * 128 + (uint32_t)((chunk ^ rr) << 4);  // + 32 * 128 per call
         UnitWalk w(tiles, KB);
         const int n_units = w.u1 - w.u;
-        for (int it = grp; it < n_units; it += Cfg::REGROUP_GROUPS) {
+        for (int it = 0; it < n_units; ++it) {
             const int s = it % STAGES, round = it / STAGES;
             const int ab = it % F8_ABUF, around = it / F8_ABUF;
             // the unit's words landed, and the MMA is done with the weight buffer they go to
