@@ -87,9 +87,34 @@ def test_argument_errors_need_no_gpu():
     # fused GEMM epilogues
     rc, msg = _err(lib.awq_b200_gemm_fused_bf16(p, p, p, p, p, p, 1, 64, 256, 512, 128, None))
     assert rc == INV and "do not combine" in msg
+    # batched-decode GEMMs: formats and epilogues that do not combine are refused before anything is launched
+    for fn in (lib.awq_b200_gemm_decode_act, lib.awq_b200_gemm_decode_f8):
+        assert _err(fn(p, 2, p, p, p, None, p, 0, 0, 16, 256, 512, 128, p, 1 << 24, None))[0] == INV  # a_format
+        assert _err(fn(p, 0, p, p, p, None, p, 3, 0, 16, 256, 512, 128, p, 1 << 24, None))[0] == INV  # c_format
+        assert _err(fn(p, 0, p, p, p, p, p, 0, 1, 16, 256, 512, 128, p, 1 << 24, None))[0] == INV    # SwiGLU + residual
+        assert _err(fn(p, 0, p, p, p, p, p, 1, 0, 16, 256, 512, 128, p, 1 << 24, None))[0] == INV    # residual + fp16 output
+        assert _err(fn(p, 0, p, p, p, None, p, 2, 1, 16, 256, 512, 128, p, 1 << 24, None))[0] == INV  # f32 sums + SwiGLU
+        assert _err(fn(ctypes.c_void_p(258), 0, p, p, p, None, p, 0, 0, 16, 256, 512, 128, p, 1 << 24, None))[0] == INV  # misaligned rows
+        assert fn(p, 0, p, p, p, None, p, 0, 0, 0, 256, 512, 128, p, 1 << 24, None) == 0  # empty batch
     # knobs
     assert _err(lib.awq_b200_set_decode_kernel(7))[0] == INV
     assert lib.awq_b200_set_decode_kernel(0) == 0 and lib.awq_b200_set_ffn_stack_tuning(-1, -1) == 0
+
+
+def test_gemm_decode_f8_workspace_holds_split_rows_and_slots():
+    """The fp8-operand GEMM's workspace = the split token rows (two bytes per element of the padded rows, their group sums,
+    the rows' powers of two) in front of the 16-bit kernel's slots; it grows with K and N and is 0 for sizes it cannot be."""
+    lib = _lib.load()
+    for rows, m in ((16, 9), (16, 16), (32, 17), (32, 32)):
+        for k in (128, 4096, 28672):
+            g = k // 128
+            split = g * 2 * rows * 128 + g * rows * 4 + rows * 4
+            split = (split + 1023) // 1024 * 1024
+            for n in (32, 8192, 57344):
+                assert int(lib.awq_b200_gemm_decode_f8_workspace_bytes(m, k, n)) == \
+                    split + int(lib.awq_b200_gemm_decode_workspace_bytes(m, n)), (m, k, n)
+    assert lib.awq_b200_gemm_decode_f8_workspace_bytes(0, 128, 32) == 0
+    assert lib.awq_b200_gemm_decode_f8_workspace_bytes(8, 64, 32) == 0
 
 
 def test_gemm_decode_workspace_serves_every_narrower_product():
