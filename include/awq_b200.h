@@ -362,7 +362,9 @@ int awq_b200_gemm_decode_act(const void *A, int a_format, const int32_t *qweight
 
 /* The same product for M <= 32 token rows with the packed nibbles themselves as the tensor core's operand
  * (a nibble q in a byte is the e4m3 number q * 2^-9) and the token rows split into two e4m3 pieces per
- * element (exact for a bf16 value within 2^-14 of its row's largest magnitude); zero point and scale are
+ * element (exact for a value of 8 significant bits, i.e. any bf16 value or an fp16 copy of one, within
+ * 2^-14 of its row's largest magnitude; a genuine fp16 value is rounded to 8 significant bits, as a bf16
+ * conversion would); zero point and scale are
  * applied to the per-group sums in f32, as the reference's golden does, so no weight is rounded.  Three
  * launches: the split of the token rows, the product, the addition of the partial sums.  Arguments as
  * awq_b200_gemm_decode_act; the workspace also holds the split rows, hence K in its size. */

@@ -353,6 +353,10 @@ def test_gemm_decode_fp8_operands_vs_oracle(ops, M, K, N):
     Ah = to_dev(A).to(torch.float16)  # fp16 token rows: the bf16 values that fp16 holds exactly, others rounded by the cast
     yh = ops.gemm_decode(Ah, dw, ws, f32_out=True, f8=True)
     assert O.rel_l2(yh.cpu().numpy(), Ah.float().cpu().numpy() @ O.dequant_f32(*w, 128)) <= 1e-4
+    # genuine fp16 values (11 significant bits) are rounded to the 8 that the two pieces hold, like a bf16 conversion
+    Ag = (to_dev(A).float() * 1.0009765625).to(torch.float16)
+    yg = ops.gemm_decode(Ag, dw, ws, f32_out=True, f8=True)
+    assert O.rel_l2(yg.cpu().numpy(), Ag.float().cpu().numpy() @ O.dequant_f32(*w, 128)) <= 3e-3
     y16 = ops.gemm_decode(to_dev(A), dw, ws, out_f16=True, f8=True)
     assert y16.dtype == torch.float16 and torch.equal(y16, yf.to(torch.float16))
     yr = to_host(ops.gemm_decode(to_dev(A), dw, ws, residual=to_dev(R), f8=True))
