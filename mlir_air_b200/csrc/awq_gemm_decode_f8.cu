@@ -339,15 +339,21 @@ gemm_decode_f8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
             for (int c = 0; c < 4; ++c) ldmatrix_x4_trans(r[c], st + w_off + c * 32 * 128);
             const uint32_t a_tmem = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(ab * F8_ABUF_COLS + h * (F8_ABUF_COLS / 2));
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {  // 32-k step c of the unit
-                // byte 0 / byte 1 of the half word at the step's bytes 8 t .. 8 t + 3 (lo) and 8 t + 4 .. 8 t + 7 (hi)
-                const uint32_t b0lo = f8_prmt(r[c][0], r[c][1], 0x6420u), b1lo = f8_prmt(r[c][0], r[c][1], 0x7531u);
-                const uint32_t b0hi = f8_prmt(r[c][2], r[c][3], 0x6420u), b1hi = f8_prmt(r[c][2], r[c][3], 0x7531u);
-                // nibble e of the half word = column 2 e + (g & 1) of its packed word; TMEM lanes g, g + 8, g + 16, g + 24
-                dg_tmem_st_16x256b(a_tmem + 8 * c, b0lo & 0x0F0F0F0Fu, b0hi & 0x0F0F0F0Fu, (b0lo >> 4) & 0x0F0F0F0Fu,
-                                   (b0hi >> 4) & 0x0F0F0F0Fu);
-                dg_tmem_st_16x256b(a_tmem + (16u << 16) + 8 * c, b1lo & 0x0F0F0F0Fu, b1hi & 0x0F0F0F0Fu,
-                                   (b1lo >> 4) & 0x0F0F0F0Fu, (b1hi >> 4) & 0x0F0F0F0Fu);
+            for (int c = 0; c < 4; c += 2) {  // 32-k steps c and c + 1 of the unit: one store per 16 TMEM lanes for both
+                uint32_t lo[8], hi[8];
+#pragma unroll
+                for (int d = 0; d < 2; ++d) {
+                    // byte 0 / byte 1 of the half word at the step's bytes 8 t .. 8 t + 3 (lo) and 8 t + 4 .. 8 t + 7 (hi)
+                    const uint32_t b0lo = f8_prmt(r[c + d][0], r[c + d][1], 0x6420u), b1lo = f8_prmt(r[c + d][0], r[c + d][1], 0x7531u);
+                    const uint32_t b0hi = f8_prmt(r[c + d][2], r[c + d][3], 0x6420u), b1hi = f8_prmt(r[c + d][2], r[c + d][3], 0x7531u);
+                    // nibble e of the half word = column 2 e + (g & 1) of its packed word; TMEM lanes g, g + 8, g + 16, g + 24
+                    lo[4 * d] = b0lo & 0x0F0F0F0Fu, lo[4 * d + 1] = b0hi & 0x0F0F0F0Fu;
+                    lo[4 * d + 2] = (b0lo >> 4) & 0x0F0F0F0Fu, lo[4 * d + 3] = (b0hi >> 4) & 0x0F0F0F0Fu;
+                    hi[4 * d] = b1lo & 0x0F0F0F0Fu, hi[4 * d + 1] = b1hi & 0x0F0F0F0Fu;
+                    hi[4 * d + 2] = (b1lo >> 4) & 0x0F0F0F0Fu, hi[4 * d + 3] = (b1hi >> 4) & 0x0F0F0F0Fu;
+                }
+                dg_tmem_st_16x256b_x2(a_tmem + 8 * c, lo);
+                dg_tmem_st_16x256b_x2(a_tmem + (16u << 16) + 8 * c, hi);
             }
             dg_tmem_st_wait();
             dg_fence_before();
