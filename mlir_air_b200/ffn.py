@@ -208,10 +208,19 @@ class DecodeFFNStack:
     # Up to here the GEMM is the kernel that feeds the tensor core the packed nibbles and split token rows as fp8 (scale and
     # zero point in f32): 10 % faster than the 16-bit-operand kernel at 16 rows, 3 % at 32, and no weight is rounded.
     GEMM_F8_BATCH = 32
+    # ... where a layer is large enough for its three launches per product to pay: measured on one box (us per layer,
+    # 16-bit against fp8 operands, by weights per layer on this rank): 88 M 27.0 / 28.3 at 16 rows and 28.7 / 32.3 at 32;
+    # 135 M 33.4 / 34.1 and 36.5 / 40.8; 176 M 38.3 / 37.0 and 40.6 / 43.5; 352 M 60.4 / 54.9 and 63.6 / 63.1; 705 M
+    # 104.4 / 89.8 and 112.0 / 104.5.
+    GEMM_F8_MIN_WEIGHTS = {16: 150e6, 32: 300e6}
 
     def uses_gemm_f8(self, batch: int) -> bool:
-        return self.uses_gemm(batch) and batch <= self.GEMM_F8_BATCH and all(
-            self.gemm_ws.fits_f8(batch, w.K, w.N) for l in self.layers for w in (l.gateup, l.down))
+        if not self.uses_gemm(batch) or batch > self.GEMM_F8_BATCH:
+            return False
+        weights = min(l.gateup.K * l.gateup.N + l.down.K * l.down.N for l in self.layers)
+        if weights < self.GEMM_F8_MIN_WEIGHTS[16 if batch <= 16 else 32]:
+            return False
+        return all(self.gemm_ws.fits_f8(batch, w.K, w.N) for l in self.layers for w in (l.gateup, l.down))
 
     def uses_gemm(self, batch: int) -> bool:
         if batch < self.GEMM_BATCH or batch > 64 or self.gemm_ws is None:

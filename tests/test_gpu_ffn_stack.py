@@ -209,7 +209,10 @@ def test_stack_large_batch_takes_the_gemm_path(ops):
     plan, gus, downs, gammas = _plan(ops, layers_np)
     stack = ffn.DecodeFFNStack([ffn.FFNLayer(g, d, gm) for g, d, gm in zip(gus, downs, gammas)], H, max_batch=64)
     assert stack.uses_gemm(9) and stack.uses_gemm(64) and not stack.uses_gemm(8)
-    # up to 32 rows the kernel with fp8 operands (a third launch per product splits the token rows), the 16-bit one beyond
+    # layers of this size take the 16-bit kernel at every batch; with the size bar out of the way, the kernel with fp8
+    # operands up to 32 rows (a third launch per product splits the token rows)
+    assert not stack.uses_gemm_f8(16) and stack.launches_per_step(32) == 5 * L
+    stack.GEMM_F8_MIN_WEIGHTS = {16: 0, 32: 0}
     assert stack.uses_gemm_f8(9) and stack.uses_gemm_f8(32) and not stack.uses_gemm_f8(33)
     assert stack.launches_per_step(64) == 5 * L and stack.launches_per_step(32) == 7 * L
     for B in (9, 17, 32, 40, 64):
