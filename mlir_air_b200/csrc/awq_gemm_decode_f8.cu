@@ -327,33 +327,39 @@ gemm_decode_f8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
         for (int it = 0; it < n_units; ++it) {
             const int s = it % STAGES, round = it / STAGES;
             const int ab = it % F8_ABUF, around = it / F8_ABUF;
-            // the unit's words landed, and the MMA is done with the weight buffer they go to
-            if (!mbar_wait_multi_warp(around > 0 ? 2 : 1, full_bar(s), round & 1, bfree_bar(ab), (around - 1) & 1, 0, 0, wait_limit)) {
+            // the unit's words landed: fetch them, and only then wait for the MMA to be done with the weight buffer they go to
+            if (!mbar_wait_bounded(full_bar(s), round & 1, wait_limit)) {
                 if (lane == 0) atomicExch(&g_gemm_f8_error, 3);
                 break;
             }
-            dg_fence_after();
             const uint32_t st = stage_addr(s) + Cfg::X_BYTES;
             uint32_t r[4][4];
 #pragma unroll
             for (int c = 0; c < 4; ++c) ldmatrix_x4_trans(r[c], st + w_off + c * 32 * 128);
+            // all the bit work first; only the stores need the weight buffer, i.e. the MMA to be done with it
+            uint32_t lo[2][8], hi[2][8];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {  // 32-k step c of the unit
+                // byte 0 / byte 1 of the half word at the step's bytes 8 t .. 8 t + 3 (lo) and 8 t + 4 .. 8 t + 7 (hi)
+                const uint32_t b0lo = f8_prmt(r[c][0], r[c][1], 0x6420u), b1lo = f8_prmt(r[c][0], r[c][1], 0x7531u);
+                const uint32_t b0hi = f8_prmt(r[c][2], r[c][3], 0x6420u), b1hi = f8_prmt(r[c][2], r[c][3], 0x7531u);
+                // nibble e of the half word = column 2 e + (g & 1) of its packed word; TMEM lanes g, g + 8, g + 16, g + 24
+                const int p = c >> 1, d = c & 1;
+                lo[p][4 * d] = b0lo & 0x0F0F0F0Fu, lo[p][4 * d + 1] = b0hi & 0x0F0F0F0Fu;
+                lo[p][4 * d + 2] = (b0lo >> 4) & 0x0F0F0F0Fu, lo[p][4 * d + 3] = (b0hi >> 4) & 0x0F0F0F0Fu;
+                hi[p][4 * d] = b1lo & 0x0F0F0F0Fu, hi[p][4 * d + 1] = b1hi & 0x0F0F0F0Fu;
+                hi[p][4 * d + 2] = (b1lo >> 4) & 0x0F0F0F0Fu, hi[p][4 * d + 3] = (b1hi >> 4) & 0x0F0F0F0Fu;
+            }
+            if (around > 0 && !mbar_wait_bounded(bfree_bar(ab), (around - 1) & 1, wait_limit)) {
+                if (lane == 0) atomicExch(&g_gemm_f8_error, 3);
+                break;
+            }
+            dg_fence_after();
             const uint32_t a_tmem = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(ab * F8_ABUF_COLS + h * (F8_ABUF_COLS / 2));
 #pragma unroll
-            for (int c = 0; c < 4; c += 2) {  // 32-k steps c and c + 1 of the unit: one store per 16 TMEM lanes for both
-                uint32_t lo[8], hi[8];
-#pragma unroll
-                for (int d = 0; d < 2; ++d) {
-                    // byte 0 / byte 1 of the half word at the step's bytes 8 t .. 8 t + 3 (lo) and 8 t + 4 .. 8 t + 7 (hi)
-                    const uint32_t b0lo = f8_prmt(r[c + d][0], r[c + d][1], 0x6420u), b1lo = f8_prmt(r[c + d][0], r[c + d][1], 0x7531u);
-                    const uint32_t b0hi = f8_prmt(r[c + d][2], r[c + d][3], 0x6420u), b1hi = f8_prmt(r[c + d][2], r[c + d][3], 0x7531u);
-                    // nibble e of the half word = column 2 e + (g & 1) of its packed word; TMEM lanes g, g + 8, g + 16, g + 24
-                    lo[4 * d] = b0lo & 0x0F0F0F0Fu, lo[4 * d + 1] = b0hi & 0x0F0F0F0Fu;
-                    lo[4 * d + 2] = (b0lo >> 4) & 0x0F0F0F0Fu, lo[4 * d + 3] = (b0hi >> 4) & 0x0F0F0F0Fu;
-                    hi[4 * d] = b1lo & 0x0F0F0F0Fu, hi[4 * d + 1] = b1hi & 0x0F0F0F0Fu;
-                    hi[4 * d + 2] = (b1lo >> 4) & 0x0F0F0F0Fu, hi[4 * d + 3] = (b1hi >> 4) & 0x0F0F0F0Fu;
-                }
-                dg_tmem_st_16x256b_x2(a_tmem + 8 * c, lo);
-                dg_tmem_st_16x256b_x2(a_tmem + (16u << 16) + 8 * c, hi);
+            for (int p = 0; p < 2; ++p) {  // 32-k steps 2 p and 2 p + 1: one store per 16 TMEM lanes for both
+                dg_tmem_st_16x256b_x2(a_tmem + 16 * p, lo[p]);
+                dg_tmem_st_16x256b_x2(a_tmem + (16u << 16) + 16 * p, hi[p]);
             }
             dg_tmem_st_wait();
             dg_fence_before();

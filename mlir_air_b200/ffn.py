@@ -209,10 +209,10 @@ class DecodeFFNStack:
     # zero point in f32): 10 % faster than the 16-bit-operand kernel at 16 rows, 3 % at 32, and no weight is rounded.
     GEMM_F8_BATCH = 32
     # ... where a layer is large enough for its three launches per product to pay: measured on one box (us per layer,
-    # 16-bit against fp8 operands, by weights per layer on this rank): 88 M 27.0 / 28.3 at 16 rows and 28.7 / 32.3 at 32;
-    # 135 M 33.4 / 34.1 and 36.5 / 40.8; 176 M 38.3 / 37.0 and 40.6 / 43.5; 352 M 60.4 / 54.9 and 63.6 / 63.1; 705 M
-    # 104.4 / 89.8 and 112.0 / 104.5.
-    GEMM_F8_MIN_WEIGHTS = {16: 150e6, 32: 300e6}
+    # 16-bit against fp8 operands, by weights per layer on this rank): 35 M 21.0 / 22.3 at 16 rows and 24.0 / 27.0 at 32;
+    # 88 M 28.6 / 30.9 at 32; 135 M 33.4 / 32.6 and 36.6 / 38.3; 176 M 38.2 / 36.0 and 40.4 / 41.2; 352 M 60.3 / 54.7 and
+    # 63.4 / 59.9; 705 M 104.4 / 89.6 and 111.3 / 99.4.
+    GEMM_F8_MIN_WEIGHTS = {16: 120e6, 32: 250e6}
 
     def uses_gemm_f8(self, batch: int) -> bool:
         if not self.uses_gemm(batch) or batch > self.GEMM_F8_BATCH:

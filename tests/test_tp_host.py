@@ -107,7 +107,7 @@ def test_stack_launch_accounting():
 
 def test_which_batched_decode_gemm_a_stack_takes():
     """Up to 32 rows the kernel with fp8 operands, but only where a layer (on this rank) is large enough for its three
-    launches per product to pay: the full 70B layer and its halves, not an eighth of it nor a 7B layer at 32 rows."""
+    launches per product to pay: the full 70B layer and its halves, not an eighth of it, a 7B layer up to 16 rows only."""
     class _W:
         def __init__(self, K, N):
             self.K, self.N, self.group_size = K, N, 128
@@ -128,6 +128,6 @@ def test_which_batched_decode_gemm_a_stack_takes():
     assert full.uses_gemm_f8(9) and full.uses_gemm_f8(32) and not full.uses_gemm_f8(33) and not full.uses_gemm_f8(8)
     assert half.uses_gemm_f8(16) and half.uses_gemm_f8(32)
     assert not eighth.uses_gemm_f8(16) and not eighth.uses_gemm_f8(32) and eighth.uses_gemm(32)
-    assert not small.uses_gemm_f8(16) and not small.uses_gemm_f8(32)
+    assert small.uses_gemm_f8(16) and not small.uses_gemm_f8(32)
     assert stack(8192, 7168).uses_gemm_f8(16) and not stack(8192, 7168).uses_gemm_f8(17)
     assert full.launches_per_step(32) == 2 * 7 and eighth.launches_per_step(32) == 2 * 5 and full.launches_per_step(64) == 2 * 5
