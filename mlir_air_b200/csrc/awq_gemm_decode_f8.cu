@@ -32,7 +32,8 @@
 //   warps 2-9    regroup the nibbles into tensor memory (a warp: 32 weight columns x 128 k)
 //   warps 10-17  promote (a warp: 32 weight columns x all token rows): tcgen05.ld of the unit's sums, three FMAs per
 //                (column, row); their arrival also frees the unit's input stage
-// Tensor memory: four weight buffers of 64 columns, two accumulator sets of 4 x rows columns.  Every wait is bounded.
+// Tensor memory: two accumulator sets of 4 x rows columns, the rest weight buffers of 64 columns (six up to 16 rows, four
+// with 32).  Every wait is bounded.
 #include <cudaTypedefs.h>
 #include <cuda_fp8.h>
 
@@ -48,7 +49,6 @@ namespace awq {
 
 constexpr int F8_REGROUP_WARPS = 8, F8_REGROUP_WARP0 = 2;
 constexpr int F8_ABUF_COLS = 64;  // a weight buffer: two 128-column halves x 128 k bytes = 2 x 32 TMEM columns
-constexpr int F8_ABUF = 4;
 constexpr int F8_MAX_ROWS = 32;
 constexpr uint32_t F8_TMEM_COLS = 512;
 
@@ -61,7 +61,8 @@ struct F8Cfg {
     static constexpr int RING_BUDGET = 220 * 1024;
     static constexpr int STAGES = RING_BUDGET / STAGE_BYTES < 8 ? RING_BUDGET / STAGE_BYTES : 8;
     static constexpr int ACC_COLS = 4 * NB;  // two halves x (hi, lo) x rows
-    static constexpr int ACC_COL0 = F8_ABUF * F8_ABUF_COLS;
+    static constexpr int ABUF = ((int)F8_TMEM_COLS - 2 * ACC_COLS) / F8_ABUF_COLS;  // weight buffers: 6 up to 16 rows, 4 with 32
+    static constexpr int ACC_COL0 = ABUF * F8_ABUF_COLS;
     // a promote warp: 32 weight columns x all token rows.  (Measured: a second set of eight warps for rows 16-31 made the
     // kernel 9 % slower, 120 against 110 us per 70B layer: the waiting warps' polls cost more than the shorter chain wins.)
     static constexpr int PROMOTE_WARPS = 8;
@@ -70,7 +71,7 @@ struct F8Cfg {
     // against 94 us per 70B layer; the one group taking two units per round of waits 110 against 90.)
     static constexpr int PROMOTE_WARP0 = F8_REGROUP_WARP0 + F8_REGROUP_WARPS;
     static constexpr int THREADS = (PROMOTE_WARP0 + PROMOTE_WARPS) * 32;  // 576
-    static constexpr int NUM_BARS = 3 * STAGES + 2 * F8_ABUF + 4;
+    static constexpr int NUM_BARS = 3 * STAGES + 2 * ABUF + 4;
     static constexpr int OFF_BARS = STAGES * STAGE_BYTES;
     static constexpr int SMEM_BYTES = OFF_BARS + NUM_BARS * 8 + 16 + 1024;
     // kind::f8f6f4: f32 accumulate, both operands e4m3 (format 0), K-major, M 128, N 2 NB
@@ -200,9 +201,9 @@ gemm_decode_f8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
     auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };       // MMA, regroup and promote warps done with stage s
     auto xfull_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };   // its token rows and group sums landed
     auto ready_bar = [&](int b) { return bar_base + 8u * (3 * STAGES + b); };   // weight buffer b written
-    auto bfree_bar = [&](int b) { return bar_base + 8u * (3 * STAGES + F8_ABUF + b); };      // MMA done with weight buffer b
-    auto acc_full = [&](int b) { return bar_base + 8u * (3 * STAGES + 2 * F8_ABUF + b); };   // a unit's sums complete
-    auto acc_empty = [&](int b) { return bar_base + 8u * (3 * STAGES + 2 * F8_ABUF + 2 + b); };  // and promoted
+    auto bfree_bar = [&](int b) { return bar_base + 8u * (3 * STAGES + Cfg::ABUF + b); };      // MMA done with weight buffer b
+    auto acc_full = [&](int b) { return bar_base + 8u * (3 * STAGES + 2 * Cfg::ABUF + b); };   // a unit's sums complete
+    auto acc_empty = [&](int b) { return bar_base + 8u * (3 * STAGES + 2 * Cfg::ABUF + 2 + b); };  // and promoted
     auto stage_addr = [&](int s) { return smem_base + (uint32_t)s * Cfg::STAGE_BYTES; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -216,7 +217,7 @@ gemm_decode_f8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
             mbar_init(xfull_bar(s), 1);
             mbar_init(empty_bar(s), Cfg::PROMOTE_WARPS);  // the promote warps are the last to need a stage
         }
-        for (int b = 0; b < F8_ABUF; ++b) {
+        for (int b = 0; b < Cfg::ABUF; ++b) {
             mbar_init(ready_bar(b), F8_REGROUP_WARPS);
             mbar_init(bfree_bar(b), 1);
         }
@@ -286,7 +287,7 @@ gemm_decode_f8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
         int it = 0;
         for (UnitWalk w(tiles, KB); w.valid(); ++w.u, ++it) {
             const int s = it % STAGES, round = it / STAGES;
-            const int ab = it % F8_ABUF, around = it / F8_ABUF;
+            const int ab = it % Cfg::ABUF, around = it / Cfg::ABUF;
             const int b = it & 1, use = it >> 1;
             // token rows landed, weight buffer written, accumulator set promoted: three lanes wait side by side
             if (!mbar_wait_multi_warp(use >= 1 ? 3 : 2, xfull_bar(s), round & 1, ready_bar(ab), around & 1, acc_empty(b), (use - 1) & 1,
@@ -326,7 +327,7 @@ gemm_decode_f8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
         const int n_units = w.u1 - w.u;
         for (int it = 0; it < n_units; ++it) {
             const int s = it % STAGES, round = it / STAGES;
-            const int ab = it % F8_ABUF, around = it / F8_ABUF;
+            const int ab = it % Cfg::ABUF, around = it / Cfg::ABUF;
             // the unit's words landed: fetch them, and only then wait for the MMA to be done with the weight buffer they go to
             if (!mbar_wait_bounded(full_bar(s), round & 1, wait_limit)) {
                 if (lane == 0) atomicExch(&g_gemm_f8_error, 3);
